@@ -1,0 +1,274 @@
+"""ctypes access to the CPU checker (liboracle.so) and, where it was built, to the reference's own host
+code (_ref/libref.so, _ref/libref_group.so).
+
+Test infrastructure only: imported by tests/, by the smoke check and by the benchmark's CPU-baseline and
+reference legs. The product package never imports this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+U8P, U16P, U32P, U64P = (C.POINTER(t) for t in (C.c_uint8, C.c_uint16, C.c_uint32, C.c_uint64))
+F32P, F64P = C.POINTER(C.c_float), C.POINTER(C.c_double)
+
+
+def _ptr(a, typ):
+    return None if a is None else a.ctypes.data_as(typ)
+
+
+def build(ref=False):
+    """Compile the checker (and, with ref=True and the reference tree present, the reference build)."""
+    subprocess.run(["make", "-s", "-C", HERE, "all"], check=True)
+    if ref and os.path.isdir(os.environ.get("B200MOE_REFERENCE", "/root/reference")):
+        subprocess.run(["make", "-s", "-C", HERE, "ref", "REF=" + os.environ.get("B200MOE_REFERENCE", "/root/reference")], check=True)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.orc_bf16_to_f32.restype = C.c_float; L.orc_bf16_to_f32.argtypes = [C.c_uint16]
+        L.orc_f32_to_bf16.restype = C.c_uint16; L.orc_f32_to_bf16.argtypes = [C.c_float]
+        L.orc_e4m3_decode.restype = C.c_float; L.orc_e4m3_decode.argtypes = [C.c_uint8]
+        L.orc_e4m3_encode.restype = C.c_uint8; L.orc_e4m3_encode.argtypes = [C.c_float]
+        L.orc_f32_to_f16.restype = C.c_uint16; L.orc_f32_to_f16.argtypes = [C.c_float]
+        L.orc_f16_to_f32.restype = C.c_float; L.orc_f16_to_f32.argtypes = [C.c_uint16]
+        L.orc_gemv_emu_row.restype = C.c_float
+        for n in ("orc_moe_plan", "orc_moe_ids32", "orc_moe_maps32", "orc_moe_segs32", "orc_moe_windows", "orc_moe_group"):
+            getattr(L, n).restype = C.c_uint64
+        L.orc_plan_global.restype = C.c_int64
+        _lib = L
+    return _lib
+
+
+def ref_lib():
+    """The reference's own host functions, or None when that build is not present."""
+    path = os.path.join(HERE, "_ref", "libref.so")
+    if not os.path.exists(path):
+        return None
+    L = C.CDLL(path)
+    L.omega_fp8_e4m3_ref.restype = C.c_float; L.omega_fp8_e4m3_ref.argtypes = [C.c_uint8]
+    L.omega_gpu_fp8_e4m3_rne.restype = C.c_uint8; L.omega_gpu_fp8_e4m3_rne.argtypes = [C.c_float]
+    L.omega_bf16_to_fp32.restype = C.c_float; L.omega_bf16_to_fp32.argtypes = [C.c_uint16]
+    L.omega_fp32_to_bf16.restype = C.c_uint16; L.omega_fp32_to_bf16.argtypes = [C.c_float]
+    return L
+
+
+def ref_group_lib():
+    path = os.path.join(HERE, "_ref", "libref_group.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
+# ---------------------------------------------------------------- numpy front ends
+
+def bf16_bits(x):
+    """f32 array -> bf16 bit patterns (uint16), round to nearest even (vectorised orc_f32_to_bf16)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    nan = (b & 0x7FFFFFFF) > 0x7F800000
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    return np.where(nan, ((b >> 16) | 0x40).astype(np.uint16), r)
+
+
+def bf16_to_f32(b):
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def e4m3_table():
+    L = lib()
+    return np.array([L.orc_e4m3_decode(i) for i in range(256)], dtype=np.float32)
+
+
+def quantize_bf16(w_bf16):
+    """bf16 bits [n][k] -> (e4m3 codes [n][k], bf16 scales [n/128][k/128])."""
+    n, k = w_bf16.shape
+    w = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+    w8 = np.empty((n, k), np.uint8); sc = np.empty((n // 128, k // 128), np.uint16)
+    rc = lib().orc_quantize_bf16(C.c_uint32(n), C.c_uint32(k), _ptr(w, U16P), _ptr(w8, U8P), _ptr(sc, U16P))
+    if rc != 0:
+        raise ValueError("orc_quantize_bf16 refused the input")
+    return w8, sc
+
+
+def gemv(w8, sc, x, mag=False):
+    n, k = w8.shape
+    w8 = np.ascontiguousarray(w8); sc = np.ascontiguousarray(sc); x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(n, np.float64); m = np.empty(n, np.float64) if mag else None
+    lib().orc_gemv(_ptr(w8, U8P), _ptr(sc, U16P), C.c_uint32(n), C.c_uint32(k), _ptr(x, F32P), _ptr(y, F64P), _ptr(m, F64P))
+    return (y, m) if mag else y
+
+
+def gemv_emu(w8, sc, x):
+    n, k = w8.shape
+    w8 = np.ascontiguousarray(w8); sc = np.ascontiguousarray(sc); x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(n, np.float32)
+    lib().orc_gemv_emu(_ptr(w8, U8P), _ptr(sc, U16P), C.c_uint32(n), C.c_uint32(k), _ptr(x, F32P), _ptr(y, F32P))
+    return y
+
+
+def topk(logits, k=8, norm=True):
+    """logits f32 [T][E] -> (ids u32 [T][k], weights f64 [T][k])."""
+    lg = np.ascontiguousarray(logits, dtype=np.float32)
+    T, E = lg.shape
+    ids = np.empty((T, k), np.uint32); w = np.empty((T, k), np.float64)
+    L = lib()
+    for t in range(T):
+        L.orc_topk(_ptr(lg[t], F32P), C.c_uint32(E), C.c_uint32(k), C.c_int(1 if norm else 0), _ptr(ids[t], U32P), _ptr(w[t], F64P))
+    return ids, w
+
+
+def swiglu(gu):
+    gu = np.ascontiguousarray(gu, dtype=np.float32)
+    rows, two_i = gu.shape
+    act = np.empty((rows, two_i // 2), np.float32)
+    L = lib()
+    for r in range(rows):
+        L.orc_swiglu(_ptr(gu[r], F32P), C.c_uint32(two_i // 2), _ptr(act[r], F32P))
+    return act
+
+
+def combine(w, d):
+    """w f32 [T][S], d f32 [T][S][H] -> out f32 [T][H] (multiply then add, slot order)."""
+    w = np.ascontiguousarray(w, dtype=np.float32); d = np.ascontiguousarray(d, dtype=np.float32)
+    T, S, H = d.shape
+    out = np.empty((T, H), np.float32)
+    L = lib()
+    for t in range(T):
+        L.orc_combine(_ptr(w[t], F32P), _ptr(d[t], F32P), C.c_uint32(S), C.c_uint32(H), _ptr(out[t], F32P))
+    return out
+
+
+def rmsnorm(x, eps=1e-6):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    L = lib()
+    for t in range(x.shape[0]):
+        L.orc_rmsnorm(_ptr(x[t], F32P), None, C.c_uint32(x.shape[1]), C.c_float(eps), _ptr(out[t], F32P))
+    return out
+
+
+def plan_buffers(fill=0x5A):
+    mk = lambda n: np.full(n, fill * 0x0101010101010101, np.uint64)
+    return mk(10368), mk(1028), mk(2320), mk(8)
+
+
+def moe_plan(cfg, ids, work, seg, maps, meta):
+    cfg = np.ascontiguousarray(cfg, dtype=np.uint64); ids = np.ascontiguousarray(ids, dtype=np.uint64)
+    return int(lib().orc_moe_plan(_ptr(cfg, U64P), _ptr(ids, U64P), _ptr(work, U64P), _ptr(seg, U64P), _ptr(maps, U64P), _ptr(meta, U64P)))
+
+
+def plan_global(ids, experts, ystride=None):
+    """ids u32 [T][S] -> dict(counts, starts, xmap, ymap, seg3 [segs][3], rows). Any T."""
+    ids = np.ascontiguousarray(ids, dtype=np.uint32)
+    T, S = ids.shape
+    ystride = S if ystride is None else ystride
+    counts = np.empty(experts, np.uint32); starts = np.empty(experts, np.uint32)
+    xmap = np.zeros(T * S + 8, np.uint32); ymap = np.zeros(T * S + 8, np.uint32)
+    seg3 = np.zeros((experts, 3), np.uint32); rows = C.c_uint32(0)
+    n = lib().orc_plan_global(C.c_uint32(T), C.c_uint32(S), C.c_uint32(experts), C.c_uint32(ystride), _ptr(ids, U32P),
+                              _ptr(counts, U32P), _ptr(starts, U32P), _ptr(xmap, U32P), _ptr(ymap, U32P), _ptr(seg3, U32P), C.byref(rows))
+    if n < 0:
+        raise ValueError("expert id out of range")
+    return dict(counts=counts, starts=starts, xmap=xmap[: rows.value + 8], ymap=ymap[: rows.value + 8], seg3=seg3[:n], rows=rows.value)
+
+
+def act_quant(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, k = x.shape
+    q = np.empty((rows, k), np.uint8); s = np.empty((rows, k // 128), np.float32)
+    L = lib()
+    for r in range(rows):
+        L.orc_act_quant(_ptr(x[r], F32P), C.c_uint32(k), _ptr(q[r], U8P), _ptr(s[r], F32P))
+    return q, s
+
+
+def act_pieces(x, pieces):
+    """x f32 [rows][k] -> (q u8 [rows][pieces][k], s f32 [rows][k/128])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, k = x.shape
+    q = np.empty((rows, pieces, k), np.uint8); s = np.empty((rows, k // 128), np.float32)
+    L = lib()
+    for r in range(rows):
+        L.orc_act_pieces(_ptr(x[r], F32P), C.c_uint32(k), C.c_uint32(pieces), _ptr(q[r], U8P), _ptr(s[r], F32P))
+    return q, s
+
+
+def act_pieces_decode(q, s):
+    rows, pieces, k = q.shape
+    out = np.empty((rows, k), np.float64)
+    L = lib()
+    for r in range(rows):
+        L.orc_act_pieces_decode(_ptr(np.ascontiguousarray(q[r]), U8P), _ptr(np.ascontiguousarray(s[r]), F32P), C.c_uint32(k), C.c_uint32(pieces), _ptr(out[r], F64P))
+    return out
+
+
+def w4_quantize(w):
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    packed = np.empty((n, k // 2), np.uint8); sc = np.empty((n, k // 32), np.uint16)
+    lib().orc_w4_quantize(C.c_uint32(n), C.c_uint32(k), _ptr(w, F32P), _ptr(packed, U8P), _ptr(sc, U16P))
+    return packed, sc
+
+
+def w4_gemm(packed, sc, x, threads=None):
+    import concurrent.futures as cf
+    packed = np.ascontiguousarray(packed); sc = np.ascontiguousarray(sc); x = np.ascontiguousarray(x, dtype=np.float32)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    m = x.shape[0]
+    y = np.empty((m, n), np.float64)
+    L = lib()
+    threads = threads or min(os.cpu_count() or 1, 32)
+    step = max(1, (n + threads - 1) // threads)
+
+    def run(r0):
+        L.orc_w4_gemm_rows(_ptr(packed, U8P), _ptr(sc, U16P), C.c_uint32(k), C.c_uint32(r0), C.c_uint32(min(n, r0 + step)),
+                           C.c_uint32(n), _ptr(x, F32P), C.c_uint32(m), _ptr(y, F64P))
+    with cf.ThreadPoolExecutor(threads) as ex:
+        list(ex.map(run, range(0, n, step)))
+    return y
+
+
+def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, threads=None):
+    """Gate|up GEMV, SwiGLU and down GEMV for every sorted row (the reference host glue); ctypes releases
+    the GIL, so rows are spread over `threads` host threads. Returns dn f32 [n_dest][hidden]."""
+    import concurrent.futures as cf
+    E, n2, hidden = wgu.shape
+    inter = n2 // 2
+    wgu = np.ascontiguousarray(wgu); sgu = np.ascontiguousarray(sgu); wdn = np.ascontiguousarray(wdn); sdn = np.ascontiguousarray(sdn)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    re_ = np.ascontiguousarray(row_expert, dtype=np.uint32); rt = np.ascontiguousarray(row_token, dtype=np.uint32)
+    rd = np.ascontiguousarray(row_dest, dtype=np.uint32)
+    rows = len(re_)
+    dn = np.zeros((n_dest, hidden), np.float32)
+    L = lib()
+    threads = threads or min(os.cpu_count() or 1, 64)
+    step = max(1, (rows + threads * 4 - 1) // (threads * 4))
+
+    def run(p0):
+        L.orc_expert_rows(_ptr(wgu, U8P), _ptr(sgu, U16P), _ptr(wdn, U8P), _ptr(sdn, U16P), C.c_uint32(hidden), C.c_uint32(inter),
+                          _ptr(x, F32P), _ptr(re_, U32P), _ptr(rt, U32P), _ptr(rd, U32P), C.c_uint32(p0), C.c_uint32(min(rows, p0 + step)), _ptr(dn, F32P))
+    with cf.ThreadPoolExecutor(threads) as ex:
+        list(ex.map(run, range(0, rows, step)))
+    return dn
+
+
+def moe_layer(logits_bf16, x_bf16, wgu, sgu, wdn, sdn, topk_k=8, threads=None):
+    """One MoE layer exactly as the reference host glue strings the operators together: top-k (lowest
+    index on ties, renormalised softmax), per pick gate|up GEMV -> SwiGLU -> down GEMV, slot-order weighted
+    sum. Inputs bf16 bit patterns; returns (out f32 [T][H], ids, wts f32)."""
+    lg = bf16_to_f32(logits_bf16); x = bf16_to_f32(x_bf16)
+    T, H = x.shape
+    ids, w64 = topk(lg, topk_k, True)
+    wts = w64.astype(np.float32)
+    re_ = ids.reshape(-1); rt = np.repeat(np.arange(T, dtype=np.uint32), topk_k); rd = np.arange(T * topk_k, dtype=np.uint32)
+    dn = expert_rows(wgu, sgu, wdn, sdn, x, re_, rt, rd, T * topk_k, threads)
+    out = combine(wts, dn.reshape(T, topk_k, H))
+    return out, ids, wts

@@ -1,0 +1,52 @@
+"""The CPU checker against the committed golden vectors (outputs of the reference's own host code; see
+tests/golden/make_golden.py). Runs without the reference tree."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from oracle import oracle as orc
+from tests.test_oracle_pin import plan_cases
+
+G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
+
+
+def test_formats():
+    L = orc.lib()
+    mine = np.array([L.orc_e4m3_decode(i) for i in range(256)], np.float32)
+    assert np.array_equal(mine.view(np.uint32)[np.isfinite(mine)], G["e4m3_decode"].view(np.uint32)[np.isfinite(mine)])
+    assert np.array_equal(np.isnan(mine), np.isnan(G["e4m3_decode"]))
+    v = G["encode_in"]
+    assert np.array_equal(np.array([L.orc_e4m3_encode(C.c_float(float(x))) for x in v], np.uint8), G["encode_out"])
+    assert np.array_equal(orc.bf16_bits(v), G["bf16_out"])
+
+
+def test_quantiser_and_gemv():
+    w8, sc = orc.quantize_bf16(G["q_w"])
+    assert np.array_equal(w8, G["q_w8"]) and np.array_equal(sc, G["q_scale"])
+    y, m = orc.gemv(w8, sc, G["gemv_x"], mag=True)
+    assert np.array_equal(y, G["gemv_y"]) and np.array_equal(m, G["gemv_mag"])
+
+
+def test_plan_cases():
+    blob = G["plan_blob"].astype(np.uint64); at = 0
+    for (cfg, ids, name), rc, ln in zip(plan_cases(), G["plan_rc"], G["plan_len"]):
+        work, seg, maps, meta = orc.plan_buffers()
+        assert orc.moe_plan(cfg, ids, work, seg, maps, meta) == rc, name
+        if rc == 0:
+            nw, ns = int(meta[0]), int(meta[1])
+            got = np.concatenate([work[: nw * 9], seg[: ns * 4], maps[: nw + 8], maps[1160: 1160 + nw + 8], meta])
+            assert np.array_equal(got, blob[at: at + int(ln)]), name
+            fill = np.uint64(0x5A5A5A5A5A5A5A5A)  # nothing past the written prefix is touched
+            assert np.all(work[nw * 9:] == fill) and np.all(seg[ns * 4:] == fill) and np.all(maps[nw + 8: 1160] == fill)
+        else:
+            assert all(np.all(b == np.uint64(0x5A5A5A5A5A5A5A5A)) for b in (work, seg, maps, meta)), name
+        at += int(ln)
+    assert at == len(blob)
+
+
+def test_incumbent_group():
+    g = orc.plan_global(G["grp_ids"], 128, ystride=9)
+    assert np.array_equal(g["xmap"][:512], G["grp_x"][:512]) and np.array_equal(g["ymap"][:512], G["grp_y"][:512])
+    seg = G["grp_seg"].reshape(-1, 4)
+    assert np.array_equal(g["seg3"], seg[:-1, :3]) and tuple(seg[-1]) == (256, 512, 64, 1)

@@ -1,0 +1,280 @@
+"""Pins the CPU checker (oracle/moe_oracle.c) to the reference's own host code.
+
+Two anchors: (1) where the reference build is present (oracle/_ref, made by `make -C oracle ref` from the
+reference sources), every function is compared with it directly on seeded inputs and on the cases the
+reference's own tests use (tests/gpu_fp8_api_test.c:250-339, tests/moe/caller.c:91-157); (2) everywhere,
+the committed vectors in tests/golden/, which tests/golden/make_golden.py produced from that build.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+
+REF = orc.ref_lib()
+REFG = orc.ref_group_lib()
+need_ref = pytest.mark.skipif(REF is None, reason="reference build (oracle/_ref) not present")
+U8P, U16P, U32P, U64P, F32P, F64P = orc.U8P, orc.U16P, orc.U32P, orc.U64P, orc.F32P, orc.F64P
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def ptr(a, t):
+    return a.ctypes.data_as(t)
+
+
+# ------------------------------------------------------------------ e4m3 known answers (tests/gpu_fp8_api_test.c:313-339)
+def test_e4m3_known_answers():
+    L = orc.lib()
+    assert L.orc_e4m3_decode(0x38) == 1.0
+    assert L.orc_e4m3_decode(0x7E) == 448.0
+    assert L.orc_e4m3_decode(0x01) == 2.0 ** -9
+    assert L.orc_e4m3_decode(0x07) == 7 * 2.0 ** -9
+    assert L.orc_e4m3_decode(0x08) == 2.0 ** -6
+    assert L.orc_e4m3_decode(0xB8) == -1.0
+    assert np.isnan(L.orc_e4m3_decode(0x7F)) and np.isnan(L.orc_e4m3_decode(0xFF))
+    # every finite code survives encode(decode(code)); -0 keeps its sign
+    for c in range(256):
+        if c & 0x7F == 0x7F:
+            continue
+        assert L.orc_e4m3_encode(L.orc_e4m3_decode(c)) == c
+    assert L.orc_e4m3_encode(1e9) == 0x7E and L.orc_e4m3_encode(-1e9) == 0xFE
+    assert L.orc_e4m3_encode(float("nan")) & 0x7F == 0x7E
+    assert L.orc_e4m3_encode(448.0) == 0x7E and L.orc_e4m3_encode(464.0) == 0x7E
+
+
+def test_e4m3_encode_brute_force():
+    """nearest code, ties to the even code, saturating (the reference's rule, tests/gpu_fp8_api_test.c:250-288)"""
+    L = orc.lib()
+    tab = orc.e4m3_table()[:0x7F].astype(np.float64)  # non-negative finite codes, ascending
+    rng = np.random.default_rng(11)
+    vals = np.concatenate([rng.normal(0, 100, 4000), rng.normal(0, 0.05, 3000), rng.uniform(-500, 500, 2000),
+                           (tab[:-1] + tab[1:]) / 2, -(tab[:-1] + tab[1:]) / 2, tab, [0.0, -0.0, 2.0 ** -10, 3 * 2.0 ** -10]]).astype(np.float32)
+    for v in vals:
+        a = abs(float(v))
+        d = np.abs(tab - a)
+        best = int(np.argmin(d))
+        ties = np.nonzero(d == d[best])[0]
+        if len(ties) > 1:
+            best = int([t for t in ties if t % 2 == 0][0])
+        if a >= 448.0:
+            best = 0x7E
+        want = best | (0x80 if np.signbit(v) else 0)
+        assert L.orc_e4m3_encode(C.c_float(float(v))) == want, (v, want)
+
+
+@need_ref
+def test_formats_against_reference():
+    L = orc.lib()
+    for c in range(256):
+        a, b = L.orc_e4m3_decode(c), REF.omega_fp8_e4m3_ref(c)
+        assert (np.isnan(a) and np.isnan(b)) or a == b
+    rng = np.random.default_rng(5)
+    vals = np.concatenate([rng.normal(0, 120, 20000), rng.normal(0, 0.02, 20000), rng.uniform(-460, 460, 5000),
+                           [0.0, -0.0, 448.0, 447.99, 1e-30, -1e-30, np.inf, -np.inf]]).astype(np.float32)
+    for v in vals:
+        assert L.orc_e4m3_encode(C.c_float(float(v))) == REF.omega_gpu_fp8_e4m3_rne(C.c_float(float(v))), v
+        assert L.orc_f32_to_bf16(C.c_float(float(v))) == REF.omega_fp32_to_bf16(C.c_float(float(v))), v
+
+
+@need_ref
+def test_quantiser_and_gemv_against_reference():
+    rng = np.random.default_rng(0)
+    n, k = 256, 384
+    w = orc.bf16_bits(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+    w[0:128, 0:128] = 0  # an all-zero block: scale 1.0
+    w8, sc = orc.quantize_bf16(w)
+    r8 = np.empty_like(w8); rs = np.empty_like(sc)
+    assert REF.omega_gpu_fp8_quantize_bf16(C.c_uint32(n), C.c_uint32(k), ptr(w, U16P), ptr(r8, U8P), ptr(rs, U16P)) == 0
+    assert np.array_equal(w8, r8) and np.array_equal(sc, rs)
+    assert sc[0, 0] == 0x3F80
+    x = rng.normal(0, 1, k).astype(np.float32)
+    y, m = orc.gemv(w8, sc, x, mag=True)
+    ry = np.empty(n, np.float64); rm = np.empty(n, np.float64)
+    REF.omega_fp8_gemv_oracle(ptr(w8, U8P), ptr(sc, U16P), C.c_uint32(n), C.c_uint32(k), ptr(x, F32P), ptr(ry, F64P), ptr(rm, F64P))
+    assert np.array_equal(y, ry) and np.array_equal(m, rm)
+    # inf weight refused by both
+    w[3, 3] = 0x7F80
+    assert REF.omega_gpu_fp8_quantize_bf16(C.c_uint32(n), C.c_uint32(k), ptr(w, U16P), ptr(r8, U8P), ptr(rs, U16P)) == -1
+    with pytest.raises(ValueError):
+        orc.quantize_bf16(w)
+
+
+def _ref_plan(cfg, ids, bufs):
+    r = C.c_uint64(99)
+    rc = REF.omega_moe_plan(C.byref(r), ptr(cfg, U64P), C.c_uint64(8), ptr(ids, U64P), C.c_uint64(1024), ptr(bufs[0], U64P), C.c_uint64(10368),
+                            ptr(bufs[1], U64P), C.c_uint64(1028), ptr(bufs[2], U64P), C.c_uint64(2320), ptr(bufs[3], U64P), C.c_uint64(8))
+    assert rc == 0
+    return r.value
+
+
+def plan_cases():
+    """the id patterns and sizes of tests/moe/caller.c:34-50, :91-111"""
+    for n in (0, 1, 2, 3, 7, 14, 15, 31, 127, 128):
+        for mode in range(5):
+            ids = np.zeros(1024, np.uint64)
+            for t in range(n):
+                for s in range(8):
+                    ids[t * 8 + s] = [7, (t * 8 + s) % 256, s % 3, 255 if t % 2 else s, (t * 17 + s * 13) % 256][mode]
+            yield np.array([1, n, 8, 256, 256, 1152, 257, 1160], np.uint64), ids, "dense n=%d mode=%d" % (n, mode)
+    ids = np.zeros(1024, np.uint64)
+    for j in range(24):
+        ids[j] = 0xFFFFFFFF if j % 4 else j
+    yield np.array([1, 3, 8, 256, 256, 1152, 257, 1160], np.uint64), ids, "sparse"
+    yield np.array([1, 128, 8, 256, 256, 1152, 257, 1160], np.uint64), np.full(1024, 0xFFFFFFFF, np.uint64), "all absent"
+    yield np.array([1, 5, 0, 256, 256, 1152, 257, 1160], np.uint64), np.zeros(1024, np.uint64), "zero slots"
+    yield np.array([1, 64, 8, 128, 128, 1152, 257, 1160], np.uint64), (np.arange(1024) * 37 % 128).astype(np.uint64), "128 experts"
+    # refusals (tests/moe/caller.c:98-107)
+    base = [1, 1, 8, 256, 256, 1152, 257, 1160]
+    z = np.zeros(1024, np.uint64)
+    for field, val in ((5, 1151), (7, 1159)):
+        c = np.array([1, 128, 8, 256, 256, 1152, 257, 1160], np.uint64); c[field] = val
+        yield c, z, "capacity %d" % field
+    for field, val in ((6, 1), (0, 2), (1, 129), (2, 9), (4, 255), (5, 1153), (6, 258), (7, 1161), (3, 0), (3, 257)):
+        c = np.array(base, np.uint64); c[field] = val
+        yield c, z, "cfg %d=%d" % (field, val)
+    for bad in (256, 0xFFFFFFFE):
+        ids = np.zeros(1024, np.uint64); ids[3] = bad
+        yield np.array(base, np.uint64), ids, "bad id"
+
+
+@need_ref
+def test_plan_against_reference():
+    for cfg, ids, name in plan_cases():
+        mine, theirs = orc.plan_buffers(), orc.plan_buffers()
+        rc = orc.moe_plan(cfg, ids, *mine)
+        assert rc == _ref_plan(cfg, ids, theirs), name
+        for a, b in zip(mine, theirs):  # word for word, including every untouched (0x5a) word
+            assert np.array_equal(a, b), name
+
+
+@need_ref
+def test_serialisers_against_reference():
+    L = orc.lib()
+    cfg = np.array([1, 31, 8, 256, 256, 1152, 257, 1160], np.uint64)
+    ids = (np.arange(1024) * 29 % 256).astype(np.uint64)
+    work, seg, maps, meta = orc.plan_buffers()
+    assert orc.moe_plan(cfg, ids, work, seg, maps, meta) == 0
+    dirs = np.zeros(514, np.uint64)
+    for j in range(257):
+        dirs[2 * j] = j * 256 + 4096; dirs[2 * j + 1] = dirs[2 * j] + 128
+    r = C.c_uint64(0)
+    for mut in ("ok", "map", "dir", "seg"):
+        mp, sg, dr = maps.copy(), seg.copy(), dirs.copy()
+        if mut == "map": mp[0] = 2 ** 64 - 1
+        if mut == "dir": dr[0] = 0
+        if mut == "seg": sg[2] = 2 ** 64 - 1
+        a = np.full(9280, 90, np.uint8); b = a.copy()
+        rc = L.orc_moe_maps32(ptr(meta, U64P), ptr(mp, U64P), ptr(a, U8P))
+        assert REF.omega_moe_maps32(C.byref(r), ptr(meta, U64P), C.c_uint64(8), ptr(mp, U64P), C.c_uint64(2320), ptr(b, U8P), C.c_uint64(9280)) == 0
+        assert rc == r.value and np.array_equal(a, b), mut
+        a = np.full(8224, 90, np.uint8); b = a.copy()
+        rc = L.orc_moe_segs32(ptr(sg, U64P), ptr(meta, U64P), ptr(dr, U64P), ptr(a, U8P))
+        assert REF.omega_moe_segs32(C.byref(r), ptr(sg, U64P), C.c_uint64(1028), ptr(meta, U64P), C.c_uint64(8), ptr(dr, U64P), C.c_uint64(514), ptr(b, U8P), C.c_uint64(8224)) == 0
+        assert rc == r.value and np.array_equal(a, b), mut
+    wire = np.zeros(4096, np.uint8)
+    wire.view(np.uint32)[:] = np.arange(1024) % 257
+    for n in (0, 5, 1024, 1025):
+        a = np.full(1024, 7, np.uint64); b = a.copy()
+        rc = L.orc_moe_ids32(ptr(wire, U8P), C.c_uint64(n), ptr(a, U64P))
+        assert REF.omega_moe_ids32(C.byref(r), ptr(wire, U8P), C.c_uint64(4096), C.c_uint64(n), ptr(b, U64P), C.c_uint64(1024)) == 0
+        assert rc == r.value and np.array_equal(a, b)
+    for n in list(range(0, 129)) + [129]:
+        for cap, flush in ((128, 0), (1, 0), (128, 1)):
+            c = np.array([1, n, 2048, 512, 9, 512, cap, flush], np.uint64)
+            a = np.full(1024, 3, np.uint64); am = np.full(4, 3, np.uint64); b = a.copy(); bm = am.copy()
+            rc = L.orc_moe_windows(ptr(c, U64P), ptr(a, U64P), ptr(am, U64P))
+            assert REF.omega_moe_windows(C.byref(r), ptr(c, U64P), C.c_uint64(8), ptr(b, U64P), C.c_uint64(1024), ptr(bm, U64P), C.c_uint64(4)) == 0
+            assert rc == r.value and np.array_equal(a, b) and np.array_equal(am, bm), (n, cap, flush)
+    q = [4096, 8192, 12288, 65536, 131072, 196608, 262144, 512, 14, 126, 134, 9, 1, 1, 1, 256]
+    bads = [(None, None)] + [(8, 15), (8, 0), (11, 8), (15, 255), (9, 125), (10, 133), (7, 0), (7, 513), (0, 4097), (12, 0), (13, 2), (14, 0),
+                             (3, 4096), (4, 65536), (5, 65536), (6, 196608), (0, 2 ** 64 - 8), (3, 2 ** 64 - 8), (7, 128), (8, 2 ** 64 - 1)]
+    for f, v in bads:
+        req = np.array(q, np.uint64)
+        if f is not None: req[f] = v
+        a = np.full(64, 9, np.uint8); b = a.copy()
+        rc = L.orc_moe_group(ptr(req, U64P), ptr(a, U8P))
+        assert REF.omega_moe_group(C.byref(r), ptr(req, U64P), C.c_uint64(16), ptr(b, U8P), C.c_uint64(64)) == 0
+        assert rc == r.value and np.array_equal(a, b), (f, v)
+
+
+@pytest.mark.skipif(REFG is None, reason="reference build (oracle/_ref) not present")
+def test_global_plan_against_incumbent_group():
+    """the u32 form against the reference's unchanged host GROUP (tests/moe/incumbent.c; 9-wide Y rows)"""
+    rng = np.random.default_rng(3)
+    for n in (1, 2, 7, 14, 64, 128):
+        ids = np.stack([rng.choice(128, 8, replace=False) for _ in range(n)]).astype(np.uint32)
+        ox = np.zeros(1152 + 16, np.uint32); oy = np.zeros(1152 + 16, np.uint32); os_ = np.zeros(1028, np.uint32)
+        ns = REFG.moe_incumbent(C.c_uint32(n), ptr(ids, U32P), ptr(ox, U32P), ptr(oy, U32P), ptr(os_, U32P))
+        g = orc.plan_global(ids, 128, ystride=9)
+        assert g["rows"] == n * 8 and len(g["seg3"]) == ns - 1  # the incumbent appends the shared segment
+        assert np.array_equal(g["xmap"][: n * 8], ox[: n * 8]) and np.array_equal(g["ymap"][: n * 8], oy[: n * 8])
+        assert np.array_equal(g["seg3"].reshape(-1), os_.reshape(-1, 4)[: ns - 1, :3].reshape(-1))
+
+
+def test_global_plan_rank_rule():
+    """independent check of the ordering rule: rank = #{(e',t',s') < (e,t,s)} (tests/moe/caller.c:66-73)"""
+    rng = np.random.default_rng(4)
+    ids = rng.integers(0, 16, (40, 8)).astype(np.uint32)
+    ids[5, 2] = 0xFFFFFFFF
+    g = orc.plan_global(ids, 16)
+    key = [(int(ids[t, s]), t * 8 + s) for t in range(40) for s in range(8) if ids[t, s] != 0xFFFFFFFF]
+    for (e, i) in key:
+        rank = sum(1 for (f, j) in key if f < e or (f == e and j < i))
+        assert g["xmap"][rank] == i // 8 and g["ymap"][rank] == i
+    assert np.all(g["xmap"][g["rows"]:] == 0) and g["rows"] == len(key)
+
+
+def test_emu_order_is_close_to_double():
+    rng = np.random.default_rng(8)
+    for k in (512, 768, 2048):
+        w8, sc = orc.quantize_bf16(orc.bf16_bits(rng.normal(0, 0.02, (128, k)).astype(np.float32)))
+        x = rng.normal(0, 1, k).astype(np.float32)
+        y, m = orc.gemv(w8, sc, x, mag=True)
+        e = orc.gemv_emu(w8, sc, x)
+        assert np.max(np.abs(e - y) / m) < 1e-5  # the reference's parity rule (tests/gpu_fp8_api_test.c:51)
+
+
+def test_act_quant_and_pieces():
+    rng = np.random.default_rng(9)
+    x = (rng.uniform(-1, 1, (6, 256)) * rng.choice([1, 300, 1e-3, 0], (6, 256), p=[.9, .04, .03, .03])).astype(np.float32)
+    x[5] = 0
+    q, s = orc.act_quant(x)
+    tab = orc.e4m3_table()
+    amax = np.abs(x.reshape(6, 2, 128)).max(-1)
+    assert np.all(np.log2(s) == np.round(np.log2(s)))  # powers of two
+    nz = amax > 0
+    assert np.all(amax[nz] / s[nz] <= 448) and np.all(amax[nz] / s[nz] > 224)
+    assert np.all(s[~nz] == 2.0 ** -108)
+    q3, s3 = orc.act_pieces(x, 3)
+    assert np.array_equal(q3[:, 0], q) and np.array_equal(s3, s)
+    bf = orc.bf16_to_f32(orc.bf16_bits(x))
+    q2, s2 = orc.act_pieces(bf, 2)
+    back = orc.act_pieces_decode(q2, s2)
+    big = np.abs(bf) >= np.repeat(s2, 128, axis=1) * 2.0 ** -6
+    assert np.array_equal(back[big], bf[big].astype(np.float64))  # two pieces hold a bf16 value exactly
+    assert np.max(np.abs(back - bf)) <= np.max(s2) * 2.0 ** -14
+    back3 = orc.act_pieces_decode(q3, s3)
+    rel = np.abs(back3 - x)[np.abs(x) > 0] / np.abs(x)[np.abs(x) > 0]
+    assert np.median(rel) < 2.0 ** -13
+
+
+def test_w4_self_consistency():
+    rng = np.random.default_rng(1)
+    w = rng.normal(0, 0.02, (64, 128)).astype(np.float32); w[0, :32] = 0
+    p, sc = orc.w4_quantize(w)
+    L = orc.lib()
+    scf = np.array([L.orc_f16_to_f32(int(v)) for v in sc.reshape(-1)], np.float32).reshape(sc.shape)
+    assert scf[0, 0] == 1.0
+    assert np.array_equal(sc.view(np.float16).astype(np.float32), scf)
+    lo = (p & 15).astype(np.int8); hi = (p >> 4).astype(np.int8)
+    q = np.stack([lo, hi], -1).reshape(64, 128); q[q > 7] -= 16
+    deq = q * np.repeat(scf, 32, axis=1)
+    assert np.max(np.abs(deq - w)) <= np.max(scf) * 0.5 + 1e-7
+    x = rng.normal(0, 1, (3, 128)).astype(np.float32)
+    y = orc.w4_gemm(p, sc, x, threads=2)
+    assert np.allclose(y, x.astype(np.float64) @ deq.astype(np.float64).T, rtol=1e-12, atol=1e-12)
+    h = rng.normal(0, 30, 2000).astype(np.float32)
+    mine = np.array([L.orc_f32_to_f16(C.c_float(float(v))) for v in h], np.uint16)
+    assert np.array_equal(mine, h.astype(np.float16).view(np.uint16))
