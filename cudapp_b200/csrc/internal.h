@@ -1,0 +1,96 @@
+// internal.h: shared state and helpers of libb200moe.so (not installed; the public surface is include/*.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <time.h>
+#include <mutex>
+
+#include "../../include/b200moe_ext.h"
+#include "../../include/b200moe_plan.h"
+
+static_assert(sizeof(OmegaGpuFp8Info) == 160 && offsetof(OmegaGpuFp8Info, weight_bytes) == 48 &&
+              offsetof(OmegaGpuFp8Info, elapsed_ns) == 64 && offsetof(OmegaGpuFp8Info, call_ns) == 72 &&
+              offsetof(OmegaGpuFp8Info, kernel_cache_hit) == 84 && offsetof(OmegaGpuFp8Info, target_chip) == 85 &&
+              offsetof(OmegaGpuFp8Info, sm_architecture) == 152 && offsetof(OmegaGpuFp8Info, general) == 156,
+              "OmegaGpuFp8Info must keep the reference's binary layout");
+static_assert(sizeof(OmegaGpuFp8GemmInfo) == 88 && offsetof(OmegaGpuFp8GemmInfo, streamed_bytes) == 48 &&
+              offsetof(OmegaGpuFp8GemmInfo, elapsed_ns) == 56 && offsetof(OmegaGpuFp8GemmInfo, call_ns) == 64 &&
+              offsetof(OmegaGpuFp8GemmInfo, general) == 80,
+              "OmegaGpuFp8GemmInfo must keep the reference's binary layout");
+
+struct OmegaGpuFp8Tensor {
+    uint32_t experts, n, k;
+    uint8_t *w;   // device, [experts][n][k] e4m3, checkpoint order
+    float *s;     // device, [experts][n/128][k/128] f32
+    int device;
+};
+
+struct Seg32 { uint64_t w_va, s_va; uint32_t row0, cnt; uint64_t pad; };
+static_assert(sizeof(Seg32) == OMEGA_GEMM_SEG_BYTES, "segment record layout");
+
+namespace b200 {
+
+#define POISON_F32 (-999.0f)
+
+struct State {
+    std::recursive_mutex mu;        // one process-wide lock, as the reference session has
+    char err[256] = {0};
+    bool latched = false;           // a CUDA failure of unknown outcome: every later call is refused
+    bool opened = false;
+    int device = 0;
+    int sm_count = 0;
+    char chip[64] = {0};
+    cudaStream_t stream = nullptr;  // the library's own stream for host-staged calls
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int gemv_mutant = 0, gemm_mutant = 0;
+    uint32_t cta_budget = 0;
+    int sealed = 0;
+    // grow-only staging buffers for host-staged calls
+    void *stage[8] = {nullptr}; size_t stage_bytes[8] = {0};
+};
+State &st();
+
+void set_error(const char *fmt, ...);
+// true when the device is open (opens it on first use); false + last_error otherwise
+bool dev_open();
+// records a failing CUDA call; sticky errors latch the process
+bool cuda_ok(cudaError_t e, const char *what);
+// staging slot `i` with at least `bytes` (device memory); nullptr on failure
+void *stage(int i, size_t bytes);
+uint64_t now_ns();
+
+struct Lock { Lock() { st().mu.lock(); } ~Lock() { st().mu.unlock(); } };
+
+// ---- launchers implemented across the .cu files (all stream-ordered, device pointers)
+// y poison / generic fill
+void launch_fill_f32(float *p, size_t n, float v, cudaStream_t s);
+
+struct GemvArgs {
+    const Seg32 *seg;        // grouped GEMM form: segment records (nullptr for the GEMV forms)
+    const uint64_t *tab;     // GEMV forms: {w_va, s_va} per group
+    const void *x; int x_bf16; uint32_t x_rows;  // activation rows
+    const uint32_t *xmap, *ymap;                 // optional row maps (grouped GEMM form)
+    float *y;
+    uint32_t n, k, groups_or_segs, rows;
+    float out_mul;           // exact power of two applied to the result (removes a caller-side fold)
+    int mutant;
+};
+cudaError_t launch_gemv_grouped(const GemvArgs &a, uint32_t cta_budget, uint32_t *grid_x, uint32_t *warps, cudaStream_t s);
+cudaError_t launch_gemm_rows(const GemvArgs &a, uint32_t *grid_x, uint32_t *mt, cudaStream_t s);
+
+cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s);
+cudaError_t launch_plan(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
+                        const OmegaGpuMoePlanOut &o, cudaStream_t s);
+cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s);
+cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out_f32, uint16_t *out_bf16, cudaStream_t s);
+// quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
+cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap,
+                             const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s);
+bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s);
+bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src);
+void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens);
+float *layer_out32(OmegaGpuMoeLayer *L);
+uint16_t *layer_stage_x(OmegaGpuMoeLayer *L);
+}  // namespace b200

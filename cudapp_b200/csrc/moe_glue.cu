@@ -1,0 +1,167 @@
+// moe_glue.cu: the small operators between the expert GEMMs: SiLU gate, router-weighted combine, and the
+// activation quantiser that feeds the FP8 tensor-core GEMM.
+#include "internal.h"
+
+namespace b200 {
+
+// act[r][c] = g / (1 + exp(-g)) * u with g = gu[r][c], u = gu[r][inter + c]: the reference host glue's form
+// (tests/gpu_decode_graph_test.c:61-66); its kernel computes the same with EX2/RCP approximations
+// (src/omega_blackwell_codegen_dec.c:291-324).
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
+
+__global__ void __launch_bounds__(256) swiglu_kernel(uint32_t rows, uint32_t inter, const float *__restrict__ gu, float *__restrict__ act) {
+    const size_t total = (size_t)rows * inter;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / inter, c = i - r * inter;
+        act[i] = silu_mul(gu[r * 2 * inter + c], gu[r * 2 * inter + inter + c]);
+    }
+}
+cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s) {
+    const size_t total = (size_t)rows * inter;
+    if (!total) return cudaSuccess;
+    size_t blocks = (total + 255) / 256; if (blocks > 148 * 8) blocks = 148 * 8;
+    swiglu_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, inter, gu, act);
+    return cudaGetLastError();
+}
+
+// out[t][c] = w0*d0 ; then m = m + w_s*d_s for s = 1.. in slot order, multiply and add kept separate
+// (src/omega_blackwell_codegen_dec.c:226-255: FMUL then FADD, never FFMA).
+__global__ void __launch_bounds__(256) combine_kernel(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *__restrict__ w,
+                                                      const float *__restrict__ d, float *__restrict__ out, uint16_t *__restrict__ out_bf16) {
+    const uint32_t t = blockIdx.x;
+    for (uint32_t c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+        float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s = 0; s < slots; s++) {
+            const float ws = __ldg(w + (size_t)t * slots + s);
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(d + ((size_t)t * slots + s) * hidden + c));
+            const float4 p = make_float4(__fmul_rn(ws, v.x), __fmul_rn(ws, v.y), __fmul_rn(ws, v.z), __fmul_rn(ws, v.w));
+            if (s == 0) m = p;
+            else m = make_float4(__fadd_rn(m.x, p.x), __fadd_rn(m.y, p.y), __fadd_rn(m.z, p.z), __fadd_rn(m.w, p.w));
+        }
+        if (out) *reinterpret_cast<float4 *>(out + (size_t)t * hidden + c) = m;
+        if (out_bf16) {
+            const uint32_t lo = __float_as_uint(m.x), hi = __float_as_uint(m.y), lo2 = __float_as_uint(m.z), hi2 = __float_as_uint(m.w);
+            auto rne = [](uint32_t x) -> uint32_t { return ((x & 0x7fffffffu) > 0x7f800000u) ? ((x >> 16) | 0x40u) : ((x + 0x7fffu + ((x >> 16) & 1u)) >> 16); };
+            uint2 pk; pk.x = rne(lo) | (rne(hi) << 16); pk.y = rne(lo2) | (rne(hi2) << 16);
+            *reinterpret_cast<uint2 *>(out_bf16 + (size_t)t * hidden + c) = pk;
+        }
+    }
+}
+cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out_f32, uint16_t *out_bf16, cudaStream_t s) {
+    if (!tokens) return cudaSuccess;
+    combine_kernel<<<tokens, 256, 0, s>>>(tokens, slots, hidden, w, d, out_f32, out_bf16);
+    return cudaGetLastError();
+}
+
+// Activation quantiser (src/omega_blackwell_codegen_qg.h:7-19): per row and 128-column group, amax floored at
+// 2^-100, scale = the smallest power of two with amax / scale <= 448, code = e4m3 round-to-nearest-even,
+// saturating. pieces > 1 (this library's exact-activation format): piece p re-encodes the residual the earlier
+// pieces left, scaled by 16^p; every step is exact in f32. One warp per (row, group); lane = 4 columns.
+__device__ __forceinline__ float pq_scale_dev(float amax) {
+    amax = fmaxf(amax, 7.888609052210118e-31f /* 2^-100 */);
+    const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, c = (M + 0x1fffffu) >> 23;
+    return __uint_as_float((E + c - 8u) << 23);
+}
+__device__ __forceinline__ uint32_t enc4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+__device__ __forceinline__ void dec4(uint32_t v, float *o) {
+    uint32_t lo, hi;
+    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.rn.f16x2.e4m3x2 %0, a; cvt.rn.f16x2.e4m3x2 %1, b; }" : "=r"(lo) , "=r"(hi) : "r"(v));
+    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(o[0]), "=f"(o[1]) : "r"(lo));
+    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(o[2]), "=f"(o[3]) : "r"(hi));
+}
+
+__global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, const void *__restrict__ x, int x_bf16,
+                                                        const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
+                                                        uint8_t *__restrict__ q, float *__restrict__ sc) {
+    const uint32_t lane = threadIdx.x & 31u, kb = k / 128u;
+    const uint32_t nrows = rows_dev ? min(rows, *rows_dev) : rows;
+    const size_t tasks = (size_t)nrows * kb;
+    for (size_t task = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); task < tasks; task += (size_t)gridDim.x * (blockDim.x >> 5)) {
+        const uint32_t r = (uint32_t)(task / kb), b = (uint32_t)(task - (size_t)r * kb);
+        const uint32_t src = xmap ? xmap[r] : r;
+        float v[4];
+        if (x_bf16) {
+            const uint2 u = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(x) + (size_t)src * k + b * 128u + lane * 4u));
+            v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u); v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+        } else {
+            const float4 u = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + (size_t)src * k + b * 128u + lane * 4u));
+            v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+        }
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float s = pq_scale_dev(amax);
+        if (lane == 0) sc[(size_t)r * kb + b] = s;
+        float res[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], s);
+        for (uint32_t p = 0; p < pieces; p++) {
+            const uint32_t code = enc4(res[0], res[1], res[2], res[3]);
+            *reinterpret_cast<uint32_t *>(q + ((size_t)r * pieces + p) * k + b * 128u + lane * 4u) = code;
+            float d[4]; dec4(code, d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
+        }
+    }
+}
+cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap, const uint32_t *rows_dev,
+                             uint8_t *q, float *sc, cudaStream_t s) {
+    const size_t tasks = (size_t)rows * (k / 128u);
+    if (!tasks) return cudaSuccess;
+    size_t blocks = (tasks + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8;
+    act_quant_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, x, x_bf16, xmap, rows_dev, q, sc);
+    return cudaGetLastError();
+}
+
+}  // namespace b200
+using namespace b200;
+
+extern "C" {
+
+int omega_gpu_swiglu_f32(uint32_t rows, uint32_t inter, const float *gu, float *act) {
+    if (!rows || !inter || !gu || !act) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t ib = (size_t)rows * inter * 8, ob = (size_t)rows * inter * 4;
+    float *dg = (float *)stage(0, ib), *da = (float *)stage(1, ob);
+    if (!dg || !da) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaStream_t s = st().stream;
+    const bool ok = cuda_ok(cudaMemcpyAsync(dg, gu, ib, cudaMemcpyHostToDevice, s), "copy gu") && cuda_ok(launch_swiglu(rows, inter, dg, da, s), "swiglu launch") &&
+                    cuda_ok(cudaMemcpyAsync(act, da, ob, cudaMemcpyDeviceToHost, s), "copy act") && cuda_ok(cudaStreamSynchronize(s), "swiglu");
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+int omega_gpu_moe_combine_f32(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out) {
+    if (!tokens || !slots || !hidden || hidden % 4 || !w || !d || !out) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t wb = (size_t)tokens * slots * 4, db = wb * hidden, ob = (size_t)tokens * hidden * 4;
+    float *dw = (float *)stage(0, wb), *dd = (float *)stage(1, db), *dout = (float *)stage(2, ob);
+    if (!dw || !dd || !dout) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaStream_t s = st().stream;
+    const bool ok = cuda_ok(cudaMemcpyAsync(dw, w, wb, cudaMemcpyHostToDevice, s), "copy w") && cuda_ok(cudaMemcpyAsync(dd, d, db, cudaMemcpyHostToDevice, s), "copy d") &&
+                    cuda_ok(launch_combine(tokens, slots, hidden, dw, dd, dout, nullptr, s), "combine launch") &&
+                    cuda_ok(cudaMemcpyAsync(out, dout, ob, cudaMemcpyDeviceToHost, s), "copy out") && cuda_ok(cudaStreamSynchronize(s), "combine");
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+int omega_gpu_act_quant_f32(uint32_t rows, uint32_t k, uint32_t pieces, const float *x, uint8_t *q, float *sc) {
+    if (!rows || !k || k % 128 || !pieces || pieces > 4 || !x || !q || !sc) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t xb = (size_t)rows * k * 4, qb = (size_t)rows * pieces * k, sb = (size_t)rows * (k / 128) * 4;
+    float *dx = (float *)stage(0, xb); uint8_t *dq = (uint8_t *)stage(1, qb); float *ds = (float *)stage(2, sb);
+    if (!dx || !dq || !ds) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaStream_t s = st().stream;
+    const bool ok = cuda_ok(cudaMemcpyAsync(dx, x, xb, cudaMemcpyHostToDevice, s), "copy x") &&
+                    cuda_ok(launch_act_quant(rows, k, pieces, dx, 0, nullptr, nullptr, dq, ds, s), "act quant launch") &&
+                    cuda_ok(cudaMemcpyAsync(q, dq, qb, cudaMemcpyDeviceToHost, s), "copy q") && cuda_ok(cudaMemcpyAsync(sc, ds, sb, cudaMemcpyDeviceToHost, s), "copy s") &&
+                    cuda_ok(cudaStreamSynchronize(s), "act quant");
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+// moe_layer.cu: the quantized MoE layer and layer stack as host-side orchestration of this library's kernels.
+// One layer = the MoE part of the reference decode graph (src/omega_gpu_decode_graph.c:341-351) and of its
+// prefill recorder (src/omega_gpu_q36_graph.c:1147): router top-k, routing plan, gate|up grouped GEMM with the
+// SiLU gate, down grouped GEMM, router-weighted combine. Everything between the input copy and the output copy
+// stays on the device; the routing plan is never read back.
+#include <stdlib.h>
+#include <vector>
+#include "internal.h"
+
+namespace b200 {
+
+struct Workspace {
+    uint32_t max_tokens, topk, experts, hidden, inter;
+    int refs;
+    uint32_t *ids, *counts, *starts, *xmap, *ymap, *header;
+    float *wts;
+    Seg32 *seg_gu, *seg_dn;
+    uint4 *tiles;
+    float *gu, *act, *dn;          // [R][2I], [R][I], [R][H]
+    uint8_t *qx, *qa;              // e4m3 pieces of x rows / act rows (tensor-core engine)
+    float *sx, *sa;                // their per-128 scales
+    uint16_t *logits, *x, *out16;  // staging for the host-buffer entry
+    float *out32;
+    char *base;
+};
+
+static size_t align_up(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t experts, uint32_t hidden, uint32_t inter) {
+    Workspace *w = (Workspace *)calloc(1, sizeof *w);
+    if (!w) return nullptr;
+    w->max_tokens = max_tokens; w->topk = topk; w->experts = experts; w->hidden = hidden; w->inter = inter; w->refs = 1;
+    const size_t R = (size_t)max_tokens * topk, Rp = R + 8;
+    const size_t max_tiles = R / 8 + experts + 8;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off += align_up(bytes); return o; };
+    const size_t o_ids = take(R * 4), o_wts = take(R * 4), o_cnt = take((size_t)experts * 4), o_st = take((size_t)experts * 4),
+                 o_xm = take(Rp * 4), o_ym = take(Rp * 4), o_hdr = take(64), o_sgu = take((size_t)experts * 32), o_sdn = take((size_t)experts * 32),
+                 o_tiles = take(max_tiles * 16), o_gu = take(Rp * 2 * inter * 4), o_act = take(Rp * inter * 4), o_dn = take(Rp * hidden * 4),
+                 o_qx = take(Rp * 4 * hidden), o_qa = take(Rp * 4 * inter), o_sx = take(Rp * (hidden / 128) * 4), o_sa = take(Rp * (inter / 128) * 4),
+                 o_lg = take((size_t)max_tokens * experts * 2), o_x = take((size_t)max_tokens * hidden * 2), o_o16 = take((size_t)max_tokens * hidden * 2),
+                 o_o32 = take((size_t)max_tokens * hidden * 4);
+    if (!cuda_ok(cudaMalloc(&w->base, off), "cudaMalloc(workspace)")) { free(w); return nullptr; }
+    if (!cuda_ok(cudaMemset(w->base, 0, off), "cudaMemset(workspace)")) { cudaFree(w->base); free(w); return nullptr; }
+    char *b = w->base;
+    w->ids = (uint32_t *)(b + o_ids); w->wts = (float *)(b + o_wts); w->counts = (uint32_t *)(b + o_cnt); w->starts = (uint32_t *)(b + o_st);
+    w->xmap = (uint32_t *)(b + o_xm); w->ymap = (uint32_t *)(b + o_ym); w->header = (uint32_t *)(b + o_hdr);
+    w->seg_gu = (Seg32 *)(b + o_sgu); w->seg_dn = (Seg32 *)(b + o_sdn); w->tiles = (uint4 *)(b + o_tiles);
+    w->gu = (float *)(b + o_gu); w->act = (float *)(b + o_act); w->dn = (float *)(b + o_dn);
+    w->qx = (uint8_t *)(b + o_qx); w->qa = (uint8_t *)(b + o_qa); w->sx = (float *)(b + o_sx); w->sa = (float *)(b + o_sa);
+    w->logits = (uint16_t *)(b + o_lg); w->x = (uint16_t *)(b + o_x); w->out16 = (uint16_t *)(b + o_o16); w->out32 = (float *)(b + o_o32);
+    return w;
+}
+static void workspace_release(Workspace *w) {
+    if (!w || --w->refs > 0) return;
+    if (w->base) cudaFree(w->base);
+    free(w);
+}
+
+}  // namespace b200
+
+struct OmegaGpuMoeLayer {
+    const OmegaGpuFp8Tensor *gu, *dn;
+    OmegaGpuMoeConfig cfg;
+    uint32_t experts, hidden, inter;
+    uint64_t *dir_gu, *dir_dn;   // device {w_va, s_va} per expert
+    b200::Workspace *ws;
+    uint32_t launches;
+};
+
+namespace b200 {
+
+// one forward, device pointers, stream-ordered. out32 required; out16 optional.
+bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s) {
+    Workspace *w = L->ws;
+    const uint32_t K = L->cfg.topk, E = L->experts, H = L->hidden, I = L->inter, R = tokens * K;
+    uint32_t n = 0;
+    if (!cuda_ok(launch_topk(tokens, E, K, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s), "topk launch")) return false; n++;
+    OmegaGpuMoePlanOut o = {};
+    o.counts_va = (uint64_t)(uintptr_t)w->counts; o.starts_va = (uint64_t)(uintptr_t)w->starts;
+    o.xmap_va = (uint64_t)(uintptr_t)w->xmap; o.ymap_va = (uint64_t)(uintptr_t)w->ymap; o.header_va = (uint64_t)(uintptr_t)w->header;
+    o.seg_a_va = (uint64_t)(uintptr_t)w->seg_gu; o.dir_a_va = (uint64_t)(uintptr_t)L->dir_gu;
+    o.seg_b_va = (uint64_t)(uintptr_t)w->seg_dn; o.dir_b_va = (uint64_t)(uintptr_t)L->dir_dn;
+    if (!cuda_ok(launch_plan(tokens, K, E, K, 0, w->ids, o, s), "plan launch")) return false; n++;
+    // gate|up: sorted row p reads x[xmap[p]], writes gu row p
+    GemvArgs a = {};
+    a.seg = w->seg_gu; a.x = x; a.x_bf16 = 1; a.x_rows = tokens; a.xmap = w->xmap; a.ymap = nullptr;
+    a.y = w->gu; a.n = 2 * I; a.k = H; a.groups_or_segs = E; a.rows = R; a.out_mul = 1.0f;
+    if (!cuda_ok(launch_gemm_rows(a, nullptr, nullptr, s), "gate|up launch")) return false; n++;
+    if (!cuda_ok(launch_swiglu(R, I, w->gu, w->act, s), "swiglu launch")) return false; n++;
+    // down: sorted row p reads act row p, writes dn row ymap[p] = token * topk + slot
+    GemvArgs d = {};
+    d.seg = w->seg_dn; d.x = w->act; d.x_bf16 = 0; d.x_rows = R; d.xmap = nullptr; d.ymap = w->ymap;
+    d.y = w->dn; d.n = H; d.k = I; d.groups_or_segs = E; d.rows = R; d.out_mul = 1.0f;
+    if (!cuda_ok(launch_gemm_rows(d, nullptr, nullptr, s), "down launch")) return false; n++;
+    if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; n++;
+    L->launches = n;
+    return true;
+}
+
+// dst drops its own workspace and uses src's (same shape, at least as many tokens); calls on them must then be stream-ordered
+bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src) {
+    if (dst->ws == src->ws) return true;
+    if (dst->experts != src->experts || dst->hidden != src->hidden || dst->inter != src->inter || dst->cfg.topk != src->cfg.topk ||
+        dst->cfg.max_tokens > src->cfg.max_tokens) return false;
+    workspace_release(dst->ws);
+    dst->ws = src->ws; src->ws->refs++;
+    return true;
+}
+void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens) { *experts = L->experts; *hidden = L->hidden; *max_tokens = L->cfg.max_tokens; }
+float *layer_out32(OmegaGpuMoeLayer *L) { return L->ws->out32; }
+uint16_t *layer_stage_x(OmegaGpuMoeLayer *L) { return L->ws->x; }
+
+}  // namespace b200
+using namespace b200;
+
+extern "C" {
+
+int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuFp8Tensor *down, const OmegaGpuMoeConfig *cfg, OmegaGpuMoeLayer **out) {
+    if (out) *out = nullptr;
+    if (!gate_up || !down || !cfg || !out) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (gate_up->experts != down->experts || gate_up->n != 2 * down->k || gate_up->k != down->n) { set_error("moe layer: gate|up [E][2I][H] and down [E][H][I] do not match"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (cfg->topk == 0 || cfg->topk > 32 || cfg->topk > gate_up->experts || cfg->max_tokens == 0 || gate_up->experts > 1024) return OMEGA_GPU_FP8_BAD_ARGS;
+    if ((uint64_t)cfg->max_tokens * cfg->topk > (1u << 24)) return OMEGA_GPU_FP8_TOO_LARGE;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    OmegaGpuMoeLayer *L = (OmegaGpuMoeLayer *)calloc(1, sizeof *L);
+    if (!L) return OMEGA_GPU_FP8_BAD_ARGS;
+    L->gu = gate_up; L->dn = down; L->cfg = *cfg; L->experts = gate_up->experts; L->hidden = gate_up->k; L->inter = down->k;
+    if (L->cfg.engine == OMEGA_GPU_MOE_ENGINE_AUTO) L->cfg.engine = OMEGA_GPU_MOE_ENGINE_FMA;
+    if (!L->cfg.x_pieces) L->cfg.x_pieces = 2;
+    if (!L->cfg.act_pieces) L->cfg.act_pieces = 3;
+    const uint32_t E = L->experts;
+    std::vector<uint64_t> dir((size_t)E * 4);
+    for (uint32_t e = 0; e < E; e++) {
+        (void)omega_gpu_fp8_tensor_entry(gate_up, e, &dir[2 * e], &dir[2 * e + 1]);
+        (void)omega_gpu_fp8_tensor_entry(down, e, &dir[2 * E + 2 * e], &dir[2 * E + 2 * e + 1]);
+    }
+    bool ok = cuda_ok(cudaMalloc(&L->dir_gu, (size_t)E * 32), "cudaMalloc(directory)");
+    if (ok) { L->dir_dn = L->dir_gu + 2 * E; ok = cuda_ok(cudaMemcpy(L->dir_gu, dir.data(), (size_t)E * 32, cudaMemcpyHostToDevice), "copy directory"); }
+    if (ok) { L->ws = workspace_create(cfg->max_tokens, cfg->topk, E, L->hidden, L->inter); ok = L->ws != nullptr; }
+    if (!ok) { if (L->dir_gu) cudaFree(L->dir_gu); free(L); return OMEGA_GPU_FP8_CHIP_FAIL; }
+    *out = L;
+    return OMEGA_GPU_FP8_OK;
+}
+
+void omega_gpu_moe_layer_free(OmegaGpuMoeLayer *L) {
+    if (!L) return;
+    Lock l;
+    workspace_release(L->ws);
+    if (L->dir_gu) cudaFree(L->dir_gu);
+    free(L);
+}
+
+uint32_t omega_gpu_moe_layer_launches(const OmegaGpuMoeLayer *L) { return L ? L->launches : 0; }
+
+int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va, uint64_t out_bf16_va, void *stream) {
+    if (!L || !tokens || !logits_va || !x_va || !out_f32_va) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (tokens > L->cfg.max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    return layer_forward(L, tokens, (const uint16_t *)(uintptr_t)logits_va, (const uint16_t *)(uintptr_t)x_va, (float *)(uintptr_t)out_f32_va,
+                         (uint16_t *)(uintptr_t)out_bf16_va, (cudaStream_t)stream) ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, uint16_t *out_bf16, float *out_f32,
+                             uint32_t *ids, float *wts) {
+    if (!L || !tokens || !logits || !x || (!out_bf16 && !out_f32)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (tokens > L->cfg.max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    Workspace *w = L->ws; cudaStream_t s = st().stream;
+    const size_t lb = (size_t)tokens * L->experts * 2, xb = (size_t)tokens * L->hidden * 2, rb = (size_t)tokens * L->cfg.topk * 4;
+    bool ok = cuda_ok(cudaMemcpyAsync(w->logits, logits, lb, cudaMemcpyHostToDevice, s), "copy logits") &&
+              cuda_ok(cudaMemcpyAsync(w->x, x, xb, cudaMemcpyHostToDevice, s), "copy x") &&
+              layer_forward(L, tokens, w->logits, w->x, w->out32, w->out16, s);
+    if (ok && out_bf16) ok = cuda_ok(cudaMemcpyAsync(out_bf16, w->out16, xb, cudaMemcpyDeviceToHost, s), "copy out");
+    if (ok && out_f32) ok = cuda_ok(cudaMemcpyAsync(out_f32, w->out32, xb * 2, cudaMemcpyDeviceToHost, s), "copy out");
+    if (ok && ids) ok = cuda_ok(cudaMemcpyAsync(ids, w->ids, rb, cudaMemcpyDeviceToHost, s), "copy ids");
+    if (ok && wts) ok = cuda_ok(cudaMemcpyAsync(wts, w->wts, rb, cudaMemcpyDeviceToHost, s), "copy weights");
+    ok = ok && cuda_ok(cudaStreamSynchronize(s), "moe layer");
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+/*
+ * b200moe_ext.h: entry points with no same-named counterpart in the reference: the router top-k on given logits,
+ * the device-resident routing plan at any token count, the glue operators as single calls, the W4 GEMM, and the
+ * whole quantized MoE layer / layer stack. Each cites the reference operator whose arithmetic it carries.
+ *
+ * Forms: a name ending in _async takes device addresses and a cudaStream_t (as void *) and neither copies nor
+ * synchronises; every other entry takes HOST buffers, stages them, runs the kernels and copies the result back.
+ * Return codes are the OMEGA_GPU_FP8_* values of b200moe_fp8.h; the failing stage is in omega_gpu_fp8_last_error().
+ */
+#ifndef B200MOE_EXT_H
+#define B200MOE_EXT_H
+#include "b200moe_fp8gemm.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- device-resident forms of upload and quantise (weights produced on the GPU, e.g. synthetic benchmark data).
+ * Same rules as omega_gpu_fp8_tensor_upload / omega_gpu_fp8_quantize_bf16; the sources are device addresses and are
+ * copied, so the caller may free them afterwards. Synchronous. */
+int omega_gpu_fp8_tensor_upload_dev(uint32_t experts, uint32_t n, uint32_t k, uint64_t w_va, uint64_t scale_inv_bf16_va,
+                                    OmegaGpuFp8Tensor **out);
+int omega_gpu_fp8_quantize_bf16_dev(uint32_t n, uint32_t k, uint64_t w_bf16_va, uint64_t w8_va, uint64_t scale_inv_bf16_va);
+
+/* ---- router top-k on given logits: k rounds of "largest remaining, lowest index on ties", ids in selection order,
+ * weights = softmax over the selected logits (norm_topk) or over all experts (src/omega_blackwell_codegen_router.c:298-401,
+ * oracle tests/gpu_router_test.c:62-79). logits bf16 [tokens][experts], experts <= 1024, topk <= 32. */
+int omega_gpu_moe_topk_bf16(uint32_t tokens, uint32_t experts, uint32_t topk, int norm_topk, const uint16_t *logits_bf16,
+                            uint32_t *ids, float *wts);
+int omega_gpu_moe_topk_async(uint32_t tokens, uint32_t experts, uint32_t topk, int norm_topk, uint64_t logits_va,
+                             uint64_t ids_va, uint64_t wts_va, void *stream);
+
+/* ---- routing plan, device u32 form, any token count (the on-chip GROUP of src/omega_blackwell_codegen_dec.c:534-651
+ * and the host GROUP of src/omega_gpu_q36_graph.c:1107-1144, same ordering rule: expert, token, slot).
+ * ids u32 [tokens][slots] (0xFFFFFFFF = absent). Outputs: counts[experts], starts[experts] (exclusive scan),
+ * xmap[rows+8] = token, ymap[rows+8] = token*ystride+slot (8 zero pads), seg: 32-byte records for the non-empty
+ * experts in ascending id built from the two directories ({w_va, s_va} per expert), records past the last
+ * non-empty expert up to `experts` zeroed; tiles: one {expert, row0, cnt} u32 x4 entry per `tile_rows` slice of
+ * a segment (tile_rows 0 = none); header u32[8] = {rows, segments, tiles, status, 0...}; status 2 = id out of range. */
+typedef struct {
+    uint64_t counts_va, starts_va, xmap_va, ymap_va;
+    uint64_t seg_a_va, dir_a_va; /* first projection's segment records and {w_va, s_va} directory (may be 0) */
+    uint64_t seg_b_va, dir_b_va; /* second projection's (may be 0) */
+    uint64_t tiles_va;           /* u32 x4 per tile (may be 0) */
+    uint64_t header_va;          /* u32[8] */
+} OmegaGpuMoePlanOut;
+int omega_gpu_moe_plan_async(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
+                             uint64_t ids_va, const OmegaGpuMoePlanOut *out, void *stream);
+/* host form for tests: returns rows/segments through the arrays; seg3 = {expert, row0, cnt} per segment */
+int omega_gpu_moe_plan_u32(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, const uint32_t *ids,
+                           uint32_t *counts, uint32_t *starts, uint32_t *xmap, uint32_t *ymap, uint32_t *seg3,
+                           uint32_t *rows, uint32_t *segments);
+
+/* ---- glue operators as single host calls (parity with the reference's separate launches) */
+/* act[r][c] = silu(gu[r][c]) * gu[r][inter + c] (src/omega_blackwell_codegen_dec.c:291-324) */
+int omega_gpu_swiglu_f32(uint32_t rows, uint32_t inter, const float *gu, float *act);
+/* out[t] = sum over slots of w[t][s] * d[t][s], multiply then add in slot order, never fused
+ * (src/omega_blackwell_codegen_dec.c:226-255) */
+int omega_gpu_moe_combine_f32(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out);
+/* per row, per 128 columns: power-of-two scale, e4m3 codes (src/omega_blackwell_codegen_qg.h:7-19). pieces > 1
+ * adds residual pieces at scale/16^p (this library's exact-activation format). q: [rows][pieces][k]. */
+int omega_gpu_act_quant_f32(uint32_t rows, uint32_t k, uint32_t pieces, const float *x, uint8_t *q, float *s);
+
+/* ---- W4: signed int4 weights, two per byte along K (low nibble = even column), fp16 scale per 32 columns.
+ * The reference has no integer-W4 arithmetic (docs/models/QUANT.md:62); this follows the benchmark definition. */
+typedef struct OmegaGpuW4Tensor OmegaGpuW4Tensor;
+int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint16_t *scale_f16, OmegaGpuW4Tensor **out);
+void omega_gpu_w4_free(OmegaGpuW4Tensor *t);
+/* y bf16 [m][n] = x bf16 [m][k] * W^T, f32 accumulation; yf32 (optional) receives the unrounded values */
+int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32);
+
+/* ---- the MoE layer: top-k -> plan -> gate|up grouped GEMM + SiLU gate -> down grouped GEMM -> weighted combine
+ * (the MoE part of src/omega_gpu_decode_graph.c:341-351 for decode, src/omega_gpu_q36_graph.c:1147 for prefill). */
+typedef struct OmegaGpuMoeLayer OmegaGpuMoeLayer;
+enum { OMEGA_GPU_MOE_ENGINE_AUTO = 0, OMEGA_GPU_MOE_ENGINE_FMA = 1, OMEGA_GPU_MOE_ENGINE_MMA = 2 };
+typedef struct {
+    uint32_t topk;        /* 8 */
+    uint32_t max_tokens;  /* scratch is sized for this many tokens per call */
+    uint32_t engine;      /* AUTO, FMA (CUDA-core, reference summation order) or MMA (tcgen05 FP8 tensor cores) */
+    uint32_t x_pieces;    /* MMA: e4m3 pieces per bf16 input value (2 = exact, 1 = plain FP8 activations); 0 = 2 */
+    uint32_t act_pieces;  /* MMA: pieces per f32 SwiGLU output (0 = 3) */
+    uint32_t norm_topk;   /* 1: weights renormalised over the selected experts */
+    uint32_t first_expert, local_experts; /* expert-parallel shard held here; 0, 0 = all */
+    uint32_t reserved;
+} OmegaGpuMoeConfig;
+/* gate_up: [E][2I][H] (gate rows first), down: [E][H][I]; both stay owned by the caller and must outlive the layer */
+int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuFp8Tensor *down, const OmegaGpuMoeConfig *cfg,
+                               OmegaGpuMoeLayer **out);
+void omega_gpu_moe_layer_free(OmegaGpuMoeLayer *l);
+/* host buffers: logits bf16 [tokens][E], x bf16 [tokens][H] -> out bf16 [tokens][H]; out_f32, ids, wts optional */
+int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *l, uint32_t tokens, const uint16_t *logits_bf16, const uint16_t *x_bf16,
+                             uint16_t *out_bf16, float *out_f32, uint32_t *ids, float *wts);
+/* device buffers, stream-ordered: out_f32_va f32 [tokens][H] (required), out_bf16_va optional (0 = skip) */
+int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
+                              uint64_t out_bf16_va, void *stream);
+/* number of kernels the last forward of this layer launched */
+uint32_t omega_gpu_moe_layer_launches(const OmegaGpuMoeLayer *l);
+
+/* ---- a stack of MoE layers, the MoE part of the reference's whole-token decode graph (src/omega_gpu_decode_graph.c:321-351):
+ * h = x; per layer: xn = bf16(RMSNorm(h)) (unit norm weights; sum of squares in double as the reference host glue,
+ * tests/gpu_decode_graph_test.c:56-60), h = h + MoE_l(xn, logits_l). Router logits are inputs (one [tokens][E] block per
+ * layer). Layers of one stack share one scratch workspace and run as one CUDA graph per token count. */
+typedef struct OmegaGpuMoeStack OmegaGpuMoeStack;
+int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, float eps, OmegaGpuMoeStack **out);
+void omega_gpu_moe_stack_free(OmegaGpuMoeStack *s);
+/* host buffers: logits bf16 [layers][tokens][E], x bf16 [tokens][H] -> out bf16 [tokens][H] (final h), out_f32 optional */
+int omega_gpu_moe_stack_bf16(OmegaGpuMoeStack *s, uint32_t tokens, const uint16_t *logits_bf16, const uint16_t *x_bf16,
+                             uint16_t *out_bf16, float *out_f32);
+/* device buffers, stream-ordered (captures and replays a graph on `stream`) */
+int omega_gpu_moe_stack_async(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
+                              uint64_t out_bf16_va, void *stream);
+uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

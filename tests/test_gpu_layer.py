@@ -1,0 +1,89 @@
+"""GPU parity of the whole MoE layer and of the layer stack against the CPU checker, through the C-ABI.
+
+The checker strings the reference's operators together exactly as its host glue does
+(tests/gpu_decode_graph_test.c:129-147): top-k, per pick gate|up GEMV -> SiLU gate -> down GEMV, slot-order weighted
+sum. Bars (the benchmark's): routing ids bit-exact, outputs max-abs <= 1e-2 and rel-L2 <= 1e-3 on the f32 result.
+"""
+import numpy as np
+import pytest
+
+from cudapp_b200 import api
+from oracle import oracle as orc
+from tests.test_gpu_ops import make_weights, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def build_layer(rng, E, H, I, max_tokens, engine, topk=8, **kw):
+    wgu, sgu = make_weights(rng, E, 2 * I, H)
+    wdn, sdn = make_weights(rng, E, H, I)
+    rc, tgu = api.fp8_tensor_upload(E, 2 * I, H, wgu, sgu); assert rc == 0, api.last_error()
+    rc, tdn = api.fp8_tensor_upload(E, H, I, wdn, sdn); assert rc == 0, api.last_error()
+    rc, layer = api.moe_layer_create(tgu, tdn, topk=topk, max_tokens=max_tokens, engine=engine, **kw)
+    assert rc == 0, api.last_error()
+    return dict(wgu=wgu, sgu=sgu, wdn=wdn, sdn=sdn, tgu=tgu, tdn=tdn, layer=layer)
+
+
+def free_layer(m):
+    api.lib.omega_gpu_moe_layer_free(m["layer"]); api.fp8_tensor_free(m["tgu"]); api.fp8_tensor_free(m["tdn"])
+
+
+def check_layer(m, logits, xb, topk, tol_abs=1e-2, tol_rel=1e-3):
+    rc, o16, o32, ids, w = api.moe_layer_bf16(m["layer"], logits, xb, topk)
+    assert rc == 0, api.last_error()
+    ref, rid, rw = orc.moe_layer(logits, xb, m["wgu"], m["sgu"], m["wdn"], m["sdn"], topk)
+    assert np.array_equal(ids, rid)
+    assert np.max(np.abs(w - rw)) <= 1e-5
+    err, rl2 = float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref)
+    assert err <= tol_abs and rl2 <= tol_rel, (err, rl2)
+    assert np.array_equal(o16, orc.bf16_bits(o32))
+    return err, rl2
+
+
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA])
+@pytest.mark.parametrize("tokens", [1, 7, 64])
+def test_layer_small(engine, tokens):
+    rng = np.random.default_rng(100 + tokens)
+    E, H, I, topk = 16, 512, 256, 4
+    m = build_layer(rng, E, H, I, 64, engine, topk)
+    logits = orc.bf16_bits(rng.normal(0, 1, (tokens, E)).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (tokens, H)).astype(np.float32))
+    check_layer(m, logits, xb, topk)
+    assert api.lib.omega_gpu_moe_layer_launches(m["layer"]) >= 4
+    free_layer(m)
+
+
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA])
+def test_layer_decode_shape(engine):
+    """the decode configuration's architecture (hidden 2048, expert intermediate 768, top-8) on 32 experts, 64 tokens"""
+    rng = np.random.default_rng(7)
+    E, H, I = 32, 2048, 768
+    m = build_layer(rng, E, H, I, 64, engine)
+    logits = orc.bf16_bits(rng.normal(0, 1, (64, E)).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (64, H)).astype(np.float32))
+    check_layer(m, logits, xb, 8)
+    free_layer(m)
+
+
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA])
+def test_stack_small(engine):
+    rng = np.random.default_rng(9)
+    E, H, I, topk, T, Ln = 16, 512, 256, 4, 24, 3
+    ms = [build_layer(rng, E, H, I, 32, engine, topk) for _ in range(Ln)]
+    rc, stack = api.moe_stack_create([m["layer"] for m in ms], 1e-6); assert rc == 0, api.last_error()
+    logits = orc.bf16_bits(rng.normal(0, 1, (Ln, T, E)).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    rc, o16, o32 = api.moe_stack_bf16(stack, logits, xb); assert rc == 0, api.last_error()
+    h = orc.bf16_to_f32(xb)
+    for l in range(Ln):
+        xn = orc.bf16_bits(orc.rmsnorm(h, 1e-6))
+        mo, _, _ = orc.moe_layer(logits[l], xn, ms[l]["wgu"], ms[l]["sgu"], ms[l]["wdn"], ms[l]["sdn"], topk)
+        h = h + mo
+    assert np.max(np.abs(o32 - h)) <= 1e-2 and rel_l2(o32, h) <= 1e-3
+    assert np.array_equal(o16, orc.bf16_bits(o32))
+    rc, o16b, o32b = api.moe_stack_bf16(stack, logits, xb)          # graph replay: identical bits
+    assert rc == 0 and np.array_equal(o32, o32b)
+    assert api.lib.omega_gpu_moe_stack_launches(stack) > Ln * 4
+    api.lib.omega_gpu_moe_stack_free(stack)
+    for m in ms:
+        free_layer(m)
