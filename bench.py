@@ -1,0 +1,295 @@
+"""Benchmark of the quantized MoE expert path on B200: MoE-layer tokens/s.
+
+Workload (the configuration the metric is quoted on): a 48-layer MoE expert stack, each layer 128 experts, top-8,
+hidden 2048, expert intermediate 768, FP8 e4m3 weights with 128x128 block scales drawn from N(0, 0.02), 256 decode
+tokens per step; router logits bf16 ~N(0,1) are inputs. Synthetic seeded data (no checkpoint). A "step" is one pass
+of 256 tokens through all 48 layers. Weights are 29 GB per step, far larger than L2, so every step streams them
+from HBM again.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints one JSON line (rank 0). `value` = tokens/s with inputs resident in HBM (CUDA events on the launching stream);
+`e2e` = the same through the host-buffer C-ABI call, copies included; `roofline` = the dominant kernel against the
+measured HBM copy bandwidth; `cpu_baseline` = the reference's own host GEMV oracle on a bounded sample.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+E, H, I, TOPK = 128, 2048, 768, 8
+GU_BYTES = 2 * I * H + (2 * I // 128) * (H // 128) * 4      # one expert's gate|up codes + f32 scales
+DN_BYTES = H * I + (H // 128) * (I // 128) * 4
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--tokens", type=int, default=256)
+    ap.add_argument("--engine", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=8)
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------- CPU arm
+def cpu_layer_sample(tokens, steps, warmup, seed=0):
+    """Times the reference's own host GEMV oracle (oracle/_ref, built from the reference sources) or, where that
+    build is absent, the checker's restatement of it, on `tokens` tokens through ONE layer with every host thread.
+    Returns (seconds per step, kind, cores)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as orc
+    cores = len(os.sched_getaffinity(0))
+    rng = np.random.default_rng(seed)
+    logits = orc.bf16_bits(rng.normal(0, 1, (tokens, E)).astype(np.float32))
+    x = orc.bf16_to_f32(orc.bf16_bits(rng.normal(0, 1, (tokens, H)).astype(np.float32)))
+    ids, w64 = orc.topk(orc.bf16_to_f32(logits), TOPK, True)
+    used = np.unique(ids)
+    wgu, sgu, wdn, sdn = {}, {}, {}, {}
+
+    def make(e):
+        r = np.random.default_rng([seed, int(e)])
+        wgu[e], sgu[e] = orc.quantize_bf16(orc.bf16_bits((r.standard_normal((2 * I, H), dtype=np.float32) * 0.02)))
+        wdn[e], sdn[e] = orc.quantize_bf16(orc.bf16_bits((r.standard_normal((H, I), dtype=np.float32) * 0.02)))
+    with ThreadPoolExecutor(cores) as ex:
+        list(ex.map(make, used))
+    R = orc.ref_lib()
+    kind = "reference" if R is not None else "port"
+    L = orc.lib()
+    p = lambda a, t: a.ctypes.data_as(t)
+
+    def gemv(w8, sc, n, k, xv, y):
+        if R is not None:
+            R.omega_fp8_gemv_oracle(p(w8, orc.U8P), p(sc, orc.U16P), C.c_uint32(n), C.c_uint32(k), p(xv, orc.F32P), p(y, orc.F64P), None)
+        else:
+            L.orc_gemv(p(w8, orc.U8P), p(sc, orc.U16P), C.c_uint32(n), C.c_uint32(k), p(xv, orc.F32P), p(y, orc.F64P), None)
+
+    dn = np.zeros((tokens * TOPK, H), np.float32)
+
+    def row(i):
+        t, e = i // TOPK, int(ids.reshape(-1)[i])
+        y = np.empty(2 * I, np.float64); gemv(wgu[e], sgu[e], 2 * I, H, x[t], y)
+        gu = y.astype(np.float32); act = np.empty(I, np.float32)
+        L.orc_swiglu(p(gu, orc.F32P), C.c_uint32(I), p(act, orc.F32P))
+        y2 = np.empty(H, np.float64); gemv(wdn[e], sdn[e], H, I, act, y2)
+        dn[i] = y2
+    times = []
+    with ThreadPoolExecutor(cores) as ex:
+        for s in range(warmup + steps):
+            t0 = time.perf_counter()
+            list(ex.map(row, range(tokens * TOPK)))
+            orc.combine(w64.astype(np.float32), dn.reshape(tokens, TOPK, H))
+            if s >= warmup:
+                times.append(time.perf_counter() - t0)
+    return float(np.mean(times)), kind, cores
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    tok = max(args.cpu_sample_tokens, 8)
+    sec, kind, cores = cpu_layer_sample(tok, max(1, args.steps), min(args.warmup, 1))
+    value = tok / (sec * args.layers)
+    sample = "%d tokens through 1 of %d layers per step (x%d extrapolated), double-precision host GEMV oracle per routed row, %d threads" % (tok, args.layers, args.layers, cores)
+    print(json.dumps({
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * args.layers * args.tokens / tok * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 weights, f64 accumulate", "data": "synthetic",
+        "config": {"workload": "48-layer MoE expert stack, 256 decode tokens/step, 128 experts top-8, hidden 2048, inter 768", "layers": args.layers,
+                   "tokens_per_step": args.tokens},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ---------------------------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    QUERY = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.rows = []
+        self.stop = threading.Event()
+        self.index = index
+        self.th = threading.Thread(target=self.run, daemon=True)
+
+    def run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self.stop.wait(0.1)
+
+    def __enter__(self):
+        self.th.start(); return self
+
+    def __exit__(self, *a):
+        self.stop.set(); self.th.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for j, n in enumerate(names) if any(r[3 + j].lower().startswith("active") for r in self.rows if len(r) > 3 + j)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(self.rows[0][1]) if self.rows[0][1].replace(".", "").isdigit() else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def measured_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def run_ours(args, rank, world):
+    import torch
+    from cudapp_b200 import api
+    if world > 1:
+        from cudapp_b200 import ep
+        return ep.bench(args, rank, world)
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    Ln, T = args.layers, args.tokens
+    layers, tensors = [], []
+    w8 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=dev); sc = torch.empty((E, 2 * I // 128, H // 128), dtype=torch.int16, device=dev)
+    d8 = torch.empty((E, H, I), dtype=torch.uint8, device=dev); dsc = torch.empty((E, H // 128, I // 128), dtype=torch.int16, device=dev)
+    for l in range(Ln):
+        g = torch.Generator(device=dev); g.manual_seed(l)
+        wgu = (torch.randn((E * 2 * I, H), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        wdn = (torch.randn((E * H, I), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        torch.cuda.synchronize()
+        assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * 2 * I), C.c_uint32(H), C.c_uint64(wgu.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0, api.last_error()
+        assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * H), C.c_uint32(I), C.c_uint64(wdn.data_ptr()), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr())) == 0, api.last_error()
+        tg, td = C.c_void_p(), C.c_void_p()
+        assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(2 * I), C.c_uint32(H), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr()), C.byref(tg)) == 0, api.last_error()
+        assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(H), C.c_uint32(I), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr()), C.byref(td)) == 0, api.last_error()
+        rc, layer = api.moe_layer_create(tg, td, topk=TOPK, max_tokens=T, engine=args.engine)
+        assert rc == 0, api.last_error()
+        layers.append(layer); tensors += [tg, td]
+        del wgu, wdn
+    del w8, sc, d8, dsc
+    torch.cuda.empty_cache()
+    rc, stack = api.moe_stack_create(layers, 1e-6)
+    assert rc == 0, api.last_error()
+
+    rng = np.random.default_rng(0)
+    from oracle.oracle import bf16_bits   # number-format helper only (input generation), not the checker's arithmetic
+    logits_h = torch.from_numpy(bf16_bits(rng.normal(0, 1, (Ln, T, E)).astype(np.float32)).view(np.int16)).pin_memory()
+    x_h = torch.from_numpy(bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32)).view(np.int16)).pin_memory()
+    out_h = torch.empty((T, H), dtype=torch.int16).pin_memory()
+    logits_d, x_d = logits_h.to(dev), x_h.to(dev)
+    out32_d = torch.empty((T, H), dtype=torch.float32, device=dev); out16_d = torch.empty((T, H), dtype=torch.int16, device=dev)
+    stream = torch.cuda.Stream()
+
+    def step_dev():
+        rc = api.lib.omega_gpu_moe_stack_async(stack, C.c_uint32(T), C.c_uint64(logits_d.data_ptr()), C.c_uint64(x_d.data_ptr()), C.c_uint64(out32_d.data_ptr()),
+                                               C.c_uint64(out16_d.data_ptr()), C.c_void_p(stream.cuda_stream))
+        assert rc == 0, api.last_error()
+
+    def step_host():
+        rc = api.lib.omega_gpu_moe_stack_bf16(stack, C.c_uint32(T), C.c_void_p(logits_h.data_ptr()), C.c_void_p(x_h.data_ptr()), C.c_void_p(out_h.data_ptr()), None)
+        assert rc == 0, api.last_error()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step_dev()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0) as clocks:
+            ev0.record(stream)
+            for _ in range(args.steps):
+                step_dev()
+            ev1.record(stream)
+            torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+    launches_per_step = api.lib.omega_gpu_moe_stack_launches(stack)
+    assert torch.isfinite(out32_d).all()
+
+    # end to end through the host-buffer C-ABI call: pinned host inputs in, result out, every step
+    for _ in range(2):
+        step_host()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_host()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+
+    # per-kernel device times of single layers (rotating over layers so no launch finds its weights in L2)
+    names_t = (C.c_char_p * 12)(); ms_t = (C.c_float * 12)(); cnt = C.c_uint32(0)
+    per_kernel = {}
+    rounds = 0
+    for rep in range(2):
+        for l in range(Ln):
+            rc = api.lib.omega_gpu_moe_layer_profile(layers[l], C.c_uint32(T), C.c_uint64(logits_d[l].data_ptr()), C.c_uint64(x_d.data_ptr()),
+                                                     C.c_uint64(out32_d.data_ptr()), C.c_uint32(12), ms_t, names_t, C.byref(cnt))
+            assert rc == 0, api.last_error()
+            if rep == 0 and l < 4:
+                continue      # warm-up launches
+            rounds += 1
+            for i in range(cnt.value):
+                per_kernel.setdefault(names_t[i].decode(), []).append(ms_t[i])
+    kern_ms = {k: float(np.mean(v)) for k, v in per_kernel.items()}
+    top = max(kern_ms, key=kern_ms.get)
+    # algorithmic bytes of the dominant kernel per launch: every distinct expert's codes + scales once, plus its input rows
+    from oracle.oracle import bf16_to_f32
+    ids = np.stack([np.argsort(-bf16_to_f32(logits_h[l].numpy().view(np.uint16)), axis=1, kind="stable")[:, :TOPK] for l in range(min(Ln, 4))])
+    distinct = float(np.mean([len(np.unique(ids[l])) for l in range(ids.shape[0])]))
+    per_expert = GU_BYTES if top.startswith("gate") else DN_BYTES
+    in_bytes = T * H * 2 if top.startswith("gate") else T * TOPK * I * 4
+    alg_bytes = distinct * per_expert + in_bytes
+    peak, peak_kind = measured_peak()
+    achieved = alg_bytes / (kern_ms[top] * 1e-3) / 1e9
+    traffic = None
+    tp = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tp):
+        traffic = json.load(open(tp)).get(top)
+
+    cpu_sec, kind, cores = cpu_layer_sample(args.cpu_sample_tokens, 1, 0)
+    cpu_value = args.cpu_sample_tokens / (cpu_sec * Ln)
+    total_s = ms * 1e-3
+    out = {
+        "metric": "moe_layer_tokens_per_s", "value": T * args.steps / total_s, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "48-layer MoE expert stack, 256 decode tokens/step, 128 experts top-8, hidden 2048, inter 768", "layers": Ln, "tokens_per_step": T,
+                   "parallelism": "single GPU", "l2": "29 GB of weights per step: inputs larger than L2, no flush needed", "engine": args.engine,
+                   "layer_tokens_per_s": T * Ln * args.steps / total_s, "kernel_ms": kern_ms},
+        "e2e": {"value": T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(logits_h.numel() * 2 + x_h.numel() * 2), "d2h_bytes_per_step": int(out_h.numel() * 2)},
+        "gpu_launches": int(launches_per_step) * args.steps,
+        "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind + " copy bandwidth",
+                     "algorithmic_bytes": alg_bytes, "kernel_ms": kern_ms[top], "traffic": traffic, "frac_of_8TBps": achieved / 8000.0},
+        "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": kind,
+                         "sample": "%d tokens through 1 of %d layers (x%d extrapolated), double-precision host GEMV oracle per routed row, %d threads" % (args.cpu_sample_tokens, Ln, Ln, cores)},
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(out))
+    api.lib.omega_gpu_moe_stack_free(stack)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

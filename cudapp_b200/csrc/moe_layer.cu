@@ -66,6 +66,8 @@ struct OmegaGpuMoeLayer {
     uint64_t *dir_gu, *dir_dn;   // device {w_va, s_va} per expert
     b200::Workspace *ws;
     uint32_t launches;
+    cudaEvent_t *prof;           // when set: prof[i] is recorded after the i-th launch of a forward
+    const char *names[12];
 };
 
 namespace b200 {
@@ -75,25 +77,28 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     Workspace *w = L->ws;
     const uint32_t K = L->cfg.topk, E = L->experts, H = L->hidden, I = L->inter, R = tokens * K;
     uint32_t n = 0;
-    if (!cuda_ok(launch_topk(tokens, E, K, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s), "topk launch")) return false; n++;
+#define MARK(name) do { L->names[n] = name; if (L->prof) cudaEventRecord(L->prof[n + 1], s); n++; } while (0)
+    if (L->prof) cudaEventRecord(L->prof[0], s);
+    if (!cuda_ok(launch_topk(tokens, E, K, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s), "topk launch")) return false; MARK("topk");
     OmegaGpuMoePlanOut o = {};
     o.counts_va = (uint64_t)(uintptr_t)w->counts; o.starts_va = (uint64_t)(uintptr_t)w->starts;
     o.xmap_va = (uint64_t)(uintptr_t)w->xmap; o.ymap_va = (uint64_t)(uintptr_t)w->ymap; o.header_va = (uint64_t)(uintptr_t)w->header;
     o.seg_a_va = (uint64_t)(uintptr_t)w->seg_gu; o.dir_a_va = (uint64_t)(uintptr_t)L->dir_gu;
     o.seg_b_va = (uint64_t)(uintptr_t)w->seg_dn; o.dir_b_va = (uint64_t)(uintptr_t)L->dir_dn;
-    if (!cuda_ok(launch_plan(tokens, K, E, K, 0, w->ids, o, s), "plan launch")) return false; n++;
+    if (!cuda_ok(launch_plan(tokens, K, E, K, 0, w->ids, o, s), "plan launch")) return false; MARK("plan");
     // gate|up: sorted row p reads x[xmap[p]], writes gu row p
     GemvArgs a = {};
     a.seg = w->seg_gu; a.x = x; a.x_bf16 = 1; a.x_rows = tokens; a.xmap = w->xmap; a.ymap = nullptr;
     a.y = w->gu; a.n = 2 * I; a.k = H; a.groups_or_segs = E; a.rows = R; a.out_mul = 1.0f;
-    if (!cuda_ok(launch_gemm_rows(a, nullptr, nullptr, s), "gate|up launch")) return false; n++;
-    if (!cuda_ok(launch_swiglu(R, I, w->gu, w->act, s), "swiglu launch")) return false; n++;
+    if (!cuda_ok(launch_gemm_rows(a, nullptr, nullptr, s), "gate|up launch")) return false; MARK("gate_up_gemm");
+    if (!cuda_ok(launch_swiglu(R, I, w->gu, w->act, s), "swiglu launch")) return false; MARK("swiglu");
     // down: sorted row p reads act row p, writes dn row ymap[p] = token * topk + slot
     GemvArgs d = {};
     d.seg = w->seg_dn; d.x = w->act; d.x_bf16 = 0; d.x_rows = R; d.xmap = nullptr; d.ymap = w->ymap;
     d.y = w->dn; d.n = H; d.k = I; d.groups_or_segs = E; d.rows = R; d.out_mul = 1.0f;
-    if (!cuda_ok(launch_gemm_rows(d, nullptr, nullptr, s), "down launch")) return false; n++;
-    if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; n++;
+    if (!cuda_ok(launch_gemm_rows(d, nullptr, nullptr, s), "down launch")) return false; MARK("down_gemm");
+    if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
+#undef MARK
     L->launches = n;
     return true;
 }
@@ -160,6 +165,28 @@ int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t log
     if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
     return layer_forward(L, tokens, (const uint16_t *)(uintptr_t)logits_va, (const uint16_t *)(uintptr_t)x_va, (float *)(uintptr_t)out_f32_va,
                          (uint16_t *)(uintptr_t)out_bf16_va, (cudaStream_t)stream) ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va, uint32_t cap,
+                                float *ms, const char **names, uint32_t *count) {
+    if (!L || !tokens || !logits_va || !x_va || !out_f32_va || !ms || !count || cap == 0) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (tokens > L->cfg.max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaEvent_t ev[13];
+    for (auto &e : ev) if (!cuda_ok(cudaEventCreate(&e), "cudaEventCreate")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaStream_t s = st().stream;
+    L->prof = ev;
+    bool ok = layer_forward(L, tokens, (const uint16_t *)(uintptr_t)logits_va, (const uint16_t *)(uintptr_t)x_va, (float *)(uintptr_t)out_f32_va, nullptr, s);
+    L->prof = nullptr;
+    ok = ok && cuda_ok(cudaStreamSynchronize(s), "moe layer profile");
+    *count = 0;
+    for (uint32_t i = 0; ok && i < L->launches && i < cap; i++) {
+        float t = 0; ok = cuda_ok(cudaEventElapsedTime(&t, ev[i], ev[i + 1]), "event time");
+        ms[i] = t; if (names) names[i] = L->names[i]; *count = i + 1;
+    }
+    for (auto &e : ev) cudaEventDestroy(e);
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
 int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, uint16_t *out_bf16, float *out_f32,

@@ -92,6 +92,10 @@ int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *l, uint32_t tokens, const uint16_
 /* device buffers, stream-ordered: out_f32_va f32 [tokens][H] (required), out_bf16_va optional (0 = skip) */
 int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
                               uint64_t out_bf16_va, void *stream);
+/* One forward on the library's stream with a CUDA event between consecutive launches: ms[i] = device time of the i-th
+ * kernel (launch order), names[i] = its static name; *count entries (at most cap). For measurement. */
+int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
+                                uint32_t cap, float *ms, const char **names, uint32_t *count);
 /* number of kernels the last forward of this layer launched */
 uint32_t omega_gpu_moe_layer_launches(const OmegaGpuMoeLayer *l);
 

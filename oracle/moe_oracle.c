@@ -125,9 +125,11 @@ void orc_gemv(const uint8_t *w, const uint16_t *scale, uint32_t n, uint32_t k, c
  * 32 lanes, lane L owns lb contiguous columns per K step of 32 * lb columns; dot = fma chain over those
  * bytes; acc = fma(dot, scale, acc) per step; then a shuffle-down tree 16, 8, 4, 2, 1 read at lane 0.
  * The reference folds 2^-120, 2^64 and 2^56 into w, x and scale; those are exact powers of two whose
- * product is 1, so the unfolded chain below gives the same bits. lb is 16 when k % 512 == 0, else 8. */
+ * product is 1, so the unfolded chain below gives the same bits. lb is 16 when k % 512 == 0, 8 when k % 256 == 0.
+ * The reference kernel refuses any other k (it falls back to a general GEMM); the library extends the same order
+ * with lb = 4 there, which this function mirrors (no reference counterpart for that case). */
 float orc_gemv_emu_row(const uint8_t *w, const uint16_t *s, const float *x, uint32_t k) {
-    const uint32_t lb = (k % 512u == 0) ? 16u : 8u, steps = k / (32u * lb);
+    const uint32_t lb = (k % 512u == 0) ? 16u : (k % 256u == 0) ? 8u : 4u, steps = k / (32u * lb);
     float a[32];
     for (uint32_t lane = 0; lane < 32; lane++) {
         float acc = 0.0f;
