@@ -1,0 +1,289 @@
+// fp8_mma_sm100.cu: grouped FP8 GEMM on the B200 tensor cores (tcgen05, kind::f8f6f4) for the MoE expert path.
+//
+// What it computes is the reference's grouped GEMM (src/omega_blackwell_codegen_gemm.h:5-14; block-scale promotion
+// as its QMMA path does it, src/omega_blackwell_codegen_qg.h:24-37): for a segment of rows routed to one expert,
+//   y[row][f] = sum over 128-column blocks kb of  Sw[f/128][kb] * Sa[row][kb] * sum_c W[f][c] * A[row][c]
+// with W the e4m3 weights exactly as uploaded (no repack, no conversion) and A the activations as e4m3 "pieces".
+//
+// Mapping ("swap-AB"): the weight tile is the MMA's M operand (128 output features x 128 K bytes straight from a
+// TMA load of the checkpoint-order tensor, SWIZZLE_128B), the routed rows are the N operand (up to 64 columns of
+// activation pieces). So the work per weight byte does not depend on how few rows an expert received: decode is a
+// pure weight stream. An activation value is held as P e4m3 pieces (piece p = the residual left by pieces < p,
+// scaled by 16^p; P = 2 represents a bf16 value exactly, P = 3 gives 12 significant bits of an f32), each piece a
+// separate MMA column; columns are folded back (Horner, factor 1/16) when the accumulator is read.
+//
+// One persistent CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane each, the
+// tcgen05 model), warps 2-5 = promotion/epilogue (one TMEM lane quarter each). A unit of work is (row tile, pair of
+// 128-feature blocks): gate block j with up block j (SiLU gate fused in the epilogue) or two adjacent down blocks.
+// Per 128-wide K block: 2 x 4 MMAs (K = 32 each) into a double-buffered TMEM partial, tcgen05.commit, then the
+// epilogue warps tcgen05.ld the partial and add scale * partial into register accumulators while the next block's
+// MMAs run. Shared memory: 4 stages x (2 weight tiles 16 KB + activation tile 8 KB).
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a code in *err, lets its own copies land, frees its
+// TMEM and returns (no trap, no endless spin).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "internal.h"
+
+namespace b200 {
+
+constexpr int MMA_N = 64;                       // accumulator columns per weight tile
+constexpr int MMA_STAGES = 4;
+constexpr uint32_t A_TILE = 128 * 128, B_TILE = MMA_N * 128, STAGE_BYTES = 2 * A_TILE + B_TILE;
+constexpr int KB_MAX = 32;                      // k <= 4096 on this engine
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t TMEM_COLS = 256;             // 2 buffers x 2 accumulators x 64 columns
+
+struct MmaArgs {
+    const float *wscale, *ascale;
+    const uint4 *tiles; const uint32_t *header;
+    const uint32_t *ymap;
+    float *out;
+    uint32_t n, k, pairs, mode, inter, out_stride;
+    uint32_t *err;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false (and *err = code) when the limit runs out or another role already gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t *err, uint32_t code) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1; atomicCAS(err, 0u, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p; }"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// K-major operand tile, rows of 128 bytes, SWIZZLE_128B: 8-row groups 1024 bytes apart (stride offset), version 1
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f8f6f4, D = f32, A = B = e4m3, both K-major, M = 128, N = MMA_N
+constexpr uint32_t MMA_IDESC = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+#define TMEM_LD32(taddr, r)                                                                                                              \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];" \
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),       \
+                   "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),           \
+                   "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) \
+                 : "r"(taddr))
+
+__device__ __forceinline__ float silu_mul_dev(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
+
+template <int P>
+__global__ void __launch_bounds__(192, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
+    constexpr int NTOK = MMA_N / P;             // routed rows per tile
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t s_bar[2 * MMA_STAGES + 5];
+    __shared__ uint32_t s_tmem, s_abort;
+    __shared__ float s_sw[2][KB_MAX];
+    __shared__ float s_cs[KB_MAX][NTOK];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem_u32(s_bar);
+    auto full_bar = [&](uint32_t s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar0 + 8u * (MMA_STAGES + s); };
+    auto accfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * MMA_STAGES + b); };
+    auto accempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * MMA_STAGES + 2 + b); };
+    const uint32_t epi_bar = bar0 + 8u * (2 * MMA_STAGES + 4);   // the 128 epilogue threads' own rendezvous
+    volatile uint32_t *abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (uint32_t s = 0; s < MMA_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128); }
+        mbar_init(epi_bar, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // TMEM allocation by one whole warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t KB = a.k / 128u, n_tiles = a.header[2], total = n_tiles * a.pairs;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0; bool ok = true;
+            for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
+                const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs;
+                const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+                const int wy0 = (int)(t.x * a.n + r0), wy1 = (int)(t.x * a.n + r1), qy = (int)(t.y * P);
+                for (uint32_t kb = 0; kb < KB; kb++, it++) {
+                    const uint32_t s = it % MMA_STAGES, ph = (it / MMA_STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
+                    const uint32_t dst = smem_base + s * STAGE_BYTES;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    tma_load_2d(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0);
+                    tma_load_2d(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1);
+                    tma_load_2d(dst + 2 * A_TILE, &tm_q, full_bar(s), (int)(kb * 128u), qy);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0; bool ok = true;
+            for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
+                for (uint32_t kb = 0; kb < KB; kb++, it++) {
+                    const uint32_t s = it % MMA_STAGES, ph = (it / MMA_STAGES) & 1u, buf = it & 1u, bph = (it >> 1) & 1u;
+                    if (!(ok = mbar_wait(accempty_bar(buf), bph ^ 1u, abort_flag, a.err, 2))) break;
+                    if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, a.err, 3))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * STAGE_BYTES;
+                    const uint64_t da0 = umma_desc(sa), da1 = umma_desc(sa + A_TILE), db = umma_desc(sa + 2 * A_TILE);
+                    const uint32_t d0 = tmem + buf * 2u * MMA_N, d1 = d0 + MMA_N;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < 4; ks++) {   // 32 K bytes per MMA: advance the start address inside the swizzle row
+                        tc_mma_f8(d0, da0 + 2u * ks, db + 2u * ks, MMA_IDESC, ks);
+                        tc_mma_f8(d1, da1 + 2u * ks, db + 2u * ks, MMA_IDESC, ks);
+                    }
+                    tc_commit(empty_bar(s));       // the stage is free once these MMAs have read it
+                    tc_commit(accfull_bar(buf));   // the partial is complete
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- promotion + epilogue (warps 2..5)
+        const uint32_t q = warp & 3u, row = q * 32u + lane, et = threadIdx.x - 64u;   // TMEM lane quarter of this warp
+        uint32_t it = 0, syncs = 0; bool ok = true;
+        for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
+            const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, cnt = t.z;
+            const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+            mbar_arrive(epi_bar);                             // everyone is done with the previous unit's scales
+            if (!(ok = mbar_wait(epi_bar, syncs++ & 1u, abort_flag, a.err, 5))) break;
+            if (et < KB) {
+                s_sw[0][et] = a.wscale[((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB + et];
+                s_sw[1][et] = a.wscale[((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB + et];
+            }
+            for (uint32_t i = et; i < KB * NTOK; i += 128u) {
+                const uint32_t kb = i / NTOK, tk = i - kb * NTOK;
+                s_cs[kb][tk] = tk < cnt ? a.ascale[(size_t)(t.y + tk) * KB + kb] : 0.0f;
+            }
+            mbar_arrive(epi_bar);
+            if (!(ok = mbar_wait(epi_bar, syncs++ & 1u, abort_flag, a.err, 6))) break;
+            float acc0[NTOK], acc1[NTOK];
+#pragma unroll
+            for (int i = 0; i < NTOK; i++) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
+            for (uint32_t kb = 0; kb < KB; kb++, it++) {
+                const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+                if (!(ok = mbar_wait(accfull_bar(buf), bph, abort_flag, a.err, 4))) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem + ((q * 32u) << 16) + buf * 2u * MMA_N;
+                const float sw0 = s_sw[0][kb], sw1 = s_sw[1][kb];
+#pragma unroll
+                for (int half = 0; half < 2; half++) {      // accumulator 0 then 1, 64 columns each
+                    uint32_t d[MMA_N];
+                    TMEM_LD32(taddr + half * MMA_N, d);
+                    uint32_t *dh = d + 32;
+                    TMEM_LD32(taddr + half * MMA_N + 32, dh);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (half == 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // both accumulators are in registers
+                    const float sw = half ? sw1 : sw0;
+#pragma unroll
+                    for (int i = 0; i < NTOK; i++) {
+                        float v = __uint_as_float(d[i * P + P - 1]);
+#pragma unroll
+                        for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(d[i * P + p]));
+                        const float sc = sw * s_cs[kb][i];
+                        if (half) acc1[i] = fmaf(v, sc, acc1[i]); else acc0[i] = fmaf(v, sc, acc0[i]);
+                    }
+                }
+            }
+            if (!ok) break;
+            // ---- write the unit's results: 128 consecutive features per routed row
+            if (a.mode == 0) {
+#pragma unroll
+                for (int i = 0; i < NTOK; i++)
+                    if ((uint32_t)i < cnt) a.out[(size_t)(t.y + i) * a.out_stride + j * 128u + row] = silu_mul_dev(acc0[i], acc1[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < NTOK; i++)
+                    if ((uint32_t)i < cnt) {
+                        float *o = a.out + (size_t)a.ymap[t.y + i] * a.out_stride;
+                        o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
+                    }
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) { for (int i = 0; i < 64; i++) __nanosleep(1000); }   // let copies already issued land before the CTA goes away
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr; cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+// 2-D map over a row-major u8 matrix [rows][cols], box [box_rows][128 bytes], 128-byte swizzle
+bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return false; }
+    const cuuint64_t dims[2] = {cols, rows}, strides[1] = {cols};
+    const cuuint32_t box[2] = {128, box_rows}, estr[2] = {1, 1};
+    const CUresult r = fn((CUtensorMap *)out_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return false; }
+    return true;
+}
+
+uint32_t mma_tile_rows(uint32_t pieces) { return MMA_N / pieces; }
+bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode) { return k % 128u == 0 && k <= 128u * KB_MAX && n % 128u == 0 && (mode == 0 || (n / 128u) % 2u == 0); }
+
+cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s) {
+    MmaArgs a = {};
+    a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
+    a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.mode == 0 ? m.n / 256u : m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
+    const size_t smem = (size_t)MMA_STAGES * STAGE_BYTES + 1024;
+    const int sms = st().sm_count ? st().sm_count : 148;
+    const CUtensorMap *w = (const CUtensorMap *)tm_w, *q = (const CUtensorMap *)tm_q;
+#define LAUNCH(PV)                                                                                                                      \
+    do {                                                                                                                                \
+        static bool attr = false;                                                                                                       \
+        if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
+        fp8_mma_grouped_kernel<PV><<<sms, 192, smem, s>>>(*w, *q, a);                                                                 \
+    } while (0)
+    switch (pieces) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 3: LAUNCH(3); break;
+    case 4: LAUNCH(4); break;
+    default: return cudaErrorInvalidValue;
+    }
+#undef LAUNCH
+    return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -88,6 +88,18 @@ cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, con
 // quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap,
                              const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s);
+// tcgen05 grouped GEMM (fp8_mma_sm100.cu)
+struct MmaLaunch {
+    const float *wscale, *ascale;      // weight scales [E][n/128][k/128]; activation scales [rows][k/128]
+    const void *tiles;                 // uint4 {expert, row0, cnt, segment} per row tile
+    const uint32_t *header, *ymap;     // header[2] = tile count; ymap: destination rows (mode 1)
+    float *out; uint32_t n, k, mode, out_stride;   // mode 0: gate|up + SiLU gate -> out[row][n/2]; mode 1: out[ymap[row]][n]
+    uint32_t *err;                     // device word: non-zero = a bounded wait inside the kernel ran out
+};
+bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+uint32_t mma_tile_rows(uint32_t pieces);
+bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
+cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s);
 bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s);
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src);
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens);

@@ -68,6 +68,8 @@ struct OmegaGpuMoeLayer {
     uint32_t launches;
     cudaEvent_t *prof;           // when set: prof[i] is recorded after the i-th launch of a forward
     const char *names[12];
+    alignas(128) unsigned char tm_gu[128], tm_dn[128], tm_qx[128], tm_qa[128];   // TMA descriptors (tensor-core engine)
+    uint32_t tile_rows;
 };
 
 namespace b200 {
@@ -85,7 +87,26 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     o.xmap_va = (uint64_t)(uintptr_t)w->xmap; o.ymap_va = (uint64_t)(uintptr_t)w->ymap; o.header_va = (uint64_t)(uintptr_t)w->header;
     o.seg_a_va = (uint64_t)(uintptr_t)w->seg_gu; o.dir_a_va = (uint64_t)(uintptr_t)L->dir_gu;
     o.seg_b_va = (uint64_t)(uintptr_t)w->seg_dn; o.dir_b_va = (uint64_t)(uintptr_t)L->dir_dn;
-    if (!cuda_ok(launch_plan(tokens, K, E, K, 0, w->ids, o, s), "plan launch")) return false; MARK("plan");
+    const bool mma = L->cfg.engine == OMEGA_GPU_MOE_ENGINE_MMA;
+    o.tiles_va = mma ? (uint64_t)(uintptr_t)w->tiles : 0;
+    if (!cuda_ok(launch_plan(tokens, K, E, K, mma ? L->tile_rows : 0, w->ids, o, s), "plan launch")) return false; MARK("plan");
+    if (mma) {
+        // activations as e4m3 pieces in sorted-row order, then the two tensor-core grouped GEMMs
+        const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces;
+        if (!cuda_ok(launch_act_quant(R, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s), "x quant launch")) return false; MARK("x_quant");
+        MmaLaunch g = {};
+        g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.ymap = nullptr; g.out = w->act;
+        g.n = 2 * I; g.k = H; g.mode = 0; g.out_stride = I; g.err = w->header + 4;
+        if (!cuda_ok(launch_mma_grouped(L->tm_gu, L->tm_qx, Px, g, s), "gate|up mma launch")) return false; MARK("gate_up_mma");
+        if (!cuda_ok(launch_act_quant(R, I, Pa, w->act, 0, nullptr, w->header, w->qa, w->sa, s), "act quant launch")) return false; MARK("act_quant");
+        MmaLaunch dd = {};
+        dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = w->dn;
+        dd.n = H; dd.k = I; dd.mode = 1; dd.out_stride = H; dd.err = w->header + 4;
+        if (!cuda_ok(launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false; MARK("down_mma");
+        if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
+        L->launches = n;
+        return true;
+    }
     // gate|up: sorted row p reads x[xmap[p]], writes gu row p
     GemvArgs a = {};
     a.seg = w->seg_gu; a.x = x; a.x_bf16 = 1; a.x_rows = tokens; a.xmap = w->xmap; a.ymap = nullptr;
@@ -103,6 +124,16 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     return true;
 }
 
+// TMA descriptors of the weights (fixed) and of the workspace's piece buffers (rebuilt when the workspace changes)
+static bool layer_build_maps(OmegaGpuMoeLayer *L) {
+    if (L->cfg.engine != OMEGA_GPU_MOE_ENGINE_MMA) return true;
+    const uint64_t Rp = (uint64_t)L->ws->max_tokens * L->cfg.topk + 8;
+    return make_tmap_u8(L->tm_gu, L->gu->w, (uint64_t)L->experts * 2 * L->inter, L->hidden, 128) &&
+           make_tmap_u8(L->tm_dn, L->dn->w, (uint64_t)L->experts * L->hidden, L->inter, 128) &&
+           make_tmap_u8(L->tm_qx, L->ws->qx, Rp * L->cfg.x_pieces, L->hidden, 64) &&
+           make_tmap_u8(L->tm_qa, L->ws->qa, Rp * L->cfg.act_pieces, L->inter, 64);
+}
+
 // dst drops its own workspace and uses src's (same shape, at least as many tokens); calls on them must then be stream-ordered
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src) {
     if (dst->ws == src->ws) return true;
@@ -110,7 +141,7 @@ bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src) {
         dst->cfg.max_tokens > src->cfg.max_tokens) return false;
     workspace_release(dst->ws);
     dst->ws = src->ws; src->ws->refs++;
-    return true;
+    return layer_build_maps(dst);
 }
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens) { *experts = L->experts; *hidden = L->hidden; *max_tokens = L->cfg.max_tokens; }
 float *layer_out32(OmegaGpuMoeLayer *L) { return L->ws->out32; }
@@ -132,9 +163,13 @@ int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuF
     OmegaGpuMoeLayer *L = (OmegaGpuMoeLayer *)calloc(1, sizeof *L);
     if (!L) return OMEGA_GPU_FP8_BAD_ARGS;
     L->gu = gate_up; L->dn = down; L->cfg = *cfg; L->experts = gate_up->experts; L->hidden = gate_up->k; L->inter = down->k;
-    if (L->cfg.engine == OMEGA_GPU_MOE_ENGINE_AUTO) L->cfg.engine = OMEGA_GPU_MOE_ENGINE_FMA;
     if (!L->cfg.x_pieces) L->cfg.x_pieces = 2;
     if (!L->cfg.act_pieces) L->cfg.act_pieces = 3;
+    if (L->cfg.x_pieces > 4 || L->cfg.act_pieces > 4) { free(L); return OMEGA_GPU_FP8_BAD_ARGS; }
+    const bool mma_ok = mma_shape_ok(2 * L->inter, L->hidden, 0) && mma_shape_ok(L->hidden, L->inter, 1);
+    if (L->cfg.engine == OMEGA_GPU_MOE_ENGINE_AUTO) L->cfg.engine = mma_ok ? OMEGA_GPU_MOE_ENGINE_MMA : OMEGA_GPU_MOE_ENGINE_FMA;
+    if (L->cfg.engine == OMEGA_GPU_MOE_ENGINE_MMA && !mma_ok) { free(L); set_error("moe layer: shape outside the tensor-core engine (k <= 4096, even number of 128-row blocks)"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    L->tile_rows = mma_tile_rows(L->cfg.x_pieces > L->cfg.act_pieces ? L->cfg.x_pieces : L->cfg.act_pieces);
     const uint32_t E = L->experts;
     std::vector<uint64_t> dir((size_t)E * 4);
     for (uint32_t e = 0; e < E; e++) {
@@ -144,6 +179,7 @@ int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuF
     bool ok = cuda_ok(cudaMalloc(&L->dir_gu, (size_t)E * 32), "cudaMalloc(directory)");
     if (ok) { L->dir_dn = L->dir_gu + 2 * E; ok = cuda_ok(cudaMemcpy(L->dir_gu, dir.data(), (size_t)E * 32, cudaMemcpyHostToDevice), "copy directory"); }
     if (ok) { L->ws = workspace_create(cfg->max_tokens, cfg->topk, E, L->hidden, L->inter); ok = L->ws != nullptr; }
+    if (ok) ok = layer_build_maps(L);
     if (!ok) { if (L->dir_gu) cudaFree(L->dir_gu); free(L); return OMEGA_GPU_FP8_CHIP_FAIL; }
     *out = L;
     return OMEGA_GPU_FP8_OK;
@@ -204,7 +240,10 @@ int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_
     if (ok && out_f32) ok = cuda_ok(cudaMemcpyAsync(out_f32, w->out32, xb * 2, cudaMemcpyDeviceToHost, s), "copy out");
     if (ok && ids) ok = cuda_ok(cudaMemcpyAsync(ids, w->ids, rb, cudaMemcpyDeviceToHost, s), "copy ids");
     if (ok && wts) ok = cuda_ok(cudaMemcpyAsync(wts, w->wts, rb, cudaMemcpyDeviceToHost, s), "copy weights");
-    ok = ok && cuda_ok(cudaStreamSynchronize(s), "moe layer");
+    uint32_t hdr[8] = {0};
+    ok = ok && cuda_ok(cudaMemcpyAsync(hdr, w->header, 32, cudaMemcpyDeviceToHost, s), "copy status") && cuda_ok(cudaStreamSynchronize(s), "moe layer");
+    if (ok && hdr[3]) { set_error("moe layer: routing plan refused (status %u)", hdr[3]); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (ok && hdr[4]) { set_error("moe layer: a bounded wait inside the tensor-core kernel ran out (code %u)", hdr[4]); st().latched = true; return OMEGA_GPU_FP8_CHIP_FAIL; }
     return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 

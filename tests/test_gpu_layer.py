@@ -40,7 +40,7 @@ def check_layer(m, logits, xb, topk, tol_abs=1e-2, tol_rel=1e-3):
     return err, rl2
 
 
-@pytest.mark.parametrize("engine", [api.ENGINE_FMA])
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA, api.ENGINE_MMA])
 @pytest.mark.parametrize("tokens", [1, 7, 64])
 def test_layer_small(engine, tokens):
     rng = np.random.default_rng(100 + tokens)
@@ -53,7 +53,7 @@ def test_layer_small(engine, tokens):
     free_layer(m)
 
 
-@pytest.mark.parametrize("engine", [api.ENGINE_FMA])
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA, api.ENGINE_MMA])
 def test_layer_decode_shape(engine):
     """the decode configuration's architecture (hidden 2048, expert intermediate 768, top-8) on 32 experts, 64 tokens"""
     rng = np.random.default_rng(7)
@@ -65,7 +65,7 @@ def test_layer_decode_shape(engine):
     free_layer(m)
 
 
-@pytest.mark.parametrize("engine", [api.ENGINE_FMA])
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA, api.ENGINE_MMA])
 def test_stack_small(engine):
     rng = np.random.default_rng(9)
     E, H, I, topk, T, Ln = 16, 512, 256, 4, 24, 3
