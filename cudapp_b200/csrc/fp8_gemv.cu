@@ -288,6 +288,57 @@ static int gemm_core(const OmegaGpuFp8Tensor *t, uint32_t M, const uint32_t *ids
     return rc;
 }
 
+
+// ---------------------------------------------------------------- allocation-free row-table GEMM
+// The segment table the grouped GEMM kernel reads normally lives in a cudaMalloc'ed staging buffer. This variant
+// keeps it in a fixed device array instead, so the whole call touches no allocator. Layout of the array:
+// [0, 32 * NOALLOC_MAX_SEGMENTS) segment records, then one 16-byte header {segments, status, 0, 0}.
+constexpr uint32_t NOALLOC_MAX_SEGMENTS = OMEGA_GPU_FP8GEMM_NOALLOC_MAX_SEGMENTS;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_MAX_SEGMENTS * 32 + 256];
+static void *g_noalloc_ptr[64];   // per device: the array's DEVICE address (the symbol itself is only a host-side stand-in)
+
+// One CTA. Turns M sorted expert ids into segment records {w_va, s_va, row0, cnt}. status: 0 ok, 1 ids not sorted or
+// out of range, 2 more segments than the table holds. Everything a previous call left behind is overwritten:
+// the header is rewritten, records [segments, max) are zeroed.
+__global__ void __launch_bounds__(1024) noalloc_segments_kernel(unsigned char *scratch, uint32_t M, uint32_t experts, const uint32_t *__restrict__ ids,
+                                                                uint64_t w_base, uint64_t s_base, uint64_t w_stride, uint64_t s_stride) {
+    __shared__ uint32_t warp_sum[32];
+    __shared__ uint32_t s_run, s_bad;
+    Seg32 *seg = reinterpret_cast<Seg32 *>(scratch);
+    uint32_t *hdr = reinterpret_cast<uint32_t *>(scratch + NOALLOC_MAX_SEGMENTS * 32);
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) { s_run = 0; s_bad = 0; }
+    __syncthreads();
+    for (uint32_t base = 0; base < M; base += 1024) {
+        const uint32_t i = base + tid;
+        uint32_t flag = 0, e = 0;
+        if (i < M) {
+            e = ids[i];
+            const uint32_t prev = i ? ids[i - 1] : 0xffffffffu;
+            if (e >= experts || (i && e < prev)) s_bad = 1;
+            flag = (i == 0 || e != prev) ? 1u : 0u;
+        }
+        uint32_t inc = flag;
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= (uint32_t)o) inc += u; }
+        if (lane == 31) warp_sum[warp] = inc;
+        __syncthreads();
+        uint32_t before = s_run;
+        for (uint32_t w = 0; w < warp; w++) before += warp_sum[w];
+        const uint32_t si = before + inc - flag;
+        if (flag && si < NOALLOC_MAX_SEGMENTS && e < experts) {
+            Seg32 r; r.w_va = w_base + (uint64_t)e * w_stride; r.s_va = s_base + (uint64_t)e * s_stride; r.row0 = i; r.cnt = 0; r.pad = 0;
+            seg[si] = r;
+        }
+        __syncthreads();
+        if (tid == 0) { uint32_t tot = 0; for (int w = 0; w < 32; w++) tot += warp_sum[w]; s_run += tot; }
+        __syncthreads();
+    }
+    const uint32_t S = s_run, kept = min(S, NOALLOC_MAX_SEGMENTS);
+    for (uint32_t z = tid; z < kept; z += 1024) seg[z].cnt = (z + 1 < kept ? seg[z + 1].row0 : M) - seg[z].row0;
+    for (uint32_t z = kept + tid; z < NOALLOC_MAX_SEGMENTS; z += 1024) { const Seg32 zero = {0, 0, 0, 0, 0}; seg[z] = zero; }
+    if (tid == 0) { hdr[0] = kept; hdr[1] = s_bad ? 1u : (S > NOALLOC_MAX_SEGMENTS ? 2u : 0u); hdr[2] = 0; hdr[3] = 0; }
+}
+
 }  // namespace b200
 using namespace b200;
 
@@ -329,5 +380,49 @@ int omega_gpu_fp8gemm_async(const OmegaGpuFp8Tensor *t, uint32_t rows, uint32_t 
     a.xmap = (const uint32_t *)(uintptr_t)xmap_va; a.ymap = (const uint32_t *)(uintptr_t)ymap_va;
     a.y = (float *)(uintptr_t)y_va; a.n = t->n; a.k = t->k; a.groups_or_segs = segs; a.rows = rows; a.out_mul = 1.0f;
     return cuda_ok(launch_gemm_rows(a, nullptr, nullptr, (cudaStream_t)stream), "fp8gemm launch") ? OMEGA_GPU_FP8GEMM_OK : OMEGA_GPU_FP8GEMM_CHIP_FAIL;
+}
+
+// Allocation-free entry (declared in b200moe_fp8gemm.h). Some hosts of this library may not allocate device memory
+// at all once they are running: a serving process that has handed every byte to its own arena, a caller inside a
+// latency-critical section, a plugin whose embedder forbids cudaMalloc after start-up. The host-staged calls above
+// grow staging buffers on demand, so they are closed to such callers; this one is not.
+int omega_gpu_fp8gemm_noalloc(const OmegaGpuFp8Tensor *t, uint32_t M, uint64_t expert_ids_va, uint64_t token_rows_va, uint64_t x_va, int x_bf16,
+                              uint32_t x_rows, uint64_t y_va, void *stream) {
+    if (!t || !t->w || !M || !expert_ids_va || !token_rows_va || !x_va || !y_va || !x_rows) return OMEGA_GPU_FP8GEMM_BAD_ARGS;
+    if (t->experts > NOALLOC_MAX_SEGMENTS) {
+        set_error("fp8gemm_noalloc: the tensor has %u experts but the fixed segment table holds %u segments", t->experts, NOALLOC_MAX_SEGMENTS);
+        return OMEGA_GPU_FP8GEMM_TOO_LARGE;
+    }
+    if (M > OMEGA_GPU_FP8GEMM_NOALLOC_MAX_ROWS) {
+        set_error("fp8gemm_noalloc: %u rows is past the stated maximum of %u", M, OMEGA_GPU_FP8GEMM_NOALLOC_MAX_ROWS);
+        return OMEGA_GPU_FP8GEMM_TOO_LARGE;
+    }
+    Lock l;
+    State &g = st();
+    if (!g.opened || g.latched) { set_error("fp8gemm_noalloc: the device is not open (upload a tensor first)"); return OMEGA_GPU_FP8GEMM_CHIP_FAIL; }
+    if (!cuda_ok(cudaSetDevice(t->device), "cudaSetDevice")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
+    if (t->device < 0 || t->device >= 64) return OMEGA_GPU_FP8GEMM_BAD_ARGS;
+    if (!g_noalloc_ptr[t->device]) {   // set-up, once per device, with that device current
+        void *p = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(noalloc scratch)") || !p) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
+        g_noalloc_ptr[t->device] = p;
+    }
+    unsigned char *scratch = (unsigned char *)g_noalloc_ptr[t->device];
+    cudaStream_t s = (cudaStream_t)stream;
+    uint64_t w0 = 0, s0 = 0;
+    (void)omega_gpu_fp8_tensor_entry(t, 0, &w0, &s0);
+    noalloc_segments_kernel<<<1, 1024, 0, s>>>(scratch, M, t->experts, (const uint32_t *)(uintptr_t)expert_ids_va, w0, s0, (uint64_t)t->n * t->k,
+                                               (uint64_t)(t->n / 128u) * (t->k / 128u) * 4u);
+    if (!cuda_ok(cudaGetLastError(), "noalloc segments launch")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
+    uint32_t hdr[4] = {0, 0, 0, 0};
+    if (!cuda_ok(cudaMemcpyAsync(hdr, scratch + NOALLOC_MAX_SEGMENTS * 32, 16, cudaMemcpyDeviceToHost, s), "copy status") ||
+        !cuda_ok(cudaStreamSynchronize(s), "noalloc segments")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
+    if (hdr[1] == 1) { set_error("fp8gemm_noalloc: expert ids must be non-decreasing and below the expert count"); return OMEGA_GPU_FP8GEMM_BAD_ARGS; }
+    if (hdr[1] == 2) { set_error("fp8gemm_noalloc: more segments than the fixed table holds"); return OMEGA_GPU_FP8GEMM_TOO_LARGE; }
+    GemvArgs a = {};
+    a.seg = (const Seg32 *)scratch; a.x = (const void *)(uintptr_t)x_va; a.x_bf16 = x_bf16; a.x_rows = x_rows;
+    a.xmap = (const uint32_t *)(uintptr_t)token_rows_va; a.ymap = nullptr;
+    a.y = (float *)(uintptr_t)y_va; a.n = t->n; a.k = t->k; a.groups_or_segs = hdr[0]; a.rows = M; a.out_mul = 1.0f;
+    return cuda_ok(launch_gemm_rows(a, nullptr, nullptr, s), "fp8gemm_noalloc launch") ? OMEGA_GPU_FP8GEMM_OK : OMEGA_GPU_FP8GEMM_CHIP_FAIL;
 }
 }  // extern "C"

@@ -54,6 +54,23 @@ void omega_gpu_fp8gemm_test_set_mutant(int mutant);
  * output lands in y row YMAP[p]. stream is a cudaStream_t as void *. */
 int omega_gpu_fp8gemm_async(const OmegaGpuFp8Tensor *t, uint32_t rows, uint32_t segs, uint64_t seg_va, uint64_t x_va,
                             int x_bf16, uint64_t y_va, uint64_t xmap_va, uint64_t ymap_va, void *stream);
+/* No counterpart in the reference. The row-table GEMM for callers that must not allocate device memory: an
+ * embedder that has given all device memory to its own arena, or a host in a section where cudaMalloc (which can
+ * synchronise the whole device) is not allowed. Inputs and the output are the caller's DEVICE buffers: expert_ids
+ * (u32 [M], non-decreasing), token_rows (u32 [M], each below x_rows), x (f32 or bf16 [x_rows][k]), y (f32 [M][n]).
+ * The segment table, which the other entries keep in a staging buffer they allocate, lives in one fixed device array
+ * inside the library (about 33 KB per GPU that loads the library, held until the process exits). Limits: at most
+ * OMEGA_GPU_FP8GEMM_NOALLOC_MAX_SEGMENTS experts in the tensor and OMEGA_GPU_FP8GEMM_NOALLOC_MAX_ROWS rows; more is
+ * refused with TOO_LARGE and a message. The call runs on `stream` (a cudaStream_t as void *) and waits once for its
+ * small table-building kernel, so a bad id table is reported (BAD_ARGS) before the GEMM is queued; y is complete when
+ * work queued on `stream` after the call runs. The first call on a device looks up the array's device address; make
+ * that first call outside any stream capture. All calls share the one array: calls that overlap on the GPU (two
+ * streams, two threads) race on it; calls ordered on one stream do not. Results are bit-identical to
+ * omega_gpu_fp8gemm_f32 / _bf16 on the same table. */
+#define OMEGA_GPU_FP8GEMM_NOALLOC_MAX_SEGMENTS 1024u
+#define OMEGA_GPU_FP8GEMM_NOALLOC_MAX_ROWS 1048576u
+int omega_gpu_fp8gemm_noalloc(const OmegaGpuFp8Tensor *t, uint32_t M, uint64_t expert_ids_va, uint64_t token_rows_va, uint64_t x_va,
+                              int x_bf16, uint32_t x_rows, uint64_t y_va, void *stream);
 #ifdef __cplusplus
 }
 #endif
