@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(256) fp8_rows_kernel(const GemvArgs a) {
     const uint8_t *W = reinterpret_cast<const uint8_t *>(w_va);
     const float *S = reinterpret_cast<const float *>(s_va);
     const uint32_t n = a.n, k = a.k, kb = k / 128u, steps = k / (32u * LB);
-    const size_t xstride = (size_t)k * (a.x_bf16 ? 2 : 4);
+    const size_t xstride = a.x_stride_bytes ? a.x_stride_bytes : (size_t)k * (a.x_bf16 ? 2 : 4);
     for (uint32_t rb = (blockIdx.x * nw + warp) * R; rb < n; rb += gridDim.x * nw * R) {
         const uint8_t *wrow = W + (size_t)rb * k + lane * LB;
         const float *srow = S + (size_t)(rb / 128u) * kb;   // R divides 128: the R rows share a scale row

@@ -71,6 +71,7 @@ struct GemvArgs {
     const Seg32 *seg;        // grouped GEMM form: segment records (nullptr for the GEMV forms)
     const uint64_t *tab;     // GEMV forms: {w_va, s_va} per group
     const void *x; int x_bf16; uint32_t x_rows;  // activation rows
+    size_t x_stride_bytes;                       // 0 = rows are dense (k elements apart)
     const uint32_t *xmap, *ymap;                 // optional row maps (grouped GEMM form)
     float *y;
     uint32_t n, k, groups_or_segs, rows;
@@ -87,7 +88,7 @@ cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float 
 cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out_f32, uint16_t *out_bf16, cudaStream_t s);
 // quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap,
-                             const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s);
+                             const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes = 0);
 // tcgen05 grouped GEMM (fp8_mma_sm100.cu)
 struct MmaLaunch {
     const float *wscale, *ascale;      // weight scales [E][n/128][k/128]; activation scales [rows][k/128]
@@ -101,6 +102,9 @@ uint32_t mma_tile_rows(uint32_t pieces);
 bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
 cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s);
 bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s);
+// expert side only (expert-parallel receive path): `rows` candidate rows, ids[row] = local expert or 0xFFFFFFFF,
+// x row r at x + r * x_stride_bytes (bf16); writes dn[row][hidden] f32 for the present rows
+bool layer_forward_routed(OmegaGpuMoeLayer *L, uint32_t rows, const uint32_t *ids, const void *x, size_t x_stride_bytes, float *dn, cudaStream_t s);
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src);
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens);
 float *layer_out32(OmegaGpuMoeLayer *L);

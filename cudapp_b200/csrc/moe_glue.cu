@@ -75,7 +75,7 @@ __device__ __forceinline__ void dec4(uint32_t v, float *o) {
     asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(o[2]), "=f"(o[3]) : "r"(hi));
 }
 
-__global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, const void *__restrict__ x, int x_bf16,
+__global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, const void *__restrict__ x, int x_bf16, size_t x_stride,
                                                         const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
                                                         uint8_t *__restrict__ q, float *__restrict__ sc) {
     const uint32_t lane = threadIdx.x & 31u, kb = k / 128u;
@@ -86,10 +86,10 @@ __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t 
         const uint32_t src = xmap ? xmap[r] : r;
         float v[4];
         if (x_bf16) {
-            const uint2 u = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(x) + (size_t)src * k + b * 128u + lane * 4u));
+            const uint2 u = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * x_stride + (b * 128u + lane * 4u) * 2u));
             v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u); v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
         } else {
-            const float4 u = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + (size_t)src * k + b * 128u + lane * 4u));
+            const float4 u = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * x_stride + (b * 128u + lane * 4u) * 4u));
             v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
         }
         float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
@@ -109,11 +109,12 @@ __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t 
     }
 }
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap, const uint32_t *rows_dev,
-                             uint8_t *q, float *sc, cudaStream_t s) {
+                             uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes) {
+    if (!x_stride_bytes) x_stride_bytes = (size_t)k * (x_bf16 ? 2 : 4);
     const size_t tasks = (size_t)rows * (k / 128u);
     if (!tasks) return cudaSuccess;
     size_t blocks = (tasks + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8;
-    act_quant_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, x, x_bf16, xmap, rows_dev, q, sc);
+    act_quant_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, x, x_bf16, x_stride_bytes, xmap, rows_dev, q, sc);
     return cudaGetLastError();
 }
 

@@ -124,6 +124,46 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     return true;
 }
 
+bool layer_forward_routed(OmegaGpuMoeLayer *L, uint32_t rows, const uint32_t *ids, const void *x, size_t x_stride_bytes, float *dn, cudaStream_t s) {
+    Workspace *w = L->ws;
+    const uint32_t E = L->experts, H = L->hidden, I = L->inter;
+    if (rows > w->max_tokens * w->topk) return false;
+    uint32_t n = 0;
+    OmegaGpuMoePlanOut o = {};
+    o.counts_va = (uint64_t)(uintptr_t)w->counts; o.starts_va = (uint64_t)(uintptr_t)w->starts;
+    o.xmap_va = (uint64_t)(uintptr_t)w->xmap; o.ymap_va = (uint64_t)(uintptr_t)w->ymap; o.header_va = (uint64_t)(uintptr_t)w->header;
+    o.seg_a_va = (uint64_t)(uintptr_t)w->seg_gu; o.dir_a_va = (uint64_t)(uintptr_t)L->dir_gu;
+    o.seg_b_va = (uint64_t)(uintptr_t)w->seg_dn; o.dir_b_va = (uint64_t)(uintptr_t)L->dir_dn;
+    const bool mma = L->cfg.engine == OMEGA_GPU_MOE_ENGINE_MMA;
+    o.tiles_va = mma ? (uint64_t)(uintptr_t)w->tiles : 0;
+    if (!cuda_ok(launch_plan(rows, 1, E, 1, mma ? L->tile_rows : 0, ids, o, s), "plan launch")) return false; n++;
+    if (mma) {
+        const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces;
+        if (!cuda_ok(launch_act_quant(rows, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, x_stride_bytes), "x quant launch")) return false; n++;
+        MmaLaunch g = {};
+        g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.out = w->act;
+        g.n = 2 * I; g.k = H; g.mode = 0; g.out_stride = I; g.err = w->header + 4;
+        if (!cuda_ok(launch_mma_grouped(L->tm_gu, L->tm_qx, Px, g, s), "gate|up mma launch")) return false; n++;
+        if (!cuda_ok(launch_act_quant(rows, I, Pa, w->act, 0, nullptr, w->header, w->qa, w->sa, s), "act quant launch")) return false; n++;
+        MmaLaunch dd = {};
+        dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = dn;
+        dd.n = H; dd.k = I; dd.mode = 1; dd.out_stride = H; dd.err = w->header + 4;
+        if (!cuda_ok(launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false; n++;
+    } else {
+        GemvArgs a = {};
+        a.seg = w->seg_gu; a.x = x; a.x_bf16 = 1; a.x_rows = rows; a.x_stride_bytes = x_stride_bytes; a.xmap = w->xmap;
+        a.y = w->gu; a.n = 2 * I; a.k = H; a.groups_or_segs = E; a.rows = rows; a.out_mul = 1.0f;
+        if (!cuda_ok(launch_gemm_rows(a, nullptr, nullptr, s), "gate|up launch")) return false; n++;
+        if (!cuda_ok(launch_swiglu(rows, I, w->gu, w->act, s), "swiglu launch")) return false; n++;
+        GemvArgs d = {};
+        d.seg = w->seg_dn; d.x = w->act; d.x_rows = rows; d.ymap = w->ymap;
+        d.y = dn; d.n = H; d.k = I; d.groups_or_segs = E; d.rows = rows; d.out_mul = 1.0f;
+        if (!cuda_ok(launch_gemm_rows(d, nullptr, nullptr, s), "down launch")) return false; n++;
+    }
+    L->launches = n;
+    return true;
+}
+
 // TMA descriptors of the weights (fixed) and of the workspace's piece buffers (rebuilt when the workspace changes)
 static bool layer_build_maps(OmegaGpuMoeLayer *L) {
     if (L->cfg.engine != OMEGA_GPU_MOE_ENGINE_MMA) return true;

@@ -91,6 +91,14 @@ static bool stack_run(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *logi
 
 extern "C" {
 
+int omega_gpu_residual_norm_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va, uint64_t xn_va, uint64_t h16_va, void *stream) {
+    if (!tokens || !hidden || !h_va) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    residual_norm_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(hidden, eps, (const uint16_t *)(uintptr_t)x16_va, (const float *)(uintptr_t)m_va, (float *)(uintptr_t)h_va,
+                                                                    (uint16_t *)(uintptr_t)xn_va, (uint16_t *)(uintptr_t)h16_va);
+    return cuda_ok(cudaGetLastError(), "residual norm launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
 int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, float eps, OmegaGpuMoeStack **out) {
     if (out) *out = nullptr;
     if (!layers || !layer || !out || !(eps >= 0.0f)) return OMEGA_GPU_FP8_BAD_ARGS;

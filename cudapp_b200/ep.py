@@ -1,0 +1,240 @@
+"""Expert-parallel driver for the MoE layer stack: one process per GPU, torch.distributed for the plumbing.
+
+Rank r of G holds experts [r*E/G, (r+1)*E/G) of every layer and tokens [r*T/G, (r+1)*T/G). Per layer each rank runs
+the library's dispatch / experts / combine entry points (csrc/moe_ep.cu); rows travel either by NCCL all-to-all of
+fixed-capacity regions ("nccl") or by direct peer stores over NVLink inside the kernels ("p2p", CUDA IPC mappings
+exchanged once at start-up). The whole step is captured in a CUDA graph. The reference has no multi-GPU path; the
+contract here is "same numbers as one GPU".
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+E, H, I, TOPK = 128, 2048, 768, 8
+
+
+def expert_range(rank, world, experts):
+    per = experts // world
+    return rank * per, (rank + 1) * per
+
+
+def token_range(rank, world, tokens):
+    per = tokens // world
+    return rank * per, (rank + 1) * per
+
+
+def region_layout(tokens_local, topk, hidden):
+    """(rows per region incl. its header row, bytes per activation row) -- must match csrc/moe_ep.cu"""
+    return tokens_local * topk + 1, hidden * 2 + 16
+
+
+def pack_regions(ids, x_bf16, world, experts, rank_unused=None):
+    """numpy restatement of the dispatch packing for protocol tests: ids u32 [T][K], x uint16 [T][H] ->
+    (send uint8 [world][rows][row_bytes], slot_pos u32 [T*K]). Region d holds this rank's picks for rank d in
+    (token, slot) order; row 0 of a region is its header {count}."""
+    T, K = ids.shape
+    Hh = x_bf16.shape[1]
+    rows, rb = region_layout(T, K, Hh)
+    per = experts // world
+    send = np.zeros((world, rows, rb), np.uint8)
+    slot_pos = np.zeros(T * K, np.uint32)
+    fill = [0] * world
+    for t in range(T):
+        for s in range(K):
+            d = int(ids[t, s]) // per
+            j = fill[d]; fill[d] += 1
+            send[d, 1 + j, : Hh * 2] = x_bf16[t].view(np.uint8)
+            send[d, 1 + j, Hh * 2:].view(np.uint32)[:2] = (int(ids[t, s]) - d * per, t * K + s)
+            slot_pos[t * K + s] = d * rows + 1 + j
+    for d in range(world):
+        send[d, 0, :4].view(np.uint32)[0] = fill[d]
+    return send, slot_pos
+
+
+class EpStack:
+    """48-layer (or fewer) expert-parallel stack on this rank's GPU."""
+
+    def __init__(self, api, torch, dist, rank, world, layers, tokens, mode="p2p", engine=0, seed_base=0):
+        self.api, self.torch, self.dist, self.rank, self.world, self.mode = api, torch, dist, rank, world, mode
+        self.T, self.Tl, self.Ln = tokens, tokens // world, layers
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        e0, e1 = expert_range(rank, world, E)
+        El = e1 - e0
+        self.layers, self.tensors = [], []
+        w8 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=dev); sc = torch.empty((E, 2 * I // 128, H // 128), dtype=torch.int16, device=dev)
+        d8 = torch.empty((E, H, I), dtype=torch.uint8, device=dev); dsc = torch.empty((E, H // 128, I // 128), dtype=torch.int16, device=dev)
+        lib = api.lib
+        for l in range(layers):
+            g = torch.Generator(device=dev); g.manual_seed(seed_base + l)     # same stream of numbers as the 1-GPU benchmark
+            wgu = (torch.randn((E * 2 * I, H), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            wdn = (torch.randn((E * H, I), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            torch.cuda.synchronize()
+            assert lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * 2 * I), C.c_uint32(H), C.c_uint64(wgu.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0, api.last_error()
+            assert lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * H), C.c_uint32(I), C.c_uint64(wdn.data_ptr()), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr())) == 0, api.last_error()
+            tg, td = C.c_void_p(), C.c_void_p()
+            assert lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(El), C.c_uint32(2 * I), C.c_uint32(H), C.c_uint64(w8[e0:e1].data_ptr()), C.c_uint64(sc[e0:e1].data_ptr()), C.byref(tg)) == 0, api.last_error()
+            assert lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(El), C.c_uint32(H), C.c_uint32(I), C.c_uint64(d8[e0:e1].data_ptr()), C.c_uint64(dsc[e0:e1].data_ptr()), C.byref(td)) == 0, api.last_error()
+            rc, layer = api.moe_layer_create(tg, td, topk=TOPK, max_tokens=tokens + 1, engine=engine)
+            assert rc == 0, api.last_error()
+            self.layers.append(layer); self.tensors += [tg, td]
+            del wgu, wdn
+        del w8, sc, d8, dsc
+        torch.cuda.empty_cache()
+        rc, self.share = api.moe_stack_create(self.layers, 1e-6)       # one scratch workspace for all local layers
+        assert rc == 0, api.last_error()
+        ep = C.c_void_p()
+        assert lib.omega_gpu_moe_ep_create(C.c_uint32(world), C.c_uint32(rank), C.c_uint32(E), C.c_uint32(TOPK), C.c_uint32(H), C.c_uint32(self.Tl), C.byref(ep)) == 0, api.last_error()
+        self.ep = ep
+        buf = (C.c_uint64 * 8)()
+        assert lib.omega_gpu_moe_ep_buffers(ep, buf) == 0
+        self.buf = list(buf)
+        if mode == "p2p":
+            h = (C.c_uint8 * 64)()
+            assert lib.omega_gpu_moe_ep_export(ep, h) == 0, api.last_error()
+            mine = torch.tensor(list(h), dtype=torch.uint8, device=dev)
+            allh = torch.empty(world * 64, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh, mine)
+            hb = (C.c_uint8 * (world * 64))(*allh.cpu().tolist())
+            assert lib.omega_gpu_moe_ep_connect(ep, hb) == 0, api.last_error()
+            dist.barrier()
+        else:
+            self._send = self._wrap(self.buf[0], world * self.buf[4]); self._recv = self._wrap(self.buf[1], world * self.buf[4])
+            self._dn = self._wrap(self.buf[2], world * self.buf[5]); self._back = self._wrap(self.buf[3], world * self.buf[5])
+        Tl = self.Tl
+        self.h = torch.empty((Tl, H), dtype=torch.float32, device=dev); self.xn = torch.empty((Tl, H), dtype=torch.int16, device=dev)
+        self.m = torch.empty((Tl, H), dtype=torch.float32, device=dev); self.out16 = torch.empty((Tl, H), dtype=torch.int16, device=dev)
+        self.logits = torch.empty((layers, Tl, E), dtype=torch.int16, device=dev); self.x = torch.empty((Tl, H), dtype=torch.int16, device=dev)
+        self.graph = None
+        self.launches = 0
+
+    def _wrap(self, va, nbytes):
+        """a torch uint8 view over library-owned device memory (for the NCCL collectives)"""
+        torch = self.torch
+
+        class _Iface:
+            pass
+        o = _Iface()
+        o.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(va), False), "version": 2}
+        return torch.as_tensor(o, device=self.dev)
+
+    def record(self, stream):
+        """enqueue one whole step (all layers) on `stream`"""
+        lib, api, Tl = self.api.lib, self.api, self.Tl
+        sp = C.c_void_p(stream)
+        n = 0
+        ok = lib.omega_gpu_residual_norm_async(C.c_uint32(Tl), C.c_uint32(H), C.c_float(1e-6), C.c_uint64(self.x.data_ptr()), C.c_uint64(0), C.c_uint64(self.h.data_ptr()),
+                                               C.c_uint64(self.xn.data_ptr()), C.c_uint64(0), sp); n += 1
+        assert ok == 0, api.last_error()
+        for l in range(self.Ln):
+            assert lib.omega_gpu_moe_ep_dispatch_async(self.ep, C.c_uint32(Tl), C.c_uint64(self.logits[l].data_ptr()), C.c_uint64(self.xn.data_ptr()), sp) == 0, api.last_error()
+            n += 4 + (1 if self.mode == "p2p" else 0)
+            if self.mode == "nccl":
+                self.dist.all_to_all_single(self._recv, self._send)
+            assert lib.omega_gpu_moe_ep_experts_async(self.ep, self.layers[l], sp) == 0, api.last_error()
+            n += 1 + int(lib.omega_gpu_moe_layer_launches(self.layers[l])) + (3 if self.mode == "p2p" else 0)
+            if self.mode == "nccl":
+                self.dist.all_to_all_single(self._back, self._dn)
+            assert lib.omega_gpu_moe_ep_combine_async(self.ep, C.c_uint32(Tl), C.c_uint64(self.m.data_ptr()), C.c_uint64(0), sp) == 0, api.last_error()
+            n += 1 + (1 if self.mode == "p2p" else 0)
+            last = l + 1 == self.Ln
+            assert lib.omega_gpu_residual_norm_async(C.c_uint32(Tl), C.c_uint32(H), C.c_float(1e-6), C.c_uint64(0), C.c_uint64(self.m.data_ptr()), C.c_uint64(self.h.data_ptr()),
+                                                     C.c_uint64(0 if last else self.xn.data_ptr()), C.c_uint64(self.out16.data_ptr() if last else 0), sp) == 0, api.last_error()
+            n += 1
+        self.launches = n
+
+    def capture(self):
+        torch = self.torch
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.record(s.cuda_stream)          # one eager step first (lazy initialisation, NCCL warm-up)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize(); self.dist.barrier()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.record(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize(); self.dist.barrier()
+
+    def step(self):
+        self.graph.replay()
+
+    def status(self):
+        return int(self.api.lib.omega_gpu_moe_ep_status(self.ep, C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
+
+
+def make_inputs(layers, tokens, seed=0):
+    from oracle.oracle import bf16_bits   # number-format helper only
+    rng = np.random.default_rng(seed)
+    logits = bf16_bits(rng.normal(0, 1, (layers, tokens, E)).astype(np.float32))
+    x = bf16_bits(rng.normal(0, 1, (tokens, H)).astype(np.float32))
+    return logits, x
+
+
+def bench(args, rank, world):
+    import json
+    import time
+    import torch
+    import torch.distributed as dist
+    from cudapp_b200 import api
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("B200MOE_DEVICE", str(local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    mode = os.environ.get("B200MOE_EP_MODE", "p2p")
+    Ln, T = args.layers, args.tokens
+    st = EpStack(api, torch, dist, rank, world, Ln, T, mode=mode, engine=args.engine)
+    logits, x = make_inputs(Ln, T)
+    t0, t1 = token_range(rank, world, T)
+    lg_h = torch.from_numpy(np.ascontiguousarray(logits[:, t0:t1]).view(np.int16)).pin_memory(); x_h = torch.from_numpy(np.ascontiguousarray(x[t0:t1]).view(np.int16)).pin_memory()
+    out_h = torch.empty((t1 - t0, H), dtype=torch.int16).pin_memory()
+    st.logits.copy_(lg_h); st.x.copy_(x_h)
+    st.capture()
+    from bench import ClockSampler
+    for _ in range(max(args.warmup, 3)):
+        st.step()
+    torch.cuda.synchronize(); dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            st.step()
+        ev1.record()
+        torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device="cuda"); dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    status = st.status()
+    assert status == 0, "a bounded cross-GPU wait ran out (code %d)" % status
+    assert torch.isfinite(st.h).all()
+    # end to end: this rank's slice from pinned host memory in, its output slice back, every step
+    def e2e_step():
+        st.logits.copy_(lg_h, non_blocking=True); st.x.copy_(x_h, non_blocking=True)
+        st.step()
+        out_h.copy_(st.out16, non_blocking=True)
+        torch.cuda.synchronize()
+    e2e_step(); dist.barrier()
+    t_0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e = torch.tensor([(time.perf_counter() - t_0) / args.steps], device="cuda"); dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        total_s = float(ms.item()) * 1e-3
+        from bench import GU_BYTES, DN_BYTES, measured_peak
+        peak, kind = measured_peak()
+        per_gpu_bytes = Ln * (E // world) * (GU_BYTES + DN_BYTES)
+        achieved = per_gpu_bytes / (total_s / args.steps) / 1e9
+        print(json.dumps({
+            "metric": "moe_layer_tokens_per_s", "value": T * args.steps / total_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": float(ms.item()) / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "48-layer MoE expert stack, 256 decode tokens/step, 128 experts top-8, hidden 2048, inter 768", "layers": Ln, "tokens_per_step": T,
+                       "parallelism": "ep%d (experts and tokens sharded; %s)" % (world, "direct peer stores over NVLink" if mode == "p2p" else "NCCL all-to-all"),
+                       "l2": "%.1f GB of weights per GPU per step: larger than L2" % (per_gpu_bytes / 1e9)},
+            "e2e": {"value": T / float(e2e.item()), "unit": "tokens/s", "h2d_bytes_per_step": int((lg_h.numel() + x_h.numel()) * 2 * world), "d2h_bytes_per_step": int(out_h.numel() * 2 * world)},
+            "gpu_launches": int(st.launches) * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "whole step per GPU (weights streamed once)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": kind + " copy bandwidth", "traffic": None},
+            "clocks": clocks.summary()}))
+    dist.barrier()
+    dist.destroy_process_group()

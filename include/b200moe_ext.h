@@ -114,6 +114,32 @@ int omega_gpu_moe_stack_async(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t log
                               uint64_t out_bf16_va, void *stream);
 uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *s);
 
+/* ---- residual stream step as one call (the stack uses it; exposed for callers that drive layers themselves):
+ * h = (x16 ? bf16->f32(x16) : h) + (m ? m : 0); xn = bf16(RMSNorm(h)) when xn_va != 0; h16 = bf16(h) when h16_va != 0 */
+int omega_gpu_residual_norm_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va,
+                                  uint64_t xn_va, uint64_t h16_va, void *stream);
+
+/* ---- expert parallelism over the GPUs of one node (no counterpart in the reference, which runs one device).
+ * Rank r of `world` holds experts [r*E/world, (r+1)*E/world) as an ordinary OmegaGpuMoeLayer over its local tensors
+ * (created with max_tokens >= world * tokens_local_max + 1) and a slice of the tokens. One OmegaGpuMoeEp per rank holds
+ * the exchange buffers, shared by all layers. Per layer the caller runs dispatch -> [all-to-all send->recv] -> experts
+ * -> [all-to-all dn->back] -> combine; the two collectives (equal chunks of buffers[4] and buffers[5] bytes per rank)
+ * are the caller's (NCCL). After omega_gpu_moe_ep_connect the rows instead travel by direct peer stores inside
+ * dispatch/experts and no collective is needed. Outputs equal the single-GPU layer's. */
+typedef struct OmegaGpuMoeEp OmegaGpuMoeEp;
+int omega_gpu_moe_ep_create(uint32_t world, uint32_t rank, uint32_t experts, uint32_t topk, uint32_t hidden, uint32_t tokens_local_max,
+                            OmegaGpuMoeEp **out);
+void omega_gpu_moe_ep_free(OmegaGpuMoeEp *ep);
+/* out[0..7] = send_va, recv_va, dn_va, back_va, activation chunk bytes, result chunk bytes, comm block va, comm block bytes */
+int omega_gpu_moe_ep_buffers(const OmegaGpuMoeEp *ep, uint64_t *out);
+/* 64-byte inter-process handle of this rank's comm block; connect takes world x 64 bytes in rank order */
+int omega_gpu_moe_ep_export(const OmegaGpuMoeEp *ep, uint8_t *handle64);
+int omega_gpu_moe_ep_connect(OmegaGpuMoeEp *ep, const uint8_t *handles);
+int omega_gpu_moe_ep_dispatch_async(OmegaGpuMoeEp *ep, uint32_t tokens_local, uint64_t logits_va, uint64_t x_va, void *stream);
+int omega_gpu_moe_ep_experts_async(OmegaGpuMoeEp *ep, OmegaGpuMoeLayer *local, void *stream);
+int omega_gpu_moe_ep_combine_async(OmegaGpuMoeEp *ep, uint32_t tokens_local, uint64_t out_f32_va, uint64_t out_bf16_va, void *stream);
+/* synchronises `stream`; 0, or the code of a bounded cross-GPU wait that ran out (11 dispatch, 12 return) */
+int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream);
 #ifdef __cplusplus
 }
 #endif

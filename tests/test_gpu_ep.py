@@ -1,0 +1,88 @@
+"""Expert-parallel stack on 2 GPUs against the single-GPU stack on the same seeded weights and inputs: every routed
+row goes through the same kernels and the combine keeps slot order, so the outputs must be bit-identical.
+Needs two visible GPUs; skipped otherwise."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _gpus():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+def _worker(rank, world, port, mode, ret):
+    sys.path.insert(0, ROOT)
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port); os.environ["B200MOE_DEVICE"] = str(rank)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from cudapp_b200 import api, ep
+    Ln, T = 2, 64
+    st = ep.EpStack(api, torch, dist, rank, world, Ln, T, mode=mode)
+    logits, x = ep.make_inputs(Ln, T, seed=3)
+    t0, t1 = ep.token_range(rank, world, T)
+    st.logits.copy_(torch.from_numpy(np.ascontiguousarray(logits[:, t0:t1]).view(np.int16))); st.x.copy_(torch.from_numpy(np.ascontiguousarray(x[t0:t1]).view(np.int16)))
+    st.capture()
+    st.step(); st.step()
+    torch.cuda.synchronize()
+    assert st.status() == 0
+    mine = st.h.cpu().numpy()
+    ok = True
+    if rank == 0:   # the single-GPU stack with the same seeds on this GPU
+        one = ep.EpStack.__new__(ep.EpStack)
+        layers = []
+        dev = torch.device("cuda", 0)
+        for l in range(Ln):
+            g = torch.Generator(device=dev); g.manual_seed(l)
+            wgu = (torch.randn((ep.E * 2 * ep.I, ep.H), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            wdn = (torch.randn((ep.E * ep.H, ep.I), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            w8 = torch.empty((ep.E * 2 * ep.I, ep.H), dtype=torch.uint8, device=dev); sc = torch.empty((ep.E * 12 * 16,), dtype=torch.int16, device=dev)
+            d8 = torch.empty((ep.E * ep.H, ep.I), dtype=torch.uint8, device=dev); dsc = torch.empty((ep.E * 16 * 6,), dtype=torch.int16, device=dev)
+            torch.cuda.synchronize()
+            assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(ep.E * 2 * ep.I), C.c_uint32(ep.H), C.c_uint64(wgu.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0
+            assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(ep.E * ep.H), C.c_uint32(ep.I), C.c_uint64(wdn.data_ptr()), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr())) == 0
+            tg, td = C.c_void_p(), C.c_void_p()
+            assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(ep.E), C.c_uint32(2 * ep.I), C.c_uint32(ep.H), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr()), C.byref(tg)) == 0
+            assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(ep.E), C.c_uint32(ep.H), C.c_uint32(ep.I), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr()), C.byref(td)) == 0
+            rc, layer = api.moe_layer_create(tg, td, topk=8, max_tokens=T); assert rc == 0, api.last_error()
+            layers.append(layer)
+        rc, stack = api.moe_stack_create(layers, 1e-6); assert rc == 0
+        rc, o16, o32 = api.moe_stack_bf16(stack, logits, x); assert rc == 0, api.last_error()
+        ok = bool(np.array_equal(mine, o32[t0:t1]))
+        if not ok:
+            print("max abs diff", float(np.max(np.abs(mine - o32[t0:t1]))), flush=True)
+    parts = [None] * world
+    dist.all_gather_object(parts, mine)
+    if rank == 0:
+        full = np.concatenate(parts)
+        ret.put(ok and bool(np.array_equal(full, o32)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_ep_equals_single_gpu(mode):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29600 + (os.getpid() % 2000) + (0 if mode == "nccl" else 1)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert p.exitcode == 0
+    assert q.get(timeout=5) is True
