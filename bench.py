@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--engine", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8)
+    ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline out (profiling runs)")
     return ap.parse_args()
 
 
@@ -260,7 +261,10 @@ def run_ours(args, rank, world):
     if os.path.exists(tp):
         traffic = json.load(open(tp)).get(top)
 
-    cpu_sec, kind, cores = cpu_layer_sample(args.cpu_sample_tokens, 1, 0)
+    if args.skip_cpu:
+        cpu_sec, kind, cores = float("nan"), "skipped", 0
+    else:
+        cpu_sec, kind, cores = cpu_layer_sample(args.cpu_sample_tokens, 1, 0)
     cpu_value = args.cpu_sample_tokens / (cpu_sec * Ln)
     total_s = ms * 1e-3
     out = {

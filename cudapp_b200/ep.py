@@ -236,5 +236,7 @@ def bench(args, rank, world):
             "roofline": {"bound": "hbm", "kernel": "whole step per GPU (weights streamed once)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": kind + " copy bandwidth", "traffic": None},
             "clocks": clocks.summary()}))
-    dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize(); dist.barrier()
+    import sys
+    sys.stdout.flush(); sys.stderr.flush()
+    os._exit(0)   # a process group whose collectives sit in a captured graph does not tear down reliably; leave at once

@@ -68,8 +68,9 @@ def _worker(rank, world, port, mode, ret):
     if rank == 0:
         full = np.concatenate(parts)
         ret.put(ok and bool(np.array_equal(full, o32)))
-    dist.barrier()
-    dist.destroy_process_group()
+        ret.close(); ret.join_thread()
+    torch.cuda.synchronize(); dist.barrier()
+    os._exit(0)   # collectives captured in a CUDA graph make process-group teardown unreliable: leave at once
 
 
 @pytest.mark.parametrize("mode", ["nccl", "p2p"])
@@ -83,6 +84,6 @@ def test_ep_equals_single_gpu(mode):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(600)
+        p.join(240)
         assert p.exitcode == 0
     assert q.get(timeout=5) is True
