@@ -194,8 +194,9 @@ def moe_combine_f32(w, d):
 def act_quant_f32(x, pieces=1):
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, k = x.shape
-    q = np.empty((rows, pieces, k), np.uint8); s = np.empty((rows, k // 128), np.float32)
-    return lib.omega_gpu_act_quant_f32(C.c_uint32(rows), C.c_uint32(k), C.c_uint32(pieces), _p(x), _p(q), _p(s)), q, s
+    q = np.empty((pieces, rows, k), np.uint8); s = np.empty((rows, k // 128), np.float32)   # the library's layout is piece-major
+    rc = lib.omega_gpu_act_quant_f32(C.c_uint32(rows), C.c_uint32(k), C.c_uint32(pieces), _p(x), _p(q), _p(s))
+    return rc, np.ascontiguousarray(q.transpose(1, 0, 2)), s
 
 
 # ---------------------------------------------------------------- W4

@@ -27,19 +27,19 @@
 
 namespace b200 {
 
-constexpr int MMA_N = 64;                       // accumulator columns per weight tile
-constexpr int MMA_STAGES = 4;
-constexpr uint32_t A_TILE = 128 * 128, B_TILE = MMA_N * 128, STAGE_BYTES = 2 * A_TILE + B_TILE;
+constexpr int MMA_TOK = 32;                     // routed rows per tile; accumulator columns = 32 per activation piece
+constexpr uint32_t A_TILE = 128 * 128, B_PIECE = MMA_TOK * 128;
 constexpr int KB_MAX = 32;                      // k <= 4096 on this engine
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr uint32_t TMEM_COLS = 256;             // 2 buffers x 2 accumulators x 64 columns
+constexpr int MMA_THREADS = 32 * 11;            // TMA, MMA, scale loader, 2 x 4 epilogue warps
 
 struct MmaArgs {
     const float *wscale, *ascale;
     const uint4 *tiles; const uint32_t *header;
     const uint32_t *ymap;
-    float *out;
-    uint32_t n, k, pairs, mode, inter, out_stride;
+    float *out;                      // mode 1: y rows; mode 0: optional f32 copy of the gated activations (may be null)
+    uint8_t *q_out; float *s_out;    // mode 0: gated activations as e4m3 pieces [piece][q_rows][inter] + scales [row][inter/128]
+    uint32_t n, k, pairs, mode, inter, out_stride, q_rows, q_pieces;
     uint32_t *err;
 };
 
@@ -77,8 +77,6 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint6
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// kind::f8f6f4, D = f32, A = B = e4m3, both K-major, M = 128, N = MMA_N
-constexpr uint32_t MMA_IDESC = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
 #define TMEM_LD32(taddr, r)                                                                                                              \
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];" \
@@ -89,29 +87,57 @@ constexpr uint32_t MMA_IDESC = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(
 
 __device__ __forceinline__ float silu_mul_dev(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
 
+// activation-piece helpers (same arithmetic as act_quant_kernel in moe_glue.cu)
+__device__ __forceinline__ float pq_scale_mma(float amax) {
+    amax = fmaxf(amax, 7.888609052210118e-31f /* 2^-100 */);
+    const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, c = (M + 0x1fffffu) >> 23;
+    return __uint_as_float((E + c - 8u) << 23);
+}
+__device__ __forceinline__ uint32_t enc2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float2 dec2(uint32_t v) {
+    uint32_t h2; float2 f;
+    asm("{ .reg .b16 a; cvt.u16.u32 a, %1; cvt.rn.f16x2.e4m3x2 %0, a; }" : "=r"(h2) : "r"(v));
+    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(f.x), "=f"(f.y) : "r"(h2));
+    return f;
+}
+
 template <int P>
-__global__ void __launch_bounds__(192, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
-    constexpr int NTOK = MMA_N / P;             // routed rows per tile
+__global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
+    constexpr int N = MMA_TOK * P;                                   // accumulator columns per weight tile
+    constexpr int STAGES = P <= 2 ? 5 : 4;
+    constexpr uint32_t STAGE_BYTES = 2 * A_TILE + P * B_PIECE;
+    constexpr uint32_t TMEM_COLS = 4 * N <= 128 ? 128 : 4 * N <= 256 ? 256 : 512;   // 2 buffers x 2 accumulators x N
+    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // f8f6f4, D f32, A = B = e4m3 K-major, M 128
     extern __shared__ uint8_t dyn_smem[];
-    __shared__ __align__(8) uint64_t s_bar[2 * MMA_STAGES + 5];
+    __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 12];
     __shared__ uint32_t s_tmem, s_abort;
-    __shared__ float s_sw[2][KB_MAX];
-    __shared__ float s_cs[KB_MAX][NTOK];
+    __shared__ float s_sw[2][2][KB_MAX];          // [scale buffer][weight tile][k block]
+    __shared__ float s_cs[2][KB_MAX][MMA_TOK];    // [scale buffer][k block][row]
+    __shared__ float s_red[2][4][MMA_TOK];        // [epilogue group][warp][row]: amax exchange
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
     const uint32_t bar0 = smem_u32(s_bar);
     auto full_bar = [&](uint32_t s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](uint32_t s) { return bar0 + 8u * (MMA_STAGES + s); };
-    auto accfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * MMA_STAGES + b); };
-    auto accempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * MMA_STAGES + 2 + b); };
-    const uint32_t epi_bar = bar0 + 8u * (2 * MMA_STAGES + 4);   // the 128 epilogue threads' own rendezvous
+    auto empty_bar = [&](uint32_t s) { return bar0 + 8u * (STAGES + s); };
+    auto accfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + b); };
+    auto accempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+    auto scfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 4 + b); };
+    auto scempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 6 + b); };
+    auto group_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 8 + g); };
+    auto turn_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 10 + g); };   // "the other group has drained its unit's partials"
     volatile uint32_t *abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (uint32_t s = 0; s < MMA_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (uint32_t b = 0; b < 2; b++) { mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128); }
-        mbar_init(epi_bar, 128);
+        for (uint32_t s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (uint32_t b = 0; b < 2; b++) {
+            mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128);
+            mbar_init(scfull_bar(b), 32); mbar_init(scempty_bar(b), 128); mbar_init(group_bar(b), 128); mbar_init(turn_bar(b), 128);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // TMEM allocation by one whole warp
@@ -131,15 +157,17 @@ __global__ void __launch_bounds__(192, 1) fp8_mma_grouped_kernel(const __grid_co
             for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
                 const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs;
                 const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
-                const int wy0 = (int)(t.x * a.n + r0), wy1 = (int)(t.x * a.n + r1), qy = (int)(t.y * P);
+                const int wy0 = (int)(t.x * a.n + r0), wy1 = (int)(t.x * a.n + r1);
                 for (uint32_t kb = 0; kb < KB; kb++, it++) {
-                    const uint32_t s = it % MMA_STAGES, ph = (it / MMA_STAGES) & 1u;
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
                     const uint32_t dst = smem_base + s * STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
                     tma_load_2d(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0);
                     tma_load_2d(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1);
-                    tma_load_2d(dst + 2 * A_TILE, &tm_q, full_bar(s), (int)(kb * 128u), qy);
+#pragma unroll
+                    for (int p = 0; p < P; p++)   // piece p of the tile's rows: 32 rows x 128 bytes
+                        tma_load_2d(dst + 2 * A_TILE + p * B_PIECE, &tm_q, full_bar(s), (int)(kb * 128u), (int)(p * a.q_rows + t.y));
                 }
             }
         }
@@ -149,79 +177,114 @@ __global__ void __launch_bounds__(192, 1) fp8_mma_grouped_kernel(const __grid_co
             uint32_t it = 0; bool ok = true;
             for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
                 for (uint32_t kb = 0; kb < KB; kb++, it++) {
-                    const uint32_t s = it % MMA_STAGES, ph = (it / MMA_STAGES) & 1u, buf = it & 1u, bph = (it >> 1) & 1u;
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u, buf = it & 1u, bph = (it >> 1) & 1u;
                     if (!(ok = mbar_wait(accempty_bar(buf), bph ^ 1u, abort_flag, a.err, 2))) break;
                     if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, a.err, 3))) break;
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
                     const uint64_t da0 = umma_desc(sa), da1 = umma_desc(sa + A_TILE), db = umma_desc(sa + 2 * A_TILE);
-                    const uint32_t d0 = tmem + buf * 2u * MMA_N, d1 = d0 + MMA_N;
+                    const uint32_t d0 = tmem + buf * 2u * N, d1 = d0 + N;
 #pragma unroll
                     for (uint32_t ks = 0; ks < 4; ks++) {   // 32 K bytes per MMA: advance the start address inside the swizzle row
-                        tc_mma_f8(d0, da0 + 2u * ks, db + 2u * ks, MMA_IDESC, ks);
-                        tc_mma_f8(d1, da1 + 2u * ks, db + 2u * ks, MMA_IDESC, ks);
+                        tc_mma_f8(d0, da0 + 2u * ks, db + 2u * ks, IDESC, ks);
+                        tc_mma_f8(d1, da1 + 2u * ks, db + 2u * ks, IDESC, ks);
                     }
                     tc_commit(empty_bar(s));       // the stage is free once these MMAs have read it
                     tc_commit(accfull_bar(buf));   // the partial is complete
                 }
             }
         }
-    } else {
-        // ---------------------------------------------------------------- promotion + epilogue (warps 2..5)
-        const uint32_t q = warp & 3u, row = q * 32u + lane, et = threadIdx.x - 64u;   // TMEM lane quarter of this warp
-        uint32_t it = 0, syncs = 0; bool ok = true;
-        for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
-            const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, cnt = t.z;
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
+        uint32_t n = 0; bool ok = true;
+        for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
+            const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
-            mbar_arrive(epi_bar);                             // everyone is done with the previous unit's scales
-            if (!(ok = mbar_wait(epi_bar, syncs++ & 1u, abort_flag, a.err, 5))) break;
-            if (et < KB) {
-                s_sw[0][et] = a.wscale[((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB + et];
-                s_sw[1][et] = a.wscale[((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB + et];
+            if (!(ok = mbar_wait(scempty_bar(b), ((n >> 1) & 1u) ^ 1u, abort_flag, a.err, 7))) break;
+            if (lane < KB) {
+                s_sw[b][0][lane] = a.wscale[((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB + lane];
+                s_sw[b][1][lane] = a.wscale[((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB + lane];
             }
-            for (uint32_t i = et; i < KB * NTOK; i += 128u) {
-                const uint32_t kb = i / NTOK, tk = i - kb * NTOK;
-                s_cs[kb][tk] = tk < cnt ? a.ascale[(size_t)(t.y + tk) * KB + kb] : 0.0f;
-            }
-            mbar_arrive(epi_bar);
-            if (!(ok = mbar_wait(epi_bar, syncs++ & 1u, abort_flag, a.err, 6))) break;
-            float acc0[NTOK], acc1[NTOK];
+            for (uint32_t kb = 0; kb < KB; kb++) s_cs[b][kb][lane] = lane < t.z ? a.ascale[(size_t)(t.y + lane) * KB + kb] : 0.0f;
+            mbar_arrive(scfull_bar(b));
+        }
+    } else {
+        // ---------------------------------------------------------------- promotion + epilogue: two groups of 4 warps take alternate units
+        const uint32_t g = (warp - 3u) >> 2, q = warp & 3u, row = q * 32u + lane;   // q: the TMEM lane quarter this warp may read
+        uint32_t n = 0, gsync = 0, turns = 0; bool ok = true;
+        for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
+            if ((n & 1u) != g) continue;
+            // partial sums are consumed strictly in order: start only when the other group has taken the last partial of unit n-1
+            // (a parity wait can only tell the next phase from the current one, never a later one)
+            if (n > 0 && !(ok = mbar_wait(turn_bar(g), turns++ & 1u, abort_flag, a.err, 9))) break;
+            const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, cnt = t.z, b = n & 1u;
+            const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+            if (!(ok = mbar_wait(scfull_bar(b), (n >> 1) & 1u, abort_flag, a.err, 8))) break;
+            float acc0[MMA_TOK], acc1[MMA_TOK];
 #pragma unroll
-            for (int i = 0; i < NTOK; i++) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
-            for (uint32_t kb = 0; kb < KB; kb++, it++) {
-                const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
+            for (int i = 0; i < MMA_TOK; i++) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
+            for (uint32_t kb = 0; kb < KB; kb++) {
+                const uint32_t it = n * KB + kb, buf = it & 1u, bph = (it >> 1) & 1u;
                 if (!(ok = mbar_wait(accfull_bar(buf), bph, abort_flag, a.err, 4))) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem + ((q * 32u) << 16) + buf * 2u * MMA_N;
-                const float sw0 = s_sw[0][kb], sw1 = s_sw[1][kb];
+                const uint32_t taddr = tmem + ((q * 32u) << 16) + buf * 2u * N;
+                const float sw0 = s_sw[b][0][kb], sw1 = s_sw[b][1][kb];
 #pragma unroll
-                for (int half = 0; half < 2; half++) {      // accumulator 0 then 1, 64 columns each
-                    uint32_t d[MMA_N];
-                    TMEM_LD32(taddr + half * MMA_N, d);
-                    uint32_t *dh = d + 32;
-                    TMEM_LD32(taddr + half * MMA_N + 32, dh);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (half == 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // both accumulators are in registers
-                    const float sw = half ? sw1 : sw0;
+                for (int half = 0; half < 2; half++) {
+                    float pw = half ? sw1 : sw0;                       // weight scale x 16^-piece
 #pragma unroll
-                    for (int i = 0; i < NTOK; i++) {
-                        float v = __uint_as_float(d[i * P + P - 1]);
+                    for (int p = 0; p < P; p++) {
+                        uint32_t d[MMA_TOK];
+                        TMEM_LD32(taddr + half * N + p * MMA_TOK, d);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (half == 1 && p == P - 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // the partial is in registers
 #pragma unroll
-                        for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(d[i * P + p]));
-                        const float sc = sw * s_cs[kb][i];
-                        if (half) acc1[i] = fmaf(v, sc, acc1[i]); else acc0[i] = fmaf(v, sc, acc0[i]);
+                        for (int i = 0; i < MMA_TOK; i++) {
+                            const float sc = pw * s_cs[b][kb][i];
+                            if (half) acc1[i] = fmaf(__uint_as_float(d[i]), sc, acc1[i]); else acc0[i] = fmaf(__uint_as_float(d[i]), sc, acc0[i]);
+                        }
+                        pw *= 0.0625f;
                     }
                 }
             }
             if (!ok) break;
-            // ---- write the unit's results: 128 consecutive features per routed row
+            mbar_arrive(turn_bar(g ^ 1u));   // the other group may start on the next unit's partials
+            mbar_arrive(scempty_bar(b));   // this unit's scales may be overwritten
             if (a.mode == 0) {
+                // ---- SiLU gate, then the gated activations leave as e4m3 pieces: amax over the unit's 128 features per row
 #pragma unroll
-                for (int i = 0; i < NTOK; i++)
-                    if ((uint32_t)i < cnt) a.out[(size_t)(t.y + i) * a.out_stride + j * 128u + row] = silu_mul_dev(acc0[i], acc1[i]);
+                for (int i = 0; i < MMA_TOK; i++) acc0[i] = silu_mul_dev(acc0[i], acc1[i]);
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i++) {
+                    float m = fabsf(acc0[i]);
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                    if (lane == (uint32_t)i) s_red[g][q][i] = m;
+                }
+                mbar_arrive(group_bar(g));
+                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 5))) break;
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i += 2) {
+                    if ((uint32_t)i >= cnt) break;
+                    const float s0 = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][i], s_red[g][1][i]), fmaxf(s_red[g][2][i], s_red[g][3][i])));
+                    const float s1 = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][i + 1], s_red[g][1][i + 1]), fmaxf(s_red[g][2][i + 1], s_red[g][3][i + 1])));
+                    if (a.out) { a.out[(size_t)(t.y + i) * a.out_stride + j * 128u + row] = acc0[i]; if ((uint32_t)i + 1 < cnt) a.out[(size_t)(t.y + i + 1) * a.out_stride + j * 128u + row] = acc0[i + 1]; }
+                    float ra = __fdiv_rn(acc0[i], s0), rb = __fdiv_rn(acc0[i + 1], s1);
+                    for (uint32_t p = 0; p < a.q_pieces; p++) {
+                        const uint32_t code = enc2(ra, rb);
+                        uint8_t *qd = a.q_out + ((size_t)p * a.q_rows + t.y + i) * a.inter + j * 128u + row;
+                        qd[0] = (uint8_t)(code & 0xffu);
+                        if ((uint32_t)i + 1 < cnt) qd[a.inter] = (uint8_t)(code >> 8);
+                        const float2 dv = dec2(code);
+                        ra = (ra - dv.x) * 16.0f; rb = (rb - dv.y) * 16.0f;
+                    }
+                    if (row == 0) { a.s_out[(size_t)(t.y + i) * (a.inter / 128u) + j] = s0; if ((uint32_t)i + 1 < cnt) a.s_out[(size_t)(t.y + i + 1) * (a.inter / 128u) + j] = s1; }
+                }
+                mbar_arrive(group_bar(g));   // s_red is free again
+                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 6))) break;
             } else {
 #pragma unroll
-                for (int i = 0; i < NTOK; i++)
+                for (int i = 0; i < MMA_TOK; i++)
                     if ((uint32_t)i < cnt) {
                         float *o = a.out + (size_t)a.ymap[t.y + i] * a.out_stride;
                         o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
@@ -259,21 +322,22 @@ bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols,
     return true;
 }
 
-uint32_t mma_tile_rows(uint32_t pieces) { return MMA_N / pieces; }
+uint32_t mma_tile_rows(uint32_t) { return MMA_TOK; }
 bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode) { return k % 128u == 0 && k <= 128u * KB_MAX && n % 128u == 0 && (mode == 0 || (n / 128u) % 2u == 0); }
 
 cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s) {
     MmaArgs a = {};
     a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
-    a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.mode == 0 ? m.n / 256u : m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
-    const size_t smem = (size_t)MMA_STAGES * STAGE_BYTES + 1024;
+    a.q_out = m.q_out; a.s_out = m.s_out; a.q_rows = m.q_rows; a.q_pieces = m.q_pieces;
+    a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
     const int sms = st().sm_count ? st().sm_count : 148;
     const CUtensorMap *w = (const CUtensorMap *)tm_w, *q = (const CUtensorMap *)tm_q;
 #define LAUNCH(PV)                                                                                                                      \
     do {                                                                                                                                \
+        const size_t smem = (size_t)((PV) <= 2 ? 5 : 4) * (2 * A_TILE + (PV) * B_PIECE) + 1024;                                        \
         static bool attr = false;                                                                                                       \
         if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
-        fp8_mma_grouped_kernel<PV><<<sms, 192, smem, s>>>(*w, *q, a);                                                                 \
+        fp8_mma_grouped_kernel<PV><<<sms, MMA_THREADS, smem, s>>>(*w, *q, a);                                                          \
     } while (0)
     switch (pieces) {
     case 1: LAUNCH(1); break;

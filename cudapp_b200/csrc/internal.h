@@ -88,13 +88,14 @@ cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float 
 cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out_f32, uint16_t *out_bf16, cudaStream_t s);
 // quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap,
-                             const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes = 0);
+                             const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes = 0, uint32_t q_rows = 0);
 // tcgen05 grouped GEMM (fp8_mma_sm100.cu)
 struct MmaLaunch {
     const float *wscale, *ascale;      // weight scales [E][n/128][k/128]; activation scales [rows][k/128]
     const void *tiles;                 // uint4 {expert, row0, cnt, segment} per row tile
     const uint32_t *header, *ymap;     // header[2] = tile count; ymap: destination rows (mode 1)
-    float *out; uint32_t n, k, mode, out_stride;   // mode 0: gate|up + SiLU gate -> out[row][n/2]; mode 1: out[ymap[row]][n]
+    float *out; uint32_t n, k, mode, out_stride;   // mode 1: out[ymap[row]][n]; mode 0: gate|up + SiLU gate, f32 copy to out[row][n/2] when out != null
+    uint8_t *q_out; float *s_out; uint32_t q_rows, q_pieces;   // mode 0 result as e4m3 pieces [piece][q_rows][n/2] + scales [row][n/256]; q_rows also = row capacity of the input pieces
     uint32_t *err;                     // device word: non-zero = a bounded wait inside the kernel ran out
 };
 bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);

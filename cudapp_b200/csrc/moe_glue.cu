@@ -75,7 +75,7 @@ __device__ __forceinline__ void dec4(uint32_t v, float *o) {
     asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(o[2]), "=f"(o[3]) : "r"(hi));
 }
 
-__global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, const void *__restrict__ x, int x_bf16, size_t x_stride,
+__global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, size_t piece_stride, const void *__restrict__ x, int x_bf16, size_t x_stride,
                                                         const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
                                                         uint8_t *__restrict__ q, float *__restrict__ sc) {
     const uint32_t lane = threadIdx.x & 31u, kb = k / 128u;
@@ -101,20 +101,22 @@ __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t 
         for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], s);
         for (uint32_t p = 0; p < pieces; p++) {
             const uint32_t code = enc4(res[0], res[1], res[2], res[3]);
-            *reinterpret_cast<uint32_t *>(q + ((size_t)r * pieces + p) * k + b * 128u + lane * 4u) = code;
+            *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)r * k + b * 128u + lane * 4u) = code;
             float d[4]; dec4(code, d);
 #pragma unroll
             for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
         }
     }
 }
+// q: piece p of row r at q[p * q_rows * k + r * k] (piece-major; q_rows = row capacity, 0 = rows)
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap, const uint32_t *rows_dev,
-                             uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes) {
+                             uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes, uint32_t q_rows) {
+    if (!q_rows) q_rows = rows;
     if (!x_stride_bytes) x_stride_bytes = (size_t)k * (x_bf16 ? 2 : 4);
     const size_t tasks = (size_t)rows * (k / 128u);
     if (!tasks) return cudaSuccess;
     size_t blocks = (tasks + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8;
-    act_quant_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, x, x_bf16, x_stride_bytes, xmap, rows_dev, q, sc);
+    act_quant_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, (size_t)q_rows * k, x, x_bf16, x_stride_bytes, xmap, rows_dev, q, sc);
     return cudaGetLastError();
 }
 

@@ -92,15 +92,15 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     if (!cuda_ok(launch_plan(tokens, K, E, K, mma ? L->tile_rows : 0, w->ids, o, s), "plan launch")) return false; MARK("plan");
     if (mma) {
         // activations as e4m3 pieces in sorted-row order, then the two tensor-core grouped GEMMs
-        const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces;
-        if (!cuda_ok(launch_act_quant(R, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s), "x quant launch")) return false; MARK("x_quant");
+        const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces, Rp = w->max_tokens * w->topk + 8;
+        if (!cuda_ok(launch_act_quant(R, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, 0, Rp), "x quant launch")) return false; MARK("x_quant");
         MmaLaunch g = {};
-        g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.ymap = nullptr; g.out = w->act;
+        g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.ymap = nullptr; g.out = nullptr;
+        g.q_out = w->qa; g.s_out = w->sa; g.q_rows = Rp; g.q_pieces = Pa;
         g.n = 2 * I; g.k = H; g.mode = 0; g.out_stride = I; g.err = w->header + 4;
         if (!cuda_ok(launch_mma_grouped(L->tm_gu, L->tm_qx, Px, g, s), "gate|up mma launch")) return false; MARK("gate_up_mma");
-        if (!cuda_ok(launch_act_quant(R, I, Pa, w->act, 0, nullptr, w->header, w->qa, w->sa, s), "act quant launch")) return false; MARK("act_quant");
         MmaLaunch dd = {};
-        dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = w->dn;
+        dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = w->dn; dd.q_rows = Rp;
         dd.n = H; dd.k = I; dd.mode = 1; dd.out_stride = H; dd.err = w->header + 4;
         if (!cuda_ok(launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false; MARK("down_mma");
         if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
@@ -138,15 +138,15 @@ bool layer_forward_routed(OmegaGpuMoeLayer *L, uint32_t rows, const uint32_t *id
     o.tiles_va = mma ? (uint64_t)(uintptr_t)w->tiles : 0;
     if (!cuda_ok(launch_plan(rows, 1, E, 1, mma ? L->tile_rows : 0, ids, o, s), "plan launch")) return false; n++;
     if (mma) {
-        const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces;
-        if (!cuda_ok(launch_act_quant(rows, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, x_stride_bytes), "x quant launch")) return false; n++;
+        const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces, Rp = w->max_tokens * w->topk + 8;
+        if (!cuda_ok(launch_act_quant(rows, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, x_stride_bytes, Rp), "x quant launch")) return false; n++;
         MmaLaunch g = {};
-        g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.out = w->act;
+        g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.out = nullptr;
+        g.q_out = w->qa; g.s_out = w->sa; g.q_rows = Rp; g.q_pieces = Pa;
         g.n = 2 * I; g.k = H; g.mode = 0; g.out_stride = I; g.err = w->header + 4;
         if (!cuda_ok(launch_mma_grouped(L->tm_gu, L->tm_qx, Px, g, s), "gate|up mma launch")) return false; n++;
-        if (!cuda_ok(launch_act_quant(rows, I, Pa, w->act, 0, nullptr, w->header, w->qa, w->sa, s), "act quant launch")) return false; n++;
         MmaLaunch dd = {};
-        dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = dn;
+        dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = dn; dd.q_rows = Rp;
         dd.n = H; dd.k = I; dd.mode = 1; dd.out_stride = H; dd.err = w->header + 4;
         if (!cuda_ok(launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false; n++;
     } else {
@@ -170,8 +170,8 @@ static bool layer_build_maps(OmegaGpuMoeLayer *L) {
     const uint64_t Rp = (uint64_t)L->ws->max_tokens * L->cfg.topk + 8;
     return make_tmap_u8(L->tm_gu, L->gu->w, (uint64_t)L->experts * 2 * L->inter, L->hidden, 128) &&
            make_tmap_u8(L->tm_dn, L->dn->w, (uint64_t)L->experts * L->hidden, L->inter, 128) &&
-           make_tmap_u8(L->tm_qx, L->ws->qx, Rp * L->cfg.x_pieces, L->hidden, 64) &&
-           make_tmap_u8(L->tm_qa, L->ws->qa, Rp * L->cfg.act_pieces, L->inter, 64);
+           make_tmap_u8(L->tm_qx, L->ws->qx, Rp * L->cfg.x_pieces, L->hidden, 32) &&
+           make_tmap_u8(L->tm_qa, L->ws->qa, Rp * L->cfg.act_pieces, L->inter, 32);
 }
 
 // dst drops its own workspace and uses src's (same shape, at least as many tokens); calls on them must then be stream-ordered

@@ -57,7 +57,7 @@ int omega_gpu_swiglu_f32(uint32_t rows, uint32_t inter, const float *gu, float *
  * (src/omega_blackwell_codegen_dec.c:226-255) */
 int omega_gpu_moe_combine_f32(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out);
 /* per row, per 128 columns: power-of-two scale, e4m3 codes (src/omega_blackwell_codegen_qg.h:7-19). pieces > 1
- * adds residual pieces at scale/16^p (this library's exact-activation format). q: [rows][pieces][k]. */
+ * adds residual pieces at scale/16^p (this library's exact-activation format). q: [pieces][rows][k] (piece-major). */
 int omega_gpu_act_quant_f32(uint32_t rows, uint32_t k, uint32_t pieces, const float *x, uint8_t *q, float *s);
 
 /* ---- W4: signed int4 weights, two per byte along K (low nibble = even column), fp16 scale per 32 columns.
