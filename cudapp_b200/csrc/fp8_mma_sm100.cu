@@ -115,8 +115,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     extern __shared__ uint8_t dyn_smem[];
     __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 12];
     __shared__ uint32_t s_tmem, s_abort;
-    __shared__ float s_sw[2][2][KB_MAX];          // [scale buffer][weight tile][k block]
-    __shared__ float s_cs[2][KB_MAX][MMA_TOK];    // [scale buffer][k block][row]
+    __shared__ float s_sc[2][2][KB_MAX][MMA_TOK]; // [scale buffer][weight tile][k block][row] = weight scale x row scale
     __shared__ float s_red[2][4][MMA_TOK];        // [epilogue group][warp][row]: amax exchange
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
@@ -201,11 +200,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
             if (!(ok = mbar_wait(scempty_bar(b), ((n >> 1) & 1u) ^ 1u, abort_flag, a.err, 7))) break;
-            if (lane < KB) {
-                s_sw[b][0][lane] = a.wscale[((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB + lane];
-                s_sw[b][1][lane] = a.wscale[((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB + lane];
+            const float *w0 = a.wscale + ((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB, *w1 = a.wscale + ((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB;
+            for (uint32_t kb = 0; kb < KB; kb++) {
+                const float cs = lane < t.z ? a.ascale[(size_t)(t.y + lane) * KB + kb] : 0.0f;
+                s_sc[b][0][kb][lane] = __ldg(w0 + kb) * cs;
+                s_sc[b][1][kb][lane] = __ldg(w1 + kb) * cs;
             }
-            for (uint32_t kb = 0; kb < KB; kb++) s_cs[b][kb][lane] = lane < t.z ? a.ascale[(size_t)(t.y + lane) * KB + kb] : 0.0f;
             mbar_arrive(scfull_bar(b));
         }
     } else {
@@ -228,22 +228,29 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
                 if (!(ok = mbar_wait(accfull_bar(buf), bph, abort_flag, a.err, 4))) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem + ((q * 32u) << 16) + buf * 2u * N;
-                const float sw0 = s_sw[b][0][kb], sw1 = s_sw[b][1][kb];
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
-                    float pw = half ? sw1 : sw0;                       // weight scale x 16^-piece
+                    // pieces folded highest first (Horner, x 1/16) with at most two 32-column chunks in registers
+                    uint32_t da[MMA_TOK], db[MMA_TOK];
+                    TMEM_LD32(taddr + half * N + (P - 1) * MMA_TOK, da);
+                    if (P > 1) TMEM_LD32(taddr + half * N + (P - 2) * MMA_TOK, db);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (P > 1) {
 #pragma unroll
-                    for (int p = 0; p < P; p++) {
-                        uint32_t d[MMA_TOK];
-                        TMEM_LD32(taddr + half * N + p * MMA_TOK, d);
+                        for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));
+                    }
+#pragma unroll
+                    for (int p = P - 3; p >= 0; p--) {
+                        TMEM_LD32(taddr + half * N + p * MMA_TOK, db);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (half == 1 && p == P - 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // the partial is in registers
 #pragma unroll
-                        for (int i = 0; i < MMA_TOK; i++) {
-                            const float sc = pw * s_cs[b][kb][i];
-                            if (half) acc1[i] = fmaf(__uint_as_float(d[i]), sc, acc1[i]); else acc0[i] = fmaf(__uint_as_float(d[i]), sc, acc0[i]);
-                        }
-                        pw *= 0.0625f;
+                        for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));
+                    }
+                    if (half == 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // the partial is in registers
+#pragma unroll
+                    for (int i = 0; i < MMA_TOK; i++) {
+                        const float sc = s_sc[b][half][kb][i];
+                        if (half) acc1[i] = fmaf(__uint_as_float(da[i]), sc, acc1[i]); else acc0[i] = fmaf(__uint_as_float(da[i]), sc, acc0[i]);
                     }
                 }
             }

@@ -84,6 +84,10 @@ cudaError_t launch_gemm_rows(const GemvArgs &a, uint32_t *grid_x, uint32_t *mt, 
 cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s);
 cudaError_t launch_plan(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
                         const OmegaGpuMoePlanOut &o, cudaStream_t s);
+// routing plans of several layers in one launch (one CTA per layer); element strides between layers
+struct PlanBatch { uint32_t *counts, *starts, *xmap, *ymap, *pos, *header; uint4 *tiles; size_t map_stride, tile_stride; };
+cudaError_t launch_plan_batch(uint32_t layers, uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
+                              const PlanBatch &b, cudaStream_t s);
 cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s);
 cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out_f32, uint16_t *out_bf16, cudaStream_t s);
 // quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
@@ -106,6 +110,13 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
 // expert side only (expert-parallel receive path): `rows` candidate rows, ids[row] = local expert or 0xFFFFFFFF,
 // x row r at x + r * x_stride_bytes (bf16); writes dn[row][hidden] f32 for the present rows
 bool layer_forward_routed(OmegaGpuMoeLayer *L, uint32_t rows, const uint32_t *ids, const void *x, size_t x_stride_bytes, float *dn, cudaStream_t s);
+// what the stack needs from a layer to drive the tensor-core kernels itself
+struct LayerView {
+    uint32_t engine, topk, experts, hidden, inter, x_pieces, act_pieces, tile_rows, max_tokens, row_cap, norm_topk;
+    const float *gu_scale, *dn_scale; const void *tm_gu, *tm_dn, *tm_qa;
+    uint8_t *qa; float *sa, *dn;
+};
+void layer_view(OmegaGpuMoeLayer *L, LayerView *v);
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src);
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens);
 float *layer_out32(OmegaGpuMoeLayer *L);

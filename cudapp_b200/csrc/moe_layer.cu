@@ -184,6 +184,13 @@ bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src) {
     return layer_build_maps(dst);
 }
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens) { *experts = L->experts; *hidden = L->hidden; *max_tokens = L->cfg.max_tokens; }
+void layer_view(OmegaGpuMoeLayer *L, LayerView *v) {
+    v->engine = L->cfg.engine; v->topk = L->cfg.topk; v->experts = L->experts; v->hidden = L->hidden; v->inter = L->inter;
+    v->x_pieces = L->cfg.x_pieces; v->act_pieces = L->cfg.act_pieces; v->tile_rows = L->tile_rows; v->max_tokens = L->ws->max_tokens;
+    v->row_cap = L->ws->max_tokens * L->ws->topk + 8; v->norm_topk = L->cfg.norm_topk;
+    v->gu_scale = L->gu->s; v->dn_scale = L->dn->s; v->tm_gu = L->tm_gu; v->tm_dn = L->tm_dn; v->tm_qa = L->tm_qa;
+    v->qa = L->ws->qa; v->sa = L->ws->sa; v->dn = L->ws->dn;
+}
 float *layer_out32(OmegaGpuMoeLayer *L) { return L->ws->out32; }
 uint16_t *layer_stage_x(OmegaGpuMoeLayer *L) { return L->ws->x; }
 

@@ -80,8 +80,9 @@ __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t *buf, u
 }
 
 // dynamic shared: counts[E] | starts[E] | run[E] | scan buf[96] | wcnt u16 [32][E]
-__global__ void __launch_bounds__(1024) plan_kernel(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
-                                                    const uint32_t *__restrict__ ids, const OmegaGpuMoePlanOut o) {
+// pos (optional): inverse of the Y map, pos[token * slots + slot] = sorted row of that pick
+__device__ __forceinline__ void plan_body(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
+                                          const uint32_t *__restrict__ ids, const OmegaGpuMoePlanOut &o, uint32_t *__restrict__ pos) {
     extern __shared__ uint32_t smem[];
     uint32_t *counts = smem, *starts = smem + experts, *run = smem + 2 * experts, *sbuf = smem + 3 * experts;
     uint16_t *wcnt = reinterpret_cast<uint16_t *>(sbuf + 96);
@@ -161,11 +162,37 @@ __global__ void __launch_bounds__(1024) plan_kernel(uint32_t tokens, uint32_t sl
             const uint32_t p = starts[e] + run[e] + wcnt[warp * experts + e] + rank_w;
             const uint32_t t = i / slots, s = i - t * slots;
             xmap[p] = t; ymap[p] = t * ystride + s;
+            if (pos) pos[i] = p;
         }
         __syncthreads();
         for (uint32_t ee = tid; ee < experts; ee += 1024) run[ee] += counts[ee];
         __syncthreads();
     }
+}
+
+__global__ void __launch_bounds__(1024) plan_kernel(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
+                                                    const uint32_t *__restrict__ ids, const OmegaGpuMoePlanOut o) {
+    plan_body(tokens, slots, experts, ystride, tile_rows, ids, o, nullptr);
+}
+// one CTA per layer: layer l's picks at ids + l * tokens * slots, its outputs at the PlanBatch strides
+__global__ void __launch_bounds__(1024) plan_batch_kernel(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
+                                                          const uint32_t *__restrict__ ids, const PlanBatch b) {
+    const uint32_t l = blockIdx.x;
+    OmegaGpuMoePlanOut o = {};
+    o.counts_va = (uint64_t)(uintptr_t)(b.counts + (size_t)l * experts); o.starts_va = (uint64_t)(uintptr_t)(b.starts + (size_t)l * experts);
+    o.xmap_va = (uint64_t)(uintptr_t)(b.xmap + (size_t)l * b.map_stride); o.ymap_va = (uint64_t)(uintptr_t)(b.ymap + (size_t)l * b.map_stride);
+    o.tiles_va = (uint64_t)(uintptr_t)(b.tiles + (size_t)l * b.tile_stride); o.header_va = (uint64_t)(uintptr_t)(b.header + (size_t)l * 8);
+    plan_body(tokens, slots, experts, ystride, tile_rows, ids + (size_t)l * tokens * slots, o, b.pos + (size_t)l * b.map_stride);
+}
+cudaError_t launch_plan_batch(uint32_t layers, uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
+                              const PlanBatch &b, cudaStream_t s) {
+    const size_t smem = (size_t)experts * 12 + 96 * 4 + (size_t)32 * experts * 2;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(plan_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    plan_batch_kernel<<<layers, 1024, smem, s>>>(tokens, slots, experts, ystride, tile_rows, ids, b);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_plan(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,

@@ -39,6 +39,91 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(uint32_t hidden, flo
     }
 }
 
+
+// Fused step between two layers on the tensor-core engine, one CTA per token:
+//   m = sum over slots, in slot order, of w[t][s] * dn[t*K+s] (multiply then add, never fused: the reference's combine,
+//   src/omega_blackwell_codegen_dec.c:226-255); h = (x16 ? f32(x16) : h) + m; then, when a next layer follows,
+//   xn = bf16(RMSNorm(h)) is cut into e4m3 pieces per 128 columns (the activation quantiser of moe_glue.cu) and
+//   written straight to the sorted rows the NEXT layer's plan assigns to this token's K picks (pos[t*K+s]).
+// Same arithmetic, value for value, as combine_kernel -> residual_norm_kernel -> act_quant_kernel.
+__global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidden, uint32_t topk, float eps, const uint16_t *__restrict__ x16,
+                                                                   const float *__restrict__ w, const float *__restrict__ dn, float *__restrict__ h,
+                                                                   const uint32_t *__restrict__ pos, uint32_t pieces, size_t piece_stride, uint8_t *__restrict__ q,
+                                                                   float *__restrict__ sx, uint16_t *__restrict__ h16) {
+    __shared__ double red[8];
+    __shared__ float s_scale;
+    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
+    double sq = 0.0;
+    for (uint32_t c = tid * 4; c < hidden; c += 1024) {
+        const size_t i = (size_t)t * hidden + c;
+        float4 v;
+        if (x16) { const uint2 u = *reinterpret_cast<const uint2 *>(x16 + i); v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u)); }
+        else v = *reinterpret_cast<const float4 *>(h + i);
+        if (dn) {
+            float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s = 0; s < topk; s++) {
+                const float ws = __ldg(w + (size_t)t * topk + s);
+                const float4 d = __ldg(reinterpret_cast<const float4 *>(dn + ((size_t)t * topk + s) * hidden + c));
+                const float4 p = make_float4(__fmul_rn(ws, d.x), __fmul_rn(ws, d.y), __fmul_rn(ws, d.z), __fmul_rn(ws, d.w));
+                m = s == 0 ? p : make_float4(__fadd_rn(m.x, p.x), __fadd_rn(m.y, p.y), __fadd_rn(m.z, p.z), __fadd_rn(m.w, p.w));
+            }
+            v = make_float4(__fadd_rn(v.x, m.x), __fadd_rn(v.y, m.y), __fadd_rn(v.z, m.z), __fadd_rn(v.w, m.w));
+        }
+        *reinterpret_cast<float4 *>(h + i) = v;
+        if (h16) {
+            auto rne = [](float f) -> uint32_t { const uint32_t b = __float_as_uint(f); return ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16); };
+            uint2 pk; pk.x = rne(v.x) | (rne(v.y) << 16); pk.y = rne(v.z) | (rne(v.w) << 16);
+            *reinterpret_cast<uint2 *>(h16 + i) = pk;
+        }
+        sq += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+    }
+    if (!q) return;
+    for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0) red[tid >> 5] = sq;
+    __syncthreads();
+    if (tid == 0) { double acc = 0; for (int i = 0; i < 8; i++) acc += red[i]; s_scale = (float)(1.0 / sqrt(acc / (double)hidden + (double)eps)); }
+    __syncthreads();
+    const float sc = s_scale;
+    // one warp per 128-column block, lane = 4 columns (the quantiser's own mapping)
+    for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
+        const uint32_t c = kb * 128u + lane * 4u;
+        const float4 hv = *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);   // written by this CTA above
+        float v[4] = {hv.x * sc, hv.y * sc, hv.z * sc, hv.w * sc};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {   // xn is a bf16 tensor: round first, then quantise the rounded value
+            const uint32_t b = __float_as_uint(v[i]);
+            const uint32_t r = ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
+            v[i] = __uint_as_float(r << 16);
+        }
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        amax = fmaxf(amax, 7.888609052210118e-31f);
+        const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, cc = (M + 0x1fffffu) >> 23;
+        const float qs = __uint_as_float((E + cc - 8u) << 23);
+        float res[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], qs);
+        uint32_t codes[4];
+        for (uint32_t p = 0; p < pieces; p++) {
+            uint16_t lo, hi;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(res[1]), "f"(res[0]));
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(res[3]), "f"(res[2]));
+            codes[p] = (uint32_t)lo | ((uint32_t)hi << 16);
+            uint32_t l2, h2; float d[4];
+            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.rn.f16x2.e4m3x2 %0, a; cvt.rn.f16x2.e4m3x2 %1, b; }" : "=r"(l2), "=r"(h2) : "r"(codes[p]));
+            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[0]), "=f"(d[1]) : "r"(l2));
+            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[2]), "=f"(d[3]) : "r"(h2));
+#pragma unroll
+            for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
+        }
+        for (uint32_t s = 0; s < topk; s++) {
+            const uint32_t row = pos[(size_t)t * topk + s];
+            for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)row * hidden + c) = codes[p];
+            if (lane == 0) sx[(size_t)row * kb_total + kb] = qs;
+        }
+    }
+}
+
 }  // namespace b200
 using namespace b200;
 
@@ -50,12 +135,46 @@ struct OmegaGpuMoeStack {
     cudaGraphExec_t graph; uint32_t graph_tokens; cudaStream_t graph_stream;
     uint64_t g_logits, g_x, g_out32, g_out16;         // addresses the captured graph was built for
     uint32_t launches;
+    // fused path (every layer on the tensor-core engine): routing of all layers up front, three launches per layer
+    bool fused;
+    uint32_t topk, row_cap, x_pieces, tile_rows;
+    uint32_t *ids_all; float *wts_all; PlanBatch pb; size_t map_stride, tile_stride;
+    uint8_t *qx; float *sx; char *fused_base;
+    alignas(128) unsigned char tm_qx[128];
 };
 
 namespace b200 {
 static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s) {
     const uint32_t H = S->hidden, E = S->experts, Ln = (uint32_t)S->layers.size();
     uint32_t n = 0;
+    if (S->fused) {
+        const uint32_t K = S->topk, Px = S->x_pieces;
+        LayerView v0; layer_view(S->layers[0], &v0);
+        if (!cuda_ok(launch_topk(Ln * tokens, E, K, (int)v0.norm_topk, logits, S->ids_all, S->wts_all, s), "topk launch")) return false; n++;
+        if (!cuda_ok(launch_plan_batch(Ln, tokens, K, E, K, S->tile_rows, S->ids_all, S->pb, s), "plan launch")) return false; n++;
+        const size_t pstride = (size_t)S->row_cap * H;
+        combine_norm_scatter_kernel<<<tokens, 256, 0, s>>>(H, K, S->eps, x, nullptr, nullptr, S->h, S->pb.pos, Px, pstride, S->qx, S->sx, nullptr); n++;
+        for (uint32_t l = 0; l < Ln; l++) {
+            LayerView v; layer_view(S->layers[l], &v);
+            const uint32_t *hdr = S->pb.header + (size_t)l * 8;
+            MmaLaunch g = {};
+            g.wscale = v.gu_scale; g.ascale = S->sx; g.tiles = S->pb.tiles + (size_t)l * S->tile_stride; g.header = hdr; g.out = nullptr;
+            g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
+            g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
+            if (!cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s), "gate|up mma launch")) return false; n++;
+            MmaLaunch d = {};
+            d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pb.ymap + (size_t)l * S->map_stride; d.out = v.dn; d.q_rows = S->row_cap;
+            d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
+            if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s), "down mma launch")) return false; n++;
+            const bool last = l + 1 == Ln;
+            combine_norm_scatter_kernel<<<tokens, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_all + (size_t)l * tokens * K, v.dn, S->h,
+                                                              last ? nullptr : S->pb.pos + (size_t)(l + 1) * S->map_stride, Px, pstride, last ? nullptr : S->qx, S->sx,
+                                                              last ? out16 : nullptr); n++;
+        }
+        if (out32 && !cuda_ok(cudaMemcpyAsync(out32, S->h, (size_t)tokens * H * 4, cudaMemcpyDeviceToDevice, s), "copy h")) return false;
+        S->launches = n;
+        return cuda_ok(cudaGetLastError(), "stack launch");
+    }
     residual_norm_kernel<<<tokens, 256, 0, s>>>(H, S->eps, x, nullptr, S->h, S->xn, nullptr); n++;
     for (uint32_t l = 0; l < Ln; l++) {
         OmegaGpuMoeLayer *L = S->layers[l];
@@ -120,6 +239,35 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
     char *b = nullptr;
     if (!cuda_ok(cudaMalloc(&b, bytes), "cudaMalloc(stack)")) { delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
     S->h = (float *)b; S->xn = (uint16_t *)(b + T * H * 4); S->x = S->xn + T * H; S->out16 = S->x + T * H; S->logits = S->out16 + T * H;
+    // fused path when every layer runs the tensor-core engine with the same piece counts
+    LayerView v0; layer_view(layer[0], &v0);
+    S->fused = v0.engine == OMEGA_GPU_MOE_ENGINE_MMA && H % 128 == 0;
+    for (uint32_t i = 0; i < layers && S->fused; i++) {
+        LayerView v; layer_view(layer[i], &v);
+        S->fused = v.engine == OMEGA_GPU_MOE_ENGINE_MMA && v.x_pieces == v0.x_pieces && v.topk == v0.topk && v.tile_rows == v0.tile_rows && v.norm_topk == v0.norm_topk;
+    }
+    S->fused_base = nullptr;
+    if (S->fused) {
+        const size_t K = v0.topk, R = T * K, Rp = v0.row_cap, E = S->experts, Ln = layers;
+        S->topk = v0.topk; S->row_cap = v0.row_cap; S->x_pieces = v0.x_pieces; S->tile_rows = v0.tile_rows;
+        S->map_stride = (R + 8 + 63) & ~(size_t)63; S->tile_stride = (R / 8 + E + 8 + 15) & ~(size_t)15;
+        size_t off = 0;
+        auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+        const size_t o_ids = take(Ln * R * 4), o_w = take(Ln * R * 4), o_c = take(Ln * E * 4), o_s = take(Ln * E * 4), o_x = take(Ln * S->map_stride * 4),
+                     o_y = take(Ln * S->map_stride * 4), o_p = take(Ln * S->map_stride * 4), o_h = take(Ln * 32), o_t = take(Ln * S->tile_stride * 16),
+                     o_q = take((size_t)v0.x_pieces * Rp * H), o_sx = take(Rp * (H / 128) * 4);
+        bool ok = cuda_ok(cudaMalloc(&S->fused_base, off), "cudaMalloc(stack routing)") && cuda_ok(cudaMemset(S->fused_base, 0, off), "memset");
+        if (ok) {
+            char *f = S->fused_base;
+            S->ids_all = (uint32_t *)(f + o_ids); S->wts_all = (float *)(f + o_w);
+            S->pb.counts = (uint32_t *)(f + o_c); S->pb.starts = (uint32_t *)(f + o_s); S->pb.xmap = (uint32_t *)(f + o_x); S->pb.ymap = (uint32_t *)(f + o_y);
+            S->pb.pos = (uint32_t *)(f + o_p); S->pb.header = (uint32_t *)(f + o_h); S->pb.tiles = (uint4 *)(f + o_t);
+            S->pb.map_stride = S->map_stride; S->pb.tile_stride = S->tile_stride;
+            S->qx = (uint8_t *)(f + o_q); S->sx = (float *)(f + o_sx);
+            ok = make_tmap_u8(S->tm_qx, S->qx, (uint64_t)v0.x_pieces * Rp, H, 32);
+        }
+        if (!ok) { if (S->fused_base) cudaFree(S->fused_base); cudaFree(S->h); delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
+    }
     *out = S;
     return OMEGA_GPU_FP8_OK;
 }
@@ -129,6 +277,7 @@ void omega_gpu_moe_stack_free(OmegaGpuMoeStack *S) {
     Lock l;
     if (S->graph) cudaGraphExecDestroy(S->graph);
     if (S->h) cudaFree(S->h);
+    if (S->fused_base) cudaFree(S->fused_base);
     delete S;
 }
 
@@ -155,7 +304,13 @@ int omega_gpu_moe_stack_bf16(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_
               stack_run(S, tokens, S->logits, S->x, nullptr, S->out16, s);
     if (ok && out_bf16) ok = cuda_ok(cudaMemcpyAsync(out_bf16, S->out16, xb, cudaMemcpyDeviceToHost, s), "copy out");
     if (ok && out_f32) ok = cuda_ok(cudaMemcpyAsync(out_f32, S->h, xb * 2, cudaMemcpyDeviceToHost, s), "copy out");
+    std::vector<uint32_t> hdr;
+    if (ok && S->fused) { hdr.resize(S->layers.size() * 8); ok = cuda_ok(cudaMemcpyAsync(hdr.data(), S->pb.header, hdr.size() * 4, cudaMemcpyDeviceToHost, s), "copy status"); }
     ok = ok && cuda_ok(cudaStreamSynchronize(s), "moe stack");
+    for (size_t l = 0; ok && l * 8 < hdr.size(); l++) {
+        if (hdr[l * 8 + 3]) { set_error("moe stack: routing plan of layer %zu refused (status %u)", l, hdr[l * 8 + 3]); return OMEGA_GPU_FP8_BAD_ARGS; }
+        if (hdr[l * 8 + 4]) { set_error("moe stack: a bounded wait inside the tensor-core kernel ran out (layer %zu, code %u)", l, hdr[l * 8 + 4]); st().latched = true; return OMEGA_GPU_FP8_CHIP_FAIL; }
+    }
     return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 

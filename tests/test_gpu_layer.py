@@ -83,7 +83,7 @@ def test_stack_small(engine):
     assert np.array_equal(o16, orc.bf16_bits(o32))
     rc, o16b, o32b = api.moe_stack_bf16(stack, logits, xb)          # graph replay: identical bits
     assert rc == 0 and np.array_equal(o32, o32b)
-    assert api.lib.omega_gpu_moe_stack_launches(stack) > Ln * 4
+    assert api.lib.omega_gpu_moe_stack_launches(stack) >= Ln * 3
     api.lib.omega_gpu_moe_stack_free(stack)
     for m in ms:
         free_layer(m)
