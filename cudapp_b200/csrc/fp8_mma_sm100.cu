@@ -31,7 +31,8 @@ constexpr int MMA_TOK = 32;                     // routed rows per tile; accumul
 constexpr uint32_t A_TILE = 128 * 128, B_PIECE = MMA_TOK * 128;
 constexpr int KB_MAX = 32;                      // k <= 4096 on this engine
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int MMA_THREADS = 32 * 11;            // TMA, MMA, scale loader, 2 x 4 epilogue warps
+constexpr int MMA_THREADS = 32 * 11;
+constexpr uint32_t Q_STAGE_BYTES = 2 * 4 * MMA_TOK * 128;   // per epilogue group: up to 4 pieces x 32 rows x 128 bytes of output codes            // TMA, MMA, scale loader, 2 x 4 epilogue warps
 
 struct MmaArgs {
     const float *wscale, *ascale;
@@ -85,7 +86,9 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
                    "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) \
                  : "r"(taddr))
 
-__device__ __forceinline__ float silu_mul_dev(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
+// SiLU gate with the fast exponential and division (the reference kernel itself uses EX2 / RCP approximations here,
+// src/omega_blackwell_codegen_dec.c:291-324)
+__device__ __forceinline__ float silu_mul_dev(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // activation-piece helpers (same arithmetic as act_quant_kernel in moe_glue.cu)
 __device__ __forceinline__ float pq_scale_mma(float amax) {
@@ -108,7 +111,7 @@ __device__ __forceinline__ float2 dec2(uint32_t v) {
 template <int P>
 __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
     constexpr int N = MMA_TOK * P;                                   // accumulator columns per weight tile
-    constexpr int STAGES = P <= 2 ? 5 : 4;
+    constexpr int STAGES = P <= 3 ? 4 : 3;
     constexpr uint32_t STAGE_BYTES = 2 * A_TILE + P * B_PIECE;
     constexpr uint32_t TMEM_COLS = 4 * N <= 128 ? 128 : 4 * N <= 256 ? 256 : 512;   // 2 buffers x 2 accumulators x N
     constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // f8f6f4, D f32, A = B = e4m3 K-major, M 128
@@ -117,6 +120,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     __shared__ uint32_t s_tmem, s_abort;
     __shared__ float s_sc[2][2][KB_MAX][MMA_TOK]; // [scale buffer][weight tile][k block][row] = weight scale x row scale
     __shared__ float s_red[2][4][MMA_TOK];        // [epilogue group][warp][row]: amax exchange
+    __shared__ uint32_t s_ymap[2][MMA_TOK];       // [scale buffer][row]: destination rows (mode 1)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
     const uint32_t bar0 = smem_u32(s_bar);
@@ -200,6 +204,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
             if (!(ok = mbar_wait(scempty_bar(b), ((n >> 1) & 1u) ^ 1u, abort_flag, a.err, 7))) break;
+            if (a.mode == 1) s_ymap[b][lane] = lane < t.z ? a.ymap[t.y + lane] : 0u;
             const float *w0 = a.wscale + ((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB, *w1 = a.wscale + ((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB;
             for (uint32_t kb = 0; kb < KB; kb++) {
                 const float cs = lane < t.z ? a.ascale[(size_t)(t.y + lane) * KB + kb] : 0.0f;
@@ -256,47 +261,61 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             }
             if (!ok) break;
             mbar_arrive(turn_bar(g ^ 1u));   // the other group may start on the next unit's partials
-            mbar_arrive(scempty_bar(b));   // this unit's scales may be overwritten
             if (a.mode == 0) {
-                // ---- SiLU gate, then the gated activations leave as e4m3 pieces: amax over the unit's 128 features per row
+                // ---- SiLU gate, then the gated activations leave as e4m3 pieces with one scale per (row, this unit's 128 features)
+                float m[MMA_TOK];
 #pragma unroll
-                for (int i = 0; i < MMA_TOK; i++) acc0[i] = silu_mul_dev(acc0[i], acc1[i]);
+                for (int i = 0; i < MMA_TOK; i++) { acc0[i] = silu_mul_dev(acc0[i], acc1[i]); m[i] = fabsf(acc0[i]); }
+                // per-row maximum over the warp's 32 features: butterfly that halves the rows kept per lane (31 shuffles, lane l ends with row l)
 #pragma unroll
-                for (int i = 0; i < MMA_TOK; i++) {
-                    float m = fabsf(acc0[i]);
+                for (int o = 16; o >= 1; o >>= 1) {
+                    const bool up = (lane & (uint32_t)o) != 0;
 #pragma unroll
-                    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                    if (lane == (uint32_t)i) s_red[g][q][i] = m;
+                    for (int jj = 0; jj < o; jj++) {
+                        const float keep = up ? m[jj + o] : m[jj], send = up ? m[jj] : m[jj + o];
+                        m[jj] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, o));
+                    }
                 }
+                s_red[g][q][lane] = m[0];
                 mbar_arrive(group_bar(g));
                 if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 5))) break;
+                // lane = row: maximum over the four warps, power-of-two scale and its exact reciprocal
+                const float sc = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][lane], s_red[g][1][lane]), fmaxf(s_red[g][2][lane], s_red[g][3][lane])));
+                const float inv = __uint_as_float((254u - (__float_as_uint(sc) >> 23)) << 23);
+                if (q == 0 && lane < cnt) a.s_out[(size_t)(t.y + lane) * (a.inter / 128u) + j] = sc;
+                uint8_t *sq = dyn_smem + (smem_base - smem_u32(dyn_smem)) + STAGES * STAGE_BYTES + g * (Q_STAGE_BYTES / 2);   // [piece][row][128]
 #pragma unroll
                 for (int i = 0; i < MMA_TOK; i += 2) {
-                    if ((uint32_t)i >= cnt) break;
-                    const float s0 = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][i], s_red[g][1][i]), fmaxf(s_red[g][2][i], s_red[g][3][i])));
-                    const float s1 = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][i + 1], s_red[g][1][i + 1]), fmaxf(s_red[g][2][i + 1], s_red[g][3][i + 1])));
-                    if (a.out) { a.out[(size_t)(t.y + i) * a.out_stride + j * 128u + row] = acc0[i]; if ((uint32_t)i + 1 < cnt) a.out[(size_t)(t.y + i + 1) * a.out_stride + j * 128u + row] = acc0[i + 1]; }
-                    float ra = __fdiv_rn(acc0[i], s0), rb = __fdiv_rn(acc0[i + 1], s1);
+                    float ra = acc0[i] * __shfl_sync(0xffffffffu, inv, i), rb = acc0[i + 1] * __shfl_sync(0xffffffffu, inv, i + 1);
                     for (uint32_t p = 0; p < a.q_pieces; p++) {
                         const uint32_t code = enc2(ra, rb);
-                        uint8_t *qd = a.q_out + ((size_t)p * a.q_rows + t.y + i) * a.inter + j * 128u + row;
-                        qd[0] = (uint8_t)(code & 0xffu);
-                        if ((uint32_t)i + 1 < cnt) qd[a.inter] = (uint8_t)(code >> 8);
+                        sq[(p * MMA_TOK + i) * 128u + row] = (uint8_t)(code & 0xffu);
+                        sq[(p * MMA_TOK + i + 1) * 128u + row] = (uint8_t)(code >> 8);
                         const float2 dv = dec2(code);
                         ra = (ra - dv.x) * 16.0f; rb = (rb - dv.y) * 16.0f;
                     }
-                    if (row == 0) { a.s_out[(size_t)(t.y + i) * (a.inter / 128u) + j] = s0; if ((uint32_t)i + 1 < cnt) a.s_out[(size_t)(t.y + i + 1) * (a.inter / 128u) + j] = s1; }
                 }
-                mbar_arrive(group_bar(g));   // s_red is free again
+                mbar_arrive(group_bar(g));
                 if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 6))) break;
+                // copy out: every (piece, row) is 128 consecutive bytes in memory; 16 bytes per thread per step
+                const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                for (uint32_t c = et; c < a.q_pieces * MMA_TOK * 8u; c += 128u) {
+                    const uint32_t r = c >> 3, p = r / MMA_TOK, i = r - p * MMA_TOK;
+                    if (i < cnt) *reinterpret_cast<uint4 *>(a.q_out + ((size_t)p * a.q_rows + t.y + i) * a.inter + j * 128u + (c & 7u) * 16u) = *reinterpret_cast<const uint4 *>(sq + (size_t)c * 16u);
+                }
+                if (a.out) {
+#pragma unroll
+                    for (int i = 0; i < MMA_TOK; i++) if ((uint32_t)i < cnt) a.out[(size_t)(t.y + i) * a.out_stride + j * 128u + row] = acc0[i];
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < MMA_TOK; i++)
                     if ((uint32_t)i < cnt) {
-                        float *o = a.out + (size_t)a.ymap[t.y + i] * a.out_stride;
+                        float *o = a.out + (size_t)s_ymap[b][i] * a.out_stride;
                         o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
                     }
             }
+            mbar_arrive(scempty_bar(b));   // this unit's scales and destination rows may be overwritten
         }
     }
     // ---------------------------------------------------------------- teardown
@@ -341,7 +360,7 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
     const CUtensorMap *w = (const CUtensorMap *)tm_w, *q = (const CUtensorMap *)tm_q;
 #define LAUNCH(PV)                                                                                                                      \
     do {                                                                                                                                \
-        const size_t smem = (size_t)((PV) <= 2 ? 5 : 4) * (2 * A_TILE + (PV) * B_PIECE) + 1024;                                        \
+        const size_t smem = (size_t)((PV) <= 3 ? 4 : 3) * (2 * A_TILE + (PV) * B_PIECE) + Q_STAGE_BYTES + 1024;                                        \
         static bool attr = false;                                                                                                       \
         if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
         fp8_mma_grouped_kernel<PV><<<sms, MMA_THREADS, smem, s>>>(*w, *q, a);                                                          \
