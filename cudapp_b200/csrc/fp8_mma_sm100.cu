@@ -67,6 +67,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// programmatic dependent launch: wait = the grids this one depends on have completed and their writes are visible;
+// launch_dependents = the next grid in the stream may start occupying free SMs (it blocks in its own wait)
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
@@ -156,23 +160,39 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
+            // The weights do not depend on the previous kernel, the activation pieces do: fill the pipeline with weight tiles
+            // first, then wait for the producer grid, then add the activation tiles of those same stages.
             uint32_t it = 0; bool ok = true;
-            for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
-                const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs;
-                const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
-                const int wy0 = (int)(t.x * a.n + r0), wy1 = (int)(t.x * a.n + r1);
-                for (uint32_t kb = 0; kb < KB; kb++, it++) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
-                    const uint32_t dst = smem_base + s * STAGE_BYTES;
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
-                    tma_load_2d(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0);
-                    tma_load_2d(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1);
+            for (int phase = 0; phase < 3 && ok; phase++) {
+                if (phase == 1) { griddep_wait(); griddep_launch(); }
+                it = phase == 2 ? STAGES : 0;
+                uint32_t seen = 0;
+                for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
+                    if (phase < 2 && seen >= STAGES) break;
+                    if (phase == 2 && seen + KB <= STAGES) { seen += KB; continue; }
+                    const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs;
+                    const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+                    const int wy0 = (int)(t.x * a.n + r0), wy1 = (int)(t.x * a.n + r1);
+                    for (uint32_t kb = 0; kb < KB; kb++, seen++) {
+                        if (phase < 2 && seen >= STAGES) break;
+                        if (phase == 2 && seen < STAGES) continue;
+                        const uint32_t g_it = seen, s = g_it % STAGES, ph = (g_it / STAGES) & 1u;
+                        const uint32_t dst = smem_base + s * STAGE_BYTES;
+                        if (phase == 2 && !(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
+                        if (phase != 1) {
+                            mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                            tma_load_2d(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0);
+                            tma_load_2d(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1);
+                        }
+                        if (phase != 0) {
 #pragma unroll
-                    for (int p = 0; p < P; p++)   // piece p of the tile's rows: 32 rows x 128 bytes
-                        tma_load_2d(dst + 2 * A_TILE + p * B_PIECE, &tm_q, full_bar(s), (int)(kb * 128u), (int)(p * a.q_rows + t.y));
+                            for (int p = 0; p < P; p++)   // piece p of the tile's rows: 32 rows x 128 bytes
+                                tma_load_2d(dst + 2 * A_TILE + p * B_PIECE, &tm_q, full_bar(s), (int)(kb * 128u), (int)(p * a.q_rows + t.y));
+                        }
+                    }
                 }
             }
+            (void)it;
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -200,6 +220,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     } else if (warp == 2) {
         // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
         uint32_t n = 0; bool ok = true;
+        griddep_wait();   // the row scales below are the previous kernel's output
         for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
@@ -351,7 +372,7 @@ bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols,
 uint32_t mma_tile_rows(uint32_t) { return MMA_TOK; }
 bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode) { return k % 128u == 0 && k <= 128u * KB_MAX && n % 128u == 0 && (mode == 0 || (n / 128u) % 2u == 0); }
 
-cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s) {
+cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s, bool pdl) {
     MmaArgs a = {};
     a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
     a.q_out = m.q_out; a.s_out = m.s_out; a.q_rows = m.q_rows; a.q_pieces = m.q_pieces;
@@ -363,7 +384,12 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
         const size_t smem = (size_t)((PV) <= 3 ? 4 : 3) * (2 * A_TILE + (PV) * B_PIECE) + Q_STAGE_BYTES + 1024;                                        \
         static bool attr = false;                                                                                                       \
         if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
-        fp8_mma_grouped_kernel<PV><<<sms, MMA_THREADS, smem, s>>>(*w, *q, a);                                                          \
+        cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];                                                                         \
+        cfg.gridDim = dim3(sms); cfg.blockDim = dim3(MMA_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;           \
+        cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;                                                                                     \
+        cudaError_t le = cudaLaunchKernelEx(&cfg, fp8_mma_grouped_kernel<PV>, *w, *q, a);                                              \
+        if (le != cudaSuccess) return le;                                                                                               \
     } while (0)
     switch (pieces) {
     case 1: LAUNCH(1); break;

@@ -105,7 +105,7 @@ struct MmaLaunch {
 bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 uint32_t mma_tile_rows(uint32_t pieces);
 bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
-cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s);
+cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s, bool pdl = false);
 bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s);
 // expert side only (expert-parallel receive path): `rows` candidate rows, ids[row] = local expert or 0xFFFFFFFF,
 // x row r at x + r * x_stride_bytes (bf16); writes dn[row][hidden] f32 for the present rows

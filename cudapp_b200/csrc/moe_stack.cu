@@ -53,6 +53,9 @@ __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidd
     __shared__ double red[8];
     __shared__ float s_scale;
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
+    // launched as a programmatic dependent: everything read below is the previous kernel's output
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     double sq = 0.0;
     for (uint32_t c = tid * 4; c < hidden; c += 1024) {
         const size_t i = (size_t)t * hidden + c;
@@ -153,7 +156,14 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
         if (!cuda_ok(launch_topk(Ln * tokens, E, K, (int)v0.norm_topk, logits, S->ids_all, S->wts_all, s), "topk launch")) return false; n++;
         if (!cuda_ok(launch_plan_batch(Ln, tokens, K, E, K, S->tile_rows, S->ids_all, S->pb, s), "plan launch")) return false; n++;
         const size_t pstride = (size_t)S->row_cap * H;
-        combine_norm_scatter_kernel<<<tokens, 256, 0, s>>>(H, K, S->eps, x, nullptr, nullptr, S->h, S->pb.pos, Px, pstride, S->qx, S->sx, nullptr); n++;
+        auto launch_cns = [&](const uint16_t *x16, const float *w, const float *dn, const uint32_t *pos, uint8_t *q, uint16_t *h16) {
+            cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];
+            cfg.gridDim = dim3(tokens); cfg.blockDim = dim3(256); cfg.stream = s;
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at; cfg.numAttrs = 0;   // measured: launching this kernel (or the down GEMM) as a programmatic dependent is slower
+            return cudaLaunchKernelEx(&cfg, combine_norm_scatter_kernel, H, K, S->eps, x16, w, dn, S->h, pos, Px, pstride, q, S->sx, h16);
+        };
+        if (!cuda_ok(launch_cns(x, nullptr, nullptr, S->pb.pos, S->qx, nullptr), "norm launch")) return false; n++;
         for (uint32_t l = 0; l < Ln; l++) {
             LayerView v; layer_view(S->layers[l], &v);
             const uint32_t *hdr = S->pb.header + (size_t)l * 8;
@@ -161,15 +171,14 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
             g.wscale = v.gu_scale; g.ascale = S->sx; g.tiles = S->pb.tiles + (size_t)l * S->tile_stride; g.header = hdr; g.out = nullptr;
             g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
             g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
-            if (!cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s), "gate|up mma launch")) return false; n++;
+            if (!cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true /* weight tiles prefetched while the norm kernel runs */), "gate|up mma launch")) return false; n++;
             MmaLaunch d = {};
             d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pb.ymap + (size_t)l * S->map_stride; d.out = v.dn; d.q_rows = S->row_cap;
             d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
-            if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s), "down mma launch")) return false; n++;
+            if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch")) return false; n++;
             const bool last = l + 1 == Ln;
-            combine_norm_scatter_kernel<<<tokens, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_all + (size_t)l * tokens * K, v.dn, S->h,
-                                                              last ? nullptr : S->pb.pos + (size_t)(l + 1) * S->map_stride, Px, pstride, last ? nullptr : S->qx, S->sx,
-                                                              last ? out16 : nullptr); n++;
+            if (!cuda_ok(launch_cns(nullptr, S->wts_all + (size_t)l * tokens * K, v.dn, last ? nullptr : S->pb.pos + (size_t)(l + 1) * S->map_stride,
+                                    last ? nullptr : S->qx, last ? out16 : nullptr), "combine launch")) return false; n++;
         }
         if (out32 && !cuda_ok(cudaMemcpyAsync(out32, S->h, (size_t)tokens * H * 4, cudaMemcpyDeviceToDevice, s), "copy h")) return false;
         S->launches = n;
