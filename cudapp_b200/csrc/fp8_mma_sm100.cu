@@ -42,6 +42,12 @@ struct MmaArgs {
     uint8_t *q_out; float *s_out;    // mode 0: gated activations as e4m3 pieces [piece][q_rows][inter] + scales [row][inter/128]
     uint32_t n, k, pairs, mode, inter, out_stride, q_rows, q_pieces;
     uint32_t *err;
+    // expert parallelism (all null / 0 on one GPU)
+    const unsigned long long *gate;     // rows that peers have delivered into the input pieces; the kernel waits for header[0] of them
+    const uint64_t *out_peers;          // mode 1: base address of every rank's result buffer; row y belongs to rank y / rows_per_rank
+    const uint64_t *ret_counters;       // mode 1: address of every rank's "result slices delivered" counter
+    uint32_t rows_per_rank, ret_index;  // ret_index: which counter of the owner's counter block this launch advances
+    unsigned long long *reset;          // a counter of this rank that is no longer in use: cleared at kernel start
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -71,6 +77,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 // launch_dependents = the next grid in the stream may start occupying free SMs (it blocks in its own wait)
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// bounded wait until a counter that peers advance with system-scope atomics reaches `want`
+__device__ __forceinline__ bool gate_wait(const unsigned long long *gate, unsigned long long want, uint32_t *err, uint32_t code) {
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(gate) : "memory");
+        if (v >= want) { asm volatile("fence.proxy.async;" ::: "memory"); return true; }
+        __nanosleep(100);
+    }
+    atomicCAS(err, 0u, code);
+    return false;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
@@ -139,6 +156,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     volatile uint32_t *abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
+        if (a.reset && blockIdx.x == 0) { *a.reset = 0ull; __threadfence_system(); }
         s_abort = 0;
         for (uint32_t s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (uint32_t b = 0; b < 2; b++) {
@@ -164,7 +182,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             // first, then wait for the producer grid, then add the activation tiles of those same stages.
             uint32_t it = 0; bool ok = true;
             for (int phase = 0; phase < 3 && ok; phase++) {
-                if (phase == 1) { griddep_wait(); griddep_launch(); }
+                if (phase == 1) {
+                    griddep_wait(); griddep_launch();
+                    if (a.gate && !(ok = gate_wait(a.gate, a.header[0], a.err, 13))) { *abort_flag = 1; break; }
+                }
                 it = phase == 2 ? STAGES : 0;
                 uint32_t seen = 0;
                 for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
@@ -221,6 +242,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
         // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
         uint32_t n = 0; bool ok = true;
         griddep_wait();   // the row scales below are the previous kernel's output
+        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, a.header[0], a.err, 14)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
         for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
@@ -328,13 +350,28 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
 #pragma unroll
                     for (int i = 0; i < MMA_TOK; i++) if ((uint32_t)i < cnt) a.out[(size_t)(t.y + i) * a.out_stride + j * 128u + row] = acc0[i];
                 }
-            } else {
+            } else if (!a.out_peers) {
 #pragma unroll
                 for (int i = 0; i < MMA_TOK; i++)
                     if ((uint32_t)i < cnt) {
                         float *o = a.out + (size_t)s_ymap[b][i] * a.out_stride;
                         o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
                     }
+            } else {
+                // expert parallel: every result row goes straight into its owner's buffer (peer stores), then the owner's counter
+                // is advanced once per delivered 256-feature slice
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i++)
+                    if ((uint32_t)i < cnt) {
+                        const uint32_t y = s_ymap[b][i], owner = y / a.rows_per_rank;
+                        float *o = reinterpret_cast<float *>(a.out_peers[owner]) + (size_t)(y - owner * a.rows_per_rank) * a.out_stride;
+                        o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
+                    }
+                __threadfence_system();
+                mbar_arrive(group_bar(g));
+                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15))) break;
+                const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                if (et < cnt) atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[s_ymap[b][et] / a.rows_per_rank]) + a.ret_index, 1ull);
             }
             mbar_arrive(scempty_bar(b));   // this unit's scales and destination rows may be overwritten
         }
@@ -376,6 +413,7 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
     MmaArgs a = {};
     a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
     a.q_out = m.q_out; a.s_out = m.s_out; a.q_rows = m.q_rows; a.q_pieces = m.q_pieces;
+    a.gate = m.gate; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index; a.reset = m.reset;
     a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
     const int sms = st().sm_count ? st().sm_count : 148;
     const CUtensorMap *w = (const CUtensorMap *)tm_w, *q = (const CUtensorMap *)tm_q;

@@ -272,3 +272,310 @@ int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream) {
 }
 
 }  // extern "C"
+
+// =====================================================================================================================
+// Fused expert-parallel stack: three launches per layer and rank, as on one GPU.
+//
+// Every rank first gathers the router logits of all tokens (they are small) and computes the routing of every layer for
+// all tokens: the global plan tells a sender the sorted row each of its picks has on the rank that owns the expert
+// (global sorted row minus the start of that rank's first expert); the plan over the rank's own experts gives its
+// row tiles. Per layer a rank then runs
+//   combine+norm+quantise: its tokens' next-layer activation pieces are stored straight into the owning ranks' piece
+//       buffers (peer stores), one system-scope atomic per delivered row on the receiver's counter;
+//   gate|up GEMM: waits (bounded) until the counter shows every row of its plan, then runs as on one GPU;
+//   down GEMM: stores every result row straight into its token owner's buffer and advances the owner's counter;
+// and the next combine waits for its tokens' 8 x (hidden/256) result slices. Counters alternate by layer parity and
+// are cleared by the rank that owns them one kernel after their last use. No collective and no host round trip per layer.
+#include <vector>
+
+struct OmegaGpuMoeEpStack {
+    uint32_t world, rank, layers, topk, experts, experts_local, hidden, tokens, tokens_local, row_cap, x_pieces, tile_rows;
+    float eps;
+    std::vector<OmegaGpuMoeLayer *> local;
+    char *route;                         // routing scratch (ids, weights, two plan batches)
+    uint32_t *ids_g, *ids_l; float *wts_g;
+    b200::PlanBatch pg, pl; size_t map_stride, tile_stride;
+    uint8_t *comm; size_t comm_bytes, off_sx, off_dn, off_cnt;   // peers map this block: pieces | scales | results | counters
+    uint64_t *peer_tab;                  // device [4][world]: pieces, scales, results, counters of every rank
+    float *h; uint32_t *err;
+    void *opened[64]; int n_opened; int connected;
+    alignas(128) unsigned char tm_qx[128];
+    uint32_t launches;
+};
+
+namespace b200 {
+
+__global__ void ep_localise_kernel(size_t n, uint32_t e0, uint32_t e1, const uint32_t *__restrict__ ids, uint32_t *__restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { const uint32_t e = ids[i]; out[i] = (e >= e0 && e < e1) ? e - e0 : 0xffffffffu; }
+}
+
+// One CTA per local token. dn/w != null: wait until this rank's result buffer is complete, combine in slot order and add to h.
+// q_peers != null: quantise xn = bf16(RMSNorm(h)) into pieces and store them into the owners' piece buffers.
+__global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
+        uint32_t hidden, uint32_t topk, float eps, const uint16_t *__restrict__ x16, const float *__restrict__ w, const float *__restrict__ dn, float *__restrict__ h,
+        const unsigned long long *ret_gate, unsigned long long ret_want,
+        const uint32_t *__restrict__ ids_next, const uint32_t *__restrict__ pos_next, const uint32_t *__restrict__ starts_next, uint32_t experts_local,
+        uint32_t pieces, size_t piece_stride, const uint64_t *__restrict__ q_peers, const uint64_t *__restrict__ sx_peers, const uint64_t *__restrict__ cnt_peers,
+        uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err) {
+    __shared__ double red[8];
+    __shared__ float s_scale;
+    __shared__ uint32_t s_d[32], s_row[32], s_fail;
+    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
+    if (tid == 0) {
+        s_fail = 0;
+        if (dn && ret_gate) {
+            bool ok = false;
+            for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+                unsigned long long v;
+                asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ret_gate) : "memory");
+                ok = v >= ret_want;
+                if (!ok) __nanosleep(100);
+            }
+            if (!ok) { atomicCAS(err, 0u, 16u); s_fail = 1; }
+        }
+    }
+    if (q_peers && tid < topk) {
+        const size_t i = (size_t)t * topk + tid;        // ids_next / pos_next are already offset to this rank's first token
+        const uint32_t d = ids_next[i] / experts_local;
+        s_d[tid] = d; s_row[tid] = pos_next[i] - starts_next[d * experts_local];
+    }
+    __syncthreads();
+    if (s_fail) return;
+    double sq = 0.0;
+    for (uint32_t c = tid * 4; c < hidden; c += 1024) {
+        const size_t i = (size_t)t * hidden + c;
+        float4 v;
+        if (x16) { const uint2 u = *reinterpret_cast<const uint2 *>(x16 + i); v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u)); }
+        else v = *reinterpret_cast<const float4 *>(h + i);
+        if (dn) {
+            float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s = 0; s < topk; s++) {
+                const float ws = __ldg(w + (size_t)t * topk + s);
+                const float4 d = __ldcv(reinterpret_cast<const float4 *>(dn + ((size_t)t * topk + s) * hidden + c));   // written by peers: no stale cache line
+                const float4 p = make_float4(__fmul_rn(ws, d.x), __fmul_rn(ws, d.y), __fmul_rn(ws, d.z), __fmul_rn(ws, d.w));
+                m = s == 0 ? p : make_float4(__fadd_rn(m.x, p.x), __fadd_rn(m.y, p.y), __fadd_rn(m.z, p.z), __fadd_rn(m.w, p.w));
+            }
+            v = make_float4(__fadd_rn(v.x, m.x), __fadd_rn(v.y, m.y), __fadd_rn(v.z, m.z), __fadd_rn(v.w, m.w));
+        }
+        *reinterpret_cast<float4 *>(h + i) = v;
+        if (h16) {
+            auto rne = [](float f) -> uint32_t { const uint32_t b = __float_as_uint(f); return ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16); };
+            uint2 pk; pk.x = rne(v.x) | (rne(v.y) << 16); pk.y = rne(v.z) | (rne(v.w) << 16);
+            *reinterpret_cast<uint2 *>(h16 + i) = pk;
+        }
+        sq += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+    }
+    if (!q_peers) return;
+    for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0) red[tid >> 5] = sq;
+    __syncthreads();
+    if (tid == 0) { double acc = 0; for (int i = 0; i < 8; i++) acc += red[i]; s_scale = (float)(1.0 / sqrt(acc / (double)hidden + (double)eps)); }
+    __syncthreads();
+    const float sc = s_scale;
+    for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
+        const uint32_t c = kb * 128u + lane * 4u;
+        const float4 hv = *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);
+        float v[4] = {hv.x * sc, hv.y * sc, hv.z * sc, hv.w * sc};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t b = __float_as_uint(v[i]);
+            const uint32_t r = ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
+            v[i] = __uint_as_float(r << 16);
+        }
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        amax = fmaxf(amax, 7.888609052210118e-31f);
+        const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, cc = (M + 0x1fffffu) >> 23;
+        const float qs = __uint_as_float((E + cc - 8u) << 23);
+        float res[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], qs);
+        uint32_t codes[4];
+        for (uint32_t p = 0; p < pieces; p++) {
+            uint16_t lo, hi;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(res[1]), "f"(res[0]));
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(res[3]), "f"(res[2]));
+            codes[p] = (uint32_t)lo | ((uint32_t)hi << 16);
+            uint32_t l2, h2; float d[4];
+            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.rn.f16x2.e4m3x2 %0, a; cvt.rn.f16x2.e4m3x2 %1, b; }" : "=r"(l2), "=r"(h2) : "r"(codes[p]));
+            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[0]), "=f"(d[1]) : "r"(l2));
+            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[2]), "=f"(d[3]) : "r"(h2));
+#pragma unroll
+            for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
+        }
+        for (uint32_t s = 0; s < topk; s++) {
+            uint8_t *q = reinterpret_cast<uint8_t *>(q_peers[s_d[s]]);
+            for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)s_row[s] * hidden + c) = codes[p];
+            if (lane == 0) reinterpret_cast<float *>(sx_peers[s_d[s]])[(size_t)s_row[s] * kb_total + kb] = qs;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < topk) atomicAdd_system(reinterpret_cast<unsigned long long *>(cnt_peers[s_d[tid]]) + parity, 1ull);
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers, OmegaGpuMoeLayer *const *local, uint32_t experts, uint32_t tokens, float eps,
+                                 OmegaGpuMoeEpStack **out) {
+    if (out) *out = nullptr;
+    if (!out || !local || !layers || !world || world > 64 || rank >= world || !experts || experts % world || !tokens || tokens % world) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    LayerView v0; layer_view(local[0], &v0);
+    if (v0.engine != OMEGA_GPU_MOE_ENGINE_MMA || v0.experts != experts / world || v0.max_tokens < tokens || v0.topk > 32) { set_error("ep stack: local layers must run the tensor-core engine over experts/world experts with max_tokens >= tokens"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    OmegaGpuMoeEpStack *S = new OmegaGpuMoeEpStack();
+    S->world = world; S->rank = rank; S->layers = layers; S->topk = v0.topk; S->experts = experts; S->experts_local = experts / world; S->hidden = v0.hidden;
+    S->tokens = tokens; S->tokens_local = tokens / world; S->row_cap = v0.row_cap; S->x_pieces = v0.x_pieces; S->tile_rows = v0.tile_rows; S->eps = eps;
+    S->n_opened = 0; S->connected = 0; S->launches = 0; S->route = nullptr; S->comm = nullptr; S->peer_tab = nullptr; S->h = nullptr;
+    for (uint32_t i = 0; i < layers; i++) {
+        if (!local[i] || !layer_share_workspace(local[i], local[0])) { delete S; set_error("ep stack: layer %u does not match layer 0", i); return OMEGA_GPU_FP8_BAD_ARGS; }
+        S->local.push_back(local[i]);
+    }
+    const size_t K = S->topk, T = tokens, R = T * K, H = S->hidden, E = experts, Ln = layers, Rp = S->row_cap;
+    S->map_stride = (R + 8 + 63) & ~(size_t)63; S->tile_stride = (R / 8 + E + 8 + 15) & ~(size_t)15;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+    const size_t o_ig = take(Ln * R * 4), o_il = take(Ln * R * 4), o_w = take(Ln * R * 4);
+    size_t o_pb[2][7];
+    for (int b = 0; b < 2; b++) {
+        o_pb[b][0] = take(Ln * E * 4); o_pb[b][1] = take(Ln * E * 4); o_pb[b][2] = take(Ln * S->map_stride * 4); o_pb[b][3] = take(Ln * S->map_stride * 4);
+        o_pb[b][4] = take(Ln * S->map_stride * 4); o_pb[b][5] = take(Ln * 32); o_pb[b][6] = take(Ln * S->tile_stride * 16);
+    }
+    const size_t o_h = take((size_t)S->tokens_local * H * 4), o_err = take(64);
+    bool ok = cuda_ok(cudaMalloc(&S->route, off), "cudaMalloc(ep routing)") && cuda_ok(cudaMemset(S->route, 0, off), "memset");
+    if (ok) {
+        char *f = S->route;
+        S->ids_g = (uint32_t *)(f + o_ig); S->ids_l = (uint32_t *)(f + o_il); S->wts_g = (float *)(f + o_w);
+        PlanBatch *pb[2] = {&S->pg, &S->pl};
+        for (int b = 0; b < 2; b++) {
+            pb[b]->counts = (uint32_t *)(f + o_pb[b][0]); pb[b]->starts = (uint32_t *)(f + o_pb[b][1]); pb[b]->xmap = (uint32_t *)(f + o_pb[b][2]);
+            pb[b]->ymap = (uint32_t *)(f + o_pb[b][3]); pb[b]->pos = (uint32_t *)(f + o_pb[b][4]); pb[b]->header = (uint32_t *)(f + o_pb[b][5]);
+            pb[b]->tiles = (uint4 *)(f + o_pb[b][6]); pb[b]->map_stride = S->map_stride; pb[b]->tile_stride = S->tile_stride;
+        }
+        S->h = (float *)(f + o_h); S->err = (uint32_t *)(f + o_err);
+        // the block peers write into: activation pieces | their scales | result rows of the local tokens | counters
+        const size_t qb = ((size_t)S->x_pieces * Rp * H + 255) & ~(size_t)255, sb = (Rp * (H / 128) * 4 + 255) & ~(size_t)255, db = ((size_t)S->tokens_local * K * H * 4 + 255) & ~(size_t)255;
+        S->off_sx = qb; S->off_dn = qb + sb; S->off_cnt = qb + sb + db; S->comm_bytes = S->off_cnt + 256;
+        ok = cuda_ok(cudaMalloc(&S->comm, S->comm_bytes), "cudaMalloc(ep comm)") && cuda_ok(cudaMemset(S->comm, 0, S->comm_bytes), "memset") &&
+             cuda_ok(cudaMalloc(&S->peer_tab, (size_t)world * 32), "cudaMalloc(ep peers)") && make_tmap_u8(S->tm_qx, S->comm, (uint64_t)S->x_pieces * Rp, H, 32);
+    }
+    if (ok && world == 1) {
+        uint64_t tab[4] = {(uint64_t)(uintptr_t)S->comm, (uint64_t)(uintptr_t)(S->comm + S->off_sx), (uint64_t)(uintptr_t)(S->comm + S->off_dn), (uint64_t)(uintptr_t)(S->comm + S->off_cnt)};
+        ok = cuda_ok(cudaMemcpy(S->peer_tab, tab, 32, cudaMemcpyHostToDevice), "copy peer table"); S->connected = 1;
+    }
+    if (!ok) { if (S->route) cudaFree(S->route); if (S->comm) cudaFree(S->comm); if (S->peer_tab) cudaFree(S->peer_tab); delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
+    *out = S;
+    return OMEGA_GPU_FP8_OK;
+}
+
+void omega_gpu_moe_epstack_free(OmegaGpuMoeEpStack *S) {
+    if (!S) return;
+    Lock l;
+    for (int i = 0; i < S->n_opened; i++) cudaIpcCloseMemHandle(S->opened[i]);
+    if (S->route) cudaFree(S->route);
+    if (S->comm) cudaFree(S->comm);
+    if (S->peer_tab) cudaFree(S->peer_tab);
+    delete S;
+}
+
+int omega_gpu_moe_epstack_export(const OmegaGpuMoeEpStack *S, uint8_t *handle64) {
+    if (!S || !handle64) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    cudaIpcMemHandle_t h;
+    if (!cuda_ok(cudaIpcGetMemHandle(&h, S->comm), "cudaIpcGetMemHandle")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    memcpy(handle64, &h, 64);
+    return OMEGA_GPU_FP8_OK;
+}
+
+int omega_gpu_moe_epstack_connect(OmegaGpuMoeEpStack *S, const uint8_t *handles) {
+    if (!S || !handles) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    uint64_t tab[4 * 64];
+    for (uint32_t r = 0; r < S->world; r++) {
+        uint8_t *base = S->comm;
+        if (r != S->rank) {
+            cudaIpcMemHandle_t h; memcpy(&h, handles + (size_t)r * 64, 64);
+            void *p = nullptr;
+            if (!cuda_ok(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")) return OMEGA_GPU_FP8_CHIP_FAIL;
+            S->opened[S->n_opened++] = p; base = (uint8_t *)p;
+        }
+        tab[r] = (uint64_t)(uintptr_t)base; tab[S->world + r] = (uint64_t)(uintptr_t)(base + S->off_sx);
+        tab[2 * S->world + r] = (uint64_t)(uintptr_t)(base + S->off_dn); tab[3 * S->world + r] = (uint64_t)(uintptr_t)(base + S->off_cnt);
+    }
+    if (!cuda_ok(cudaMemcpy(S->peer_tab, tab, (size_t)S->world * 32, cudaMemcpyHostToDevice), "copy peer table")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    S->connected = 1;
+    return OMEGA_GPU_FP8_OK;
+}
+
+uint32_t omega_gpu_moe_epstack_launches(const OmegaGpuMoeEpStack *S) { return S ? S->launches : 0; }
+uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *S) { return S ? (uint64_t)(uintptr_t)S->h : 0; }
+
+/* one whole step for this rank. logits_all_va: bf16 [layers][tokens][experts] of ALL tokens (gathered by the caller);
+ * x_va: bf16 [tokens_local][hidden]; out_bf16_va: bf16 [tokens_local][hidden] (final h); the f32 h stays readable through
+ * omega_gpu_moe_epstack_h. Stream-ordered; every rank must enqueue the same number of steps. */
+int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_va, uint64_t x_va, uint64_t out_bf16_va, void *stream) {
+    if (!S || !logits_all_va || !x_va || !out_bf16_va) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!S->connected) { set_error("ep stack: not connected to its peers"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t G = S->world, K = S->topk, E = S->experts, El = S->experts_local, H = S->hidden, T = S->tokens, Tl = S->tokens_local, Ln = S->layers, Px = S->x_pieces;
+    const size_t R = (size_t)T * K, pstride = (size_t)S->row_cap * H;
+    const uint64_t *tab = S->peer_tab;
+    unsigned long long *cnt = (unsigned long long *)(S->comm + S->off_cnt);   // [0..1] delivered input rows by layer parity, [2..3] delivered result slices
+    float *dn_local = (float *)(S->comm + S->off_dn);
+    uint32_t n = 0;
+    LayerView v0; layer_view(S->local[0], &v0);
+    bool ok = cuda_ok(launch_topk(Ln * T, E, K, (int)v0.norm_topk, (const uint16_t *)(uintptr_t)logits_all_va, S->ids_g, S->wts_g, s), "topk launch"); n++;
+    if (ok) { ep_localise_kernel<<<(unsigned)((Ln * R + 255) / 256), 256, 0, s>>>(Ln * R, S->rank * El, (S->rank + 1) * El, S->ids_g, S->ids_l); n++; }
+    ok = ok && cuda_ok(launch_plan_batch(Ln, T, K, E, K, 0, S->ids_g, S->pg, s), "global plan launch") &&
+         cuda_ok(launch_plan_batch(Ln, T, K, El, K, S->tile_rows, S->ids_l, S->pl, s), "local plan launch"); n += 2;
+    if (!ok) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t tok0 = (size_t)S->rank * Tl * K;
+    const unsigned long long ret_want = (unsigned long long)Tl * K * (H / 256u);
+    ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull,
+                                                      S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err); n++;
+    for (uint32_t l = 0; l < Ln && ok; l++) {
+        LayerView v; layer_view(S->local[l], &v);
+        const uint32_t par = l & 1u;
+        const uint32_t *hdr = S->pl.header + (size_t)l * 8;
+        MmaLaunch g = {};
+        g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
+        g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
+        g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
+        g.gate = cnt + par; g.reset = cnt + 2 + (par ^ 1u);
+        ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, false), "gate|up mma launch"); n++;
+        MmaLaunch d = {};
+        d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
+        d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
+        d.out_peers = tab + 2 * G; d.ret_counters = tab + 3 * G; d.ret_index = 2 + par; d.rows_per_rank = Tl * K; d.reset = cnt + par;
+        ok = ok && cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch"); n++;
+        const bool last = l + 1 == Ln;
+        const size_t nx = (size_t)(l + 1) * S->map_stride;
+        if (ok) ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_g + (size_t)l * R + tok0, dn_local, S->h, cnt + 2 + par, ret_want,
+                                                                  last ? nullptr : S->ids_g + (size_t)(l + 1) * R + tok0, last ? nullptr : S->pg.pos + nx + tok0,
+                                                                  last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, last ? nullptr : tab, tab + G, tab + 3 * G,
+                                                                  par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err);
+        n++;
+    }
+    S->launches = n;
+    return ok && cuda_ok(cudaGetLastError(), "ep stack launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+/* synchronises `stream`; 0, or a non-zero code when a bounded wait ran out anywhere in the step */
+int omega_gpu_moe_epstack_status(OmegaGpuMoeEpStack *S, void *stream) {
+    if (!S) return OMEGA_GPU_FP8_BAD_ARGS;
+    std::vector<uint32_t> hdr(S->layers * 8); uint32_t e = 0;
+    if (!cuda_ok(cudaMemcpyAsync(&e, S->err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
+        !cuda_ok(cudaMemcpyAsync(hdr.data(), S->pl.header, hdr.size() * 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
+        !cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "ep stack status")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    if (e) return (int)e;
+    for (size_t l = 0; l < S->layers; l++) { if (hdr[l * 8 + 3]) return 100 + (int)hdr[l * 8 + 3]; if (hdr[l * 8 + 4]) return (int)hdr[l * 8 + 4]; }
+    return 0;
+}
+
+}  // extern "C"

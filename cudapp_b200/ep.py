@@ -56,7 +56,12 @@ class EpStack:
     """48-layer (or fewer) expert-parallel stack on this rank's GPU."""
 
     def __init__(self, api, torch, dist, rank, world, layers, tokens, mode="p2p", engine=0, seed_base=0):
-        self.api, self.torch, self.dist, self.rank, self.world, self.mode = api, torch, dist, rank, world, mode
+        self.mode = mode
+        self._build_local(api, torch, dist, rank, world, layers, tokens, engine, seed_base, max_tokens=tokens + 1)
+        self._build_exchange()
+
+    def _build_local(self, api, torch, dist, rank, world, layers, tokens, engine, seed_base, max_tokens):
+        self.api, self.torch, self.dist, self.rank, self.world = api, torch, dist, rank, world
         self.T, self.Tl, self.Ln = tokens, tokens // world, layers
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
@@ -76,12 +81,15 @@ class EpStack:
             tg, td = C.c_void_p(), C.c_void_p()
             assert lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(El), C.c_uint32(2 * I), C.c_uint32(H), C.c_uint64(w8[e0:e1].data_ptr()), C.c_uint64(sc[e0:e1].data_ptr()), C.byref(tg)) == 0, api.last_error()
             assert lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(El), C.c_uint32(H), C.c_uint32(I), C.c_uint64(d8[e0:e1].data_ptr()), C.c_uint64(dsc[e0:e1].data_ptr()), C.byref(td)) == 0, api.last_error()
-            rc, layer = api.moe_layer_create(tg, td, topk=TOPK, max_tokens=tokens + 1, engine=engine)
+            rc, layer = api.moe_layer_create(tg, td, topk=TOPK, max_tokens=max_tokens, engine=engine)
             assert rc == 0, api.last_error()
             self.layers.append(layer); self.tensors += [tg, td]
             del wgu, wdn
         del w8, sc, d8, dsc
         torch.cuda.empty_cache()
+
+    def _build_exchange(self):
+        api, torch, dist, rank, world, layers, tokens, dev, lib, mode = self.api, self.torch, self.dist, self.rank, self.world, self.Ln, self.T, self.dev, self.api.lib, self.mode
         rc, self.share = api.moe_stack_create(self.layers, 1e-6)       # one scratch workspace for all local layers
         assert rc == 0, api.last_error()
         ep = C.c_void_p()
@@ -164,6 +172,62 @@ class EpStack:
         return int(self.api.lib.omega_gpu_moe_ep_status(self.ep, C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
 
 
+class FusedEpStack(EpStack):
+    """Three launches per layer and rank (csrc/moe_ep.cu, "fused expert-parallel stack"): routing of all layers from the
+    gathered logits up front, activation pieces and result rows travel by peer stores, waits are atomic counters."""
+
+    def __init__(self, api, torch, dist, rank, world, layers, tokens, engine=0, seed_base=0):
+        self.mode = "fused"
+        self._build_local(api, torch, dist, rank, world, layers, tokens, engine, seed_base, max_tokens=tokens)
+        lib, dev = api.lib, self.dev
+        arr = (C.c_void_p * layers)(*self.layers)
+        eps = C.c_void_p()
+        assert lib.omega_gpu_moe_epstack_create(C.c_uint32(world), C.c_uint32(rank), C.c_uint32(layers), arr, C.c_uint32(E), C.c_uint32(tokens), C.c_float(1e-6), C.byref(eps)) == 0, api.last_error()
+        self.eps = eps
+        if world > 1:
+            h = (C.c_uint8 * 64)()
+            assert lib.omega_gpu_moe_epstack_export(eps, h) == 0, api.last_error()
+            mine = torch.tensor(list(h), dtype=torch.uint8, device=dev)
+            allh = torch.empty(world * 64, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh, mine)
+            hb = (C.c_uint8 * (world * 64))(*allh.cpu().tolist())
+            assert lib.omega_gpu_moe_epstack_connect(eps, hb) == 0, api.last_error()
+            dist.barrier()
+        Tl = self.Tl
+        self.logits = torch.empty((layers, Tl, E), dtype=torch.int16, device=dev); self.x = torch.empty((Tl, H), dtype=torch.int16, device=dev)
+        self.gathered = torch.empty((world, layers, Tl, E), dtype=torch.int16, device=dev)
+        self.logits_all = torch.empty((layers, world * Tl, E), dtype=torch.int16, device=dev)
+        self.out16 = torch.empty((Tl, H), dtype=torch.int16, device=dev)
+        lib.omega_gpu_moe_epstack_h.restype = C.c_uint64
+        self.h = self._wrap_f32(int(lib.omega_gpu_moe_epstack_h(eps)), Tl * H).view(Tl, H)
+        self.graph = None
+        self.launches = 0
+
+    def _wrap_f32(self, va, n):
+        torch = self.torch
+
+        class _Iface:
+            pass
+        o = _Iface()
+        o.__cuda_array_interface__ = {"shape": (int(n),), "typestr": "<f4", "data": (int(va), False), "version": 2}
+        return torch.as_tensor(o, device=self.dev)
+
+    def record(self, stream):
+        lib, api = self.api.lib, self.api
+        if self.world > 1:   # every rank needs the router logits of all tokens: they are small (tokens x experts x 2 bytes per layer)
+            self.dist.all_gather_into_tensor(self.gathered.view(-1), self.logits.view(-1))
+            self.logits_all.view(self.Ln, self.world, self.Tl, E).copy_(self.gathered.permute(1, 0, 2, 3))
+        else:
+            self.logits_all.copy_(self.logits)
+        assert lib.omega_gpu_moe_epstack_step_async(self.eps, C.c_uint64(self.logits_all.data_ptr()), C.c_uint64(self.x.data_ptr()), C.c_uint64(self.out16.data_ptr()),
+                                                    C.c_void_p(stream)) == 0, api.last_error()
+        lib.omega_gpu_moe_epstack_launches.restype = C.c_uint32
+        self.launches = int(lib.omega_gpu_moe_epstack_launches(self.eps)) + 2
+
+    def status(self):
+        return int(self.api.lib.omega_gpu_moe_epstack_status(self.eps, C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
+
+
 def make_inputs(layers, tokens, seed=0):
     from oracle.oracle import bf16_bits   # number-format helper only
     rng = np.random.default_rng(seed)
@@ -182,9 +246,9 @@ def bench(args, rank, world):
     torch.cuda.set_device(local)
     os.environ.setdefault("B200MOE_DEVICE", str(local))
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    mode = os.environ.get("B200MOE_EP_MODE", "p2p")
+    mode = os.environ.get("B200MOE_EP_MODE", "fused")
     Ln, T = args.layers, args.tokens
-    st = EpStack(api, torch, dist, rank, world, Ln, T, mode=mode, engine=args.engine)
+    st = FusedEpStack(api, torch, dist, rank, world, Ln, T, engine=args.engine) if mode == "fused" else EpStack(api, torch, dist, rank, world, Ln, T, mode=mode, engine=args.engine)
     logits, x = make_inputs(Ln, T)
     t0, t1 = token_range(rank, world, T)
     lg_h = torch.from_numpy(np.ascontiguousarray(logits[:, t0:t1]).view(np.int16)).pin_memory(); x_h = torch.from_numpy(np.ascontiguousarray(x[t0:t1]).view(np.int16)).pin_memory()
@@ -229,7 +293,7 @@ def bench(args, rank, world):
             "ms_per_step": float(ms.item()) / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights, f32 accumulate",
             "data": "synthetic",
             "config": {"workload": "48-layer MoE expert stack, 256 decode tokens/step, 128 experts top-8, hidden 2048, inter 768", "layers": Ln, "tokens_per_step": T,
-                       "parallelism": "ep%d (experts and tokens sharded; %s)" % (world, "direct peer stores over NVLink" if mode == "p2p" else "NCCL all-to-all"),
+                       "parallelism": "ep%d (experts and tokens sharded; %s)" % (world, {"fused": "rows and results by peer stores over NVLink inside the layer kernels, 3 launches per layer", "p2p": "direct peer stores over NVLink", "nccl": "NCCL all-to-all"}[mode]),
                        "l2": "%.1f GB of weights per GPU per step: larger than L2" % (per_gpu_bytes / 1e9)},
             "e2e": {"value": T / float(e2e.item()), "unit": "tokens/s", "h2d_bytes_per_step": int((lg_h.numel() + x_h.numel()) * 2 * world), "d2h_bytes_per_step": int(out_h.numel() * 2 * world)},
             "gpu_launches": int(st.launches) * args.steps,

@@ -140,6 +140,22 @@ int omega_gpu_moe_ep_experts_async(OmegaGpuMoeEp *ep, OmegaGpuMoeLayer *local, v
 int omega_gpu_moe_ep_combine_async(OmegaGpuMoeEp *ep, uint32_t tokens_local, uint64_t out_f32_va, uint64_t out_bf16_va, void *stream);
 /* synchronises `stream`; 0, or the code of a bounded cross-GPU wait that ran out (11 dispatch, 12 return) */
 int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream);
+
+/* ---- fused expert-parallel stack: three launches per layer and rank, rows and results travel by peer stores, waits are
+ * counters advanced with system-scope atomics (bounded). local[l]: rank's layer l over its experts/world experts, tensor-core
+ * engine, max_tokens >= tokens (all ranks' tokens). After create: export this rank's handle, gather all ranks' handles,
+ * connect (world 1 needs neither). Per step the caller gathers the router logits of ALL tokens ([layers][tokens][experts]
+ * bf16) and calls step_async on every rank; outputs are bit-identical to the single-GPU stack. */
+typedef struct OmegaGpuMoeEpStack OmegaGpuMoeEpStack;
+int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers, OmegaGpuMoeLayer *const *local, uint32_t experts,
+                                 uint32_t tokens, float eps, OmegaGpuMoeEpStack **out);
+void omega_gpu_moe_epstack_free(OmegaGpuMoeEpStack *s);
+int omega_gpu_moe_epstack_export(const OmegaGpuMoeEpStack *s, uint8_t *handle64);
+int omega_gpu_moe_epstack_connect(OmegaGpuMoeEpStack *s, const uint8_t *handles);
+int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *s, uint64_t logits_all_va, uint64_t x_va, uint64_t out_bf16_va, void *stream);
+int omega_gpu_moe_epstack_status(OmegaGpuMoeEpStack *s, void *stream);
+uint32_t omega_gpu_moe_epstack_launches(const OmegaGpuMoeEpStack *s);
+uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *s);   /* device address of the f32 residual stream [tokens_local][hidden] */
 #ifdef __cplusplus
 }
 #endif

@@ -30,7 +30,7 @@ def _worker(rank, world, port, mode, ret):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     from cudapp_b200 import api, ep
     Ln, T = 2, 64
-    st = ep.EpStack(api, torch, dist, rank, world, Ln, T, mode=mode)
+    st = ep.FusedEpStack(api, torch, dist, rank, world, Ln, T) if mode == "fused" else ep.EpStack(api, torch, dist, rank, world, Ln, T, mode=mode)
     logits, x = ep.make_inputs(Ln, T, seed=3)
     t0, t1 = ep.token_range(rank, world, T)
     st.logits.copy_(torch.from_numpy(np.ascontiguousarray(logits[:, t0:t1]).view(np.int16))); st.x.copy_(torch.from_numpy(np.ascontiguousarray(x[t0:t1]).view(np.int16)))
@@ -73,13 +73,13 @@ def _worker(rank, world, port, mode, ret):
     os._exit(0)   # collectives captured in a CUDA graph make process-group teardown unreliable: leave at once
 
 
-@pytest.mark.parametrize("mode", ["nccl", "p2p"])
+@pytest.mark.parametrize("mode", ["nccl", "p2p", "fused"])
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_ep_equals_single_gpu(mode):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29600 + (os.getpid() % 2000) + (0 if mode == "nccl" else 1)
+    port = 29600 + (os.getpid() % 2000) + ["nccl", "p2p", "fused"].index(mode)
     procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
     for p in procs:
         p.start()

@@ -87,3 +87,32 @@ def test_stack_small(engine):
     api.lib.omega_gpu_moe_stack_free(stack)
     for m in ms:
         free_layer(m)
+
+
+def test_epstack_world1_equals_stack():
+    """the fused expert-parallel stack with one rank (its own peer) against the ordinary stack: identical bits"""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(21)
+    E, H, I, topk, Ln = 16, 512, 256, 4, 3
+    ms = [build_layer(rng, E, H, I, 32, api.ENGINE_MMA, topk) for _ in range(Ln)]
+    rc, stack = api.moe_stack_create([m["layer"] for m in ms], 1e-6); assert rc == 0, api.last_error()
+    arr = (C.c_void_p * Ln)(*[m["layer"] for m in ms])
+    eps = C.c_void_p()
+    # the layers' workspace holds 32 tokens; the expert-parallel stack is created for those 32 and run with all of them
+    T2 = 32
+    logits2 = orc.bf16_bits(rng.normal(0, 1, (Ln, T2, E)).astype(np.float32)); x2 = orc.bf16_bits(rng.normal(0, 1, (T2, H)).astype(np.float32))
+    rc, want16, want32 = api.moe_stack_bf16(stack, logits2, x2); assert rc == 0, api.last_error()
+    assert api.lib.omega_gpu_moe_epstack_create(C.c_uint32(1), C.c_uint32(0), C.c_uint32(Ln), arr, C.c_uint32(E), C.c_uint32(T2), C.c_float(1e-6), C.byref(eps)) == 0, api.last_error()
+    dev = torch.device("cuda", 0)
+    d_lg = torch.from_numpy(logits2.view(np.int16)).to(dev); d_x = torch.from_numpy(x2.view(np.int16)).to(dev); d_o = torch.empty((T2, H), dtype=torch.int16, device=dev)
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for _ in range(2):   # twice: the counters must come back to their starting state
+        assert api.lib.omega_gpu_moe_epstack_step_async(eps, C.c_uint64(d_lg.data_ptr()), C.c_uint64(d_x.data_ptr()), C.c_uint64(d_o.data_ptr()), C.c_void_p(s.cuda_stream)) == 0, api.last_error()
+        assert api.lib.omega_gpu_moe_epstack_status(eps, C.c_void_p(s.cuda_stream)) == 0
+        assert np.array_equal(d_o.cpu().numpy().view(np.uint16), want16)
+    api.lib.omega_gpu_moe_epstack_free(eps)
+    api.lib.omega_gpu_moe_stack_free(stack)
+    for m in ms:
+        free_layer(m)
