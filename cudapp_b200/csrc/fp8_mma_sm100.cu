@@ -142,6 +142,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     __shared__ float s_sc[2][2][KB_MAX][MMA_TOK]; // [scale buffer][weight tile][k block][row] = weight scale x row scale
     __shared__ float s_red[2][4][MMA_TOK];        // [epilogue group][warp][row]: amax exchange
     __shared__ uint32_t s_ymap[2][MMA_TOK];       // [scale buffer][row]: destination rows (mode 1)
+    __shared__ uint32_t s_ret[2][64];             // [epilogue group][rank]: result slices stored into that rank's buffer (expert parallel)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
     const uint32_t bar0 = smem_u32(s_bar);
@@ -155,6 +156,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     auto turn_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 10 + g); };   // "the other group has drained its unit's partials"
     volatile uint32_t *abort_flag = &s_abort;
 
+    if (threadIdx.x < 128) s_ret[threadIdx.x >> 6][threadIdx.x & 63u] = 0;
     if (threadIdx.x == 0) {
         if (a.reset && blockIdx.x == 0) { *a.reset = 0ull; __threadfence_system(); }
         s_abort = 0;
@@ -367,13 +369,19 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
                         float *o = reinterpret_cast<float *>(a.out_peers[owner]) + (size_t)(y - owner * a.rows_per_rank) * a.out_stride;
                         o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
                     }
-                __threadfence_system();
-                mbar_arrive(group_bar(g));
-                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15))) break;
                 const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
-                if (et < cnt) atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[s_ymap[b][et] / a.rows_per_rank]) + a.ret_index, 1ull);
+                if (et < cnt) atomicAdd(&s_ret[g][s_ymap[b][et] / a.rows_per_rank], 1u);   // published once, after the last unit
             }
             mbar_arrive(scempty_bar(b));   // this unit's scales and destination rows may be overwritten
+        }
+        if (a.out_peers && ok) {
+            // all result rows of this group are stored: make them visible system-wide, then advance each owner's counter once
+            __threadfence_system();
+            mbar_arrive(group_bar(g));
+            if (mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15)) {
+                const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                if (et < 64u && s_ret[g][et]) atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[et]) + a.ret_index, (unsigned long long)s_ret[g][et]);
+            }
         }
     }
     // ---------------------------------------------------------------- teardown

@@ -322,6 +322,8 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     __shared__ float s_scale;
     __shared__ uint32_t s_d[32], s_row[32], s_fail;
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next gate|up GEMM may start fetching weights
     if (tid == 0) {
         s_fail = 0;
         if (dn && ret_gate) {
@@ -548,7 +550,7 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
         g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
         g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
         g.gate = cnt + par; g.reset = cnt + 2 + (par ^ 1u);
-        ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, false), "gate|up mma launch"); n++;
+        ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true), "gate|up mma launch"); n++;
         MmaLaunch d = {};
         d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
         d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;

@@ -215,7 +215,7 @@ class FusedEpStack(EpStack):
     def record(self, stream):
         lib, api = self.api.lib, self.api
         if self.world > 1:   # every rank needs the router logits of all tokens: they are small (tokens x experts x 2 bytes per layer)
-            self.dist.all_gather_into_tensor(self.gathered.view(-1), self.logits.view(-1))
+            self.dist.all_gather_into_tensor(self.gathered.view(-1).view(self.torch.uint8), self.logits.view(-1).view(self.torch.uint8))
             self.logits_all.view(self.Ln, self.world, self.Tl, E).copy_(self.gathered.permute(1, 0, 2, 3))
         else:
             self.logits_all.copy_(self.logits)
