@@ -47,7 +47,8 @@ struct MmaArgs {
     const uint64_t *out_peers;          // mode 1: base address of every rank's result buffer; row y belongs to rank y / rows_per_rank
     const uint64_t *ret_counters;       // mode 1: address of every rank's "result slices delivered" counter
     uint32_t rows_per_rank, ret_index;  // ret_index: which counter of the owner's counter block this launch advances
-    unsigned long long *reset;          // a counter of this rank that is no longer in use: cleared at kernel start
+    const unsigned long long *gate_base; // rows delivered through `gate` before this layer (counters only ever grow)
+    unsigned long long *bump;           // a base to advance by header[0] (the gate|up GEMM of this layer has consumed those rows)
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -83,6 +84,7 @@ __device__ __forceinline__ bool gate_wait(const unsigned long long *gate, unsign
         unsigned long long v;
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(gate) : "memory");
         if (v >= want) { asm volatile("fence.proxy.async;" ::: "memory"); return true; }
+        if ((i & 63u) == 63u && *reinterpret_cast<volatile uint32_t *>(err)) return false;   // somebody already gave up: do not wait out the limit again
         __nanosleep(100);
     }
     atomicCAS(err, 0u, code);
@@ -158,7 +160,6 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
 
     if (threadIdx.x < 128) s_ret[threadIdx.x >> 6][threadIdx.x & 63u] = 0;
     if (threadIdx.x == 0) {
-        if (a.reset && blockIdx.x == 0) { *a.reset = 0ull; __threadfence_system(); }
         s_abort = 0;
         for (uint32_t s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (uint32_t b = 0; b < 2; b++) {
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t KB = a.k / 128u, n_tiles = a.header[2], total = n_tiles * a.pairs;
+    const uint32_t KB = a.k / 128u, n_tiles = a.header[2], total = *reinterpret_cast<volatile uint32_t *>(a.err) ? 0u : n_tiles * a.pairs;   // after a recorded failure: no work
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -186,7 +187,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             for (int phase = 0; phase < 3 && ok; phase++) {
                 if (phase == 1) {
                     griddep_wait(); griddep_launch();
-                    if (a.gate && !(ok = gate_wait(a.gate, a.header[0], a.err, 13))) { *abort_flag = 1; break; }
+                    if (a.bump && blockIdx.x == 0) *a.bump += a.header[0];
+                    if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13))) { *abort_flag = 1; break; }
                 }
                 it = phase == 2 ? STAGES : 0;
                 uint32_t seen = 0;
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
         // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
         uint32_t n = 0; bool ok = true;
         griddep_wait();   // the row scales below are the previous kernel's output
-        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, a.header[0], a.err, 14)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
+        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 14)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
         for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
@@ -421,7 +423,7 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
     MmaArgs a = {};
     a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
     a.q_out = m.q_out; a.s_out = m.s_out; a.q_rows = m.q_rows; a.q_pieces = m.q_pieces;
-    a.gate = m.gate; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index; a.reset = m.reset;
+    a.gate = m.gate; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index; a.gate_base = m.gate_base; a.bump = m.bump;
     a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
     const int sms = st().sm_count ? st().sm_count : 148;
     const CUtensorMap *w = (const CUtensorMap *)tm_w, *q = (const CUtensorMap *)tm_q;

@@ -102,7 +102,7 @@ struct MmaLaunch {
     uint8_t *q_out; float *s_out; uint32_t q_rows, q_pieces;   // mode 0 result as e4m3 pieces [piece][q_rows][n/2] + scales [row][n/256]; q_rows also = row capacity of the input pieces
     uint32_t *err;                     // device word: non-zero = a bounded wait inside the kernel ran out
     // expert parallelism (null / 0 otherwise): wait for `*gate >= header[0]` delivered input rows; mode 1 results go to out_peers[row / rows_per_rank]
-    const unsigned long long *gate; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index; unsigned long long *reset;
+    const unsigned long long *gate; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index; const unsigned long long *gate_base; unsigned long long *bump;
 };
 bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 uint32_t mma_tile_rows(uint32_t pieces);

@@ -305,8 +305,10 @@ struct OmegaGpuMoeEpStack {
 
 namespace b200 {
 
-__global__ void ep_localise_kernel(size_t n, uint32_t e0, uint32_t e1, const uint32_t *__restrict__ ids, uint32_t *__restrict__ out) {
+// also counts the steps on the device (a replayed graph cannot carry a host counter)
+__global__ void ep_localise_kernel(size_t n, uint32_t e0, uint32_t e1, const uint32_t *__restrict__ ids, uint32_t *__restrict__ out, uint32_t *step) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i == 0) *step += 1u;
     if (i < n) { const uint32_t e = ids[i]; out[i] = (e >= e0 && e < e1) ? e - e0 : 0xffffffffu; }
 }
 
@@ -314,7 +316,7 @@ __global__ void ep_localise_kernel(size_t n, uint32_t e0, uint32_t e1, const uin
 // q_peers != null: quantise xn = bf16(RMSNorm(h)) into pieces and store them into the owners' piece buffers.
 __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         uint32_t hidden, uint32_t topk, float eps, const uint16_t *__restrict__ x16, const float *__restrict__ w, const float *__restrict__ dn, float *__restrict__ h,
-        const unsigned long long *ret_gate, unsigned long long ret_want,
+        const unsigned long long *ret_gate, unsigned long long ret_unit, const uint32_t *step, uint32_t uses_per_step, uint32_t uses_before,
         const uint32_t *__restrict__ ids_next, const uint32_t *__restrict__ pos_next, const uint32_t *__restrict__ starts_next, uint32_t experts_local,
         uint32_t pieces, size_t piece_stride, const uint64_t *__restrict__ q_peers, const uint64_t *__restrict__ sx_peers, const uint64_t *__restrict__ cnt_peers,
         uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err) {
@@ -325,13 +327,16 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next gate|up GEMM may start fetching weights
     if (tid == 0) {
-        s_fail = 0;
-        if (dn && ret_gate) {
+        s_fail = *reinterpret_cast<volatile uint32_t *>(err) ? 1u : 0u;
+        if (!s_fail && dn && ret_gate) {
+            // the counter only grows: this layer's results are complete at (uses so far + 1) x slices per use
+            const unsigned long long ret_want = ((unsigned long long)(*step - 1u) * uses_per_step + uses_before + 1ull) * ret_unit;
             bool ok = false;
             for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
                 unsigned long long v;
                 asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ret_gate) : "memory");
                 ok = v >= ret_want;
+                if (!ok && (i & 63u) == 63u && *reinterpret_cast<volatile uint32_t *>(err)) break;   // a failure is already recorded: give up at once
                 if (!ok) __nanosleep(100);
             }
             if (!ok) { atomicCAS(err, 0u, 16u); s_fail = 1; }
@@ -533,13 +538,14 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
     uint32_t n = 0;
     LayerView v0; layer_view(S->local[0], &v0);
     bool ok = cuda_ok(launch_topk(Ln * T, E, K, (int)v0.norm_topk, (const uint16_t *)(uintptr_t)logits_all_va, S->ids_g, S->wts_g, s), "topk launch"); n++;
-    if (ok) { ep_localise_kernel<<<(unsigned)((Ln * R + 255) / 256), 256, 0, s>>>(Ln * R, S->rank * El, (S->rank + 1) * El, S->ids_g, S->ids_l); n++; }
+    if (ok) { ep_localise_kernel<<<(unsigned)((Ln * R + 255) / 256), 256, 0, s>>>(Ln * R, S->rank * El, (S->rank + 1) * El, S->ids_g, S->ids_l, S->err + 4); n++; }
     ok = ok && cuda_ok(launch_plan_batch(Ln, T, K, E, K, 0, S->ids_g, S->pg, s), "global plan launch") &&
          cuda_ok(launch_plan_batch(Ln, T, K, El, K, S->tile_rows, S->ids_l, S->pl, s), "local plan launch"); n += 2;
     if (!ok) return OMEGA_GPU_FP8_CHIP_FAIL;
     const size_t tok0 = (size_t)S->rank * Tl * K;
-    const unsigned long long ret_want = (unsigned long long)Tl * K * (H / 256u);
-    ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull,
+    const unsigned long long ret_unit = (unsigned long long)Tl * K * (H / 256u);
+    unsigned long long *base = (unsigned long long *)(S->err + 8);   // [0..1]: input rows already consumed through the even / odd layer counter
+    ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull, S->err + 4, 0u, 0u,
                                                       S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err); n++;
     for (uint32_t l = 0; l < Ln && ok; l++) {
         LayerView v; layer_view(S->local[l], &v);
@@ -548,17 +554,17 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
         MmaLaunch g = {};
         g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
         g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
-        g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
-        g.gate = cnt + par; g.reset = cnt + 2 + (par ^ 1u);
+        g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = S->err;   // one failure word for the whole step: later kernels see it and do nothing
+        g.gate = cnt + par; g.gate_base = base + par;
         ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true), "gate|up mma launch"); n++;
         MmaLaunch d = {};
         d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
         d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
-        d.out_peers = tab + 2 * G; d.ret_counters = tab + 3 * G; d.ret_index = 2 + par; d.rows_per_rank = Tl * K; d.reset = cnt + par;
+        d.out_peers = tab + 2 * G; d.ret_counters = tab + 3 * G; d.ret_index = 2 + par; d.rows_per_rank = Tl * K; d.bump = base + par;
         ok = ok && cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch"); n++;
         const bool last = l + 1 == Ln;
         const size_t nx = (size_t)(l + 1) * S->map_stride;
-        if (ok) ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_g + (size_t)l * R + tok0, dn_local, S->h, cnt + 2 + par, ret_want,
+        if (ok) ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_g + (size_t)l * R + tok0, dn_local, S->h, cnt + 2 + par, ret_unit, S->err + 4, (Ln + 1u - par) / 2u, l / 2u,
                                                                   last ? nullptr : S->ids_g + (size_t)(l + 1) * R + tok0, last ? nullptr : S->pg.pos + nx + tok0,
                                                                   last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, last ? nullptr : tab, tab + G, tab + 3 * G,
                                                                   par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err);

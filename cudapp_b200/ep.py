@@ -159,7 +159,11 @@ class EpStack:
         with torch.cuda.stream(s):
             self.record(s.cuda_stream)          # one eager step first (lazy initialisation, NCCL warm-up)
         torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize(); self.dist.barrier()
+        torch.cuda.synchronize()
+        code = self.status()
+        if code != 0:   # fail at once rather than replaying a step whose cross-GPU waits run out
+            raise RuntimeError("expert-parallel step failed on rank %d: a bounded wait ran out (code %d)" % (self.rank, code))
+        self.dist.barrier()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.record(torch.cuda.current_stream().cuda_stream)
