@@ -483,3 +483,39 @@ void orc_expert_rows(const uint8_t *wgu, const uint16_t *sgu, const uint8_t *wdn
     }
     free(t); free(gu); free(act);
 }
+
+/* value (f32, exact) that `pieces` activation pieces stand for; pieces == 0 leaves x as it is */
+static void orc_requantise(float *x, uint32_t k, uint32_t pieces) {
+    if (!pieces) return;
+    uint8_t *q = malloc((size_t)pieces * k); float *s = malloc(sizeof(float) * (k / ORC_BLOCK)); double *d = malloc(sizeof(double) * k);
+    orc_act_pieces(x, k, pieces, q, s);
+    orc_act_pieces_decode(q, s, k, pieces, d);
+    for (uint32_t c = 0; c < k; c++) x[c] = (float)d[c];
+    free(q); free(s); free(d);
+}
+/* orc_expert_rows with the activations passed through the piece quantiser first (x_pieces for the layer input,
+ * act_pieces for the gated activations): the arithmetic model of the tensor-core engine, whose FP8 MMA needs FP8
+ * activations. The reference's own QMMA path is tested the same way, against a reference that applies its
+ * activation quantiser first (tests/gpu_qgemm_test.c:24-35, :231). */
+void orc_expert_rows_q(const uint8_t *wgu, const uint16_t *sgu, const uint8_t *wdn, const uint16_t *sdn,
+                       uint32_t hidden, uint32_t inter, const float *x, const uint32_t *row_expert,
+                       const uint32_t *row_token, const uint32_t *row_dest, uint32_t p0, uint32_t p1, float *dn_out,
+                       uint32_t x_pieces, uint32_t act_pieces) {
+    const size_t gu_w = (size_t)2 * inter * hidden, gu_s = (size_t)(2 * inter / ORC_BLOCK) * (hidden / ORC_BLOCK);
+    const size_t dn_w = (size_t)hidden * inter, dn_s = (size_t)(hidden / ORC_BLOCK) * (inter / ORC_BLOCK);
+    double *t = malloc(sizeof(double) * (size_t)(2 * inter > hidden ? 2 * inter : hidden));
+    float *gu = malloc(sizeof(float) * 2 * inter), *act = malloc(sizeof(float) * inter), *xq = malloc(sizeof(float) * hidden);
+    for (uint32_t p = p0; p < p1; p++) {
+        const uint32_t e = row_expert[p];
+        memcpy(xq, x + (size_t)row_token[p] * hidden, sizeof(float) * hidden);
+        orc_requantise(xq, hidden, x_pieces);
+        orc_gemv(wgu + e * gu_w, sgu + e * gu_s, 2 * inter, hidden, xq, t, NULL);
+        for (uint32_t i = 0; i < 2 * inter; i++) gu[i] = (float)t[i];
+        orc_swiglu(gu, inter, act);
+        orc_requantise(act, inter, act_pieces);
+        orc_gemv(wdn + e * dn_w, sdn + e * dn_s, hidden, inter, act, t, NULL);
+        float *o = dn_out + (size_t)row_dest[p] * hidden;
+        for (uint32_t i = 0; i < hidden; i++) o[i] = (float)t[i];
+    }
+    free(t); free(gu); free(act); free(xq);
+}

@@ -236,7 +236,7 @@ def w4_gemm(packed, sc, x, threads=None):
     return y
 
 
-def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, threads=None):
+def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, threads=None, x_pieces=0, act_pieces=0):
     """Gate|up GEMV, SwiGLU and down GEMV for every sorted row (the reference host glue); ctypes releases
     the GIL, so rows are spread over `threads` host threads. Returns dn f32 [n_dest][hidden]."""
     import concurrent.futures as cf
@@ -253,22 +253,24 @@ def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, 
     step = max(1, (rows + threads * 4 - 1) // (threads * 4))
 
     def run(p0):
-        L.orc_expert_rows(_ptr(wgu, U8P), _ptr(sgu, U16P), _ptr(wdn, U8P), _ptr(sdn, U16P), C.c_uint32(hidden), C.c_uint32(inter),
-                          _ptr(x, F32P), _ptr(re_, U32P), _ptr(rt, U32P), _ptr(rd, U32P), C.c_uint32(p0), C.c_uint32(min(rows, p0 + step)), _ptr(dn, F32P))
+        L.orc_expert_rows_q(_ptr(wgu, U8P), _ptr(sgu, U16P), _ptr(wdn, U8P), _ptr(sdn, U16P), C.c_uint32(hidden), C.c_uint32(inter),
+                            _ptr(x, F32P), _ptr(re_, U32P), _ptr(rt, U32P), _ptr(rd, U32P), C.c_uint32(p0), C.c_uint32(min(rows, p0 + step)), _ptr(dn, F32P),
+                            C.c_uint32(x_pieces), C.c_uint32(act_pieces))
     with cf.ThreadPoolExecutor(threads) as ex:
         list(ex.map(run, range(0, rows, step)))
     return dn
 
 
-def moe_layer(logits_bf16, x_bf16, wgu, sgu, wdn, sdn, topk_k=8, threads=None):
+def moe_layer(logits_bf16, x_bf16, wgu, sgu, wdn, sdn, topk_k=8, threads=None, x_pieces=0, act_pieces=0):
     """One MoE layer exactly as the reference host glue strings the operators together: top-k (lowest
     index on ties, renormalised softmax), per pick gate|up GEMV -> SwiGLU -> down GEMV, slot-order weighted
-    sum. Inputs bf16 bit patterns; returns (out f32 [T][H], ids, wts f32)."""
+    sum. Inputs bf16 bit patterns; returns (out f32 [T][H], ids, wts f32). x_pieces / act_pieces > 0 pass the layer input /
+    the gated activations through the e4m3 piece quantiser first (the tensor-core engine's arithmetic model)."""
     lg = bf16_to_f32(logits_bf16); x = bf16_to_f32(x_bf16)
     T, H = x.shape
     ids, w64 = topk(lg, topk_k, True)
     wts = w64.astype(np.float32)
     re_ = ids.reshape(-1); rt = np.repeat(np.arange(T, dtype=np.uint32), topk_k); rd = np.arange(T * topk_k, dtype=np.uint32)
-    dn = expert_rows(wgu, sgu, wdn, sdn, x, re_, rt, rd, T * topk_k, threads)
+    dn = expert_rows(wgu, sgu, wdn, sdn, x, re_, rt, rd, T * topk_k, threads, x_pieces, act_pieces)
     out = combine(wts, dn.reshape(T, topk_k, H))
     return out, ids, wts
