@@ -21,18 +21,10 @@
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a code in *err, lets its own copies land, frees its
 // TMEM and returns (no trap, no endless spin).
-#include <cuda.h>
-#include <cuda_runtime.h>
 #include "internal.h"
+#include "mma_common.cuh"
 
 namespace b200 {
-
-constexpr int MMA_TOK = 32;                     // routed rows per tile; accumulator columns = 32 per activation piece
-constexpr uint32_t A_TILE = 128 * 128, B_PIECE = MMA_TOK * 128;
-constexpr int KB_MAX = 32;                      // k <= 4096 on this engine
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int MMA_THREADS = 32 * 11;
-constexpr uint32_t Q_STAGE_BYTES = 2 * 4 * MMA_TOK * 128;   // per epilogue group: up to 4 pieces x 32 rows x 128 bytes of output codes            // TMA, MMA, scale loader, 2 x 4 epilogue warps
 
 struct MmaArgs {
     const float *wscale, *ascale;
@@ -50,86 +42,6 @@ struct MmaArgs {
     const unsigned long long *gate_base; // rows delivered through `gate` before this layer (counters only ever grow)
     unsigned long long *bump;           // a base to advance by header[0] (the gate|up GEMM of this layer has consumed those rows)
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded wait: false (and *err = code) when the limit runs out or another role already gave up
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t *err, uint32_t code) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1; atomicCAS(err, 0u, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// programmatic dependent launch: wait = the grids this one depends on have completed and their writes are visible;
-// launch_dependents = the next grid in the stream may start occupying free SMs (it blocks in its own wait)
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-// bounded wait until a counter that peers advance with system-scope atomics reaches `want`
-__device__ __forceinline__ bool gate_wait(const unsigned long long *gate, unsigned long long want, uint32_t *err, uint32_t code) {
-    for (uint32_t i = 0; i < (1u << 22); i++) {
-        unsigned long long v;
-        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(gate) : "memory");
-        if (v >= want) { asm volatile("fence.proxy.async;" ::: "memory"); return true; }
-        if ((i & 63u) == 63u && *reinterpret_cast<volatile uint32_t *>(err)) return false;   // somebody already gave up: do not wait out the limit again
-        __nanosleep(100);
-    }
-    atomicCAS(err, 0u, code);
-    return false;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
-__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p; }"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// K-major operand tile, rows of 128 bytes, SWIZZLE_128B: 8-row groups 1024 bytes apart (stride offset), version 1
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-
-#define TMEM_LD32(taddr, r)                                                                                                              \
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];" \
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),       \
-                   "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),           \
-                   "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) \
-                 : "r"(taddr))
-
-// SiLU gate with the fast exponential and division (the reference kernel itself uses EX2 / RCP approximations here,
-// src/omega_blackwell_codegen_dec.c:291-324)
-__device__ __forceinline__ float silu_mul_dev(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
-
-// activation-piece helpers (same arithmetic as act_quant_kernel in moe_glue.cu)
-__device__ __forceinline__ float pq_scale_mma(float amax) {
-    amax = fmaxf(amax, 7.888609052210118e-31f /* 2^-100 */);
-    const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, c = (M + 0x1fffffu) >> 23;
-    return __uint_as_float((E + c - 8u) << 23);
-}
-__device__ __forceinline__ uint32_t enc2(float lo, float hi) {
-    uint16_t r;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-__device__ __forceinline__ float2 dec2(uint32_t v) {
-    uint32_t h2; float2 f;
-    asm("{ .reg .b16 a; cvt.u16.u32 a, %1; cvt.rn.f16x2.e4m3x2 %0, a; }" : "=r"(h2) : "r"(v));
-    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(f.x), "=f"(f.y) : "r"(h2));
-    return f;
-}
 
 template <int P>
 __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
