@@ -108,6 +108,13 @@ bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols,
 uint32_t mma_tile_rows(uint32_t pieces);
 bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
 cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s, bool pdl = false);
+// whole expert FFN of a layer in one launch (fp8_ffn_sm100.cu); piece counts (2,3), (1,1) or (2,2)
+struct FfnLaunch {
+    const float *gu_scale, *dn_scale, *x_scale; uint8_t *qa; float *sa; const void *tiles; const uint32_t *header, *ymap; float *out;
+    uint32_t hidden, inter, q_rows; uint32_t *sched, *err;   // sched: [0] next down unit, [1 + tile] finished gate|up units; zeroed before the launch
+};
+bool ffn_shape_ok(uint32_t hidden, uint32_t inter);
+cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, const void *tm_qa, uint32_t px, uint32_t pa, const FfnLaunch &m, cudaStream_t s, bool pdl);
 bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s);
 // expert side only (expert-parallel receive path): `rows` candidate rows, ids[row] = local expert or 0xFFFFFFFF,
 // x row r at x + r * x_stride_bytes (bf16); writes dn[row][hidden] f32 for the present rows

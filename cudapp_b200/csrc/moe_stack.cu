@@ -49,13 +49,15 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(uint32_t hidden, flo
 __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidden, uint32_t topk, float eps, const uint16_t *__restrict__ x16,
                                                                    const float *__restrict__ w, const float *__restrict__ dn, float *__restrict__ h,
                                                                    const uint32_t *__restrict__ pos, uint32_t pieces, size_t piece_stride, uint8_t *__restrict__ q,
-                                                                   float *__restrict__ sx, uint16_t *__restrict__ h16) {
+                                                                   float *__restrict__ sx, uint16_t *__restrict__ h16, uint32_t *__restrict__ sched, uint32_t n_sched) {
     __shared__ double red[8];
     __shared__ float s_scale;
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
     // launched as a programmatic dependent: everything read below is the previous kernel's output
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // work-list words of the expert kernel that follows (its previous launch has completed: this kernel depends on it)
+    if (sched && blockIdx.x == 0) for (uint32_t i = tid; i < n_sched; i += 256) sched[i] = 0;
     double sq = 0.0;
     for (uint32_t c = tid * 4; c < hidden; c += 1024) {
         const size_t i = (size_t)t * hidden + c;
@@ -142,7 +144,7 @@ struct OmegaGpuMoeStack {
     bool fused;
     uint32_t topk, row_cap, x_pieces, tile_rows;
     uint32_t *ids_all; float *wts_all; PlanBatch pb; size_t map_stride, tile_stride;
-    uint8_t *qx; float *sx; char *fused_base;
+    uint8_t *qx; float *sx; char *fused_base; uint32_t *sched; bool one_launch;
     alignas(128) unsigned char tm_qx[128];
 };
 
@@ -161,21 +163,29 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
             cfg.gridDim = dim3(tokens); cfg.blockDim = dim3(256); cfg.stream = s;
             at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = at; cfg.numAttrs = 0;   // measured: launching this kernel (or the down GEMM) as a programmatic dependent is slower
-            return cudaLaunchKernelEx(&cfg, combine_norm_scatter_kernel, H, K, S->eps, x16, w, dn, S->h, pos, Px, pstride, q, S->sx, h16);
+            return cudaLaunchKernelEx(&cfg, combine_norm_scatter_kernel, H, K, S->eps, x16, w, dn, S->h, pos, Px, pstride, q, S->sx, h16, S->sched, (uint32_t)S->tile_stride + 1u);
         };
         if (!cuda_ok(launch_cns(x, nullptr, nullptr, S->pb.pos, S->qx, nullptr), "norm launch")) return false; n++;
         for (uint32_t l = 0; l < Ln; l++) {
             LayerView v; layer_view(S->layers[l], &v);
             const uint32_t *hdr = S->pb.header + (size_t)l * 8;
-            MmaLaunch g = {};
-            g.wscale = v.gu_scale; g.ascale = S->sx; g.tiles = S->pb.tiles + (size_t)l * S->tile_stride; g.header = hdr; g.out = nullptr;
-            g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
-            g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
-            if (!cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true /* weight tiles prefetched while the norm kernel runs */), "gate|up mma launch")) return false; n++;
-            MmaLaunch d = {};
-            d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pb.ymap + (size_t)l * S->map_stride; d.out = v.dn; d.q_rows = S->row_cap;
-            d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
-            if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch")) return false; n++;
+            if (S->one_launch) {
+                FfnLaunch f = {};
+                f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = S->sx; f.qa = v.qa; f.sa = v.sa; f.tiles = S->pb.tiles + (size_t)l * S->tile_stride; f.header = hdr;
+                f.ymap = S->pb.ymap + (size_t)l * S->map_stride; f.out = v.dn; f.hidden = H; f.inter = v.inter; f.q_rows = S->row_cap; f.sched = S->sched;
+                f.err = const_cast<uint32_t *>(hdr) + 4;
+                if (!cuda_ok(launch_ffn(v.tm_gu, S->tm_qx, v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, true), "expert ffn launch")) return false; n++;
+            } else {
+                MmaLaunch g = {};
+                g.wscale = v.gu_scale; g.ascale = S->sx; g.tiles = S->pb.tiles + (size_t)l * S->tile_stride; g.header = hdr; g.out = nullptr;
+                g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
+                g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = const_cast<uint32_t *>(hdr) + 4;
+                if (!cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true /* weight tiles prefetched while the norm kernel runs */), "gate|up mma launch")) return false; n++;
+                MmaLaunch d = {};
+                d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pb.ymap + (size_t)l * S->map_stride; d.out = v.dn; d.q_rows = S->row_cap;
+                d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
+                if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch")) return false; n++;
+            }
             const bool last = l + 1 == Ln;
             if (!cuda_ok(launch_cns(nullptr, S->wts_all + (size_t)l * tokens * K, v.dn, last ? nullptr : S->pb.pos + (size_t)(l + 1) * S->map_stride,
                                     last ? nullptr : S->qx, last ? out16 : nullptr), "combine launch")) return false; n++;
@@ -264,7 +274,7 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
         auto take = [&](size_t bytes) { const size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
         const size_t o_ids = take(Ln * R * 4), o_w = take(Ln * R * 4), o_c = take(Ln * E * 4), o_s = take(Ln * E * 4), o_x = take(Ln * S->map_stride * 4),
                      o_y = take(Ln * S->map_stride * 4), o_p = take(Ln * S->map_stride * 4), o_h = take(Ln * 32), o_t = take(Ln * S->tile_stride * 16),
-                     o_q = take((size_t)v0.x_pieces * Rp * H), o_sx = take(Rp * (H / 128) * 4);
+                     o_q = take((size_t)v0.x_pieces * Rp * H), o_sx = take(Rp * (H / 128) * 4), o_sched = take((S->tile_stride + 1) * 4);
         bool ok = cuda_ok(cudaMalloc(&S->fused_base, off), "cudaMalloc(stack routing)") && cuda_ok(cudaMemset(S->fused_base, 0, off), "memset");
         if (ok) {
             char *f = S->fused_base;
@@ -272,7 +282,9 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
             S->pb.counts = (uint32_t *)(f + o_c); S->pb.starts = (uint32_t *)(f + o_s); S->pb.xmap = (uint32_t *)(f + o_x); S->pb.ymap = (uint32_t *)(f + o_y);
             S->pb.pos = (uint32_t *)(f + o_p); S->pb.header = (uint32_t *)(f + o_h); S->pb.tiles = (uint4 *)(f + o_t);
             S->pb.map_stride = S->map_stride; S->pb.tile_stride = S->tile_stride;
-            S->qx = (uint8_t *)(f + o_q); S->sx = (float *)(f + o_sx);
+            S->qx = (uint8_t *)(f + o_q); S->sx = (float *)(f + o_sx); S->sched = (uint32_t *)(f + o_sched);
+            const bool pieces_ok = (v0.x_pieces == 2 && v0.act_pieces == 3) || (v0.x_pieces == 1 && v0.act_pieces == 1) || (v0.x_pieces == 2 && v0.act_pieces == 2);
+            S->one_launch = pieces_ok && ffn_shape_ok((uint32_t)H, v0.inter) && !getenv("B200MOE_TWO_LAUNCH");
             ok = make_tmap_u8(S->tm_qx, S->qx, (uint64_t)v0.x_pieces * Rp, H, 32);
         }
         if (!ok) { if (S->fused_base) cudaFree(S->fused_base); cudaFree(S->h); delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
