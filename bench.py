@@ -231,35 +231,28 @@ def run_ours(args, rank, world):
         step_host()
     e2e_s = (time.perf_counter() - t0) / args.steps
 
-    # per-kernel device times of single layers (rotating over layers so no launch finds its weights in L2)
-    names_t = (C.c_char_p * 12)(); ms_t = (C.c_float * 12)(); cnt = C.c_uint32(0)
-    per_kernel = {}
-    rounds = 0
-    for rep in range(2):
-        for l in range(Ln):
-            rc = api.lib.omega_gpu_moe_layer_profile(layers[l], C.c_uint32(T), C.c_uint64(logits_d[l].data_ptr()), C.c_uint64(x_d.data_ptr()),
-                                                     C.c_uint64(out32_d.data_ptr()), C.c_uint32(12), ms_t, names_t, C.byref(cnt))
-            assert rc == 0, api.last_error()
-            if rep == 0 and l < 4:
-                continue      # warm-up launches
-            rounds += 1
-            for i in range(cnt.value):
-                per_kernel.setdefault(names_t[i].decode(), []).append(ms_t[i])
-    kern_ms = {k: float(np.mean(v)) for k, v in per_kernel.items()}
-    top = max(kern_ms, key=kern_ms.get)
-    # algorithmic bytes of the dominant kernel per launch: every distinct expert's codes + scales once, plus its input rows
+    # device time of every layer's expert kernel inside one un-graphed step (CUDA events on the launching stream): each layer
+    # streams its own 604 MB of weights, so no launch finds its bytes in L2
+    ms_t = (C.c_float * Ln)(); cnt = C.c_uint32(0); per_layer = C.c_uint32(0)
+    layer_ms = []
+    for rep in range(4):
+        rc = api.lib.omega_gpu_moe_stack_profile(stack, C.c_uint32(T), C.c_uint64(logits_d.data_ptr()), C.c_uint64(x_d.data_ptr()), C.c_uint32(Ln), ms_t, C.byref(cnt), C.byref(per_layer))
+        assert rc == 0, api.last_error()
+        if rep:
+            layer_ms += [ms_t[i] for i in range(cnt.value)]
+    top = "expert_ffn (gate|up + SiLU + pieces -> down, one launch)" if per_layer.value == 1 else "gate|up + down (two launches)"
+    kern_ms = {top: float(np.mean(layer_ms))}
+    # algorithmic bytes of that work per layer: every distinct expert's codes + scales once, plus the layer's input and output rows
     from oracle.oracle import bf16_to_f32
     ids = np.stack([np.argsort(-bf16_to_f32(logits_h[l].numpy().view(np.uint16)), axis=1, kind="stable")[:, :TOPK] for l in range(min(Ln, 4))])
     distinct = float(np.mean([len(np.unique(ids[l])) for l in range(ids.shape[0])]))
-    per_expert = GU_BYTES if top.startswith("gate") else DN_BYTES
-    in_bytes = T * H * 2 if top.startswith("gate") else T * TOPK * I * 4
-    alg_bytes = distinct * per_expert + in_bytes
+    alg_bytes = distinct * (GU_BYTES + DN_BYTES) + 2 * T * H * 2
     peak, peak_kind = measured_peak()
     achieved = alg_bytes / (kern_ms[top] * 1e-3) / 1e9
     traffic = None
     tp = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tp):
-        traffic = json.load(open(tp)).get(top)
+        traffic = json.load(open(tp)).get("expert_ffn" if per_layer.value == 1 else "gate_up_plus_down")
 
     if args.skip_cpu:
         cpu_sec, kind, cores = float("nan"), "skipped", 0

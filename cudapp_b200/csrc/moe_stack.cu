@@ -145,6 +145,7 @@ struct OmegaGpuMoeStack {
     uint32_t topk, row_cap, x_pieces, tile_rows;
     uint32_t *ids_all; float *wts_all; PlanBatch pb; size_t map_stride, tile_stride;
     uint8_t *qx; float *sx; char *fused_base; uint32_t *sched; bool one_launch;
+    cudaEvent_t *prof;   // when set (2 per layer): recorded before and after each layer's expert kernel(s)
     alignas(128) unsigned char tm_qx[128];
 };
 
@@ -169,6 +170,7 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
         for (uint32_t l = 0; l < Ln; l++) {
             LayerView v; layer_view(S->layers[l], &v);
             const uint32_t *hdr = S->pb.header + (size_t)l * 8;
+            if (S->prof) cudaEventRecord(S->prof[2 * l], s);
             if (S->one_launch) {
                 FfnLaunch f = {};
                 f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = S->sx; f.qa = v.qa; f.sa = v.sa; f.tiles = S->pb.tiles + (size_t)l * S->tile_stride; f.header = hdr;
@@ -186,6 +188,7 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
                 d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
                 if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch")) return false; n++;
             }
+            if (S->prof) cudaEventRecord(S->prof[2 * l + 1], s);
             const bool last = l + 1 == Ln;
             if (!cuda_ok(launch_cns(nullptr, S->wts_all + (size_t)l * tokens * K, v.dn, last ? nullptr : S->pb.pos + (size_t)(l + 1) * S->map_stride,
                                     last ? nullptr : S->qx, last ? out16 : nullptr), "combine launch")) return false; n++;
@@ -244,7 +247,7 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     OmegaGpuMoeStack *S = new OmegaGpuMoeStack();
-    S->eps = eps; S->graph = nullptr; S->graph_tokens = 0; S->launches = 0;
+    S->eps = eps; S->graph = nullptr; S->graph_tokens = 0; S->launches = 0; S->prof = nullptr;
     layer_dims(layer[0], &S->experts, &S->hidden, &S->max_tokens);
     for (uint32_t i = 0; i < layers; i++) {
         uint32_t e, h, mt; layer_dims(layer[i], &e, &h, &mt);
@@ -303,6 +306,27 @@ void omega_gpu_moe_stack_free(OmegaGpuMoeStack *S) {
 }
 
 uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *S) { return S ? S->launches : 0; }
+
+int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *S, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint32_t cap, float *expert_ms, uint32_t *count, uint32_t *launches_per_layer) {
+    if (!S || !tokens || !logits_va || !x_va || !expert_ms || !count || !cap) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (tokens > S->max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
+    if (!S->fused) { set_error("moe stack profile: only the tensor-core path records per-layer times"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const uint32_t Ln = (uint32_t)S->layers.size();
+    std::vector<cudaEvent_t> ev(2 * Ln);
+    for (auto &e : ev) if (!cuda_ok(cudaEventCreate(&e), "cudaEventCreate")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    cudaStream_t s = st().stream;
+    S->prof = ev.data();
+    bool ok = stack_record(S, tokens, (const uint16_t *)(uintptr_t)logits_va, (const uint16_t *)(uintptr_t)x_va, nullptr, S->out16, s);
+    S->prof = nullptr;
+    ok = ok && cuda_ok(cudaStreamSynchronize(s), "moe stack profile");
+    *count = 0;
+    for (uint32_t i = 0; ok && i < Ln && i < cap; i++) { float t = 0; ok = cuda_ok(cudaEventElapsedTime(&t, ev[2 * i], ev[2 * i + 1]), "event time"); expert_ms[i] = t; *count = i + 1; }
+    for (auto &e : ev) cudaEventDestroy(e);
+    if (launches_per_layer) *launches_per_layer = S->one_launch ? 1u : 2u;
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
 
 int omega_gpu_moe_stack_async(OmegaGpuMoeStack *S, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va, uint64_t out_bf16_va, void *stream) {
     if (!S || !tokens || !logits_va || !x_va || (!out_f32_va && !out_bf16_va)) return OMEGA_GPU_FP8_BAD_ARGS;

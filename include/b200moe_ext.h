@@ -113,6 +113,10 @@ int omega_gpu_moe_stack_bf16(OmegaGpuMoeStack *s, uint32_t tokens, const uint16_
 int omega_gpu_moe_stack_async(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
                               uint64_t out_bf16_va, void *stream);
 uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *s);
+/* One step launched without the graph, a CUDA event before and after each layer's expert kernel(s): expert_ms[l] = device
+ * time of layer l's gate|up + down work (one launch when *launches_per_layer is 1). Tensor-core path only. For measurement. */
+int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint32_t cap, float *expert_ms,
+                                uint32_t *count, uint32_t *launches_per_layer);
 
 /* ---- residual stream step as one call (the stack uses it; exposed for callers that drive layers themselves):
  * h = (x16 ? bf16->f32(x16) : h) + (m ? m : 0); xn = bf16(RMSNorm(h)) when xn_va != 0; h16 = bf16(h) when h16_va != 0 */
