@@ -22,6 +22,9 @@ struct FfnArgs {
     uint32_t hidden, inter, q_rows;
     uint32_t *sched;                               // [0]: next down unit; [1 + tile]: gate|up units of that tile finished (zeroed by the plan kernel)
     uint32_t *err;
+    // expert parallelism (null / 0 on one GPU): wait until peers have delivered header[0] input rows past *gate_base; down results go to the
+    // owning rank's buffer (row y -> rank y / rows_per_rank) and each owner's counter [ret_index] is advanced once per delivered 256-feature slice
+    const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index;
 };
 
 constexpr uint32_t FFN_RING = 64;                 // ring of published down-unit ids; the producer is never more than a few units ahead of the slowest role
@@ -33,6 +36,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     constexpr int STAGES = PMAX <= 3 ? 4 : 3;
     constexpr uint32_t STAGE_BYTES = 2 * A_TILE + PMAX * B_PIECE;
     constexpr uint32_t TMEM_COLS = 4 * NMAX <= 128 ? 128 : 4 * NMAX <= 256 ? 256 : 512;
+    constexpr uint32_t Q_GROUP_BYTES = PA * MMA_TOK * 128;   // per epilogue group: PA pieces x 32 rows x 128 bytes of output codes
     extern __shared__ uint8_t dyn_smem[];
     __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 12];
     __shared__ uint32_t s_tmem, s_abort;
@@ -41,6 +45,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     __shared__ uint32_t s_ymap[2][MMA_TOK];
     __shared__ volatile uint32_t s_units[FFN_RING];   // down units this CTA took, in order (slot = index % FFN_RING); 0xffffffff = no more
     __shared__ volatile uint32_t s_published;
+    __shared__ uint32_t s_ret[2][64];             // [epilogue group][rank]: result slices stored into that rank's buffer (expert parallel)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
     const uint32_t bar0 = smem_u32(s_bar);
@@ -54,6 +59,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     auto turn_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 10 + g); };
     volatile uint32_t *abort_flag = &s_abort;
 
+    if (threadIdx.x < 128) s_ret[threadIdx.x >> 6][threadIdx.x & 63u] = 0;
     if (threadIdx.x == 0) {
         s_abort = 0; s_published = 0;
         for (uint32_t s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -147,6 +153,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                         tma_load_2d(dst + A_TILE, mw, full_bar(kb), (int)(kb * 128u), wy1);
                     }
                     griddep_wait(); griddep_launch();
+                    if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13))) { *abort_flag = 1; break; }
                     if (q.mode && !(ok = tile_ready(q.tile, 21))) break;
                     for (uint32_t kb = 0; kb < npre; kb++)
                         for (uint32_t p = 0; p < P; p++)
@@ -199,6 +206,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
         // ---------------------------------------------------------------- scale loader
         bool ok = true;
         griddep_wait();
+        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 14)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
         for (uint32_t n = 0; ok; n++) {
             uint32_t u = 0, have = 0;
             if (lane == 0) have = unit_at(n, u) ? 1u : 0u;
@@ -295,7 +303,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                 const float sc = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][lane], s_red[g][1][lane]), fmaxf(s_red[g][2][lane], s_red[g][3][lane])));
                 const float inv = __uint_as_float((254u - (__float_as_uint(sc) >> 23)) << 23);
                 if (q4 == 0 && lane < cnt) a.sa[(size_t)(t.y + lane) * KBA + q.j] = sc;
-                uint8_t *sq = dyn_smem + (smem_base - smem_u32(dyn_smem)) + STAGES * STAGE_BYTES + g * (Q_STAGE_BYTES / 2);
+                uint8_t *sq = dyn_smem + (smem_base - smem_u32(dyn_smem)) + STAGES * STAGE_BYTES + g * Q_GROUP_BYTES;
 #pragma unroll
                 for (int i = 0; i < MMA_TOK; i += 2) {
                     float ra = acc0[i] * __shfl_sync(0xffffffffu, inv, i), rb = acc0[i + 1] * __shfl_sync(0xffffffffu, inv, i + 1);
@@ -319,15 +327,30 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                 mbar_arrive(group_bar(g));
                 if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 10))) break;
                 if (et == 0) atomicAdd(a.sched + 1 + q.tile, 1u);
-            } else {
+            } else if (!a.out_peers) {
 #pragma unroll
                 for (int i = 0; i < MMA_TOK; i++)
                     if ((uint32_t)i < cnt) {
                         float *o = a.out + (size_t)s_ymap[b][i] * H;
                         o[q.r0 + row] = acc0[i]; o[q.r1 + row] = acc1[i];
                     }
+            } else {
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i++)
+                    if ((uint32_t)i < cnt) {
+                        const uint32_t y = s_ymap[b][i], owner = y / a.rows_per_rank;
+                        float *o = reinterpret_cast<float *>(a.out_peers[owner]) + (size_t)(y - owner * a.rows_per_rank) * H;
+                        o[q.r0 + row] = acc0[i]; o[q.r1 + row] = acc1[i];
+                    }
+                if (et < cnt) atomicAdd(&s_ret[g][s_ymap[b][et] / a.rows_per_rank], 1u);   // published once, after the last unit
             }
             mbar_arrive(scempty_bar(b));
+        }
+        if (a.out_peers && ok) {
+            __threadfence_system();
+            mbar_arrive(group_bar(g));
+            if (mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15) && et < 64u && s_ret[g][et])
+                atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[et]) + a.ret_index, (unsigned long long)s_ret[g][et]);
         }
     }
     if (*abort_flag) { for (int i = 0; i < 64; i++) __nanosleep(1000); }
@@ -342,12 +365,13 @@ cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, 
     FfnArgs a = {};
     a.gu_scale = m.gu_scale; a.dn_scale = m.dn_scale; a.x_scale = m.x_scale; a.qa = m.qa; a.sa = m.sa; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap;
     a.out = m.out; a.hidden = m.hidden; a.inter = m.inter; a.q_rows = m.q_rows; a.sched = m.sched; a.err = m.err;
+    a.gate = m.gate; a.gate_base = m.gate_base; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index;
     const int sms = st().sm_count ? st().sm_count : 148;
     const CUtensorMap *w0 = (const CUtensorMap *)tm_gu, *q0 = (const CUtensorMap *)tm_qx, *w1 = (const CUtensorMap *)tm_dn, *q1 = (const CUtensorMap *)tm_qa;
 #define LAUNCH(PXV, PAV)                                                                                                                \
     do {                                                                                                                                \
         constexpr int PM = (PXV) > (PAV) ? (PXV) : (PAV);                                                                               \
-        const size_t smem = (size_t)(PM <= 3 ? 4 : 3) * (2 * A_TILE + PM * B_PIECE) + Q_STAGE_BYTES + 1024;                             \
+        const size_t smem = (size_t)(PM <= 3 ? 4 : 3) * (2 * A_TILE + PM * B_PIECE) + 2 * (PAV) * MMA_TOK * 128 + 1024;                             \
         static bool attr = false;                                                                                                       \
         if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_ffn_kernel<PXV, PAV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
         cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];                                                                         \

@@ -112,6 +112,7 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
 struct FfnLaunch {
     const float *gu_scale, *dn_scale, *x_scale; uint8_t *qa; float *sa; const void *tiles; const uint32_t *header, *ymap; float *out;
     uint32_t hidden, inter, q_rows; uint32_t *sched, *err;   // sched: [0] next down unit, [1 + tile] finished gate|up units; zeroed before the launch
+    const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index;   // expert parallelism, as in MmaLaunch
 };
 bool ffn_shape_ok(uint32_t hidden, uint32_t inter);
 cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, const void *tm_qa, uint32_t px, uint32_t pa, const FfnLaunch &m, cudaStream_t s, bool pdl);

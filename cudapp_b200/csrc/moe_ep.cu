@@ -297,7 +297,7 @@ struct OmegaGpuMoeEpStack {
     b200::PlanBatch pg, pl; size_t map_stride, tile_stride;
     uint8_t *comm; size_t comm_bytes, off_sx, off_dn, off_cnt;   // peers map this block: pieces | scales | results | counters
     uint64_t *peer_tab;                  // device [4][world]: pieces, scales, results, counters of every rank
-    float *h; uint32_t *err;
+    float *h; uint32_t *err, *sched; bool one_launch;
     void *opened[64]; int n_opened; int connected;
     alignas(128) unsigned char tm_qx[128];
     uint32_t launches;
@@ -319,13 +319,20 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         const unsigned long long *ret_gate, unsigned long long ret_unit, const uint32_t *step, uint32_t uses_per_step, uint32_t uses_before,
         const uint32_t *__restrict__ ids_next, const uint32_t *__restrict__ pos_next, const uint32_t *__restrict__ starts_next, uint32_t experts_local,
         uint32_t pieces, size_t piece_stride, const uint64_t *__restrict__ q_peers, const uint64_t *__restrict__ sx_peers, const uint64_t *__restrict__ cnt_peers,
-        uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err) {
+        uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err, uint32_t *__restrict__ sched, uint32_t n_sched,
+        unsigned long long *bump, const uint32_t *bump_rows) {
     __shared__ double red[8];
     __shared__ float s_scale;
     __shared__ uint32_t s_d[32], s_row[32], s_fail;
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next gate|up GEMM may start fetching weights
+    // the expert kernel before this one has completed: clear its work-list words for the next launch, and count the input rows its
+    // layer consumed (the delivery counters only grow)
+    if (blockIdx.x == 0) {
+        if (sched) for (uint32_t i = tid; i < n_sched; i += 256) sched[i] = 0;
+        if (bump && tid == 0) *bump += *bump_rows;
+    }
     if (tid == 0) {
         s_fail = *reinterpret_cast<volatile uint32_t *>(err) ? 1u : 0u;
         if (!s_fail && dn && ret_gate) {
@@ -452,7 +459,7 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
         o_pb[b][0] = take(Ln * E * 4); o_pb[b][1] = take(Ln * E * 4); o_pb[b][2] = take(Ln * S->map_stride * 4); o_pb[b][3] = take(Ln * S->map_stride * 4);
         o_pb[b][4] = take(Ln * S->map_stride * 4); o_pb[b][5] = take(Ln * 32); o_pb[b][6] = take(Ln * S->tile_stride * 16);
     }
-    const size_t o_h = take((size_t)S->tokens_local * H * 4), o_err = take(64);
+    const size_t o_h = take((size_t)S->tokens_local * H * 4), o_err = take(64), o_sched = take((S->tile_stride + 1) * 4);
     bool ok = cuda_ok(cudaMalloc(&S->route, off), "cudaMalloc(ep routing)") && cuda_ok(cudaMemset(S->route, 0, off), "memset");
     if (ok) {
         char *f = S->route;
@@ -463,7 +470,9 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
             pb[b]->ymap = (uint32_t *)(f + o_pb[b][3]); pb[b]->pos = (uint32_t *)(f + o_pb[b][4]); pb[b]->header = (uint32_t *)(f + o_pb[b][5]);
             pb[b]->tiles = (uint4 *)(f + o_pb[b][6]); pb[b]->map_stride = S->map_stride; pb[b]->tile_stride = S->tile_stride;
         }
-        S->h = (float *)(f + o_h); S->err = (uint32_t *)(f + o_err);
+        S->h = (float *)(f + o_h); S->err = (uint32_t *)(f + o_err); S->sched = (uint32_t *)(f + o_sched);
+        S->one_launch = ((v0.x_pieces == 2 && v0.act_pieces == 3) || (v0.x_pieces == 1 && v0.act_pieces == 1) || (v0.x_pieces == 2 && v0.act_pieces == 2)) &&
+                        ffn_shape_ok(v0.hidden, v0.inter) && !getenv("B200MOE_TWO_LAUNCH");
         // the block peers write into: activation pieces | their scales | result rows of the local tokens | counters
         const size_t qb = ((size_t)S->x_pieces * Rp * H + 255) & ~(size_t)255, sb = (Rp * (H / 128) * 4 + 255) & ~(size_t)255, db = ((size_t)S->tokens_local * K * H * 4 + 255) & ~(size_t)255;
         S->off_sx = qb; S->off_dn = qb + sb; S->off_cnt = qb + sb + db; S->comm_bytes = S->off_cnt + 256;
@@ -546,28 +555,39 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
     const unsigned long long ret_unit = (unsigned long long)Tl * K * (H / 256u);
     unsigned long long *base = (unsigned long long *)(S->err + 8);   // [0..1]: input rows already consumed through the even / odd layer counter
     ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull, S->err + 4, 0u, 0u,
-                                                      S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err); n++;
+                                                      S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err,
+                                                      S->sched, (uint32_t)S->tile_stride + 1u, nullptr, nullptr); n++;
     for (uint32_t l = 0; l < Ln && ok; l++) {
         LayerView v; layer_view(S->local[l], &v);
         const uint32_t par = l & 1u;
         const uint32_t *hdr = S->pl.header + (size_t)l * 8;
-        MmaLaunch g = {};
-        g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
-        g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
-        g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = S->err;   // one failure word for the whole step: later kernels see it and do nothing
-        g.gate = cnt + par; g.gate_base = base + par;
-        ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true), "gate|up mma launch"); n++;
-        MmaLaunch d = {};
-        d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
-        d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
-        d.out_peers = tab + 2 * G; d.ret_counters = tab + 3 * G; d.ret_index = 2 + par; d.rows_per_rank = Tl * K; d.bump = base + par;
-        ok = ok && cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch"); n++;
+        if (S->one_launch) {
+            FfnLaunch f = {};
+            f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = (const float *)(S->comm + S->off_sx); f.qa = v.qa; f.sa = v.sa;
+            f.tiles = S->pl.tiles + (size_t)l * S->tile_stride; f.header = hdr; f.ymap = S->pl.ymap + (size_t)l * S->map_stride; f.out = dn_local;
+            f.hidden = H; f.inter = v.inter; f.q_rows = S->row_cap; f.sched = S->sched; f.err = S->err;
+            f.gate = cnt + par; f.gate_base = base + par; f.out_peers = tab + 2 * G; f.ret_counters = tab + 3 * G; f.rows_per_rank = Tl * K; f.ret_index = 2 + par;
+            ok = cuda_ok(launch_ffn(v.tm_gu, S->tm_qx, v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, true), "expert ffn launch"); n++;
+        } else {
+            MmaLaunch g = {};
+            g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
+            g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
+            g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = S->err;   // one failure word for the whole step: later kernels see it and do nothing
+            g.gate = cnt + par; g.gate_base = base + par;
+            ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true), "gate|up mma launch"); n++;
+            MmaLaunch d = {};
+            d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
+            d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
+            d.out_peers = tab + 2 * G; d.ret_counters = tab + 3 * G; d.ret_index = 2 + par; d.rows_per_rank = Tl * K; d.bump = base + par;
+            ok = ok && cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch"); n++;
+        }
         const bool last = l + 1 == Ln;
         const size_t nx = (size_t)(l + 1) * S->map_stride;
         if (ok) ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_g + (size_t)l * R + tok0, dn_local, S->h, cnt + 2 + par, ret_unit, S->err + 4, (Ln + 1u - par) / 2u, l / 2u,
                                                                   last ? nullptr : S->ids_g + (size_t)(l + 1) * R + tok0, last ? nullptr : S->pg.pos + nx + tok0,
                                                                   last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, last ? nullptr : tab, tab + G, tab + 3 * G,
-                                                                  par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err);
+                                                                  par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err,
+                                                                  S->sched, (uint32_t)S->tile_stride + 1u, S->one_launch ? base + par : nullptr, hdr);
         n++;
     }
     S->launches = n;
