@@ -1,0 +1,265 @@
+// fp8_mma_wide_sm100.cu: the grouped FP8 GEMM of fp8_mma_sm100.cu shaped for prefill-sized segments.
+//
+// Same arithmetic (weights as uploaded, activations as plain e4m3 with one power-of-two scale per (row, 128 columns), block-scale
+// promotion per 128-wide K block in f32 registers; src/omega_blackwell_codegen_qg.h:7-37 in the reference), same operand
+// mapping (weight tile = the MMA's M operand, routed rows = N), but a row tile holds 128 rows instead of 32: every weight byte that
+// reaches shared memory is used for four times as many rows, which is what a compute-bound grouped GEMM needs. One persistent
+// CTA per SM, 19 warps: TMA producer, MMA issuer, scale loader, and four groups of four promotion/epilogue warps; group g owns
+// rows [32g, 32g+32) of the tile = accumulator columns [32g, 32g+32) of both weight tiles of the unit. A unit of work is
+// (row tile, pair of 128-feature blocks) as in the narrow kernel; per 128-wide K block 2 x 4 MMAs (M 128, N 128, K 32) go into a
+// double-buffered TMEM partial (2 x 2 x 128 columns = all 512), and all four groups drain it. Only single-piece activations
+// (x_pieces = act_pieces = 1) take this path; k <= 2048.
+//
+// Every mbarrier wait is bounded; on expiry the kernel records a code in *err, lets its own copies land, frees its TMEM and returns.
+#include "internal.h"
+#include "mma_common.cuh"
+
+namespace b200 {
+
+constexpr int WIDE_GROUPS = 4;
+constexpr int WIDE_ROWS = WIDE_GROUPS * MMA_TOK;                  // 128 routed rows per tile
+constexpr int WIDE_THREADS = 32 * (3 + 4 * WIDE_GROUPS);          // 608
+constexpr int WIDE_STAGES = 3;
+constexpr int WIDE_KB_MAX = 16;
+constexpr uint32_t WIDE_STAGE_BYTES = 2 * A_TILE + WIDE_GROUPS * B_PIECE;   // 48 KB: two weight tiles + 128 activation rows
+constexpr uint32_t WIDE_Q_BYTES = MMA_TOK * 128;                  // per group: 32 rows x 128 output codes
+constexpr uint32_t WIDE_SC_FLOATS = 2 * 2 * WIDE_KB_MAX * WIDE_ROWS;       // [scale buffer][weight tile][k block][row]
+constexpr size_t WIDE_SMEM = (size_t)WIDE_STAGES * WIDE_STAGE_BYTES + WIDE_GROUPS * WIDE_Q_BYTES + WIDE_SC_FLOATS * 4 + 1024;
+
+struct WideArgs {
+    const float *wscale, *ascale;
+    const uint4 *tiles; const uint32_t *header;
+    const uint32_t *ymap;
+    float *out;                      // mode 1: y rows
+    uint8_t *q_out; float *s_out;    // mode 0: gated activations as e4m3 [q_rows][inter] + scales [row][inter/128]
+    uint32_t n, k, pairs, mode, inter, out_stride, q_rows;
+    uint32_t *err;
+};
+
+__global__ void __launch_bounds__(WIDE_THREADS, 1) fp8_mma_wide_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const WideArgs a) {
+    constexpr int N = WIDE_ROWS;
+    constexpr uint32_t TMEM_COLS = 512;                                   // 2 buffers x 2 accumulators x 128 columns
+    constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // f8f6f4, D f32, A = B = e4m3 K-major, M 128
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t s_bar[2 * WIDE_STAGES + 8 + WIDE_GROUPS];
+    __shared__ uint32_t s_tmem, s_abort;
+    __shared__ float s_red[WIDE_GROUPS][4][MMA_TOK];   // [group][warp][row]: amax exchange
+    __shared__ uint32_t s_ymap[2][WIDE_ROWS];          // [scale buffer][row]: destination rows (mode 1)
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
+    uint8_t *smem_gen = dyn_smem + (smem_base - smem_u32(dyn_smem));
+    uint8_t *q_stage = smem_gen + WIDE_STAGES * WIDE_STAGE_BYTES;
+    float *s_sc = reinterpret_cast<float *>(q_stage + WIDE_GROUPS * WIDE_Q_BYTES);
+    auto sc_at = [&](uint32_t b, uint32_t half, uint32_t kb) { return s_sc + ((b * 2u + half) * WIDE_KB_MAX + kb) * WIDE_ROWS; };
+    const uint32_t bar0 = smem_u32(s_bar);
+    auto full_bar = [&](uint32_t s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bar0 + 8u * (WIDE_STAGES + s); };
+    auto accfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * WIDE_STAGES + b); };
+    auto accempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * WIDE_STAGES + 2 + b); };
+    auto scfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * WIDE_STAGES + 4 + b); };
+    auto scempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * WIDE_STAGES + 6 + b); };
+    auto group_bar = [&](uint32_t g) { return bar0 + 8u * (2 * WIDE_STAGES + 8 + g); };
+    volatile uint32_t *abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (uint32_t s = 0; s < WIDE_STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (uint32_t b = 0; b < 2; b++) {
+            mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128 * WIDE_GROUPS);
+            mbar_init(scfull_bar(b), 32); mbar_init(scempty_bar(b), 128 * WIDE_GROUPS);
+        }
+        for (uint32_t g = 0; g < WIDE_GROUPS; g++) mbar_init(group_bar(g), 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // TMEM allocation by one whole warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t KB = a.k / 128u, n_tiles = a.header[2], total = *reinterpret_cast<volatile uint32_t *>(a.err) ? 0u : n_tiles * a.pairs;   // after a recorded failure: no work
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0; bool ok = true;
+            for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
+                const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs;
+                const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+                const int wy0 = (int)(t.x * a.n + r0), wy1 = (int)(t.x * a.n + r1);
+                for (uint32_t kb = 0; kb < KB; kb++, it++) {
+                    const uint32_t s = it % WIDE_STAGES, ph = (it / WIDE_STAGES) & 1u;
+                    const uint32_t dst = smem_base + s * WIDE_STAGE_BYTES;
+                    if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
+                    mbar_expect_tx(full_bar(s), WIDE_STAGE_BYTES);
+                    tma_load_2d(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0);
+                    tma_load_2d(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1);
+#pragma unroll
+                    for (int g = 0; g < WIDE_GROUPS; g++)   // 32 rows x 128 bytes each; rows past the segment belong to nobody and are never stored
+                        tma_load_2d(dst + 2 * A_TILE + g * B_PIECE, &tm_q, full_bar(s), (int)(kb * 128u), (int)(t.y + g * MMA_TOK));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0; bool ok = true;
+            for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x) {
+                for (uint32_t kb = 0; kb < KB; kb++, it++) {
+                    const uint32_t s = it % WIDE_STAGES, ph = (it / WIDE_STAGES) & 1u, buf = it & 1u, bph = (it >> 1) & 1u;
+                    if (!(ok = mbar_wait(accempty_bar(buf), bph ^ 1u, abort_flag, a.err, 2))) break;
+                    if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, a.err, 3))) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * WIDE_STAGE_BYTES;
+                    const uint64_t da0 = umma_desc(sa), da1 = umma_desc(sa + A_TILE), db = umma_desc(sa + 2 * A_TILE);
+                    const uint32_t d0 = tmem + buf * 2u * N, d1 = d0 + N;
+#pragma unroll
+                    for (uint32_t ks = 0; ks < 4; ks++) {   // 32 K bytes per MMA: advance the start address inside the swizzle row
+                        tc_mma_f8(d0, da0 + 2u * ks, db + 2u * ks, IDESC, ks);
+                        tc_mma_f8(d1, da1 + 2u * ks, db + 2u * ks, IDESC, ks);
+                    }
+                    tc_commit(empty_bar(s));       // the stage is free once these MMAs have read it
+                    tc_commit(accfull_bar(buf));   // the partial is complete
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
+        uint32_t n = 0; bool ok = true;
+        for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
+            const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
+            const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+            if (!(ok = mbar_wait(scempty_bar(b), ((n >> 1) & 1u) ^ 1u, abort_flag, a.err, 7))) break;
+            if (a.mode == 1) for (uint32_t r = lane; r < WIDE_ROWS; r += 32u) s_ymap[b][r] = r < t.z ? a.ymap[t.y + r] : 0u;
+            const float *w0 = a.wscale + ((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB, *w1 = a.wscale + ((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB;
+            // the tile's row scales are one contiguous block [row][k block]: read it coalesced, scatter to [k block][row]
+            const float *as = a.ascale + (size_t)t.y * KB;
+            const uint32_t total_sc = WIDE_ROWS * KB;
+#pragma unroll 4
+            for (uint32_t idx = lane; idx < total_sc; idx += 32u) {
+                const uint32_t r = idx / KB, kb = idx - r * KB;
+                const float cs = r < t.z ? as[idx] : 0.0f;
+                sc_at(b, 0, kb)[r] = __ldg(w0 + kb) * cs;
+                sc_at(b, 1, kb)[r] = __ldg(w1 + kb) * cs;
+            }
+            mbar_arrive(scfull_bar(b));
+        }
+    } else {
+        // ---------------------------------------------------------------- promotion + epilogue: group g owns rows [32g, 32g+32) of every tile
+        const uint32_t g = (warp - 3u) >> 2, q = warp & 3u, row = q * 32u + lane;   // q: the TMEM lane quarter this warp may read
+        const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;                       // thread index inside the group
+        uint32_t n = 0, gsync = 0; bool ok = true;
+        for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
+            const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
+            const uint32_t row_off = g * MMA_TOK, cnt = t.z > row_off ? min(t.z - row_off, (uint32_t)MMA_TOK) : 0u, y0 = t.y + row_off;
+            const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
+            if (!(ok = mbar_wait(scfull_bar(b), (n >> 1) & 1u, abort_flag, a.err, 8))) break;
+            float acc0[MMA_TOK], acc1[MMA_TOK];
+#pragma unroll
+            for (int i = 0; i < MMA_TOK; i++) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
+            for (uint32_t kb = 0; kb < KB; kb++) {
+                const uint32_t it = n * KB + kb, buf = it & 1u, bph = (it >> 1) & 1u;
+                if (!(ok = mbar_wait(accfull_bar(buf), bph, abort_flag, a.err, 4))) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem + ((q * 32u) << 16) + buf * 2u * N + row_off;
+#pragma unroll
+                for (int part = 0; part < 4; part++) {   // (weight tile, 16-column half of this group's rows)
+                    const int half = part >> 1, c0 = (part & 1) * 16;
+                    uint32_t da[16];
+                    TMEM_LD16(taddr + half * N + c0, da, 0);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (part == 3) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // this group's share of the partial is in registers
+                    const float4 *sc4 = reinterpret_cast<const float4 *>(sc_at(b, half, kb) + row_off + c0);
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4) {
+                        const float4 sc = sc4[i >> 2];
+                        if (half) {
+                            acc1[c0 + i] = fmaf(__uint_as_float(da[i]), sc.x, acc1[c0 + i]); acc1[c0 + i + 1] = fmaf(__uint_as_float(da[i + 1]), sc.y, acc1[c0 + i + 1]);
+                            acc1[c0 + i + 2] = fmaf(__uint_as_float(da[i + 2]), sc.z, acc1[c0 + i + 2]); acc1[c0 + i + 3] = fmaf(__uint_as_float(da[i + 3]), sc.w, acc1[c0 + i + 3]);
+                        } else {
+                            acc0[c0 + i] = fmaf(__uint_as_float(da[i]), sc.x, acc0[c0 + i]); acc0[c0 + i + 1] = fmaf(__uint_as_float(da[i + 1]), sc.y, acc0[c0 + i + 1]);
+                            acc0[c0 + i + 2] = fmaf(__uint_as_float(da[i + 2]), sc.z, acc0[c0 + i + 2]); acc0[c0 + i + 3] = fmaf(__uint_as_float(da[i + 3]), sc.w, acc0[c0 + i + 3]);
+                        }
+                    }
+                }
+            }
+            if (!ok) break;
+            if (a.mode == 0) {
+                // ---- SiLU gate, then the gated activations leave as e4m3 with one scale per (row, this unit's 128 features)
+                float m[MMA_TOK];
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i++) { acc0[i] = silu_mul_dev(acc0[i], acc1[i]); m[i] = fabsf(acc0[i]); }
+                // per-row maximum over the warp's 32 features: butterfly that halves the rows kept per lane (lane l ends with row l)
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) {
+                    const bool up = (lane & (uint32_t)o) != 0;
+#pragma unroll
+                    for (int jj = 0; jj < o; jj++) {
+                        const float keep = up ? m[jj + o] : m[jj], send = up ? m[jj] : m[jj + o];
+                        m[jj] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, o));
+                    }
+                }
+                s_red[g][q][lane] = m[0];
+                mbar_arrive(group_bar(g));
+                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 5))) break;
+                // lane = row: maximum over the four warps, power-of-two scale and its exact reciprocal
+                const float sc = pq_scale_mma(fmaxf(fmaxf(s_red[g][0][lane], s_red[g][1][lane]), fmaxf(s_red[g][2][lane], s_red[g][3][lane])));
+                const float inv = __uint_as_float((254u - (__float_as_uint(sc) >> 23)) << 23);
+                if (q == 0 && lane < cnt) a.s_out[(size_t)(y0 + lane) * (a.inter / 128u) + j] = sc;
+                uint8_t *sq = q_stage + g * WIDE_Q_BYTES;   // [row][128 features]
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i += 2) {
+                    const uint32_t code = enc2(acc0[i] * __shfl_sync(0xffffffffu, inv, i), acc0[i + 1] * __shfl_sync(0xffffffffu, inv, i + 1));
+                    sq[i * 128u + row] = (uint8_t)(code & 0xffu);
+                    sq[(i + 1) * 128u + row] = (uint8_t)(code >> 8);
+                }
+                mbar_arrive(group_bar(g));
+                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 6))) break;
+                // copy out: every row is 128 consecutive bytes in memory; 16 bytes per thread per step
+                for (uint32_t c = et; c < MMA_TOK * 8u; c += 128u) {
+                    const uint32_t i = c >> 3;
+                    if (i < cnt) *reinterpret_cast<uint4 *>(a.q_out + (size_t)(y0 + i) * a.inter + j * 128u + (c & 7u) * 16u) = *reinterpret_cast<const uint4 *>(sq + (size_t)c * 16u);
+                }
+                // the staging tile is reused by the next unit: everybody has copied before anybody writes it again
+                mbar_arrive(group_bar(g));
+                if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 10))) break;
+            } else {
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i++)
+                    if ((uint32_t)i < cnt) {
+                        float *o = a.out + (size_t)s_ymap[b][row_off + i] * a.out_stride;
+                        o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
+                    }
+            }
+            mbar_arrive(scempty_bar(b));   // this unit's scales and destination rows may be overwritten
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) { for (int i = 0; i < 64; i++) __nanosleep(1000); }   // let copies already issued land before the CTA goes away
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+uint32_t mma_wide_tile_rows() { return WIDE_ROWS; }
+bool mma_wide_shape_ok(uint32_t n, uint32_t k, uint32_t mode) { return k % 128u == 0 && k <= 128u * WIDE_KB_MAX && n % 256u == 0 && (mode == 1 || (n / 2u) % 128u == 0); }
+
+cudaError_t launch_mma_wide(const void *tm_w, const void *tm_q, const MmaLaunch &m, cudaStream_t s) {
+    WideArgs a = {};
+    a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
+    a.q_out = m.q_out; a.s_out = m.s_out; a.q_rows = m.q_rows;
+    a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(fp8_mma_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WIDE_SMEM);
+        if (e != cudaSuccess) return e;
+        attr = true;
+    }
+    const int sms = st().sm_count ? st().sm_count : 148;
+    fp8_mma_wide_kernel<<<sms, WIDE_THREADS, WIDE_SMEM, s>>>(*(const CUtensorMap *)tm_w, *(const CUtensorMap *)tm_q, a);
+    return cudaGetLastError();
+}
+
+}  // namespace b200

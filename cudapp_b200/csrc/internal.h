@@ -108,6 +108,10 @@ bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols,
 uint32_t mma_tile_rows(uint32_t pieces);
 bool mma_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
 cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t pieces, const MmaLaunch &m, cudaStream_t s, bool pdl = false);
+// the same GEMM on 128-row tiles for prefill-sized segments (fp8_mma_wide_sm100.cu); single-piece activations only, no expert-parallel fields
+uint32_t mma_wide_tile_rows();
+bool mma_wide_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
+cudaError_t launch_mma_wide(const void *tm_w, const void *tm_q, const MmaLaunch &m, cudaStream_t s);
 // whole expert FFN of a layer in one launch (fp8_ffn_sm100.cu); piece counts (2,3), (1,1) or (2,2)
 struct FfnLaunch {
     const float *gu_scale, *dn_scale, *x_scale; uint8_t *qa; float *sa; const void *tiles; const uint32_t *header, *ymap; float *out;

@@ -72,6 +72,12 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
                    "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) \
                  : "r"(taddr))
 
+#define TMEM_LD16(taddr, r, o)                                                                                                           \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"                   \
+                 : "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7]),      \
+                   "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]), "=r"(r[o + 12]), "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15]) \
+                 : "r"(taddr))
+
 // SiLU gate with the fast exponential and division (the reference kernel itself uses EX2 / RCP approximations here,
 // src/omega_blackwell_codegen_dec.c:291-324)
 __device__ __forceinline__ float silu_mul_dev(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }

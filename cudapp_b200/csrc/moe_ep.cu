@@ -284,8 +284,10 @@ int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream) {
 //       buffers (peer stores), one system-scope atomic per delivered row on the receiver's counter;
 //   gate|up GEMM: waits (bounded) until the counter shows every row of its plan, then runs as on one GPU;
 //   down GEMM: stores every result row straight into its token owner's buffer and advances the owner's counter;
-// and the next combine waits for its tokens' 8 x (hidden/256) result slices. Counters alternate by layer parity and
-// are cleared by the rank that owns them one kernel after their last use. No collective and no host round trip per layer.
+// and the next combine waits for its tokens' 8 x (hidden/256) result slices. Counters only grow; counters, piece buffers and
+// scale buffers alternate by layer parity: a peer that already has all its results of layer l may deliver rows of layer l+1
+// while this rank still reads rows of layer l, but rows of layer l+2 cannot be sent before this rank has finished layer l
+// (they depend on its layer l+1 results). No collective and no host round trip per layer.
 #include <vector>
 
 struct OmegaGpuMoeEpStack {
@@ -295,11 +297,11 @@ struct OmegaGpuMoeEpStack {
     char *route;                         // routing scratch (ids, weights, two plan batches)
     uint32_t *ids_g, *ids_l; float *wts_g;
     b200::PlanBatch pg, pl; size_t map_stride, tile_stride;
-    uint8_t *comm; size_t comm_bytes, off_sx, off_dn, off_cnt;   // peers map this block: pieces | scales | results | counters
+    uint8_t *comm; size_t comm_bytes, q_par, off_sx, sx_par, off_dn, off_cnt;   // peers map this block: pieces x2 | scales x2 | results | counters (x2: by layer parity)
     uint64_t *peer_tab;                  // device [4][world]: pieces, scales, results, counters of every rank
     float *h; uint32_t *err, *sched; bool one_launch;
     void *opened[64]; int n_opened; int connected;
-    alignas(128) unsigned char tm_qx[128];
+    alignas(128) unsigned char tm_qx[2][128];
     uint32_t launches;
 };
 
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         uint32_t hidden, uint32_t topk, float eps, const uint16_t *__restrict__ x16, const float *__restrict__ w, const float *__restrict__ dn, float *__restrict__ h,
         const unsigned long long *ret_gate, unsigned long long ret_unit, const uint32_t *step, uint32_t uses_per_step, uint32_t uses_before,
         const uint32_t *__restrict__ ids_next, const uint32_t *__restrict__ pos_next, const uint32_t *__restrict__ starts_next, uint32_t experts_local,
-        uint32_t pieces, size_t piece_stride, const uint64_t *__restrict__ q_peers, const uint64_t *__restrict__ sx_peers, const uint64_t *__restrict__ cnt_peers,
+        uint32_t pieces, size_t piece_stride, size_t q_off, size_t sx_off, const uint64_t *__restrict__ q_peers, const uint64_t *__restrict__ sx_peers, const uint64_t *__restrict__ cnt_peers,
         uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err, uint32_t *__restrict__ sched, uint32_t n_sched,
         unsigned long long *bump, const uint32_t *bump_rows) {
     __shared__ double red[8];
@@ -419,9 +421,9 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
             for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
         }
         for (uint32_t s = 0; s < topk; s++) {
-            uint8_t *q = reinterpret_cast<uint8_t *>(q_peers[s_d[s]]);
+            uint8_t *q = reinterpret_cast<uint8_t *>(q_peers[s_d[s]]) + q_off;
             for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)s_row[s] * hidden + c) = codes[p];
-            if (lane == 0) reinterpret_cast<float *>(sx_peers[s_d[s]])[(size_t)s_row[s] * kb_total + kb] = qs;
+            if (lane == 0) reinterpret_cast<float *>(sx_peers[s_d[s]] + sx_off)[(size_t)s_row[s] * kb_total + kb] = qs;
         }
     }
     __threadfence_system();
@@ -475,9 +477,10 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
                         ffn_shape_ok(v0.hidden, v0.inter) && !getenv("B200MOE_TWO_LAUNCH");
         // the block peers write into: activation pieces | their scales | result rows of the local tokens | counters
         const size_t qb = ((size_t)S->x_pieces * Rp * H + 255) & ~(size_t)255, sb = (Rp * (H / 128) * 4 + 255) & ~(size_t)255, db = ((size_t)S->tokens_local * K * H * 4 + 255) & ~(size_t)255;
-        S->off_sx = qb; S->off_dn = qb + sb; S->off_cnt = qb + sb + db; S->comm_bytes = S->off_cnt + 256;
+        S->q_par = qb; S->off_sx = 2 * qb; S->sx_par = sb; S->off_dn = 2 * qb + 2 * sb; S->off_cnt = S->off_dn + db; S->comm_bytes = S->off_cnt + 256;
         ok = cuda_ok(cudaMalloc(&S->comm, S->comm_bytes), "cudaMalloc(ep comm)") && cuda_ok(cudaMemset(S->comm, 0, S->comm_bytes), "memset") &&
-             cuda_ok(cudaMalloc(&S->peer_tab, (size_t)world * 32), "cudaMalloc(ep peers)") && make_tmap_u8(S->tm_qx, S->comm, (uint64_t)S->x_pieces * Rp, H, 32);
+             cuda_ok(cudaMalloc(&S->peer_tab, (size_t)world * 32), "cudaMalloc(ep peers)") && make_tmap_u8(S->tm_qx[0], S->comm, (uint64_t)S->x_pieces * Rp, H, 32) &&
+             make_tmap_u8(S->tm_qx[1], S->comm + S->q_par, (uint64_t)S->x_pieces * Rp, H, 32);
     }
     if (ok && world == 1) {
         uint64_t tab[4] = {(uint64_t)(uintptr_t)S->comm, (uint64_t)(uintptr_t)(S->comm + S->off_sx), (uint64_t)(uintptr_t)(S->comm + S->off_dn), (uint64_t)(uintptr_t)(S->comm + S->off_cnt)};
@@ -555,7 +558,7 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
     const unsigned long long ret_unit = (unsigned long long)Tl * K * (H / 256u);
     unsigned long long *base = (unsigned long long *)(S->err + 8);   // [0..1]: input rows already consumed through the even / odd layer counter
     ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull, S->err + 4, 0u, 0u,
-                                                      S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err,
+                                                      S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, (size_t)0, (size_t)0, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err,
                                                       S->sched, (uint32_t)S->tile_stride + 1u, nullptr, nullptr); n++;
     for (uint32_t l = 0; l < Ln && ok; l++) {
         LayerView v; layer_view(S->local[l], &v);
@@ -563,18 +566,18 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
         const uint32_t *hdr = S->pl.header + (size_t)l * 8;
         if (S->one_launch) {
             FfnLaunch f = {};
-            f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = (const float *)(S->comm + S->off_sx); f.qa = v.qa; f.sa = v.sa;
+            f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = (const float *)(S->comm + S->off_sx + par * S->sx_par); f.qa = v.qa; f.sa = v.sa;
             f.tiles = S->pl.tiles + (size_t)l * S->tile_stride; f.header = hdr; f.ymap = S->pl.ymap + (size_t)l * S->map_stride; f.out = dn_local;
             f.hidden = H; f.inter = v.inter; f.q_rows = S->row_cap; f.sched = S->sched; f.err = S->err;
             f.gate = cnt + par; f.gate_base = base + par; f.out_peers = tab + 2 * G; f.ret_counters = tab + 3 * G; f.rows_per_rank = Tl * K; f.ret_index = 2 + par;
-            ok = cuda_ok(launch_ffn(v.tm_gu, S->tm_qx, v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, true), "expert ffn launch"); n++;
+            ok = cuda_ok(launch_ffn(v.tm_gu, S->tm_qx[par], v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, true), "expert ffn launch"); n++;
         } else {
             MmaLaunch g = {};
-            g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
+            g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx + par * S->sx_par); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
             g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
             g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = S->err;   // one failure word for the whole step: later kernels see it and do nothing
             g.gate = cnt + par; g.gate_base = base + par;
-            ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, true), "gate|up mma launch"); n++;
+            ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx[par], Px, g, s, true), "gate|up mma launch"); n++;
             MmaLaunch d = {};
             d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
             d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
@@ -585,7 +588,7 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
         const size_t nx = (size_t)(l + 1) * S->map_stride;
         if (ok) ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, nullptr, S->wts_g + (size_t)l * R + tok0, dn_local, S->h, cnt + 2 + par, ret_unit, S->err + 4, (Ln + 1u - par) / 2u, l / 2u,
                                                                   last ? nullptr : S->ids_g + (size_t)(l + 1) * R + tok0, last ? nullptr : S->pg.pos + nx + tok0,
-                                                                  last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, last ? nullptr : tab, tab + G, tab + 3 * G,
+                                                                  last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, (par ^ 1u) * S->q_par, (par ^ 1u) * S->sx_par, last ? nullptr : tab, tab + G, tab + 3 * G,
                                                                   par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err,
                                                                   S->sched, (uint32_t)S->tile_stride + 1u, S->one_launch ? base + par : nullptr, hdr);
         n++;

@@ -246,10 +246,20 @@ def bench(args, rank, world):
     import torch
     import torch.distributed as dist
     from cudapp_b200 import api
+    import datetime
+    import sys
+    import threading
     local = int(os.environ.get("LOCAL_RANK", rank))
+    limit = float(os.environ.get("B200MOE_BENCH_LIMIT_S", "420"))
+
+    def give_up():
+        # every device wait is bounded, so a rank stuck here is waiting on the host for a peer that already left
+        sys.stderr.write("rank %d: benchmark exceeded %.0f s; leaving\n" % (rank, limit)); sys.stderr.flush()
+        os._exit(3)
+    watchdog = threading.Timer(limit, give_up); watchdog.daemon = True; watchdog.start()
     torch.cuda.set_device(local)
     os.environ.setdefault("B200MOE_DEVICE", str(local))
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     mode = os.environ.get("B200MOE_EP_MODE", "fused")
     Ln, T = args.layers, args.tokens
     st = FusedEpStack(api, torch, dist, rank, world, Ln, T, engine=args.engine) if mode == "fused" else EpStack(api, torch, dist, rank, world, Ln, T, mode=mode, engine=args.engine)
@@ -297,7 +307,7 @@ def bench(args, rank, world):
             "ms_per_step": float(ms.item()) / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights, f32 accumulate",
             "data": "synthetic",
             "config": {"workload": "48-layer MoE expert stack, 256 decode tokens/step, 128 experts top-8, hidden 2048, inter 768", "layers": Ln, "tokens_per_step": T,
-                       "parallelism": "ep%d (experts and tokens sharded; %s)" % (world, {"fused": "rows and results by peer stores over NVLink inside the layer kernels, 3 launches per layer", "p2p": "direct peer stores over NVLink", "nccl": "NCCL all-to-all"}[mode]),
+                       "parallelism": "ep%d (experts and tokens sharded; %s)" % (world, {"fused": "rows and results by peer stores over NVLink inside the layer kernels, 2 launches per layer", "p2p": "direct peer stores over NVLink", "nccl": "NCCL all-to-all"}[mode]),
                        "l2": "%.1f GB of weights per GPU per step: larger than L2" % (per_gpu_bytes / 1e9)},
             "e2e": {"value": T / float(e2e.item()), "unit": "tokens/s", "h2d_bytes_per_step": int((lg_h.numel() + x_h.numel()) * 2 * world), "d2h_bytes_per_step": int(out_h.numel() * 2 * world)},
             "gpu_launches": int(st.launches) * args.steps,
@@ -305,6 +315,5 @@ def bench(args, rank, world):
                          "peak_kind": kind + " copy bandwidth", "traffic": None},
             "clocks": clocks.summary()}))
     torch.cuda.synchronize(); dist.barrier()
-    import sys
     sys.stdout.flush(); sys.stderr.flush()
     os._exit(0)   # a process group whose collectives sit in a captured graph does not tear down reliably; leave at once

@@ -80,7 +80,8 @@ typedef struct {
     uint32_t act_pieces;  /* MMA: pieces per f32 SwiGLU output (0 = 3) */
     uint32_t norm_topk;   /* 1: weights renormalised over the selected experts */
     uint32_t first_expert, local_experts; /* expert-parallel shard held here; 0, 0 = all */
-    uint32_t reserved;
+    uint32_t tile_rows;   /* tensor-core engine, rows per routed-row tile: 0 = chosen per call (128 once a call brings 64 rows per expert on average and
+                             x_pieces = act_pieces = 1, else 32), 32 = always 32, 128 = always 128 (refused unless x_pieces = act_pieces = 1, k <= 2048) */
 } OmegaGpuMoeConfig;
 /* gate_up: [E][2I][H] (gate rows first), down: [E][H][I]; both stay owned by the caller and must outlive the layer */
 int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuFp8Tensor *down, const OmegaGpuMoeConfig *cfg,
@@ -160,6 +161,11 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *s, uint64_t logits_all_
 int omega_gpu_moe_epstack_status(OmegaGpuMoeEpStack *s, void *stream);
 uint32_t omega_gpu_moe_epstack_launches(const OmegaGpuMoeEpStack *s);
 uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *s);   /* device address of the f32 residual stream [tokens_local][hidden] */
+/* Measurement aid, no reference counterpart: the FP8 tensor throughput this GPU sustains when nothing has to be loaded (every SM
+ * issues iters x 4 tcgen05 MMAs of M 128, N 256, K 32 on operands resident in shared memory). *tflops = best of `repeats` timed
+ * launches (CUDA events), *ms_out (optional) that launch's duration. The denominator for "fraction of FP8 tensor peak". */
+int omega_gpu_fp8_tensor_peak(uint32_t iters, uint32_t repeats, float *tflops, float *ms_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -142,3 +142,45 @@ def test_layer_prefill_shape_skewed(pieces):
     assert np.array_equal(ids, rid)
     assert np.max(np.abs(o32 - ref)) <= 1e-2 and rel_l2(o32, ref) <= 1e-3, (float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref))
     free_layer(m)
+
+
+def test_layer_prefill_wide_tiles_equal_narrow():
+    """the 128-row-tile kernel against the 32-row-tile kernel on the same layer and inputs (plain FP8 activations): the same
+    promotion order per K block, so the results agree to rounding noise; segments of every size from a few rows to several tiles,
+    row counts that are not multiples of 32, experts with no rows at all"""
+    rng = np.random.default_rng(57)
+    E, H, I, topk, T = 32, 512, 256, 8, 700
+    wgu, sgu = make_weights(rng, E, 2 * I, H)
+    wdn, sdn = make_weights(rng, E, H, I)
+    rc, tgu = api.fp8_tensor_upload(E, 2 * I, H, wgu, sgu); assert rc == 0, api.last_error()
+    rc, tdn = api.fp8_tensor_upload(E, H, I, wdn, sdn); assert rc == 0, api.last_error()
+    bias = rng.normal(0, 1.0, E).astype(np.float32); bias[:3] = -30.0        # three experts never picked
+    logits = orc.bf16_bits((rng.normal(0, 1, (T, E)) + bias).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    outs = {}
+    for rows in (32, 128):
+        rc, layer = api.moe_layer_create(tgu, tdn, topk=topk, max_tokens=T, engine=api.ENGINE_MMA, x_pieces=1, act_pieces=1, tile_rows=rows)
+        assert rc == 0, api.last_error()
+        rc, o16, o32, ids, w = api.moe_layer_bf16(layer, logits, xb, topk)
+        assert rc == 0, api.last_error()
+        outs[rows] = (o32, ids)
+        api.lib.omega_gpu_moe_layer_free(layer)
+    counts = np.bincount(outs[32][1].reshape(-1), minlength=E)
+    assert counts.min() == 0 and counts.max() > 128 and np.any(counts % 32 != 0)
+    assert np.array_equal(outs[32][1], outs[128][1])
+    assert rel_l2(outs[128][0], outs[32][0]) <= 1e-5, rel_l2(outs[128][0], outs[32][0])
+    ref, rid, rw = orc.moe_layer(logits, xb, wgu, sgu, wdn, sdn, topk, x_pieces=1, act_pieces=1)
+    assert np.max(np.abs(outs[128][0] - ref)) <= 1e-2 and rel_l2(outs[128][0], ref) <= 1e-3
+    # a request the wide kernel cannot serve is refused, not silently served by another path
+    rc, layer = api.moe_layer_create(tgu, tdn, topk=topk, max_tokens=T, engine=api.ENGINE_MMA, x_pieces=2, act_pieces=3, tile_rows=128)
+    assert rc == api.BAD_ARGS and layer is None
+    api.fp8_tensor_free(tgu); api.fp8_tensor_free(tdn)
+
+
+def test_fp8_tensor_peak_probe():
+    """the tcgen05 probe that gives the prefill roofline its denominator returns a plausible figure for a B200"""
+    import ctypes as C
+    tf, ms = C.c_float(0), C.c_float(0)
+    rc = api.lib.omega_gpu_fp8_tensor_peak(C.c_uint32(4000), C.c_uint32(3), C.byref(tf), C.byref(ms))
+    assert rc == 0, api.last_error()
+    assert 500.0 < tf.value < 6000.0, (tf.value, ms.value)
