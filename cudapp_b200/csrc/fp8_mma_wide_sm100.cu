@@ -128,21 +128,41 @@ __global__ void __launch_bounds__(WIDE_THREADS, 1) fp8_mma_wide_kernel(const __g
     } else if (warp == 2) {
         // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
         uint32_t n = 0; bool ok = true;
+        const uint32_t kb_magic = 65536u / KB + 1u;
         for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
             if (!(ok = mbar_wait(scempty_bar(b), ((n >> 1) & 1u) ^ 1u, abort_flag, a.err, 7))) break;
-            if (a.mode == 1) for (uint32_t r = lane; r < WIDE_ROWS; r += 32u) s_ymap[b][r] = r < t.z ? a.ymap[t.y + r] : 0u;
+            // every global load of the unit is issued before the first one is used: one memory latency per unit, not one per batch
+            uint32_t ym[WIDE_ROWS / 32];
+            if (a.mode == 1) {
+#pragma unroll
+                for (int i = 0; i < WIDE_ROWS / 32; i++) { const uint32_t r = lane + 32u * i; ym[i] = r < t.z ? a.ymap[t.y + r] : 0u; }
+            }
             const float *w0 = a.wscale + ((size_t)t.x * (a.n / 128u) + r0 / 128u) * KB, *w1 = a.wscale + ((size_t)t.x * (a.n / 128u) + r1 / 128u) * KB;
+            const float wv0 = lane < KB ? __ldg(w0 + lane) : 0.0f, wv1 = lane < KB ? __ldg(w1 + lane) : 0.0f;
             // the tile's row scales are one contiguous block [row][k block]: read it coalesced, scatter to [k block][row]
             const float *as = a.ascale + (size_t)t.y * KB;
             const uint32_t total_sc = WIDE_ROWS * KB;
-#pragma unroll 4
-            for (uint32_t idx = lane; idx < total_sc; idx += 32u) {
-                const uint32_t r = idx / KB, kb = idx - r * KB;
-                const float cs = r < t.z ? as[idx] : 0.0f;
-                sc_at(b, 0, kb)[r] = __ldg(w0 + kb) * cs;
-                sc_at(b, 1, kb)[r] = __ldg(w1 + kb) * cs;
+            if (a.mode == 1) {
+#pragma unroll
+                for (int i = 0; i < WIDE_ROWS / 32; i++) s_ymap[b][lane + 32u * i] = ym[i];
+            }
+            for (uint32_t base = 0; base < total_sc; base += 32u * 2u * WIDE_KB_MAX) {   // at most two passes of 32 loads per lane
+                float v[2 * WIDE_KB_MAX];
+#pragma unroll
+                for (int i = 0; i < 2 * WIDE_KB_MAX; i++) {
+                    const uint32_t idx = base + lane + 32u * i, r = (idx * kb_magic) >> 16;   // r = idx / KB (exact for idx < 2048, KB <= 16)
+                    v[i] = (idx < total_sc && r < t.z) ? as[idx] : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 2 * WIDE_KB_MAX; i++) {
+                    const uint32_t idx = base + lane + 32u * i, r = (idx * kb_magic) >> 16, kb = idx - r * KB;
+                    if (idx < total_sc) {   // total_sc is a multiple of 32: the whole warp takes the same side
+                        sc_at(b, 0, kb)[r] = __shfl_sync(0xffffffffu, wv0, kb) * v[i];
+                        sc_at(b, 1, kb)[r] = __shfl_sync(0xffffffffu, wv1, kb) * v[i];
+                    }
+                }
             }
             mbar_arrive(scfull_bar(b));
         }

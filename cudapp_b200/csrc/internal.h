@@ -82,8 +82,11 @@ cudaError_t launch_gemv_grouped(const GemvArgs &a, uint32_t cta_budget, uint32_t
 cudaError_t launch_gemm_rows(const GemvArgs &a, uint32_t *grid_x, uint32_t *mt, cudaStream_t s);
 
 cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s);
+// scratch (optional, zero-filled once, plan_scratch_words(picks, experts) u32): lets a plan of 4096 picks or more run as three launches over many SMs
 cudaError_t launch_plan(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
-                        const OmegaGpuMoePlanOut &o, cudaStream_t s);
+                        const OmegaGpuMoePlanOut &o, cudaStream_t s, uint32_t *scratch = nullptr, size_t scratch_words = 0);
+size_t plan_scratch_words(uint32_t picks, uint32_t experts);
+uint32_t plan_launch_count(uint32_t picks, uint32_t experts, const uint32_t *scratch, size_t scratch_words, const OmegaGpuMoePlanOut &o);
 // routing plans of several layers in one launch (one CTA per layer); element strides between layers
 struct PlanBatch { uint32_t *counts, *starts, *xmap, *ymap, *pos, *header; uint4 *tiles; size_t map_stride, tile_stride; };
 cudaError_t launch_plan_batch(uint32_t layers, uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,

@@ -80,31 +80,45 @@ __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t 
                                                         uint8_t *__restrict__ q, float *__restrict__ sc) {
     const uint32_t lane = threadIdx.x & 31u, kb = k / 128u;
     const uint32_t nrows = rows_dev ? min(rows, *rows_dev) : rows;
-    const size_t tasks = (size_t)nrows * kb;
-    for (size_t task = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); task < tasks; task += (size_t)gridDim.x * (blockDim.x >> 5)) {
-        const uint32_t r = (uint32_t)(task / kb), b = (uint32_t)(task - (size_t)r * kb);
-        const uint32_t src = xmap ? xmap[r] : r;
-        float v[4];
-        if (x_bf16) {
-            const uint2 u = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * x_stride + (b * 128u + lane * 4u) * 2u));
-            v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u); v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
-        } else {
-            const float4 u = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * x_stride + (b * 128u + lane * 4u) * 4u));
-            v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+    const uint32_t tasks = nrows * kb, stride = gridDim.x * (blockDim.x >> 5);   // rows <= 2^24 and kb <= 32 on every caller's path
+    constexpr int U = 4;   // tasks in flight per warp: their loads are issued before the first value is used
+    for (uint32_t task0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); task0 < tasks; task0 += U * stride) {
+        float v[U][4]; uint32_t rr[U], bb[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t task = task0 + (uint32_t)u * stride;
+            if (task >= tasks) { rr[u] = 0xffffffffu; bb[u] = 0; v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.0f; continue; }   // warp-uniform
+            const uint32_t r = task / kb, b = task - r * kb;
+            rr[u] = r; bb[u] = b;
+            const uint32_t src = xmap ? xmap[r] : r;
+            if (x_bf16) {
+                const uint2 w = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * x_stride + (b * 128u + lane * 4u) * 2u));
+                v[u][0] = __uint_as_float(w.x << 16); v[u][1] = __uint_as_float(w.x & 0xffff0000u); v[u][2] = __uint_as_float(w.y << 16); v[u][3] = __uint_as_float(w.y & 0xffff0000u);
+            } else {
+                const float4 w = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * x_stride + (b * 128u + lane * 4u) * 4u));
+                v[u][0] = w.x; v[u][1] = w.y; v[u][2] = w.z; v[u][3] = w.w;
+            }
         }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float s = pq_scale_dev(amax);
-        if (lane == 0) sc[(size_t)r * kb + b] = s;
-        float res[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], s);
-        for (uint32_t p = 0; p < pieces; p++) {
-            const uint32_t code = enc4(res[0], res[1], res[2], res[3]);
-            *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)r * k + b * 128u + lane * 4u) = code;
-            float d[4]; dec4(code, d);
+        for (int u = 0; u < U; u++) {
+            if (rr[u] == 0xffffffffu) continue;
+            const uint32_t r = rr[u], b = bb[u];
+            float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
+            for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float s = pq_scale_dev(amax);
+            if (lane == 0) sc[(size_t)r * kb + b] = s;
+            const float inv = __uint_as_float((254u - (__float_as_uint(s) >> 23)) << 23);   // s is a power of two: exact reciprocal, v * inv == v / s
+            float res[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
+            for (int i = 0; i < 4; i++) res[i] = v[u][i] * inv;
+            for (uint32_t p = 0; p < pieces; p++) {
+                const uint32_t code = enc4(res[0], res[1], res[2], res[3]);
+                *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)r * k + b * 128u + lane * 4u) = code;
+                if (p + 1 == pieces) break;
+                float d[4]; dec4(code, d);
+#pragma unroll
+                for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
+            }
         }
     }
 }
@@ -115,6 +129,7 @@ cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const v
     if (!x_stride_bytes) x_stride_bytes = (size_t)k * (x_bf16 ? 2 : 4);
     const size_t tasks = (size_t)rows * (k / 128u);
     if (!tasks) return cudaSuccess;
+    if (tasks >= ((size_t)1 << 32)) return cudaErrorInvalidValue;
     size_t blocks = (tasks + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8;
     act_quant_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, (size_t)q_rows * k, x, x_bf16, x_stride_bytes, xmap, rows_dev, q, sc);
     return cudaGetLastError();
@@ -154,6 +169,7 @@ int omega_gpu_moe_combine_f32(uint32_t tokens, uint32_t slots, uint32_t hidden, 
 
 int omega_gpu_act_quant_f32(uint32_t rows, uint32_t k, uint32_t pieces, const float *x, uint8_t *q, float *sc) {
     if (!rows || !k || k % 128 || !pieces || pieces > 4 || !x || !q || !sc) return OMEGA_GPU_FP8_BAD_ARGS;
+    if ((uint64_t)rows * (k / 128) >= (1ull << 32)) return OMEGA_GPU_FP8_TOO_LARGE;
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     const size_t xb = (size_t)rows * k * 4, qb = (size_t)rows * pieces * k, sb = (size_t)rows * (k / 128) * 4;

@@ -12,7 +12,8 @@ namespace b200 {
 struct Workspace {
     uint32_t max_tokens, topk, experts, hidden, inter;
     int refs;
-    uint32_t *ids, *counts, *starts, *xmap, *ymap, *header;
+    uint32_t *ids, *counts, *starts, *xmap, *ymap, *header, *plan_scratch;
+    size_t plan_scratch_words;
     float *wts;
     Seg32 *seg_gu, *seg_dn;
     uint4 *tiles;
@@ -39,7 +40,7 @@ static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t 
                  o_tiles = take(max_tiles * 16), o_gu = take(Rp * 2 * inter * 4), o_act = take(Rp * inter * 4), o_dn = take(Rp * hidden * 4),
                  o_qx = take(Rp * 4 * hidden), o_qa = take(Rp * 4 * inter), o_sx = take(Rp * (hidden / 128) * 4), o_sa = take(Rp * (inter / 128) * 4),
                  o_lg = take((size_t)max_tokens * experts * 2), o_x = take((size_t)max_tokens * hidden * 2), o_o16 = take((size_t)max_tokens * hidden * 2),
-                 o_o32 = take((size_t)max_tokens * hidden * 4);
+                 o_o32 = take((size_t)max_tokens * hidden * 4), o_ps = take(plan_scratch_words((uint32_t)R, experts) * 4);
     if (!cuda_ok(cudaMalloc(&w->base, off), "cudaMalloc(workspace)")) { free(w); return nullptr; }
     if (!cuda_ok(cudaMemset(w->base, 0, off), "cudaMemset(workspace)")) { cudaFree(w->base); free(w); return nullptr; }
     char *b = w->base;
@@ -48,6 +49,7 @@ static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t 
     w->seg_gu = (Seg32 *)(b + o_sgu); w->seg_dn = (Seg32 *)(b + o_sdn); w->tiles = (uint4 *)(b + o_tiles);
     w->gu = (float *)(b + o_gu); w->act = (float *)(b + o_act); w->dn = (float *)(b + o_dn);
     w->qx = (uint8_t *)(b + o_qx); w->qa = (uint8_t *)(b + o_qa); w->sx = (float *)(b + o_sx); w->sa = (float *)(b + o_sa);
+    w->plan_scratch = (uint32_t *)(b + o_ps); w->plan_scratch_words = plan_scratch_words((uint32_t)R, experts);
     w->logits = (uint16_t *)(b + o_lg); w->x = (uint16_t *)(b + o_x); w->out16 = (uint16_t *)(b + o_o16); w->out32 = (float *)(b + o_o32);
     return w;
 }
@@ -65,7 +67,7 @@ struct OmegaGpuMoeLayer {
     uint32_t experts, hidden, inter;
     uint64_t *dir_gu, *dir_dn;   // device {w_va, s_va} per expert
     b200::Workspace *ws;
-    uint32_t launches;
+    uint32_t launches, marks;    // kernels of the last forward; profile marks of the last forward (a mark may cover several launches)
     cudaEvent_t *prof;           // when set: prof[i] is recorded after the i-th launch of a forward
     const char *names[12];
     alignas(128) unsigned char tm_gu[128], tm_dn[128], tm_qx[128], tm_qa[128];   // TMA descriptors (tensor-core engine)
@@ -92,7 +94,9 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     // prefill-sized segments (64 rows per expert on average, or on request) take the 128-row-tile kernel
     const bool wide = mma && L->wide_ok && (L->cfg.tile_rows == 128u || (L->cfg.tile_rows == 0u && R >= 64u * E));
     o.tiles_va = mma ? (uint64_t)(uintptr_t)w->tiles : 0;
-    if (!cuda_ok(launch_plan(tokens, K, E, K, mma ? (wide ? mma_wide_tile_rows() : L->tile_rows) : 0, w->ids, o, s), "plan launch")) return false; MARK("plan");
+    if (!cuda_ok(launch_plan(tokens, K, E, K, mma ? (wide ? mma_wide_tile_rows() : L->tile_rows) : 0, w->ids, o, s, w->plan_scratch, w->plan_scratch_words), "plan launch")) return false;
+    MARK("plan");
+    const uint32_t extra = plan_launch_count(R, E, w->plan_scratch, w->plan_scratch_words, o) - 1u;   // launches behind that one mark
     if (mma) {
         // activations as e4m3 pieces in sorted-row order, then the two tensor-core grouped GEMMs
         const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces, Rp = w->max_tokens * w->topk + 8;
@@ -109,7 +113,7 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
         if (!cuda_ok(wide ? launch_mma_wide(L->tm_dn, L->tm_qa, dd, s) : launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false;
         MARK(wide ? "down_mma_wide" : "down_mma");
         if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
-        L->launches = n;
+        L->launches = n + extra; L->marks = n;
         return true;
     }
     // gate|up: sorted row p reads x[xmap[p]], writes gu row p
@@ -125,7 +129,7 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     if (!cuda_ok(launch_gemm_rows(d, nullptr, nullptr, s), "down launch")) return false; MARK("down_gemm");
     if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
 #undef MARK
-    L->launches = n;
+    L->launches = n + extra; L->marks = n;
     return true;
 }
 
@@ -274,7 +278,7 @@ int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t l
     L->prof = nullptr;
     ok = ok && cuda_ok(cudaStreamSynchronize(s), "moe layer profile");
     *count = 0;
-    for (uint32_t i = 0; ok && i < L->launches && i < cap; i++) {
+    for (uint32_t i = 0; ok && i < L->marks && i < cap; i++) {
         float t = 0; ok = cuda_ok(cudaEventElapsedTime(&t, ev[i], ev[i + 1]), "event time");
         ms[i] = t; if (names) names[i] = L->names[i]; *count = i + 1;
     }

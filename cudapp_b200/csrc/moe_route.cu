@@ -79,30 +79,15 @@ __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t *buf, u
     return r;
 }
 
-// dynamic shared: counts[E] | starts[E] | run[E] | scan buf[96] | wcnt u16 [32][E]
-// pos (optional): inverse of the Y map, pos[token * slots + slot] = sorted row of that pick
-__device__ __forceinline__ void plan_body(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
-                                          const uint32_t *__restrict__ ids, const OmegaGpuMoePlanOut &o, uint32_t *__restrict__ pos) {
-    extern __shared__ uint32_t smem[];
-    uint32_t *counts = smem, *starts = smem + experts, *run = smem + 2 * experts, *sbuf = smem + 3 * experts;
-    uint16_t *wcnt = reinterpret_cast<uint16_t *>(sbuf + 96);
-    __shared__ uint32_t s_bad;
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, R = tokens * slots;
-    for (uint32_t e = tid; e < experts; e += 1024) { counts[e] = 0; run[e] = 0; }
-    if (tid == 0) s_bad = 0;
-    __syncthreads();
-    // 1. histogram (shared-memory integer atomics: the result does not depend on their order)
-    for (uint32_t i = tid; i < R; i += 1024) {
-        const uint32_t e = ids[i];
-        if (e == 0xffffffffu) continue;
-        if (e >= experts) { s_bad = 1; continue; }
-        atomicAdd(&counts[e], 1u);
-    }
-    __syncthreads();
+// Everything of a plan that follows from the per-expert counts (in shared memory): row starts, segment records, row tiles, header,
+// the zero pads after the maps. One CTA of 1024 threads; false = refused (only the status word is written).
+__device__ __forceinline__ bool plan_tables(uint32_t experts, uint32_t tile_rows, const uint32_t *counts, uint32_t *starts, uint32_t *sbuf,
+                                            const OmegaGpuMoePlanOut &o, bool bad) {
+    const uint32_t tid = threadIdx.x;
     uint32_t *hdr = reinterpret_cast<uint32_t *>(o.header_va);
-    if (s_bad) {   // refuse: nothing but the status word is written
+    if (bad) {   // refuse: nothing but the status word is written
         if (tid == 0) { hdr[0] = 0; hdr[1] = 0; hdr[2] = 0; hdr[3] = 2; }
-        return;
+        return false;
     }
     // 2. exclusive scans over experts (one expert per thread, passes of 1024): row starts, segment index, tile index
     uint32_t rows_total = 0, segs_total = 0, tiles_total = 0;
@@ -141,6 +126,31 @@ __device__ __forceinline__ void plan_body(uint32_t tokens, uint32_t slots, uint3
     uint32_t *xmap = reinterpret_cast<uint32_t *>(o.xmap_va), *ymap = reinterpret_cast<uint32_t *>(o.ymap_va);
     if (tid < 8) { xmap[rows_total + tid] = 0; ymap[rows_total + tid] = 0; }
     __syncthreads();
+    return true;
+}
+
+// dynamic shared: counts[E] | starts[E] | run[E] | scan buf[96] | wcnt u16 [32][E]
+// pos (optional): inverse of the Y map, pos[token * slots + slot] = sorted row of that pick
+__device__ __forceinline__ void plan_body(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows,
+                                          const uint32_t *__restrict__ ids, const OmegaGpuMoePlanOut &o, uint32_t *__restrict__ pos) {
+    extern __shared__ uint32_t smem[];
+    uint32_t *counts = smem, *starts = smem + experts, *run = smem + 2 * experts, *sbuf = smem + 3 * experts;
+    uint16_t *wcnt = reinterpret_cast<uint16_t *>(sbuf + 96);
+    __shared__ uint32_t s_bad;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, R = tokens * slots;
+    for (uint32_t e = tid; e < experts; e += 1024) { counts[e] = 0; run[e] = 0; }
+    if (tid == 0) s_bad = 0;
+    __syncthreads();
+    // 1. histogram (shared-memory integer atomics: the result does not depend on their order)
+    for (uint32_t i = tid; i < R; i += 1024) {
+        const uint32_t e = ids[i];
+        if (e == 0xffffffffu) continue;
+        if (e >= experts) { s_bad = 1; continue; }
+        atomicAdd(&counts[e], 1u);
+    }
+    __syncthreads();
+    if (!plan_tables(experts, tile_rows, counts, starts, sbuf, o, s_bad != 0)) return;
+    uint32_t *xmap = reinterpret_cast<uint32_t *>(o.xmap_va), *ymap = reinterpret_cast<uint32_t *>(o.ymap_va);
     // 3. stable scatter, 1024 rows per chunk in row order: rank = rows of the same expert before this one.
     //    run[e] = rows of expert e in earlier chunks; counts[] is reused for this chunk's per-expert total.
     for (uint32_t base = 0; base < R; base += 1024) {
@@ -195,8 +205,86 @@ cudaError_t launch_plan_batch(uint32_t layers, uint32_t tokens, uint32_t slots, 
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ plan of many picks: three launches, one CTA per 1024 picks in the first and the last
+// The same stable order as plan_kernel (sorted row = rows of lower experts + earlier picks of the same expert), split so that the
+// per-chunk work runs on as many SMs as there are chunks: (1) per-chunk histograms, (2) one CTA turns them into per-chunk
+// offsets and builds the tables, (3) every chunk scatters its picks. scratch: u32 [chunks][experts] + 1 flag word.
+__global__ void __launch_bounds__(1024) plan_hist_kernel(uint32_t R, uint32_t experts, const uint32_t *__restrict__ ids, uint32_t *__restrict__ scratch, uint32_t chunks) {
+    extern __shared__ uint32_t smem[];
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t e = tid; e < experts; e += 1024) smem[e] = 0;
+    __syncthreads();
+    const uint32_t i = blockIdx.x * 1024u + tid;
+    if (i < R) {
+        const uint32_t e = ids[i];
+        if (e != 0xffffffffu) { if (e >= experts) atomicOr(scratch + (size_t)chunks * experts, 1u); else atomicAdd(&smem[e], 1u); }
+    }
+    __syncthreads();
+    for (uint32_t e = tid; e < experts; e += 1024) scratch[(size_t)blockIdx.x * experts + e] = smem[e];
+}
+// dynamic shared: counts[E] | starts[E] | scan buf[96]
+__global__ void __launch_bounds__(1024) plan_scan_kernel(uint32_t experts, uint32_t tile_rows, uint32_t *__restrict__ scratch, uint32_t chunks, const OmegaGpuMoePlanOut o) {
+    extern __shared__ uint32_t smem[];
+    uint32_t *counts = smem, *starts = smem + experts, *sbuf = smem + 2 * experts;
+    const uint32_t tid = threadIdx.x;
+    const bool bad = scratch[(size_t)chunks * experts] != 0;
+    __syncthreads();
+    if (tid == 0) scratch[(size_t)chunks * experts] = 0;   // the flag is clear again for the next plan
+    for (uint32_t e = tid; e < experts; e += 1024) {        // per expert: counts of earlier chunks
+        uint32_t acc = 0;
+        for (uint32_t c = 0; c < chunks; c++) { const uint32_t v = scratch[(size_t)c * experts + e]; scratch[(size_t)c * experts + e] = acc; acc += v; }
+        counts[e] = acc;
+    }
+    __syncthreads();
+    (void)plan_tables(experts, tile_rows, counts, starts, sbuf, o, bad);
+}
+// dynamic shared: wcnt u16 [32][E]
+__global__ void __launch_bounds__(1024) plan_scatter_kernel(uint32_t R, uint32_t slots, uint32_t experts, uint32_t ystride, const uint32_t *__restrict__ ids,
+                                                            const uint32_t *__restrict__ scratch, const OmegaGpuMoePlanOut o, uint32_t *__restrict__ pos) {
+    extern __shared__ uint32_t smem[];
+    uint16_t *wcnt = reinterpret_cast<uint16_t *>(smem);
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (reinterpret_cast<const uint32_t *>(o.header_va)[3]) return;   // refused: nothing is written
+    const uint32_t *starts = reinterpret_cast<const uint32_t *>(o.starts_va);
+    uint32_t *xmap = reinterpret_cast<uint32_t *>(o.xmap_va), *ymap = reinterpret_cast<uint32_t *>(o.ymap_va);
+    for (uint32_t j = tid; j < 32u * experts; j += 1024) wcnt[j] = 0;
+    __syncthreads();
+    const uint32_t i = blockIdx.x * 1024u + tid;
+    const uint32_t e = i < R ? ids[i] : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, e);
+    const uint32_t rank_w = __popc(peers & ((1u << lane) - 1u));
+    if (e != 0xffffffffu && rank_w == 0) wcnt[warp * experts + e] = (uint16_t)__popc(peers);
+    __syncthreads();
+    for (uint32_t ee = tid; ee < experts; ee += 1024) {   // per expert: exclusive scan over the 32 warps
+        uint32_t acc = 0;
+        for (uint32_t w = 0; w < 32; w++) { const uint32_t c = wcnt[w * experts + ee]; wcnt[w * experts + ee] = (uint16_t)acc; acc += c; }
+    }
+    __syncthreads();
+    if (e != 0xffffffffu) {
+        const uint32_t p = starts[e] + scratch[(size_t)blockIdx.x * experts + e] + wcnt[warp * experts + e] + rank_w;
+        const uint32_t t = i / slots, sl = i - t * slots;
+        xmap[p] = t; ymap[p] = t * ystride + sl;
+        if (pos) pos[i] = p;
+    }
+}
+size_t plan_scratch_words(uint32_t picks, uint32_t experts) { return (size_t)((picks + 1023u) / 1024u) * experts + 1; }
+static bool plan_split(uint32_t picks, uint32_t experts, const uint32_t *scratch, size_t scratch_words, const OmegaGpuMoePlanOut &o) {
+    return scratch && picks >= 4096u && o.starts_va && plan_scratch_words(picks, experts) <= scratch_words && (size_t)32 * experts * 2 <= 48 * 1024;
+}
+uint32_t plan_launch_count(uint32_t picks, uint32_t experts, const uint32_t *scratch, size_t scratch_words, const OmegaGpuMoePlanOut &o) {
+    return plan_split(picks, experts, scratch, scratch_words, o) ? 3u : 1u;
+}
+
 cudaError_t launch_plan(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
-                        const OmegaGpuMoePlanOut &o, cudaStream_t s) {
+                        const OmegaGpuMoePlanOut &o, cudaStream_t s, uint32_t *scratch, size_t scratch_words) {
+    const uint32_t R = tokens * slots, chunks = (R + 1023u) / 1024u;
+    if (plan_split(R, experts, scratch, scratch_words, o)) {
+        plan_hist_kernel<<<chunks, 1024, (size_t)experts * 4, s>>>(R, experts, ids, scratch, chunks);
+        plan_scan_kernel<<<1, 1024, (size_t)experts * 8 + 96 * 4, s>>>(experts, tile_rows, scratch, chunks, o);
+        plan_scatter_kernel<<<chunks, 1024, (size_t)32 * experts * 2, s>>>(R, slots, experts, ystride, ids, scratch, o, nullptr);
+        return cudaGetLastError();
+    }
+
     const size_t smem = (size_t)experts * 12 + 96 * 4 + (size_t)32 * experts * 2;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
