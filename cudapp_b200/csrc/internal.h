@@ -96,6 +96,9 @@ cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, con
 // quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap,
                              const uint32_t *rows_dev, uint8_t *q, float *sc, cudaStream_t s, size_t x_stride_bytes = 0, uint32_t q_rows = 0);
+// sorted row r <- codes (all pieces, piece-major with src_rows / dst_rows rows per piece) and scales of source row xmap[r]
+cudaError_t launch_gather_rows(uint32_t rows, uint32_t k, uint32_t pieces, uint32_t src_rows, uint32_t dst_rows, const uint32_t *xmap, const uint32_t *rows_dev,
+                               const uint8_t *q_src, const float *s_src, uint8_t *q_dst, float *s_dst, cudaStream_t s);
 // tcgen05 grouped GEMM (fp8_mma_sm100.cu)
 struct MmaLaunch {
     const float *wscale, *ascale;      // weight scales [E][n/128][k/128]; activation scales [rows][k/128]

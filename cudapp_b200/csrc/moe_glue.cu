@@ -135,6 +135,38 @@ cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const v
     return cudaGetLastError();
 }
 
+// Sorted-row copies of rows that were quantised once per source row: sorted row r takes the codes (every piece) and the scales of
+// source row xmap[r]. One warp per (sorted row, piece); k is a multiple of 128, so a row is k / 16 16-byte words.
+__global__ void __launch_bounds__(256) gather_rows_kernel(uint32_t rows, uint32_t k, uint32_t pieces, size_t src_piece_stride, size_t dst_piece_stride,
+                                                          const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
+                                                          const uint8_t *__restrict__ q_src, const float *__restrict__ s_src, uint8_t *__restrict__ q_dst, float *__restrict__ s_dst) {
+    const uint32_t lane = threadIdx.x & 31u, kb = k / 128u, words = k / 16u;
+    const uint32_t nrows = rows_dev ? min(rows, *rows_dev) : rows;
+    const uint32_t tasks = nrows * pieces, stride = gridDim.x * (blockDim.x >> 5);
+    for (uint32_t task = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); task < tasks; task += stride) {
+        const uint32_t r = task / pieces, p = task - r * pieces, src = xmap[r];
+        const uint4 *from = reinterpret_cast<const uint4 *>(q_src + (size_t)p * src_piece_stride + (size_t)src * k);
+        uint4 *to = reinterpret_cast<uint4 *>(q_dst + (size_t)p * dst_piece_stride + (size_t)r * k);
+        for (uint32_t w0 = 0; w0 < words; w0 += 128u) {   // four independent 16-byte loads per lane before the first store
+            uint4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { const uint32_t w = w0 + lane + 32u * i; v[i] = w < words ? __ldg(from + w) : make_uint4(0, 0, 0, 0); }
+#pragma unroll
+            for (int i = 0; i < 4; i++) { const uint32_t w = w0 + lane + 32u * i; if (w < words) to[w] = v[i]; }
+        }
+        if (p == 0) for (uint32_t b = lane; b < kb; b += 32u) s_dst[(size_t)r * kb + b] = s_src[(size_t)src * kb + b];
+    }
+}
+cudaError_t launch_gather_rows(uint32_t rows, uint32_t k, uint32_t pieces, uint32_t src_rows, uint32_t dst_rows, const uint32_t *xmap, const uint32_t *rows_dev,
+                               const uint8_t *q_src, const float *s_src, uint8_t *q_dst, float *s_dst, cudaStream_t s) {
+    const size_t tasks = (size_t)rows * pieces;
+    if (!tasks) return cudaSuccess;
+    if (tasks >= ((size_t)1 << 32)) return cudaErrorInvalidValue;
+    size_t blocks = (tasks + 7) / 8; if (blocks > 148 * 8) blocks = 148 * 8;
+    gather_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, k, pieces, (size_t)src_rows * k, (size_t)dst_rows * k, xmap, rows_dev, q_src, s_src, q_dst, s_dst);
+    return cudaGetLastError();
+}
+
 }  // namespace b200
 using namespace b200;
 

@@ -20,6 +20,7 @@ struct Workspace {
     float *gu, *act, *dn;          // [R][2I], [R][I], [R][H]
     uint8_t *qx, *qa;              // e4m3 pieces of x rows / act rows (tensor-core engine)
     float *sx, *sa;                // their per-128 scales
+    uint8_t *qt; float *stt;       // x quantised once per token (prefill-sized calls): [piece][max_tokens][hidden], [max_tokens][hidden/128]
     uint16_t *logits, *x, *out16;  // staging for the host-buffer entry
     float *out32;
     char *base;
@@ -40,7 +41,8 @@ static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t 
                  o_tiles = take(max_tiles * 16), o_gu = take(Rp * 2 * inter * 4), o_act = take(Rp * inter * 4), o_dn = take(Rp * hidden * 4),
                  o_qx = take(Rp * 4 * hidden), o_qa = take(Rp * 4 * inter), o_sx = take(Rp * (hidden / 128) * 4), o_sa = take(Rp * (inter / 128) * 4),
                  o_lg = take((size_t)max_tokens * experts * 2), o_x = take((size_t)max_tokens * hidden * 2), o_o16 = take((size_t)max_tokens * hidden * 2),
-                 o_o32 = take((size_t)max_tokens * hidden * 4), o_ps = take(plan_scratch_words((uint32_t)R, experts) * 4);
+                 o_o32 = take((size_t)max_tokens * hidden * 4), o_ps = take(plan_scratch_words((uint32_t)R, experts) * 4),
+                 o_qt = take((size_t)max_tokens * 4 * hidden), o_stt = take((size_t)max_tokens * (hidden / 128) * 4);
     if (!cuda_ok(cudaMalloc(&w->base, off), "cudaMalloc(workspace)")) { free(w); return nullptr; }
     if (!cuda_ok(cudaMemset(w->base, 0, off), "cudaMemset(workspace)")) { cudaFree(w->base); free(w); return nullptr; }
     char *b = w->base;
@@ -49,6 +51,7 @@ static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t 
     w->seg_gu = (Seg32 *)(b + o_sgu); w->seg_dn = (Seg32 *)(b + o_sdn); w->tiles = (uint4 *)(b + o_tiles);
     w->gu = (float *)(b + o_gu); w->act = (float *)(b + o_act); w->dn = (float *)(b + o_dn);
     w->qx = (uint8_t *)(b + o_qx); w->qa = (uint8_t *)(b + o_qa); w->sx = (float *)(b + o_sx); w->sa = (float *)(b + o_sa);
+    w->qt = (uint8_t *)(b + o_qt); w->stt = (float *)(b + o_stt);
     w->plan_scratch = (uint32_t *)(b + o_ps); w->plan_scratch_words = plan_scratch_words((uint32_t)R, experts);
     w->logits = (uint16_t *)(b + o_lg); w->x = (uint16_t *)(b + o_x); w->out16 = (uint16_t *)(b + o_o16); w->out32 = (float *)(b + o_o32);
     return w;
@@ -100,7 +103,15 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
     if (mma) {
         // activations as e4m3 pieces in sorted-row order, then the two tensor-core grouped GEMMs
         const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces, Rp = w->max_tokens * w->topk + 8;
-        if (!cuda_ok(launch_act_quant(R, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, 0, Rp), "x quant launch")) return false; MARK("x_quant");
+        uint32_t extra_q = 0;
+        if (K >= 4u && tokens >= 512u) {
+            // many picks per token: quantise every token row once, then copy codes and scales into sorted-row order (the same bytes as
+            // quantising each sorted row, a fraction of the arithmetic)
+            if (!cuda_ok(launch_act_quant(tokens, H, Px, x, 1, nullptr, nullptr, w->qt, w->stt, s, 0, w->max_tokens), "x quant launch") ||
+                !cuda_ok(launch_gather_rows(R, H, Px, w->max_tokens, Rp, w->xmap, w->header, w->qt, w->stt, w->qx, w->sx, s), "x gather launch")) return false;
+            extra_q = 1;
+        } else if (!cuda_ok(launch_act_quant(R, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, 0, Rp), "x quant launch")) return false;
+        MARK("x_quant");
         MmaLaunch g = {};
         g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.ymap = nullptr; g.out = nullptr;
         g.q_out = w->qa; g.s_out = w->sa; g.q_rows = Rp; g.q_pieces = Pa;
@@ -113,7 +124,7 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
         if (!cuda_ok(wide ? launch_mma_wide(L->tm_dn, L->tm_qa, dd, s) : launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false;
         MARK(wide ? "down_mma_wide" : "down_mma");
         if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
-        L->launches = n + extra; L->marks = n;
+        L->launches = n + extra + extra_q; L->marks = n;
         return true;
     }
     // gate|up: sorted row p reads x[xmap[p]], writes gu row p
