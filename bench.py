@@ -41,10 +41,11 @@ def parse():
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--engine", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8)
-    ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline out (profiling runs)")
+    ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline and the prefill-layer measurement out (profiling runs)")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
                     help="decode: the 48-layer stack the metric is quoted on (default); prefill: one layer, 4096 tokens, skewed routing, plain FP8 activations")
     ap.add_argument("--tile-rows", type=int, default=0, help="prefill: 0 = library's choice, 32 or 128 = force the row-tile size")
+    ap.add_argument("--skip-prefill", action="store_true", help="decode workload: leave the prefill-layer measurement out of the line")
     return ap.parse_args()
 
 
@@ -278,8 +279,14 @@ def run_ours(args, rank, world):
                          "sample": "%d tokens through 1 of %d layers (x%d extrapolated), double-precision host GEMV oracle per routed row, %d threads" % (args.cpu_sample_tokens, Ln, Ln, cores)},
         "clocks": clocks.summary(),
     }
-    print(json.dumps(out))
     api.lib.omega_gpu_moe_stack_free(stack)
+    if not args.skip_prefill and not args.skip_cpu:
+        # the prefill configuration beside the headline: one layer, 4096 tokens, compute-bound grouped GEMMs against the FP8 tensor peak
+        pa = argparse.Namespace(**vars(args)); pa.steps = 10; pa.tokens = 256; pa.tile_rows = 0
+        pf = run_prefill(pa)
+        out["prefill"] = {"workload": pf["config"]["workload"], "tokens_per_s": pf["value"], "ms_per_step": pf["ms_per_step"], "kernel_ms": pf["config"]["kernel_ms"],
+                          "roofline": pf["roofline"], "gpu_launches": pf["gpu_launches"]}
+    print(json.dumps(out))
 
 
 def run_prefill(args):
@@ -346,7 +353,8 @@ def run_prefill(args):
     rc = api.lib.omega_gpu_fp8_tensor_peak(C.c_uint32(20000), C.c_uint32(5), C.byref(peak_tf), C.byref(peak_ms))
     assert rc == 0, api.last_error()
     achieved = flops / (gemm_ms * 1e-3) / 1e12
-    print(json.dumps({
+    api.lib.omega_gpu_moe_layer_free(layer)
+    return {
         "metric": "moe_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights and activations, f32 accumulate", "data": "synthetic",
         "config": {"workload": "one MoE prefill layer, %d tokens, 128 experts top-8 with skewed routing, hidden 2048, inter 768" % T, "tokens_per_step": T,
@@ -356,8 +364,7 @@ def run_prefill(args):
         "roofline": {"bound": "tensor", "kernel": "gate|up + down grouped FP8 GEMM", "achieved": achieved, "peak": float(peak_tf.value), "unit": "TFLOP/s",
                      "frac": achieved / float(peak_tf.value), "peak_kind": "measured by the library's tcgen05 probe (operands resident in shared memory, %.2f ms)" % peak_ms.value,
                      "flops": flops, "kernel_ms": gemm_ms, "traffic": None},
-        "clocks": clocks.summary()}))
-    api.lib.omega_gpu_moe_layer_free(layer)
+        "clocks": clocks.summary()}
 
 
 def main():
@@ -367,7 +374,7 @@ def main():
         run_reference(args, rank)
     elif args.workload == "prefill":
         if rank == 0:
-            run_prefill(args)
+            print(json.dumps(run_prefill(args)))
     else:
         run_ours(args, rank, world)
 

@@ -245,3 +245,21 @@ def moe_stack_bf16(stack, logits_bf16, x_bf16, want_f32=True):
     o16 = np.empty((T, H), np.uint16); o32 = np.empty((T, H), np.float32) if want_f32 else None
     rc = lib.omega_gpu_moe_stack_bf16(stack, C.c_uint32(T), _p(lg), _p(x), _p(o16), _p(o32))
     return rc, o16, o32
+
+
+def moe_router_create(gate_bf16, norm_w):
+    g = np.ascontiguousarray(gate_bf16, dtype=np.uint16); nw = np.ascontiguousarray(norm_w, dtype=np.float32)
+    E, H = g.shape
+    h = VP()
+    rc = lib.omega_gpu_moe_router_create(C.c_uint32(E), C.c_uint32(H), _p(g), _p(nw), C.byref(h))
+    return rc, (h if rc == 0 else None)
+
+
+def moe_router_f32(router, x, experts, eps=1e-6, norm_topk=True, out_scale=1.0, topk=8):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, H = x.shape
+    xn = np.empty((rows, H), np.float32); lg = np.empty((rows, experts), np.float32)
+    ids = np.empty((rows, topk), np.uint32); w = np.empty((rows, topk), np.float32)
+    rc = lib.omega_gpu_moe_router_f32(router, C.c_uint32(rows), _p(x), C.c_float(eps), C.c_int(1 if norm_topk else 0), C.c_float(out_scale), C.c_uint32(topk),
+                                      _p(xn), _p(lg), _p(ids), _p(w))
+    return rc, xn, lg, ids, w

@@ -9,6 +9,7 @@
 // order = expert, then token, then slot. Here it is histogram -> block exclusive scan -> stable scatter built from
 // warp match/ballot primitives, for any row count (the reference kernel ranks <= 128 rows with an O(R^2) loop).
 #include "internal.h"
+#include "route_common.cuh"
 
 namespace b200 {
 
@@ -19,37 +20,9 @@ __global__ void __launch_bounds__(256) topk_kernel(uint32_t tokens, uint32_t exp
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= tokens) return;
     float *l = sm + (size_t)warp * experts;
-    float lmax = -INFINITY;
-    for (uint32_t e = lane; e < experts; e += 32) { const float v = __uint_as_float((uint32_t)logits[(size_t)t * experts + e] << 16); l[e] = v; lmax = fmaxf(lmax, v); }
+    for (uint32_t e = lane; e < experts; e += 32) l[e] = __uint_as_float((uint32_t)logits[(size_t)t * experts + e] << 16);
     __syncwarp();
-    float denom_all = 0.0f;
-    if (!norm) {
-        for (int o = 16; o; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
-        for (uint32_t e = lane; e < experts; e += 32) denom_all += expf(l[e] - lmax);
-        for (int o = 16; o; o >>= 1) denom_all += __shfl_xor_sync(0xffffffffu, denom_all, o);
-    }
-    float my_logit = 0.0f, l0 = 0.0f, sum = 0.0f;   // lane r keeps the r-th selected logit
-    uint32_t my_id = 0;
-    for (uint32_t r = 0; r < topk; r++) {
-        float best = -INFINITY; uint32_t bi = 0xffffffffu;
-        for (uint32_t e = lane; e < experts; e += 32) { const float v = l[e]; if (bi == 0xffffffffu || v > best) { best = v; bi = e; } }
-        // ascending scan with strict > keeps the lowest index inside a lane; across lanes prefer larger value, then lower index
-        for (int o = 16; o; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o); const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-        }
-        if (lane == r) { my_logit = best; my_id = bi; }
-        if (r == 0) l0 = best;
-        if (lane == 0) l[bi] = -INFINITY;   // taken
-        __syncwarp();
-    }
-    const float e_i = lane < topk ? expf(my_logit - (norm ? l0 : lmax)) : 0.0f;
-    sum = e_i;
-    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane < topk) {
-        ids[(size_t)t * topk + lane] = my_id;
-        wts[(size_t)t * topk + lane] = __fdiv_rn(e_i, norm ? sum : denom_all);
-    }
+    warp_topk(l, experts, topk, norm, ids + (size_t)t * topk, wts + (size_t)t * topk);
 }
 
 cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s) {

@@ -1,0 +1,150 @@
+// moe_router.cu: the router front half in one launch for any number of residual rows: RMSNorm of the row with the layer's norm
+// weight, router logits against the bf16 gate matrix, softmax top-k with the reference's tie rule, weights.
+//
+// What it computes is the reference's one-launch router in its ROWS form (src/omega_blackwell_codegen_router.h:15-33: phase 1
+// RMSNorm and x' = xn * out_scale, phase 2 logits, phase 3 selection; API src/omega_gpu_router_api.h:74-110; double oracle
+// tests/gpu_router_test.c:62-79). The reference's group tables (directory entries of the selected experts) are not produced: this
+// library's routing plan reads the ids themselves.
+//
+// One CTA of 8 warps per row. The gate matrix (experts x hidden bf16, 512 KB at 128 x 2048) is shared by all rows and stays in L2;
+// a warp streams whole expert rows with 16-byte loads against the normalised row held in shared memory.
+#include "internal.h"
+#include "route_common.cuh"
+
+struct OmegaGpuMoeRouter {
+    uint32_t experts, hidden;
+    uint16_t *gate;      // device [experts][hidden] bf16
+    float *norm_w;       // device [hidden]
+};
+
+namespace b200 {
+
+__device__ __forceinline__ uint32_t bf16_rne_bits(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
+}
+
+// dynamic shared: xn f32 [hidden] | logits f32 [experts]
+__global__ void __launch_bounds__(256) router_rows_kernel(uint32_t hidden, uint32_t experts, uint32_t topk, int norm, float eps, float out_scale,
+                                                          const float *__restrict__ x, size_t x_stride, const float *__restrict__ norm_w,
+                                                          const uint16_t *__restrict__ gate, float *__restrict__ xn_out, uint16_t *__restrict__ xn16_out,
+                                                          float *__restrict__ logits_out, uint32_t *__restrict__ ids, float *__restrict__ wts) {
+    extern __shared__ __align__(16) float sm[];
+    float *xn = sm, *lg = sm + hidden;
+    __shared__ double red[8];
+    __shared__ float s_r;
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const float *xr = x + (size_t)row * x_stride;
+    // ---- phase 1: RMSNorm (sum of squares in double, one f32 factor, then (x * r) * w)
+    double ss = 0.0;
+    for (uint32_t i = tid * 4u; i < hidden; i += 1024u) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+    }
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (tid == 0) { double t = 0.0; for (int i = 0; i < 8; i++) t += red[i]; s_r = (float)(1.0 / sqrt(t / (double)hidden + (double)eps)); }
+    __syncthreads();
+    const float r = s_r;
+    for (uint32_t i = tid * 4u; i < hidden; i += 1024u) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i), w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
+        const float4 o = make_float4(v.x * r * w.x, v.y * r * w.y, v.z * r * w.z, v.w * r * w.w);
+        *reinterpret_cast<float4 *>(xn + i) = o;
+        if (xn_out) *reinterpret_cast<float4 *>(xn_out + (size_t)row * hidden + i) = make_float4(o.x * out_scale, o.y * out_scale, o.z * out_scale, o.w * out_scale);
+        if (xn16_out) {
+            uint2 pk; pk.x = bf16_rne_bits(o.x) | (bf16_rne_bits(o.y) << 16); pk.y = bf16_rne_bits(o.z) | (bf16_rne_bits(o.w) << 16);
+            *reinterpret_cast<uint2 *>(xn16_out + (size_t)row * hidden + i) = pk;
+        }
+    }
+    __syncthreads();
+    // ---- phase 2: logits; warp w takes experts w, w + 8, ...; a lane multiplies 8 consecutive bf16 weights per 16-byte load
+    const uint32_t words = hidden / 8u;
+    for (uint32_t e = warp; e < experts; e += 8u) {
+        const uint4 *g = reinterpret_cast<const uint4 *>(gate + (size_t)e * hidden);
+        float acc = 0.0f;
+        for (uint32_t c = lane; c < words; c += 32u) {
+            const uint4 u = __ldg(g + c);
+            const float4 a = *reinterpret_cast<const float4 *>(xn + c * 8u), b = *reinterpret_cast<const float4 *>(xn + c * 8u + 4u);
+            acc = fmaf(__uint_as_float(u.x << 16), a.x, acc); acc = fmaf(__uint_as_float(u.x & 0xffff0000u), a.y, acc);
+            acc = fmaf(__uint_as_float(u.y << 16), a.z, acc); acc = fmaf(__uint_as_float(u.y & 0xffff0000u), a.w, acc);
+            acc = fmaf(__uint_as_float(u.z << 16), b.x, acc); acc = fmaf(__uint_as_float(u.z & 0xffff0000u), b.y, acc);
+            acc = fmaf(__uint_as_float(u.w << 16), b.z, acc); acc = fmaf(__uint_as_float(u.w & 0xffff0000u), b.w, acc);
+        }
+        for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) { lg[e] = acc; if (logits_out) logits_out[(size_t)row * experts + e] = acc; }
+    }
+    __syncthreads();
+    // ---- phase 3: selection and weights
+    if (warp == 0) warp_topk(lg, experts, topk, norm, ids + (size_t)row * topk, wts + (size_t)row * topk);
+}
+
+}  // namespace b200
+using namespace b200;
+
+extern "C" {
+
+int omega_gpu_moe_router_create(uint32_t experts, uint32_t hidden, const uint16_t *gate_bf16, const float *norm_w, OmegaGpuMoeRouter **out) {
+    if (out) *out = nullptr;
+    if (!out || !gate_bf16 || !norm_w || !experts || experts > 1024 || !hidden || hidden % 8 || hidden > 8192) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    OmegaGpuMoeRouter *r = new OmegaGpuMoeRouter();
+    r->experts = experts; r->hidden = hidden; r->gate = nullptr; r->norm_w = nullptr;
+    const size_t gb = (size_t)experts * hidden * 2, nb = (size_t)hidden * 4;
+    const bool ok = cuda_ok(cudaMalloc(&r->gate, gb), "cudaMalloc(router gate)") && cuda_ok(cudaMalloc(&r->norm_w, nb), "cudaMalloc(router norm)") &&
+                    cuda_ok(cudaMemcpy(r->gate, gate_bf16, gb, cudaMemcpyHostToDevice), "copy router gate") &&
+                    cuda_ok(cudaMemcpy(r->norm_w, norm_w, nb, cudaMemcpyHostToDevice), "copy router norm");
+    if (!ok) { if (r->gate) cudaFree(r->gate); if (r->norm_w) cudaFree(r->norm_w); delete r; return OMEGA_GPU_FP8_CHIP_FAIL; }
+    *out = r;
+    return OMEGA_GPU_FP8_OK;
+}
+
+void omega_gpu_moe_router_free(OmegaGpuMoeRouter *r) {
+    if (!r) return;
+    Lock l;
+    if (r->gate) cudaFree(r->gate);
+    if (r->norm_w) cudaFree(r->norm_w);
+    delete r;
+}
+
+int omega_gpu_moe_router_rows_async(OmegaGpuMoeRouter *r, uint32_t rows, uint64_t x_va, uint32_t x_stride_bytes, float eps, int norm_topk, float out_scale,
+                                    uint32_t topk, uint64_t xn_va, uint64_t xn_bf16_va, uint64_t logits_va, uint64_t ids_va, uint64_t wts_va, void *stream) {
+    if (!r || !rows || !x_va || !ids_va || !wts_va || !topk || topk > 32 || topk > r->experts) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!x_stride_bytes) x_stride_bytes = r->hidden * 4u;
+    if (x_stride_bytes % 16u || x_stride_bytes < r->hidden * 4u || (x_va & 15u)) { set_error("router: residual rows must be 16-byte aligned f32 rows of at least `hidden` values"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t smem = ((size_t)r->hidden + r->experts) * 4;
+    if (smem > 48 * 1024) {
+        if (!cuda_ok(cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attribute")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    }
+    router_rows_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>(r->hidden, r->experts, topk, norm_topk, eps, out_scale, (const float *)(uintptr_t)x_va, x_stride_bytes / 4u,
+                                                                  r->norm_w, r->gate, (float *)(uintptr_t)xn_va, (uint16_t *)(uintptr_t)xn_bf16_va, (float *)(uintptr_t)logits_va,
+                                                                  (uint32_t *)(uintptr_t)ids_va, (float *)(uintptr_t)wts_va);
+    return cuda_ok(cudaGetLastError(), "router launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+int omega_gpu_moe_router_f32(OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, float out_scale, uint32_t topk,
+                             float *xn, float *logits, uint32_t *ids, float *wts) {
+    if (!r || !rows || !x || !ids || !wts || !topk || topk > 32 || topk > r->experts) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t xb = (size_t)rows * r->hidden * 4, lb = (size_t)rows * r->experts * 4, kb = (size_t)rows * topk * 4;
+    float *dx = (float *)stage(0, xb), *dxn = (float *)stage(1, xb), *dl = (float *)stage(2, lb + 2 * kb);
+    if (!dx || !dxn || !dl) return OMEGA_GPU_FP8_CHIP_FAIL;
+    uint32_t *di = (uint32_t *)(dl + (size_t)rows * r->experts); float *dw = (float *)(di + (size_t)rows * topk);
+    cudaStream_t s = st().stream;
+    bool ok = cuda_ok(cudaMemcpyAsync(dx, x, xb, cudaMemcpyHostToDevice, s), "copy x");
+    if (ok) {
+        const int rc = omega_gpu_moe_router_rows_async(r, rows, (uint64_t)(uintptr_t)dx, 0, eps, norm_topk, out_scale, topk, (uint64_t)(uintptr_t)dxn, 0,
+                                                       (uint64_t)(uintptr_t)dl, (uint64_t)(uintptr_t)di, (uint64_t)(uintptr_t)dw, s);
+        if (rc != OMEGA_GPU_FP8_OK) return rc;
+    }
+    if (ok && xn) ok = cuda_ok(cudaMemcpyAsync(xn, dxn, xb, cudaMemcpyDeviceToHost, s), "copy xn");
+    if (ok && logits) ok = cuda_ok(cudaMemcpyAsync(logits, dl, lb, cudaMemcpyDeviceToHost, s), "copy logits");
+    ok = ok && cuda_ok(cudaMemcpyAsync(ids, di, kb, cudaMemcpyDeviceToHost, s), "copy ids") && cuda_ok(cudaMemcpyAsync(wts, dw, kb, cudaMemcpyDeviceToHost, s), "copy weights") &&
+         cuda_ok(cudaStreamSynchronize(s), "router");
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+}  // extern "C"

@@ -161,6 +161,25 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *s, uint64_t logits_all_
 int omega_gpu_moe_epstack_status(OmegaGpuMoeEpStack *s, void *stream);
 uint32_t omega_gpu_moe_epstack_launches(const OmegaGpuMoeEpStack *s);
 uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *s);   /* device address of the f32 residual stream [tokens_local][hidden] */
+/* ---- router front half: RMSNorm of a residual row with the layer's norm weight, router logits against the bf16 gate matrix,
+ * softmax top-k (lowest index on ties, ids in descending-logit order), weights renormalised over the selected when norm_topk.
+ * Replaces omega_gpu_router / omega_gpu_router_record_rows (src/omega_gpu_router_api.h:74-110; kernel contract
+ * src/omega_blackwell_codegen_router.h:15-33) for any number of rows in one launch. The reference's group tables (directory
+ * entries of the selected experts) are not produced: this library's routing plan reads the ids themselves.
+ * gate_bf16: [experts][hidden] bf16 bits (the checkpoint's mlp.gate.weight), norm_w: f32 [hidden]; both are copied. */
+typedef struct OmegaGpuMoeRouter OmegaGpuMoeRouter;
+int omega_gpu_moe_router_create(uint32_t experts, uint32_t hidden, const uint16_t *gate_bf16, const float *norm_w, OmegaGpuMoeRouter **out);
+void omega_gpu_moe_router_free(OmegaGpuMoeRouter *r);
+/* device buffers, stream-ordered. x_va: f32 rows, x_stride_bytes apart (0 = dense; a multiple of 16). Outputs: xn_va f32
+ * [rows][hidden] = RMSNorm(x) * out_scale (0 = skip), xn_bf16_va bf16 [rows][hidden] = RMSNorm(x) rounded to nearest even (0 = skip;
+ * the input rows of omega_gpu_moe_layer_async), logits_va f32 [rows][experts] (0 = skip), ids_va u32 [rows][topk], wts_va f32 [rows][topk]. */
+int omega_gpu_moe_router_rows_async(OmegaGpuMoeRouter *r, uint32_t rows, uint64_t x_va, uint32_t x_stride_bytes, float eps, int norm_topk,
+                                    float out_scale, uint32_t topk, uint64_t xn_va, uint64_t xn_bf16_va, uint64_t logits_va, uint64_t ids_va,
+                                    uint64_t wts_va, void *stream);
+/* host buffers; xn and logits optional */
+int omega_gpu_moe_router_f32(OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, float out_scale, uint32_t topk,
+                             float *xn, float *logits, uint32_t *ids, float *wts);
+
 /* Measurement aid, no reference counterpart: the FP8 tensor throughput this GPU sustains when nothing has to be loaded (every SM
  * issues iters x 4 tcgen05 MMAs of M 128, N 256, K 32 on operands resident in shared memory). *tflops = best of `repeats` timed
  * launches (CUDA events), *ms_out (optional) that launch's duration. The denominator for "fraction of FP8 tensor peak". */

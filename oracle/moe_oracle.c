@@ -168,6 +168,34 @@ void orc_topk(const float *logits, uint32_t experts, uint32_t topk, int norm_top
     free(taken);
 }
 
+/* Router front half for one residual row (tests/gpu_router_test.c:62-79; kernel contract src/omega_blackwell_codegen_router.h:15-33):
+ * xn = x * (1 / sqrt(mean(x^2) + eps)) * norm_w, logits[e] = sum_k bf16(gate[e][k]) * xn[k], then the top-k rule of orc_topk on
+ * the double logits. margin = last selected logit minus the best unselected one (an id difference below a small margin is a
+ * near-tie, not an error). Everything in double. xn, logits: outputs. */
+void orc_router(const float *x, const float *norm_w, const uint16_t *gate_bf16, uint32_t hidden, uint32_t experts, uint32_t topk, float eps,
+                int norm_topk, double *xn, double *logits, uint32_t *ids, double *wts, double *margin) {
+    double ss = 0.0;
+    for (uint32_t i = 0; i < hidden; i++) ss += (double)x[i] * x[i];
+    const double r = 1.0 / sqrt(ss / (double)hidden + (double)eps);
+    for (uint32_t i = 0; i < hidden; i++) xn[i] = (double)x[i] * r * (double)norm_w[i];
+    double mx = -1e300, sum = 0.0, sk = 0.0;
+    for (uint32_t e = 0; e < experts; e++) {
+        double l = 0.0;
+        for (uint32_t k = 0; k < hidden; k++) l += (double)orc_bf16_to_f32(gate_bf16[(size_t)e * hidden + k]) * xn[k];
+        logits[e] = l; if (l > mx) mx = l;
+    }
+    for (uint32_t e = 0; e < experts; e++) sum += exp(logits[e] - mx);
+    uint8_t *taken = calloc(experts, 1);
+    for (uint32_t rr = 0; rr <= topk && rr < experts; rr++) {
+        int best = -1;
+        for (uint32_t e = 0; e < experts; e++) if (!taken[e] && (best < 0 || logits[e] > logits[best])) best = (int)e;
+        if (rr < topk) { ids[rr] = (uint32_t)best; taken[best] = 1; wts[rr] = exp(logits[best] - mx) / sum; sk += wts[rr]; }
+        else if (margin) *margin = logits[ids[topk - 1]] - logits[best];
+    }
+    if (norm_topk) for (uint32_t rr = 0; rr < topk; rr++) wts[rr] /= sk;
+    free(taken);
+}
+
 /* ------------------------------------------------------------------ SwiGLU and combine */
 
 /* act[c] = g / (1 + exp(-g)) * up, gate = columns [0, I), up = [I, 2I) of one gate|up row

@@ -125,6 +125,28 @@ def topk(logits, k=8, norm=True):
     return ids, w
 
 
+def router(x, norm_w, gate_bf16, eps=1e-6, k=8, norm=True):
+    """x f32 [rows][H], norm_w f32 [H], gate bf16 bits [E][H] -> (xn f64 [rows][H], logits f64 [rows][E], ids u32 [rows][k],
+    weights f64 [rows][k], margin f64 [rows])."""
+    x = np.ascontiguousarray(x, dtype=np.float32); nw = np.ascontiguousarray(norm_w, dtype=np.float32)
+    g = np.ascontiguousarray(gate_bf16, dtype=np.uint16)
+    rows, H = x.shape; E = g.shape[0]
+    xn = np.empty((rows, H), np.float64); lg = np.empty((rows, E), np.float64)
+    ids = np.empty((rows, k), np.uint32); w = np.empty((rows, k), np.float64); margin = np.empty(rows, np.float64)
+    L = lib()
+    for r in range(rows):
+        m = C.c_double(0)
+        L.orc_router(_ptr(x[r], F32P), _ptr(nw, F32P), _ptr(g, U16P), C.c_uint32(H), C.c_uint32(E), C.c_uint32(k), C.c_float(eps), C.c_int(1 if norm else 0),
+                     _ptr(xn[r], F64P), _ptr(lg[r], F64P), _ptr(ids[r], U32P), _ptr(w[r], F64P), C.byref(m))
+        margin[r] = m.value
+    return xn, lg, ids, w, margin
+
+
+def ref_router_lib():
+    path = os.path.join(HERE, "_ref", "libref_router.so")
+    return C.CDLL(path) if os.path.exists(path) else None
+
+
 def swiglu(gu):
     gu = np.ascontiguousarray(gu, dtype=np.float32)
     rows, two_i = gu.shape

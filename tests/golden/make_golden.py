@@ -15,7 +15,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import oracle as orc  # noqa: E402
-from tests.test_oracle_pin import plan_cases  # noqa: E402
+from tests.test_oracle_pin import plan_cases, router_case  # noqa: E402
 
 U8P, U16P, U32P, U64P, F32P, F64P = orc.U8P, orc.U16P, orc.U32P, orc.U64P, orc.F32P, orc.F64P
 p = lambda a, t: a.ctypes.data_as(t)
@@ -62,6 +62,19 @@ def main():
     ox = np.zeros(1168, np.uint32); oy = np.zeros(1168, np.uint32); os_ = np.zeros(1028, np.uint32)
     ns = G.moe_incumbent(C.c_uint32(64), p(ids, U32P), p(ox, U32P), p(oy, U32P), p(os_, U32P))
     out.update(grp_ids=ids, grp_x=ox[:576], grp_y=oy[:576], grp_seg=os_[: ns * 4])
+    # router front half: the double oracle inside the reference's own router test, on seeded cases (inputs are regenerated from the seeds)
+    RR = orc.ref_router_lib()
+    if RR is None:
+        raise SystemExit("reference router oracle not present: run `make -C oracle ref` first")
+    seeds = [(11, 1.0, 1), (12, 1.0, 0), (13, 0.01, 1), (14, 50.0, 1), (15, 1.0, 1), (16, 3.0, 0)]
+    r_ids, r_w, r_lg, r_xn, r_m = [], [], [], [], []
+    for seed, xscale, norm in seeds:
+        x, nw, gate = router_case(seed, xscale)
+        xn = np.empty(2048, np.float64); lg = np.empty(128, np.float64); ids = np.empty(8, np.uint32); w = np.empty(8, np.float64); m = C.c_double(0)
+        RR.ref_router_oracle(p(x, F32P), p(nw, F32P), p(gate, U16P), C.c_int(norm), p(xn, F64P), p(lg, F64P), p(ids, U32P), p(w, F64P), C.byref(m))
+        r_ids.append(ids.copy()); r_w.append(w.copy()); r_lg.append(lg.copy()); r_xn.append(xn[::16].copy()); r_m.append(m.value)
+    out.update(router_seeds=np.array(seeds, np.float64), router_ids=np.stack(r_ids), router_w=np.stack(r_w), router_logits=np.stack(r_lg),
+               router_xn16=np.stack(r_xn), router_margin=np.array(r_m))
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **out)
     print("wrote", os.path.join(HERE, "reference_vectors.npz"), {k_: v_.shape for k_, v_ in out.items()})
 

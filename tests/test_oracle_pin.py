@@ -15,6 +15,7 @@ from oracle import oracle as orc
 
 REF = orc.ref_lib()
 REFG = orc.ref_group_lib()
+REFR = orc.ref_router_lib()
 need_ref = pytest.mark.skipif(REF is None, reason="reference build (oracle/_ref) not present")
 U8P, U16P, U32P, U64P, F32P, F64P = orc.U8P, orc.U16P, orc.U32P, orc.U64P, orc.F32P, orc.F64P
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -278,3 +279,32 @@ def test_w4_self_consistency():
     h = rng.normal(0, 30, 2000).astype(np.float32)
     mine = np.array([L.orc_f32_to_f16(C.c_float(float(v))) for v in h], np.uint16)
     assert np.array_equal(mine, h.astype(np.float16).view(np.uint16))
+
+
+# ------------------------------------------------------------------ router front half (tests/gpu_router_test.c:62-79)
+def router_case(seed, xscale=1.0, hidden=2048, experts=128):
+    """seeded inputs in the ranges the reference's router test draws from: x in [-2, 2) * xscale, norm weight in [0.8, 1.2),
+    gate rows in [-0.05, 0.05) rounded to bf16"""
+    rng = np.random.default_rng([77, seed])
+    x = (rng.uniform(-2.0, 2.0, hidden) * xscale).astype(np.float32)
+    nw = rng.uniform(0.8, 1.2, hidden).astype(np.float32)
+    gate = orc.bf16_bits(rng.uniform(-0.05, 0.05, (experts, hidden)).astype(np.float32))
+    return x, nw, gate
+
+
+@pytest.mark.skipif(REFR is None, reason="reference router oracle (oracle/_ref/libref_router.so) not present")
+def test_router_against_reference():
+    REFR.ref_router_eps.restype = C.c_float
+    H, E, K = REFR.ref_router_hidden(), REFR.ref_router_experts(), REFR.ref_router_topk()
+    assert (H, E, K) == (2048, 128, 8)
+    eps = float(REFR.ref_router_eps())
+    for seed, xscale in [(1, 1.0), (2, 1.0), (3, 0.01), (4, 50.0), (5, 1.0)]:
+        x, nw, gate = router_case(seed, xscale)
+        for norm in (1, 0):
+            xn = np.empty(H, np.float64); lg = np.empty(E, np.float64); ids = np.empty(K, np.uint32); w = np.empty(K, np.float64); m = C.c_double(0)
+            REFR.ref_router_oracle(ptr(x, F32P), ptr(nw, F32P), ptr(gate, U16P), C.c_int(norm), ptr(xn, F64P), ptr(lg, F64P), ptr(ids, U32P), ptr(w, F64P), C.byref(m))
+            mxn, mlg, mids, mw, mm = orc.router(x[None], nw, gate, eps, K, bool(norm))
+            assert np.array_equal(mids[0], ids)
+            assert np.array_equal(mxn[0], xn) and np.array_equal(mlg[0], lg)          # the same double arithmetic in the same order
+            assert np.max(np.abs(mw[0] - w)) <= 1e-15 and abs(mm[0] - m.value) <= 1e-15
+            assert abs(w.sum() - 1.0) < 1e-12 if norm else w.sum() < 1.0
