@@ -126,7 +126,8 @@ struct FfnLaunch {
 };
 bool ffn_shape_ok(uint32_t hidden, uint32_t inter);
 cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, const void *tm_qa, uint32_t px, uint32_t pa, const FfnLaunch &m, cudaStream_t s, bool pdl);
-bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s);
+bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s,
+                   const uint32_t *ids_in = nullptr, const float *wts_in = nullptr);
 // expert side only (expert-parallel receive path): `rows` candidate rows, ids[row] = local expert or 0xFFFFFFFF,
 // x row r at x + r * x_stride_bytes (bf16); writes dn[row][hidden] f32 for the present rows
 bool layer_forward_routed(OmegaGpuMoeLayer *L, uint32_t rows, const uint32_t *ids, const void *x, size_t x_stride_bytes, float *dn, cudaStream_t s);

@@ -81,13 +81,22 @@ struct OmegaGpuMoeLayer {
 namespace b200 {
 
 // one forward, device pointers, stream-ordered. out32 required; out16 optional.
-bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s) {
+// routing given (ids_in / wts_in, [tokens][topk] on the device) or computed from the logits
+bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s,
+                   const uint32_t *ids_in, const float *wts_in) {
     Workspace *w = L->ws;
     const uint32_t K = L->cfg.topk, E = L->experts, H = L->hidden, I = L->inter, R = tokens * K;
     uint32_t n = 0;
 #define MARK(name) do { L->names[n] = name; if (L->prof) cudaEventRecord(L->prof[n + 1], s); n++; } while (0)
     if (L->prof) cudaEventRecord(L->prof[0], s);
-    if (!cuda_ok(launch_topk(tokens, E, K, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s), "topk launch")) return false; MARK("topk");
+    if (ids_in) {
+        if (!cuda_ok(cudaMemcpyAsync(w->ids, ids_in, (size_t)R * 4, cudaMemcpyDeviceToDevice, s), "copy ids") ||
+            !cuda_ok(cudaMemcpyAsync(w->wts, wts_in, (size_t)R * 4, cudaMemcpyDeviceToDevice, s), "copy weights")) return false;
+        MARK("routing_copy");
+    } else {
+        if (!cuda_ok(launch_topk(tokens, E, K, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s), "topk launch")) return false;
+        MARK("topk");
+    }
     OmegaGpuMoePlanOut o = {};
     o.counts_va = (uint64_t)(uintptr_t)w->counts; o.starts_va = (uint64_t)(uintptr_t)w->starts;
     o.xmap_va = (uint64_t)(uintptr_t)w->xmap; o.ymap_va = (uint64_t)(uintptr_t)w->ymap; o.header_va = (uint64_t)(uintptr_t)w->header;
@@ -273,6 +282,15 @@ int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t log
     if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
     return layer_forward(L, tokens, (const uint16_t *)(uintptr_t)logits_va, (const uint16_t *)(uintptr_t)x_va, (float *)(uintptr_t)out_f32_va,
                          (uint16_t *)(uintptr_t)out_bf16_va, (cudaStream_t)stream) ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+
+int omega_gpu_moe_layer_routed_async(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t ids_va, uint64_t wts_va, uint64_t x_va, uint64_t out_f32_va, uint64_t out_bf16_va,
+                                     void *stream) {
+    if (!L || !tokens || !ids_va || !wts_va || !x_va || !out_f32_va) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (tokens > L->cfg.max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    return layer_forward(L, tokens, nullptr, (const uint16_t *)(uintptr_t)x_va, (float *)(uintptr_t)out_f32_va, (uint16_t *)(uintptr_t)out_bf16_va, (cudaStream_t)stream,
+                         (const uint32_t *)(uintptr_t)ids_va, (const float *)(uintptr_t)wts_va) ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
 int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *L, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va, uint32_t cap,

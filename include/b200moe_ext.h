@@ -93,6 +93,10 @@ int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *l, uint32_t tokens, const uint16_
 /* device buffers, stream-ordered: out_f32_va f32 [tokens][H] (required), out_bf16_va optional (0 = skip) */
 int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
                               uint64_t out_bf16_va, void *stream);
+/* the same forward with the routing given: ids_va u32 [tokens][topk] and wts_va f32 [tokens][topk] on the device (the outputs of
+ * omega_gpu_moe_router_rows_async), x_va the bf16 input rows; an id outside the layer's experts makes the plan refuse (header status) */
+int omega_gpu_moe_layer_routed_async(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t ids_va, uint64_t wts_va, uint64_t x_va, uint64_t out_f32_va,
+                                     uint64_t out_bf16_va, void *stream);
 /* One forward on the library's stream with a CUDA event between consecutive launches: ms[i] = device time of the i-th
  * kernel (launch order), names[i] = its static name; *count entries (at most cap). For measurement. */
 int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,

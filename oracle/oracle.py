@@ -283,15 +283,18 @@ def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, 
     return dn
 
 
-def moe_layer(logits_bf16, x_bf16, wgu, sgu, wdn, sdn, topk_k=8, threads=None, x_pieces=0, act_pieces=0):
+def moe_layer(logits_bf16, x_bf16, wgu, sgu, wdn, sdn, topk_k=8, threads=None, x_pieces=0, act_pieces=0, routing=None):
     """One MoE layer exactly as the reference host glue strings the operators together: top-k (lowest
     index on ties, renormalised softmax), per pick gate|up GEMV -> SwiGLU -> down GEMV, slot-order weighted
     sum. Inputs bf16 bit patterns; returns (out f32 [T][H], ids, wts f32). x_pieces / act_pieces > 0 pass the layer input /
     the gated activations through the e4m3 piece quantiser first (the tensor-core engine's arithmetic model)."""
-    lg = bf16_to_f32(logits_bf16); x = bf16_to_f32(x_bf16)
+    x = bf16_to_f32(x_bf16)
     T, H = x.shape
-    ids, w64 = topk(lg, topk_k, True)
-    wts = w64.astype(np.float32)
+    if routing is not None:   # (ids u32 [T][k], weights f32 [T][k]) computed elsewhere (the router front half); logits_bf16 is ignored
+        ids, wts = np.ascontiguousarray(routing[0], dtype=np.uint32), np.ascontiguousarray(routing[1], dtype=np.float32)
+    else:
+        ids, w64 = topk(bf16_to_f32(logits_bf16), topk_k, True)
+        wts = w64.astype(np.float32)
     re_ = ids.reshape(-1); rt = np.repeat(np.arange(T, dtype=np.uint32), topk_k); rd = np.arange(T * topk_k, dtype=np.uint32)
     dn = expert_rows(wgu, sgu, wdn, sdn, x, re_, rt, rd, T * topk_k, threads, x_pieces, act_pieces)
     out = combine(wts, dn.reshape(T, topk_k, H))

@@ -184,3 +184,40 @@ def test_fp8_tensor_peak_probe():
     rc = api.lib.omega_gpu_fp8_tensor_peak(C.c_uint32(4000), C.c_uint32(3), C.byref(tf), C.byref(ms))
     assert rc == 0, api.last_error()
     assert 500.0 < tf.value < 6000.0, (tf.value, ms.value)
+
+
+def test_router_then_layer_routed():
+    """residual rows -> router front half (RMSNorm, gate GEMV, top-k; bf16 normalised rows out) -> the layer with that routing, all on
+    the device with no host round trip; the checker strings its router and its layer together the same way"""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(91)
+    E, H, I, topk, T = 32, 512, 256, 4, 48
+    m = build_layer(rng, E, H, I, T, api.ENGINE_MMA, topk)
+    gate = orc.bf16_bits(rng.uniform(-0.05, 0.05, (E, H)).astype(np.float32))
+    nw = rng.uniform(0.8, 1.2, H).astype(np.float32)
+    x = rng.uniform(-2.0, 2.0, (T, H)).astype(np.float32)
+    rc, r = api.moe_router_create(gate, nw); assert rc == 0, api.last_error()
+    dev = torch.device("cuda", 0)
+    xd = torch.from_numpy(x).to(dev)
+    xn16 = torch.empty((T, H), dtype=torch.int16, device=dev); ids = torch.empty((T, topk), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, topk), dtype=torch.float32, device=dev); out32 = torch.empty((T, H), dtype=torch.float32, device=dev)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    u64 = lambda t: C.c_uint64(t.data_ptr())
+    rc = api.lib.omega_gpu_moe_router_rows_async(r, C.c_uint32(T), u64(xd), C.c_uint32(0), C.c_float(1e-6), C.c_int(1), C.c_float(1.0), C.c_uint32(topk),
+                                                 C.c_uint64(0), u64(xn16), C.c_uint64(0), u64(ids), u64(wts), stream)
+    assert rc == 0, api.last_error()
+    rc = api.lib.omega_gpu_moe_layer_routed_async(m["layer"], C.c_uint32(T), u64(ids), u64(wts), u64(xn16), u64(out32), C.c_uint64(0), stream)
+    assert rc == 0, api.last_error()
+    torch.cuda.synchronize()
+    ids_h = ids.cpu().numpy().view(np.uint32); wts_h = wts.cpu().numpy(); xn_h = xn16.cpu().numpy().view(np.uint16); o32 = out32.cpu().numpy()
+    oxn, olg, oids, ow, margin = orc.router(x, nw, gate, 1e-6, topk, True)
+    sure = margin >= 1e-4
+    assert np.array_equal(ids_h[sure], oids[sure]) and np.max(np.abs(wts_h[sure] - ow[sure])) <= 1e-5
+    # bf16 rows: the double oracle rounded the same way, at most one bf16 step apart where the f32 value sits on a rounding boundary
+    want = orc.bf16_bits(oxn.astype(np.float32)).astype(np.int32)
+    assert np.max(np.abs(xn_h.astype(np.int32) - want)) <= 1 and np.mean(xn_h.astype(np.int32) != want) < 1e-2
+    ref, _, _ = orc.moe_layer(None, xn_h, m["wgu"], m["sgu"], m["wdn"], m["sdn"], topk, routing=(ids_h, wts_h))
+    assert np.max(np.abs(o32 - ref)) <= 1e-2 and rel_l2(o32, ref) <= 1e-3, (float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref))
+    api.lib.omega_gpu_moe_router_free(r)
+    free_layer(m)
