@@ -22,8 +22,9 @@ def _ptr(a, typ):
 def build(ref=False):
     """Compile the checker (and, with ref=True and the reference tree present, the reference build)."""
     subprocess.run(["make", "-s", "-C", HERE, "all"], check=True)
-    if ref and os.path.isdir(os.environ.get("B200MOE_REFERENCE", "/root/reference")):
-        subprocess.run(["make", "-s", "-C", HERE, "ref", "REF=" + os.environ.get("B200MOE_REFERENCE", "/root/reference")], check=True)
+    where = os.environ.get("B200MOE_REFERENCE", os.path.normpath(os.path.join(HERE, "..", "..", "reference")))   # beside this repository's folder
+    if ref and os.path.isdir(where):
+        subprocess.run(["make", "-s", "-C", HERE, "ref", "REF=" + where], check=True)
 
 
 _lib = None
