@@ -274,7 +274,7 @@ int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream) {
 }  // extern "C"
 
 // =====================================================================================================================
-// Fused expert-parallel stack: three launches per layer and rank, as on one GPU.
+// Fused expert-parallel stack: the same launches per layer and rank as on one GPU (expert kernel(s) + combine/norm/scatter).
 //
 // Every rank first gathers the router logits of all tokens (they are small) and computes the routing of every layer for
 // all tokens: the global plan tells a sender the sorted row each of its picks has on the rank that owns the expert

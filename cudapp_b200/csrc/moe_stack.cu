@@ -140,7 +140,7 @@ struct OmegaGpuMoeStack {
     cudaGraphExec_t graph; uint32_t graph_tokens; cudaStream_t graph_stream;
     uint64_t g_logits, g_x, g_out32, g_out16;         // addresses the captured graph was built for
     uint32_t launches;
-    // fused path (every layer on the tensor-core engine): routing of all layers up front, three launches per layer
+    // fused path (every layer on the tensor-core engine): routing of all layers up front, then per layer the expert kernel (one launch, or gate|up + down) and combine/norm/scatter
     bool fused;
     uint32_t topk, row_cap, x_pieces, tile_rows;
     uint32_t *ids_all; float *wts_all; PlanBatch pb; size_t map_stride, tile_stride;

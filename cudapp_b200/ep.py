@@ -177,7 +177,7 @@ class EpStack:
 
 
 class FusedEpStack(EpStack):
-    """Three launches per layer and rank (csrc/moe_ep.cu, "fused expert-parallel stack"): routing of all layers from the
+    """Two launches per layer and rank, three with the two-launch expert path (csrc/moe_ep.cu, "fused expert-parallel stack"): routing of all layers from the
     gathered logits up front, activation pieces and result rows travel by peer stores, waits are atomic counters."""
 
     def __init__(self, api, torch, dist, rank, world, layers, tokens, engine=0, seed_base=0):

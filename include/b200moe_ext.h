@@ -150,7 +150,7 @@ int omega_gpu_moe_ep_combine_async(OmegaGpuMoeEp *ep, uint32_t tokens_local, uin
 /* synchronises `stream`; 0, or the code of a bounded cross-GPU wait that ran out (11 dispatch, 12 return) */
 int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream);
 
-/* ---- fused expert-parallel stack: three launches per layer and rank, rows and results travel by peer stores, waits are
+/* ---- fused expert-parallel stack: two launches per layer and rank (three with the two-launch expert path), rows and results travel by peer stores, waits are
  * counters advanced with system-scope atomics (bounded). local[l]: rank's layer l over its experts/world experts, tensor-core
  * engine, max_tokens >= tokens (all ranks' tokens). After create: export this rank's handle, gather all ranks' handles,
  * connect (world 1 needs neither). Per step the caller gathers the router logits of ALL tokens ([layers][tokens][experts]
