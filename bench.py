@@ -194,7 +194,7 @@ def run_ours(args, rank, world):
     assert rc == 0, api.last_error()
 
     rng = np.random.default_rng(0)
-    from oracle.oracle import bf16_bits   # number-format helper only (input generation), not the checker's arithmetic
+    bf16_bits = api.bf16_bits
     logits_h = torch.from_numpy(bf16_bits(rng.normal(0, 1, (Ln, T, E)).astype(np.float32)).view(np.int16)).pin_memory()
     x_h = torch.from_numpy(bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32)).view(np.int16)).pin_memory()
     out_h = torch.empty((T, H), dtype=torch.int16).pin_memory()
@@ -247,7 +247,7 @@ def run_ours(args, rank, world):
     top = "expert_ffn (gate|up + SiLU + pieces -> down, one launch)" if per_layer.value == 1 else "gate|up + down (two launches)"
     kern_ms = {top: float(np.mean(layer_ms))}
     # algorithmic bytes of that work per layer: every distinct expert's codes + scales once, plus the layer's input and output rows
-    from oracle.oracle import bf16_to_f32
+    bf16_to_f32 = api.bf16_to_f32
     ids = np.stack([np.argsort(-bf16_to_f32(logits_h[l].numpy().view(np.uint16)), axis=1, kind="stable")[:, :TOPK] for l in range(min(Ln, 4))])
     distinct = float(np.mean([len(np.unique(ids[l])) for l in range(ids.shape[0])]))
     alg_bytes = distinct * (GU_BYTES + DN_BYTES) + 2 * T * H * 2
@@ -295,7 +295,7 @@ def run_prefill(args):
     here by the library's own probe (MMAs on operands resident in shared memory)."""
     import torch
     from cudapp_b200 import api
-    from oracle.oracle import bf16_bits   # number-format helper only
+    bf16_bits = api.bf16_bits
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     T = 4096 if args.tokens == 256 else args.tokens

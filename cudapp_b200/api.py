@@ -247,6 +247,19 @@ def moe_stack_bf16(stack, logits_bf16, x_bf16, want_f32=True):
     return rc, o16, o32
 
 
+def bf16_bits(x):
+    """f32 array -> bf16 bit patterns (uint16), round to nearest even, NaN kept quiet"""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    nan = (b & 0x7FFFFFFF) > 0x7F800000
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    return np.where(nan, ((b >> 16) | 0x40).astype(np.uint16), r)
+
+
+def bf16_to_f32(bits):
+    """bf16 bit patterns (uint16) -> f32"""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
 def moe_router_create(gate_bf16, norm_w):
     g = np.ascontiguousarray(gate_bf16, dtype=np.uint16); nw = np.ascontiguousarray(norm_w, dtype=np.float32)
     E, H = g.shape

@@ -233,7 +233,7 @@ class FusedEpStack(EpStack):
 
 
 def make_inputs(layers, tokens, seed=0):
-    from oracle.oracle import bf16_bits   # number-format helper only
+    from cudapp_b200.api import bf16_bits
     rng = np.random.default_rng(seed)
     logits = bf16_bits(rng.normal(0, 1, (layers, tokens, E)).astype(np.float32))
     x = bf16_bits(rng.normal(0, 1, (tokens, H)).astype(np.float32))
