@@ -73,3 +73,28 @@ def test_ranges():
     from cudapp_b200 import ep
     assert [ep.expert_range(r, 4, 128) for r in range(4)] == [(0, 32), (32, 64), (64, 96), (96, 128)]
     assert ep.token_range(7, 8, 256) == (224, 256) and ep.region_layout(32, 8, 2048) == (257, 4112)
+
+
+def test_fused_transport_row_addressing():
+    """The fused expert-parallel transport lets a sender compute where a pick's row lives on the rank that owns the expert: the pick's
+    sorted row in the plan over all experts minus the start of that rank's first expert. That must be the row the owner's own plan
+    (over its experts only, ids of other ranks absent) gives the same pick, for every rank count, so that senders and owners agree
+    without exchanging anything but the router logits."""
+    from oracle import oracle as orc
+    rng = np.random.default_rng(9)
+    E, K, T = 128, 8, 96
+    bias = rng.normal(0, 0.7, E)
+    ids, _ = orc.topk((rng.normal(0, 1, (T, E)) + bias).astype(np.float32), K, True)
+    g = orc.plan_global(ids, E)
+    pos = np.empty(T * K, np.int64); pos[g["ymap"][: g["rows"]]] = np.arange(g["rows"])          # pick (t * K + s) -> sorted row over all experts
+    for world in (1, 2, 4, 8):
+        El = E // world
+        for rank in range(world):
+            local = np.where((ids >= rank * El) & (ids < (rank + 1) * El), ids - rank * El, 0xFFFFFFFF).astype(np.uint32)
+            l = orc.plan_global(local, El)
+            mine = np.flatnonzero(local.reshape(-1) != 0xFFFFFFFF)
+            assert l["rows"] == len(mine) == int(g["counts"][rank * El:(rank + 1) * El].sum())
+            lpos = np.empty(T * K, np.int64); lpos[l["ymap"][: l["rows"]]] = np.arange(l["rows"])
+            assert np.array_equal(pos[mine] - int(g["starts"][rank * El]), lpos[mine])
+            # the owner's plan lists the same source tokens in the same order as the slice of the global plan
+            assert np.array_equal(l["xmap"][: l["rows"]], g["xmap"][int(g["starts"][rank * El]): int(g["starts"][rank * El]) + l["rows"]])
