@@ -3,8 +3,8 @@
 // accumulator columns per tcgen05.ld and pays four dependent TMEM round trips per 128-wide K block. Here the CTA has three warpgroups
 // (roles: TMA producer, MMA issuer, scale loader, one idle warp; two promotion warpgroups) and reallocates registers between them
 // (setmaxnreg: 64 for the role warps, 216 for the promotion warps; a register-file quarter then holds 64 + 2 x 216 per lane), so a promotion thread holds 64 + 64 accumulators and stages 64
-// columns at once: two round trips per K block. Selected only on request (B200MOE_WIDE8 in the environment when the layer is created); not the default, and until it has been
-// measured against the sixteen-warp kernel it stays that way.
+// columns at once: two round trips per K block. Selected only on request (B200MOE_WIDE8 in the environment when the layer is created); not the default: it matches the sixteen-warp
+// kernel's results on a B200 but has not been timed against it.
 #include "internal.h"
 #include "mma_common.cuh"
 
