@@ -354,6 +354,12 @@ def run_prefill(args):
     assert rc == 0, api.last_error()
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     api.lib.omega_gpu_moe_layer_free(layer)
+    traffic = None
+    try:   # DRAM bytes of the two GEMM launches from the committed ncu capture of this workload (the 128-row-tile kernel)
+        if T == 4096 and any("wide" in k for k in kern):
+            traffic = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get("wide_gate_up_plus_down")
+    except Exception:
+        traffic = None
     return {
         "metric": "moe_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights and activations, f32 accumulate", "data": "synthetic",
@@ -363,7 +369,7 @@ def run_prefill(args):
         "gpu_launches": launches * steps,
         "roofline": {"bound": "tensor", "kernel": "gate|up + down grouped FP8 GEMM", "achieved": achieved, "peak": float(peak_tf.value), "unit": "TFLOP/s",
                      "frac": achieved / float(peak_tf.value), "peak_kind": "measured by the library's tcgen05 probe (operands resident in shared memory, %.2f ms)" % peak_ms.value,
-                     "flops": flops, "kernel_ms": gemm_ms, "traffic": None},
+                     "flops": flops, "kernel_ms": gemm_ms, "traffic": traffic},
         "clocks": clocks.summary()}
 
 
