@@ -308,3 +308,26 @@ def test_router_against_reference():
             assert np.array_equal(mxn[0], xn) and np.array_equal(mlg[0], lg)          # the same double arithmetic in the same order
             assert np.max(np.abs(mw[0] - w)) <= 1e-15 and abs(mm[0] - m.value) <= 1e-15
             assert abs(w.sum() - 1.0) < 1e-12 if norm else w.sum() < 1.0
+
+
+@need_ref
+def test_plan_against_reference_random():
+    """seeded random plans beyond the reference test's own patterns: any token / slot / expert count inside the caps, absent picks
+    sprinkled in, with and without the shared expert; word for word against the reference's emitted unit"""
+    rng = np.random.default_rng(404)
+    for trial in range(300):
+        tokens = int(rng.integers(0, 129)); slots = int(rng.integers(0, 9)); experts = int(rng.integers(1, 257))
+        shared = int(rng.integers(0, 2))
+        cfg = np.array([shared, tokens, slots, experts, 256 if shared else int(rng.choice([experts, 256])), 1152, 257, 1160], np.uint64)
+        ids = np.zeros(1024, np.uint64)
+        n = tokens * slots
+        ids[:n] = rng.integers(0, experts, n)
+        if n and trial % 3 == 0:
+            ids[rng.integers(0, n, max(1, n // 5))] = 0xFFFFFFFF
+        if n and trial % 50 == 7:
+            ids[int(rng.integers(0, n))] = experts          # one id out of range: both must refuse the same way
+        mine, theirs = orc.plan_buffers(), orc.plan_buffers()
+        rc = orc.moe_plan(cfg, ids, *mine)
+        assert rc == _ref_plan(cfg, ids, theirs), (trial, cfg.tolist())
+        for a, b in zip(mine, theirs):
+            assert np.array_equal(a, b), (trial, cfg.tolist())
