@@ -298,22 +298,25 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_MAX_SEG
 static void *g_noalloc_ptr[64];   // per device: the array's DEVICE address (the symbol itself is only a host-side stand-in)
 
 // One CTA. Turns M sorted expert ids into segment records {w_va, s_va, row0, cnt}. status: 0 ok, 1 ids not sorted or
-// out of range, 2 more segments than the table holds. Everything a previous call left behind is overwritten:
-// the header is rewritten, records [segments, max) are zeroed.
+// out of range, 2 more segments than the table holds, 3 an activation row index at or past x_rows (the GEMM kernel would
+// read x out of bounds). Everything a previous call left behind is overwritten: the header is rewritten, records
+// [segments, max) are zeroed.
 __global__ void __launch_bounds__(1024) noalloc_segments_kernel(unsigned char *scratch, uint32_t M, uint32_t experts, const uint32_t *__restrict__ ids,
+                                                                const uint32_t *__restrict__ token_rows, uint32_t x_rows,
                                                                 uint64_t w_base, uint64_t s_base, uint64_t w_stride, uint64_t s_stride) {
     __shared__ uint32_t warp_sum[32];
-    __shared__ uint32_t s_run, s_bad;
+    __shared__ uint32_t s_run, s_bad, s_bad_row;
     Seg32 *seg = reinterpret_cast<Seg32 *>(scratch);
     uint32_t *hdr = reinterpret_cast<uint32_t *>(scratch + NOALLOC_MAX_SEGMENTS * 32);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    if (tid == 0) { s_run = 0; s_bad = 0; }
+    if (tid == 0) { s_run = 0; s_bad = 0; s_bad_row = 0; }
     __syncthreads();
     for (uint32_t base = 0; base < M; base += 1024) {
         const uint32_t i = base + tid;
         uint32_t flag = 0, e = 0;
         if (i < M) {
             e = ids[i];
+            if (token_rows[i] >= x_rows) s_bad_row = 1;
             const uint32_t prev = i ? ids[i - 1] : 0xffffffffu;
             if (e >= experts || (i && e < prev)) s_bad = 1;
             flag = (i == 0 || e != prev) ? 1u : 0u;
@@ -336,7 +339,7 @@ __global__ void __launch_bounds__(1024) noalloc_segments_kernel(unsigned char *s
     const uint32_t S = s_run, kept = min(S, NOALLOC_MAX_SEGMENTS);
     for (uint32_t z = tid; z < kept; z += 1024) seg[z].cnt = (z + 1 < kept ? seg[z + 1].row0 : M) - seg[z].row0;
     for (uint32_t z = kept + tid; z < NOALLOC_MAX_SEGMENTS; z += 1024) { const Seg32 zero = {0, 0, 0, 0, 0}; seg[z] = zero; }
-    if (tid == 0) { hdr[0] = kept; hdr[1] = s_bad ? 1u : (S > NOALLOC_MAX_SEGMENTS ? 2u : 0u); hdr[2] = 0; hdr[3] = 0; }
+    if (tid == 0) { hdr[0] = kept; hdr[1] = s_bad ? 1u : (s_bad_row ? 3u : (S > NOALLOC_MAX_SEGMENTS ? 2u : 0u)); hdr[2] = 0; hdr[3] = 0; }
 }
 
 }  // namespace b200
@@ -385,7 +388,9 @@ int omega_gpu_fp8gemm_async(const OmegaGpuFp8Tensor *t, uint32_t rows, uint32_t 
 // Allocation-free entry (declared in b200moe_fp8gemm.h). Some hosts of this library may not allocate device memory
 // at all once they are running: a serving process that has handed every byte to its own arena, a caller inside a
 // latency-critical section, a plugin whose embedder forbids cudaMalloc after start-up. The host-staged calls above
-// grow staging buffers on demand, so they are closed to such callers; this one is not.
+// grow staging buffers on demand, so they are closed to such callers; this one is not. Every call blocks once on
+// `stream` (it reads the table builder's status word back), so no call may be made while `stream` is being captured:
+// such a call is refused with BAD_ARGS and queues nothing.
 int omega_gpu_fp8gemm_noalloc(const OmegaGpuFp8Tensor *t, uint32_t M, uint64_t expert_ids_va, uint64_t token_rows_va, uint64_t x_va, int x_bf16,
                               uint32_t x_rows, uint64_t y_va, void *stream) {
     if (!t || !t->w || !M || !expert_ids_va || !token_rows_va || !x_va || !y_va || !x_rows) return OMEGA_GPU_FP8GEMM_BAD_ARGS;
@@ -400,24 +405,31 @@ int omega_gpu_fp8gemm_noalloc(const OmegaGpuFp8Tensor *t, uint32_t M, uint64_t e
     Lock l;
     State &g = st();
     if (!g.opened || g.latched) { set_error("fp8gemm_noalloc: the device is not open (upload a tensor first)"); return OMEGA_GPU_FP8GEMM_CHIP_FAIL; }
-    if (!cuda_ok(cudaSetDevice(t->device), "cudaSetDevice")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
     if (t->device < 0 || t->device >= 64) return OMEGA_GPU_FP8GEMM_BAD_ARGS;
+    cudaStream_t s = (cudaStream_t)stream;
+    // every call waits once on `stream` for its table-building kernel, which a capturing stream cannot do: refuse before
+    // anything is queued, so the caller's capture stays valid and nothing latches
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) { (void)cudaGetLastError(); set_error("fp8gemm_noalloc: not a usable stream"); return OMEGA_GPU_FP8GEMM_BAD_ARGS; }
+    if (cap != cudaStreamCaptureStatusNone) { set_error("fp8gemm_noalloc: the stream is being captured; this entry synchronises the stream once per call and cannot be captured"); return OMEGA_GPU_FP8GEMM_BAD_ARGS; }
+    if (!cuda_ok(cudaSetDevice(t->device), "cudaSetDevice")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
     if (!g_noalloc_ptr[t->device]) {   // set-up, once per device, with that device current
         void *p = nullptr;
         if (!cuda_ok(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(noalloc scratch)") || !p) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
         g_noalloc_ptr[t->device] = p;
     }
     unsigned char *scratch = (unsigned char *)g_noalloc_ptr[t->device];
-    cudaStream_t s = (cudaStream_t)stream;
     uint64_t w0 = 0, s0 = 0;
     (void)omega_gpu_fp8_tensor_entry(t, 0, &w0, &s0);
-    noalloc_segments_kernel<<<1, 1024, 0, s>>>(scratch, M, t->experts, (const uint32_t *)(uintptr_t)expert_ids_va, w0, s0, (uint64_t)t->n * t->k,
+    noalloc_segments_kernel<<<1, 1024, 0, s>>>(scratch, M, t->experts, (const uint32_t *)(uintptr_t)expert_ids_va,
+                                               (const uint32_t *)(uintptr_t)token_rows_va, x_rows, w0, s0, (uint64_t)t->n * t->k,
                                                (uint64_t)(t->n / 128u) * (t->k / 128u) * 4u);
     if (!cuda_ok(cudaGetLastError(), "noalloc segments launch")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
     uint32_t hdr[4] = {0, 0, 0, 0};
     if (!cuda_ok(cudaMemcpyAsync(hdr, scratch + NOALLOC_MAX_SEGMENTS * 32, 16, cudaMemcpyDeviceToHost, s), "copy status") ||
         !cuda_ok(cudaStreamSynchronize(s), "noalloc segments")) return OMEGA_GPU_FP8GEMM_CHIP_FAIL;
     if (hdr[1] == 1) { set_error("fp8gemm_noalloc: expert ids must be non-decreasing and below the expert count"); return OMEGA_GPU_FP8GEMM_BAD_ARGS; }
+    if (hdr[1] == 3) { set_error("fp8gemm_noalloc: a token row index is at or past x_rows (%u)", x_rows); return OMEGA_GPU_FP8GEMM_BAD_ARGS; }
     if (hdr[1] == 2) { set_error("fp8gemm_noalloc: more segments than the fixed table holds"); return OMEGA_GPU_FP8GEMM_TOO_LARGE; }
     GemvArgs a = {};
     a.seg = (const Seg32 *)scratch; a.x = (const void *)(uintptr_t)x_va; a.x_bf16 = x_bf16; a.x_rows = x_rows;

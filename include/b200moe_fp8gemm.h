@@ -61,10 +61,12 @@ int omega_gpu_fp8gemm_async(const OmegaGpuFp8Tensor *t, uint32_t rows, uint32_t 
  * The segment table, which the other entries keep in a staging buffer they allocate, lives in one fixed device array
  * inside the library (about 33 KB per GPU that loads the library, held until the process exits). Limits: at most
  * OMEGA_GPU_FP8GEMM_NOALLOC_MAX_SEGMENTS experts in the tensor and OMEGA_GPU_FP8GEMM_NOALLOC_MAX_ROWS rows; more is
- * refused with TOO_LARGE and a message. The call runs on `stream` (a cudaStream_t as void *) and waits once for its
- * small table-building kernel, so a bad id table is reported (BAD_ARGS) before the GEMM is queued; y is complete when
- * work queued on `stream` after the call runs. The first call on a device looks up the array's device address; make
- * that first call outside any stream capture. All calls share the one array: calls that overlap on the GPU (two
+ * refused with TOO_LARGE and a message. The call runs on `stream` (a cudaStream_t as void *) and EVERY call blocks
+ * once on that stream for its small table-building kernel, so an unsorted or out-of-range id table, or a token row at
+ * or past x_rows, is reported (BAD_ARGS) before the GEMM is queued; y is complete when work queued on `stream` after
+ * the call runs. Because of that wait no call may be made while `stream` is being captured: it is refused with
+ * BAD_ARGS, nothing is queued and the capture stays valid. The first call on a device also looks up the array's device
+ * address. All calls share the one array: calls that overlap on the GPU (two
  * streams, two threads) race on it; calls ordered on one stream do not. Results are bit-identical to
  * omega_gpu_fp8gemm_f32 / _bf16 on the same table. */
 #define OMEGA_GPU_FP8GEMM_NOALLOC_MAX_SEGMENTS 1024u

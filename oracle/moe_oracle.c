@@ -215,6 +215,18 @@ void orc_combine(const float *w, const float *d, uint32_t slots, uint32_t hidden
     }
 }
 
+/* The prefill form of the same combine (src/omega_blackwell_codegen_pfhost.h:23-31; host loop mc_ref,
+ * tests/gpu_pfhost_test.c:38-49): the accumulator starts at +0.0 and row s of token r is down[inv[r*K+s]].
+ * Equal to orc_combine except for the sign of an exact zero. */
+void orc_combine_mc(const float *down, const uint32_t *inv, const float *wt, uint32_t rows, uint32_t hidden, uint32_t K, float *out) {
+    for (uint32_t r = 0; r < rows; r++)
+        for (uint32_t c = 0; c < hidden; c++) {
+            float acc = 0.0f;
+            for (uint32_t g = 0; g < K; g++) { const float p = wt[(size_t)r * K + g] * down[(size_t)inv[(size_t)r * K + g] * hidden + c]; acc = acc + p; }
+            out[(size_t)r * hidden + c] = acc;
+        }
+}
+
 /* RMSNorm as the reference host glue computes it: sum of squares in double, one f32 factor, then
  * x * s * w (tests/gpu_decode_graph_test.c:56-60). w may be NULL (all ones). */
 void orc_rmsnorm(const float *x, const float *w, uint32_t hidden, float eps, float *out) {

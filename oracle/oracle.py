@@ -148,6 +148,27 @@ def ref_router_lib():
     return C.CDLL(path) if os.path.exists(path) else None
 
 
+def ref_static_lib(which):
+    """One of the reference test files' static functions, compiled in place (oracle/ref_static_shims.c): which = "emu", "pq" or "mc"."""
+    path = os.path.join(HERE, "_ref", "libref_%s.so" % which)
+    if not os.path.exists(path):
+        return None
+    L = C.CDLL(path)
+    if which == "emu":
+        L.ref_emu_row.restype = C.c_float
+    return L
+
+
+def combine_mc(down, inv, wt):
+    """prefill form of the combine: down f32 [R][H], inv u32 [T][K], wt f32 [T][K] -> out f32 [T][H] (accumulator starts at +0)."""
+    down = np.ascontiguousarray(down, dtype=np.float32); inv = np.ascontiguousarray(inv, dtype=np.uint32); wt = np.ascontiguousarray(wt, dtype=np.float32)
+    T, K = inv.shape
+    H = down.shape[1]
+    out = np.empty((T, H), np.float32)
+    lib().orc_combine_mc(_ptr(down, F32P), _ptr(inv, U32P), _ptr(wt, F32P), C.c_uint32(T), C.c_uint32(H), C.c_uint32(K), _ptr(out, F32P))
+    return out
+
+
 def swiglu(gu):
     gu = np.ascontiguousarray(gu, dtype=np.float32)
     rows, two_i = gu.shape

@@ -15,7 +15,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import oracle as orc  # noqa: E402
-from tests.test_oracle_pin import plan_cases, router_case  # noqa: E402
+from tests.test_oracle_pin import plan_cases, router_case, emu_case, ref_emu, pq_case, mc_case  # noqa: E402
 
 U8P, U16P, U32P, U64P, F32P, F64P = orc.U8P, orc.U16P, orc.U32P, orc.U64P, orc.F32P, orc.F64P
 p = lambda a, t: a.ctypes.data_as(t)
@@ -75,6 +75,22 @@ def main():
         r_ids.append(ids.copy()); r_w.append(w.copy()); r_lg.append(lg.copy()); r_xn.append(xn[::16].copy()); r_m.append(m.value)
     out.update(router_seeds=np.array(seeds, np.float64), router_ids=np.stack(r_ids), router_w=np.stack(r_w), router_logits=np.stack(r_lg),
                router_xn16=np.stack(r_xn), router_margin=np.array(r_m))
+    # three static functions of the reference's own tests, compiled in place (oracle/ref_static_shims.c)
+    EMU, PQ, MC = orc.ref_static_lib("emu"), orc.ref_static_lib("pq"), orc.ref_static_lib("mc")
+    if EMU is None or PQ is None or MC is None:
+        raise SystemExit("reference static-function shims not present: run `make -C oracle ref` first")
+    emu_seeds = [(21, 128, 512), (22, 128, 768), (23, 128, 2048)]           # inputs are regenerated from the seeds
+    out["emu_seeds"] = np.array(emu_seeds, np.uint32)
+    out["emu_y"] = np.concatenate([ref_emu(*emu_case(*c)) for c in emu_seeds])
+    x = pq_case(8, 512)                                                     # the reference generator's own stream: kept as data
+    q = np.empty((8, 512), np.uint8); s_ = np.empty((8, 4), np.float32)
+    for r in range(8):
+        PQ.ref_pq(p(x[r], F32P), C.c_uint32(512), p(q[r], U8P), p(s_[r], F32P))
+    out.update(pq_x=x, pq_q=q, pq_s=s_)
+    down, inv, wt = mc_case(31, 6, 256, 8)
+    ref = np.empty((6, 256), np.float32)
+    MC.ref_mc(p(down, F32P), p(inv, U32P), p(wt, F32P), C.c_uint32(6), C.c_uint32(256), C.c_uint32(8), p(ref, F32P))
+    out["mc_out"] = ref
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **out)
     print("wrote", os.path.join(HERE, "reference_vectors.npz"), {k_: v_.shape for k_, v_ in out.items()})
 

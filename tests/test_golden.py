@@ -6,7 +6,7 @@ import os
 import numpy as np
 
 from oracle import oracle as orc
-from tests.test_oracle_pin import plan_cases, router_case
+from tests.test_oracle_pin import plan_cases, router_case, emu_case, mc_case
 
 G = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
 
@@ -60,3 +60,24 @@ def test_router_front_half():
         assert np.array_equal(ids[0], G["router_ids"][i])
         assert np.array_equal(lg[0], G["router_logits"][i]) and np.array_equal(xn[0][::16], G["router_xn16"][i])
         assert np.max(np.abs(w[0] - G["router_w"][i])) <= 1e-15 and abs(m[0] - G["router_margin"][i]) <= 1e-15
+
+
+def test_gemv_emulation():
+    """the kernels' f32 summation order against emu_row of the reference's grouped-GEMM test"""
+    at = 0
+    for seed, n, k in G["emu_seeds"]:
+        w8, sc, x = emu_case(int(seed), int(n), int(k))
+        assert np.array_equal(orc.gemv_emu(w8, sc, x).view(np.uint32), G["emu_y"][at: at + int(n)].view(np.uint32))
+        at += int(n)
+
+
+def test_act_quant():
+    """activation quantiser against pq_ref of the reference's FP8 x FP8 GEMM test, on that test's own input stream"""
+    q, s = orc.act_quant(G["pq_x"])
+    assert np.array_equal(q, G["pq_q"]) and np.array_equal(s.view(np.uint32), G["pq_s"].view(np.uint32))
+
+
+def test_combine_prefill_form():
+    """slot-order multiply-then-add combine against mc_ref of the reference's prefill host-kernel test"""
+    down, inv, wt = mc_case(31, 6, 256, 8)
+    assert np.array_equal(orc.combine_mc(down, inv, wt).view(np.uint32), G["mc_out"].view(np.uint32))

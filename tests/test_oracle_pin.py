@@ -16,6 +16,7 @@ from oracle import oracle as orc
 REF = orc.ref_lib()
 REFG = orc.ref_group_lib()
 REFR = orc.ref_router_lib()
+REF_EMU, REF_PQ, REF_MC = orc.ref_static_lib("emu"), orc.ref_static_lib("pq"), orc.ref_static_lib("mc")
 need_ref = pytest.mark.skipif(REF is None, reason="reference build (oracle/_ref) not present")
 U8P, U16P, U32P, U64P, F32P, F64P = orc.U8P, orc.U16P, orc.U32P, orc.U64P, orc.F32P, orc.F64P
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -331,3 +332,73 @@ def test_plan_against_reference_random():
         assert rc == _ref_plan(cfg, ids, theirs), (trial, cfg.tolist())
         for a, b in zip(mine, theirs):
             assert np.array_equal(a, b), (trial, cfg.tolist())
+
+
+# ------------------------------------------------------------------ static functions of the reference's own tests, compiled in place
+def emu_case(seed, n, k):
+    """weights and scales drawn as the reference test draws them (any non-NaN code, bf16 scales of either sign: tests/gpu_fp8gemm_test.c:40-47)"""
+    rng = np.random.default_rng(seed)
+    w8 = rng.integers(0, 256, (n, k)).astype(np.uint8); w8[(w8 & 0x7F) == 0x7F] -= 1
+    sc = orc.bf16_bits((rng.uniform(0.001, 0.1, (n // 128, k // 128)) * rng.choice([-1.0, 1.0], (n // 128, k // 128))).astype(np.float32))
+    x = rng.uniform(-2, 2, k).astype(np.float32)
+    return w8, sc, x
+
+
+def ref_emu(w8, sc, x):
+    n, k = w8.shape
+    lb = 16 if k % 512 == 0 else 8
+    return np.array([REF_EMU.ref_emu_row(ptr(w8[r], U8P), ptr(sc[r // 128], U16P), ptr(x, F32P), C.c_uint32(k), C.c_uint32(lb)) for r in range(n)], np.float32)
+
+
+@pytest.mark.skipif(REF_EMU is None, reason="reference emu_row (oracle/_ref/libref_emu.so) not present")
+def test_gemv_emulation_against_reference():
+    """the kernels' exact f32 summation order: the checker's restatement against emu_row of tests/gpu_fp8gemm_test.c:48-69, bit for bit
+    (the reference folds 2^64 / 2^56 / 2^-120 into x / scale / weight; exact powers of two whose product is 1)"""
+    for seed, n, k in ((1, 128, 512), (2, 256, 768), (3, 128, 2048), (4, 128, 256), (5, 256, 1024)):
+        w8, sc, x = emu_case(seed, n, k)
+        assert np.array_equal(orc.gemv_emu(w8, sc, x).view(np.uint32), ref_emu(w8, sc, x).view(np.uint32)), (seed, n, k)
+
+
+def pq_case(rows, k):
+    """activations from the reference test's own generator (rand_act, tests/gpu_qgemm_test.c:36-40), row 3 zero, one huge outlier in row 5 (:43-47)"""
+    x = np.empty(rows * k, np.float32)
+    REF_PQ.ref_pq_rand_act(ptr(x, F32P), C.c_uint32(rows * k))
+    x = x.reshape(rows, k)
+    x[3] = 0
+    x[5, 77] = 3.0e4
+    return x
+
+
+@pytest.mark.skipif(REF_PQ is None, reason="reference pq_ref (oracle/_ref/libref_pq.so) not present")
+def test_act_quant_against_reference():
+    """activation quantiser (per row, per 128 columns: power-of-two scale, e4m3 RNE sat-finite) against pq_ref of tests/gpu_qgemm_test.c:24-35"""
+    for rows, k in ((8, 256), (16, 2048), (7, 768)):
+        x = pq_case(rows, k)
+        q, s = orc.act_quant(x)
+        for r in range(rows):
+            rq = np.empty(k, np.uint8); rs = np.empty(k // 128, np.float32)
+            REF_PQ.ref_pq(ptr(x[r], F32P), C.c_uint32(k), ptr(rq, U8P), ptr(rs, F32P))
+            assert np.array_equal(q[r], rq) and np.array_equal(s[r].view(np.uint32), rs.view(np.uint32)), (rows, k, r)
+
+
+def mc_case(seed, rows, h, K):
+    rng = np.random.default_rng(seed)
+    down = (rng.uniform(-1, 1, (rows * K, h)) * rng.choice([1.0, 40.0, 0.0], (rows * K, h), p=[0.96, 0.02, 0.02])).astype(np.float32)
+    wt = rng.uniform(0, 1, (rows, K)).astype(np.float32)
+    inv = rng.permutation(rows * K).astype(np.uint32).reshape(rows, K)
+    return down, inv, wt
+
+
+@pytest.mark.skipif(REF_MC is None, reason="reference mc_ref (oracle/_ref/libref_mc.so) not present")
+def test_combine_against_reference():
+    """slot-order multiply-then-add combine against mc_ref of tests/gpu_pfhost_test.c:38-49, bit for bit; the decode form (accumulator
+    starts at the first product) differs from it in the sign of an exact zero at most"""
+    for seed, rows, h, K in ((1, 5, 256, 8), (2, 33, 2048, 8), (3, 4, 128, 9), (4, 9, 512, 1)):
+        down, inv, wt = mc_case(seed, rows, h, K)
+        ref = np.empty((rows, h), np.float32)
+        REF_MC.ref_mc(ptr(down, F32P), ptr(inv, U32P), ptr(wt, F32P), C.c_uint32(rows), C.c_uint32(h), C.c_uint32(K), ptr(ref, F32P))
+        assert np.array_equal(orc.combine_mc(down, inv, wt).view(np.uint32), ref.view(np.uint32))
+        dec = orc.combine(wt, down[inv.reshape(-1)].reshape(rows, K, h))
+        assert np.array_equal(dec, ref)                                        # equal as numbers everywhere ...
+        nz = ref != 0
+        assert np.array_equal(dec.view(np.uint32)[nz], ref.view(np.uint32)[nz])   # ... and as bits wherever the sum is not an exact zero
