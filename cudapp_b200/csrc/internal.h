@@ -118,8 +118,6 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
 uint32_t mma_wide_tile_rows();
 bool mma_wide_shape_ok(uint32_t n, uint32_t k, uint32_t mode);
 cudaError_t launch_mma_wide(const void *tm_w, const void *tm_q, const MmaLaunch &m, cudaStream_t s);
-// variant with eight promotion warps and register reallocation (fp8_mma_wide8_sm100.cu); same tiles, same results
-cudaError_t launch_mma_wide8(const void *tm_w, const void *tm_q, const MmaLaunch &m, cudaStream_t s);
 // whole expert FFN of a layer in one launch (fp8_ffn_sm100.cu); piece counts (2,3), (1,1) or (2,2)
 struct FfnLaunch {
     const float *gu_scale, *dn_scale, *x_scale; uint8_t *qa; float *sa; const void *tiles; const uint32_t *header, *ymap; float *out;

@@ -286,8 +286,10 @@ int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream) {
 //   down GEMM: stores every result row straight into its token owner's buffer and advances the owner's counter;
 // and the next combine waits for its tokens' 8 x (hidden/256) result slices. Counters only grow; counters, piece buffers and
 // scale buffers alternate by layer parity: a peer that already has all its results of layer l may deliver rows of layer l+1
-// while this rank still reads rows of layer l, but rows of layer l+2 cannot be sent before this rank has finished layer l
-// (they depend on its layer l+1 results). No collective and no host round trip per layer.
+// while this rank still reads rows of layer l. Rows of layer l+2 go into the buffers layer l used, so a sender first waits for
+// the destination's buffer credit: every rank tells every other, after its expert kernel of a layer has completed, how many layers of
+// that parity it has consumed (one store per peer and layer), and a sender compares its local copy of that number with the
+// number of same-parity layers before the one it sends for. No collective and no host round trip per layer.
 #include <vector>
 
 struct OmegaGpuMoeEpStack {
@@ -297,8 +299,8 @@ struct OmegaGpuMoeEpStack {
     char *route;                         // routing scratch (ids, weights, two plan batches)
     uint32_t *ids_g, *ids_l; float *wts_g;
     b200::PlanBatch pg, pl; size_t map_stride, tile_stride;
-    uint8_t *comm; size_t comm_bytes, q_par, off_sx, sx_par, off_dn, off_cnt;   // peers map this block: pieces x2 | scales x2 | results | counters (x2: by layer parity)
-    uint64_t *peer_tab;                  // device [4][world]: pieces, scales, results, counters of every rank
+    uint8_t *comm; size_t comm_bytes, q_par, off_sx, sx_par, off_dn, off_cnt, off_credit;   // peers map this block: pieces x2 | scales x2 | results | counters (x2: by layer parity)
+    uint64_t *peer_tab;                  // device [5][world]: pieces, scales, results, counters, buffer credits of every rank
     float *h; uint32_t *err, *sched; bool one_launch;
     void *opened[64]; int n_opened; int connected;
     alignas(128) unsigned char tm_qx[2][128];
@@ -322,7 +324,9 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         const uint32_t *__restrict__ ids_next, const uint32_t *__restrict__ pos_next, const uint32_t *__restrict__ starts_next, uint32_t experts_local,
         uint32_t pieces, size_t piece_stride, size_t q_off, size_t sx_off, const uint64_t *__restrict__ q_peers, const uint64_t *__restrict__ sx_peers, const uint64_t *__restrict__ cnt_peers,
         uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err, uint32_t *__restrict__ sched, uint32_t n_sched,
-        unsigned long long *bump, const uint32_t *bump_rows) {
+        unsigned long long *bump, const uint32_t *bump_rows,
+        uint32_t world, uint32_t rank, const uint64_t *__restrict__ credit_peers, const unsigned long long *credit_local,
+        uint32_t done_parity, uint32_t done_uses_per_step, uint32_t done_uses_before, uint32_t next_uses_per_step, uint32_t next_uses_before) {
     __shared__ double red[8];
     __shared__ float s_scale;
     __shared__ uint32_t s_d[32], s_row[32], s_fail;
@@ -334,6 +338,14 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     if (blockIdx.x == 0) {
         if (sched) for (uint32_t i = tid; i < n_sched; i += 256) sched[i] = 0;
         if (bump && tid == 0) *bump += *bump_rows;
+        // Buffer credit: this rank's expert kernel of the layer before this kernel has completed, so the piece and scale buffers of that
+        // layer's parity may be overwritten (by rows of the layer two ahead). Tell every rank how many layers of that parity this rank
+        // has consumed since the stack was made; a sender waits on its own copy of that number before it stores into this rank.
+        if (done_parity < 2u && tid < world) {
+            const unsigned long long v = (unsigned long long)(*step - 1u) * done_uses_per_step + done_uses_before + 1ull;
+            unsigned long long *dst = reinterpret_cast<unsigned long long *>(credit_peers[tid]) + 2u * rank + done_parity;
+            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(v) : "memory");
+        }
     }
     if (tid == 0) {
         s_fail = *reinterpret_cast<volatile uint32_t *>(err) ? 1u : 0u;
@@ -355,6 +367,22 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         const size_t i = (size_t)t * topk + tid;        // ids_next / pos_next are already offset to this rank's first token
         const uint32_t d = ids_next[i] / experts_local;
         s_d[tid] = d; s_row[tid] = pos_next[i] - starts_next[d * experts_local];
+    }
+    __syncthreads();
+    if (q_peers && tid < topk && !s_fail) {
+        // the destination's buffers of the next layer's parity still hold the rows of the layer two back until that rank's expert kernel
+        // for it has completed: wait (bounded) for its credit. Data dependence through routed rows usually implies it, but not for every routing.
+        const unsigned long long want = (unsigned long long)(*step - 1u) * next_uses_per_step + next_uses_before;
+        const unsigned long long *c = credit_local + 2u * s_d[tid] + parity;
+        bool ok = want == 0ull;
+        for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+            unsigned long long v;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(c) : "memory");
+            ok = v >= want;
+            if (!ok && (i & 63u) == 63u && *reinterpret_cast<volatile uint32_t *>(err)) break;
+            if (!ok) __nanosleep(100);
+        }
+        if (!ok) { atomicCAS(err, 0u, 17u); s_fail = 1; }
     }
     __syncthreads();
     if (s_fail) return;
@@ -477,14 +505,15 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
                         ffn_shape_ok(v0.hidden, v0.inter) && !getenv("B200MOE_TWO_LAUNCH");
         // the block peers write into: activation pieces | their scales | result rows of the local tokens | counters
         const size_t qb = ((size_t)S->x_pieces * Rp * H + 255) & ~(size_t)255, sb = (Rp * (H / 128) * 4 + 255) & ~(size_t)255, db = ((size_t)S->tokens_local * K * H * 4 + 255) & ~(size_t)255;
-        S->q_par = qb; S->off_sx = 2 * qb; S->sx_par = sb; S->off_dn = 2 * qb + 2 * sb; S->off_cnt = S->off_dn + db; S->comm_bytes = S->off_cnt + 256;
+        S->q_par = qb; S->off_sx = 2 * qb; S->sx_par = sb; S->off_dn = 2 * qb + 2 * sb; S->off_cnt = S->off_dn + db; S->off_credit = S->off_cnt + 256; S->comm_bytes = S->off_credit + 64 * 2 * 8;   // counters, then credits [source rank][layer parity]
         ok = cuda_ok(cudaMalloc(&S->comm, S->comm_bytes), "cudaMalloc(ep comm)") && cuda_ok(cudaMemset(S->comm, 0, S->comm_bytes), "memset") &&
-             cuda_ok(cudaMalloc(&S->peer_tab, (size_t)world * 32), "cudaMalloc(ep peers)") && make_tmap_u8(S->tm_qx[0], S->comm, (uint64_t)S->x_pieces * Rp, H, 32) &&
+             cuda_ok(cudaMalloc(&S->peer_tab, (size_t)world * 40), "cudaMalloc(ep peers)") && make_tmap_u8(S->tm_qx[0], S->comm, (uint64_t)S->x_pieces * Rp, H, 32) &&
              make_tmap_u8(S->tm_qx[1], S->comm + S->q_par, (uint64_t)S->x_pieces * Rp, H, 32);
     }
     if (ok && world == 1) {
-        uint64_t tab[4] = {(uint64_t)(uintptr_t)S->comm, (uint64_t)(uintptr_t)(S->comm + S->off_sx), (uint64_t)(uintptr_t)(S->comm + S->off_dn), (uint64_t)(uintptr_t)(S->comm + S->off_cnt)};
-        ok = cuda_ok(cudaMemcpy(S->peer_tab, tab, 32, cudaMemcpyHostToDevice), "copy peer table"); S->connected = 1;
+        uint64_t tab[5] = {(uint64_t)(uintptr_t)S->comm, (uint64_t)(uintptr_t)(S->comm + S->off_sx), (uint64_t)(uintptr_t)(S->comm + S->off_dn), (uint64_t)(uintptr_t)(S->comm + S->off_cnt),
+                           (uint64_t)(uintptr_t)(S->comm + S->off_credit)};
+        ok = cuda_ok(cudaMemcpy(S->peer_tab, tab, 40, cudaMemcpyHostToDevice), "copy peer table"); S->connected = 1;
     }
     if (!ok) { if (S->route) cudaFree(S->route); if (S->comm) cudaFree(S->comm); if (S->peer_tab) cudaFree(S->peer_tab); delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
     *out = S;
@@ -514,7 +543,7 @@ int omega_gpu_moe_epstack_connect(OmegaGpuMoeEpStack *S, const uint8_t *handles)
     if (!S || !handles) return OMEGA_GPU_FP8_BAD_ARGS;
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
-    uint64_t tab[4 * 64];
+    uint64_t tab[5 * 64];
     for (uint32_t r = 0; r < S->world; r++) {
         uint8_t *base = S->comm;
         if (r != S->rank) {
@@ -525,8 +554,9 @@ int omega_gpu_moe_epstack_connect(OmegaGpuMoeEpStack *S, const uint8_t *handles)
         }
         tab[r] = (uint64_t)(uintptr_t)base; tab[S->world + r] = (uint64_t)(uintptr_t)(base + S->off_sx);
         tab[2 * S->world + r] = (uint64_t)(uintptr_t)(base + S->off_dn); tab[3 * S->world + r] = (uint64_t)(uintptr_t)(base + S->off_cnt);
+        tab[4 * S->world + r] = (uint64_t)(uintptr_t)(base + S->off_credit);
     }
-    if (!cuda_ok(cudaMemcpy(S->peer_tab, tab, (size_t)S->world * 32, cudaMemcpyHostToDevice), "copy peer table")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    if (!cuda_ok(cudaMemcpy(S->peer_tab, tab, (size_t)S->world * 40, cudaMemcpyHostToDevice), "copy peer table")) return OMEGA_GPU_FP8_CHIP_FAIL;
     S->connected = 1;
     return OMEGA_GPU_FP8_OK;
 }
@@ -547,6 +577,7 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
     const uint64_t *tab = S->peer_tab;
     unsigned long long *cnt = (unsigned long long *)(S->comm + S->off_cnt);   // [0..1] delivered input rows by layer parity, [2..3] delivered result slices
     float *dn_local = (float *)(S->comm + S->off_dn);
+    const unsigned long long *credit = (const unsigned long long *)(S->comm + S->off_credit);   // [source rank][parity], written by that rank
     uint32_t n = 0;
     LayerView v0; layer_view(S->local[0], &v0);
     bool ok = cuda_ok(launch_topk(Ln * T, E, K, (int)v0.norm_topk, (const uint16_t *)(uintptr_t)logits_all_va, S->ids_g, S->wts_g, s), "topk launch"); n++;
@@ -559,7 +590,8 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
     unsigned long long *base = (unsigned long long *)(S->err + 8);   // [0..1]: input rows already consumed through the even / odd layer counter
     ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull, S->err + 4, 0u, 0u,
                                                       S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, (size_t)0, (size_t)0, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err,
-                                                      S->sched, (uint32_t)S->tile_stride + 1u, nullptr, nullptr); n++;
+                                                      S->sched, (uint32_t)S->tile_stride + 1u, nullptr, nullptr,
+                                                      G, S->rank, tab + 4 * G, credit, 0xffffffffu, 0u, 0u, (Ln + 1u) / 2u, 0u); n++;
     for (uint32_t l = 0; l < Ln && ok; l++) {
         LayerView v; layer_view(S->local[l], &v);
         const uint32_t par = l & 1u;
@@ -590,7 +622,8 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
                                                                   last ? nullptr : S->ids_g + (size_t)(l + 1) * R + tok0, last ? nullptr : S->pg.pos + nx + tok0,
                                                                   last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, (par ^ 1u) * S->q_par, (par ^ 1u) * S->sx_par, last ? nullptr : tab, tab + G, tab + 3 * G,
                                                                   par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err,
-                                                                  S->sched, (uint32_t)S->tile_stride + 1u, S->one_launch ? base + par : nullptr, hdr);
+                                                                  S->sched, (uint32_t)S->tile_stride + 1u, S->one_launch ? base + par : nullptr, hdr,
+                                                                  G, S->rank, tab + 4 * G, credit, par, (Ln + 1u - par) / 2u, l / 2u, (Ln + par) / 2u, (l + 1u) / 2u);
         n++;
     }
     S->launches = n;

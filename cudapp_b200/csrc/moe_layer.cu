@@ -76,7 +76,6 @@ struct OmegaGpuMoeLayer {
     alignas(128) unsigned char tm_gu[128], tm_dn[128], tm_qx[128], tm_qa[128];   // TMA descriptors (tensor-core engine)
     uint32_t tile_rows;
     bool wide_ok;                // single-piece activations and shapes the 128-row-tile kernel takes
-    bool wide8;                  // the eight-promotion-warp variant of that kernel was asked for
 };
 
 namespace b200 {
@@ -126,12 +125,12 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
         g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.ymap = nullptr; g.out = nullptr;
         g.q_out = w->qa; g.s_out = w->sa; g.q_rows = Rp; g.q_pieces = Pa;
         g.n = 2 * I; g.k = H; g.mode = 0; g.out_stride = I; g.err = w->header + 4;
-        if (!cuda_ok(wide ? (L->wide8 ? launch_mma_wide8(L->tm_gu, L->tm_qx, g, s) : launch_mma_wide(L->tm_gu, L->tm_qx, g, s)) : launch_mma_grouped(L->tm_gu, L->tm_qx, Px, g, s), "gate|up mma launch")) return false;
+        if (!cuda_ok(wide ? launch_mma_wide(L->tm_gu, L->tm_qx, g, s) : launch_mma_grouped(L->tm_gu, L->tm_qx, Px, g, s), "gate|up mma launch")) return false;
         MARK(wide ? "gate_up_mma_wide" : "gate_up_mma");
         MmaLaunch dd = {};
         dd.wscale = L->dn->s; dd.ascale = w->sa; dd.tiles = w->tiles; dd.header = w->header; dd.ymap = w->ymap; dd.out = w->dn; dd.q_rows = Rp;
         dd.n = H; dd.k = I; dd.mode = 1; dd.out_stride = H; dd.err = w->header + 4;
-        if (!cuda_ok(wide ? (L->wide8 ? launch_mma_wide8(L->tm_dn, L->tm_qa, dd, s) : launch_mma_wide(L->tm_dn, L->tm_qa, dd, s)) : launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false;
+        if (!cuda_ok(wide ? launch_mma_wide(L->tm_dn, L->tm_qa, dd, s) : launch_mma_grouped(L->tm_dn, L->tm_qa, Pa, dd, s), "down mma launch")) return false;
         MARK(wide ? "down_mma_wide" : "down_mma");
         if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
         L->launches = n + extra + extra_q; L->marks = n;
@@ -249,7 +248,6 @@ int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuF
     L->tile_rows = mma_tile_rows(L->cfg.x_pieces > L->cfg.act_pieces ? L->cfg.x_pieces : L->cfg.act_pieces);
     L->wide_ok = L->cfg.engine == OMEGA_GPU_MOE_ENGINE_MMA && L->cfg.x_pieces == 1 && L->cfg.act_pieces == 1 && mma_wide_shape_ok(2 * L->inter, L->hidden, 0) &&
                  mma_wide_shape_ok(L->hidden, L->inter, 1);
-    L->wide8 = L->wide_ok && getenv("B200MOE_WIDE8") != nullptr;
     if ((L->cfg.tile_rows != 0 && L->cfg.tile_rows != 32 && L->cfg.tile_rows != 128) || (L->cfg.tile_rows == 128 && !L->wide_ok)) {
         free(L); set_error("moe layer: tile_rows must be 0, 32 or 128; 128 needs the tensor-core engine, x_pieces = act_pieces = 1 and k <= 2048"); return OMEGA_GPU_FP8_BAD_ARGS;
     }

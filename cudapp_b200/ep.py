@@ -231,6 +231,75 @@ class FusedEpStack(EpStack):
     def status(self):
         return int(self.api.lib.omega_gpu_moe_epstack_status(self.eps, C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
 
+    def close(self):
+        """free this rank's exchange object, layers and tensors (every rank must have finished its steps: peers map this memory)"""
+        self.torch.cuda.synchronize(); self.dist.barrier()
+        self.graph = None
+        self.api.lib.omega_gpu_moe_epstack_free(self.eps)
+        for layer in self.layers:
+            self.api.lib.omega_gpu_moe_layer_free(layer)
+        for t in self.tensors:
+            self.api.fp8_tensor_free(t)
+        self.layers, self.tensors = [], []
+        self.torch.cuda.empty_cache(); self.dist.barrier()
+
+
+def parity_check(api, torch, dist, rank, world, tokens, engine, layers=2, seed_base=0):
+    """Outside any timed region: a `layers`-deep instance of the fused expert-parallel stack (same seeds as the first layers of the
+    benchmark) against the single-GPU stack that rank 0 builds over all experts from the same seeds. Every rank's residual rows
+    must equal the single-GPU rows bit for bit. Returns the verdict agreed by all ranks."""
+    st = FusedEpStack(api, torch, dist, rank, world, layers, tokens, engine=engine, seed_base=seed_base)
+    logits, x = make_inputs(layers, tokens, seed=77)
+    t0, t1 = token_range(rank, world, tokens)
+    st.logits.copy_(torch.from_numpy(np.ascontiguousarray(logits[:, t0:t1]).view(np.int16))); st.x.copy_(torch.from_numpy(np.ascontiguousarray(x[t0:t1]).view(np.int16)))
+    st.capture()            # one eager step, then the captured graph
+    st.step()               # the replayed graph must give the same rows
+    torch.cuda.synchronize()
+    code = st.status()
+    mine = torch.cat([st.h.reshape(-1).view(torch.int32), st.out16.reshape(-1).to(torch.int32)])      # f32 bits and bf16 bits of this rank's rows
+    gathered = torch.empty((world, mine.numel()), dtype=torch.int32, device=st.dev)
+    dist.all_gather_into_tensor(gathered.view(-1), mine)
+    ok = torch.tensor([1 if code == 0 else 0], dtype=torch.int32, device=st.dev)
+    if rank == 0 and code == 0:
+        dev = st.dev
+        full = []
+        w8 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=dev); sc = torch.empty((E, 2 * I // 128, H // 128), dtype=torch.int16, device=dev)
+        d8 = torch.empty((E, H, I), dtype=torch.uint8, device=dev); dsc = torch.empty((E, H // 128, I // 128), dtype=torch.int16, device=dev)
+        lib = api.lib
+        tensors = []
+        for l in range(layers):
+            g = torch.Generator(device=dev); g.manual_seed(seed_base + l)
+            wgu = (torch.randn((E * 2 * I, H), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            wdn = (torch.randn((E * H, I), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            torch.cuda.synchronize()
+            assert lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * 2 * I), C.c_uint32(H), C.c_uint64(wgu.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0, api.last_error()
+            assert lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * H), C.c_uint32(I), C.c_uint64(wdn.data_ptr()), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr())) == 0, api.last_error()
+            tg, td = C.c_void_p(), C.c_void_p()
+            assert lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(2 * I), C.c_uint32(H), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr()), C.byref(tg)) == 0, api.last_error()
+            assert lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(H), C.c_uint32(I), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr()), C.byref(td)) == 0, api.last_error()
+            rc, layer = api.moe_layer_create(tg, td, topk=TOPK, max_tokens=tokens, engine=engine)
+            assert rc == 0, api.last_error()
+            full.append(layer); tensors += [tg, td]
+            del wgu, wdn
+        del w8, sc, d8, dsc
+        rc, stack = api.moe_stack_create(full, 1e-6); assert rc == 0, api.last_error()
+        rc, o16, o32 = api.moe_stack_bf16(stack, logits, x); assert rc == 0, api.last_error()
+        got = gathered.cpu().numpy()
+        Tl = tokens // world
+        h_bits = np.concatenate([got[r, : Tl * H] for r in range(world)]).view(np.uint32).reshape(tokens, H)
+        o_bits = np.concatenate([got[r, Tl * H:] for r in range(world)]).astype(np.uint16).reshape(tokens, H)
+        same = bool(np.array_equal(h_bits, o32.view(np.uint32)) and np.array_equal(o_bits, o16))
+        ok[0] = 1 if same else 0
+        lib.omega_gpu_moe_stack_free(stack)
+        for layer in full:
+            lib.omega_gpu_moe_layer_free(layer)
+        for t in tensors:
+            api.fp8_tensor_free(t)
+        torch.cuda.empty_cache()
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    st.close()
+    return bool(ok.item() == 1), code
+
 
 def make_inputs(layers, tokens, seed=0):
     from cudapp_b200.api import bf16_bits
@@ -259,9 +328,19 @@ def bench(args, rank, world):
     watchdog = threading.Timer(limit, give_up); watchdog.daemon = True; watchdog.start()
     torch.cuda.set_device(local)
     os.environ.setdefault("B200MOE_DEVICE", str(local))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # NCCL only carries a barrier, small gathers and reductions here; no rank's buffers get bound to a multicast object
     dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     mode = os.environ.get("B200MOE_EP_MODE", "fused")
     Ln, T = args.layers, args.tokens
+    parity = None
+    if mode == "fused":
+        same, code = parity_check(api, torch, dist, rank, world, T, args.engine)
+        parity = {"bit_equal": same, "layers": 2, "ranks": world, "against": "single-GPU stack on rank 0, same seeds", "status": code}
+        if not same:
+            if rank == 0:
+                print(json.dumps({"metric": "moe_layer_tokens_per_s", "n_gpus": world, "parity": parity, "error": "expert-parallel rows differ from the single-GPU stack"}))
+            sys.stdout.flush(); torch.cuda.synchronize(); dist.barrier()
+            os._exit(4)
     st = FusedEpStack(api, torch, dist, rank, world, Ln, T, engine=args.engine) if mode == "fused" else EpStack(api, torch, dist, rank, world, Ln, T, mode=mode, engine=args.engine)
     logits, x = make_inputs(Ln, T)
     t0, t1 = token_range(rank, world, T)
@@ -310,7 +389,7 @@ def bench(args, rank, world):
                        "parallelism": "ep%d (experts and tokens sharded; %s)" % (world, {"fused": "rows and results by peer stores over NVLink inside the layer kernels, 2 launches per layer", "p2p": "direct peer stores over NVLink", "nccl": "NCCL all-to-all"}[mode]),
                        "l2": "%.1f GB of weights per GPU per step: larger than L2" % (per_gpu_bytes / 1e9)},
             "e2e": {"value": T / float(e2e.item()), "unit": "tokens/s", "h2d_bytes_per_step": int((lg_h.numel() + x_h.numel()) * 2 * world), "d2h_bytes_per_step": int(out_h.numel() * 2 * world)},
-            "gpu_launches": int(st.launches) * args.steps,
+            "gpu_launches": int(st.launches) * args.steps, "parity": parity,
             "roofline": {"bound": "hbm", "kernel": "whole step per GPU (weights streamed once)", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": kind + " copy bandwidth", "traffic": None},
             "clocks": clocks.summary()}))

@@ -47,6 +47,23 @@ def test_rc_names_and_helpers():
     assert api.lib.omega_fp8_pack_scan_nan(w.ctypes.data_as(C.c_void_p), C.c_size_t(100), C.byref(first)) == 2 and first.value == 17
 
 
+def test_exported_double_oracle():
+    """the exported host helper omega_fp8_gemv_oracle (src/omega_gpu_fp8_api.h:224-238; never called by a compute entry) against the checker"""
+    rng = np.random.default_rng(5)
+    n, k = 256, 512
+    w8, sc = orc.quantize_bf16(orc.bf16_bits(rng.normal(0, 0.02, (n, k)).astype(np.float32)))
+    x = rng.normal(0, 1, k).astype(np.float32)
+    y = np.empty(n, np.float64); m = np.empty(n, np.float64)
+    api.lib.omega_fp8_gemv_oracle.restype = None
+    api.lib.omega_fp8_gemv_oracle(w8.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p), C.c_uint32(n), C.c_uint32(k), x.ctypes.data_as(C.c_void_p),
+                                  y.ctypes.data_as(C.c_void_p), m.ctypes.data_as(C.c_void_p))
+    ry, rm = orc.gemv(w8, sc, x, mag=True)
+    assert np.max(np.abs(y - ry) / rm) < 1e-14 and np.max(np.abs(m - rm) / rm) < 1e-14     # same products, summation order may differ
+    api.lib.omega_fp8_gemv_oracle(w8.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p), C.c_uint32(n), C.c_uint32(k), x.ctypes.data_as(C.c_void_p),
+                                  y.ctypes.data_as(C.c_void_p), None)                         # the magnitude output is optional
+    assert np.max(np.abs(y - ry) / rm) < 1e-14
+
+
 def test_upload_refusals_before_device():
     w = np.zeros((1, 128, 128), np.uint8); s = np.full((1, 1, 1), 0x3F80, np.uint16)
     assert api.fp8_tensor_upload(1, 128, 100, w, s)[0] == api.BAD_ARGS          # k not a multiple of 128

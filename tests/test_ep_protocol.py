@@ -98,3 +98,88 @@ def test_fused_transport_row_addressing():
             assert np.array_equal(pos[mine] - int(g["starts"][rank * El]), lpos[mine])
             # the owner's plan lists the same source tokens in the same order as the slice of the global plan
             assert np.array_equal(l["xmap"][: l["rows"]], g["xmap"][int(g["starts"][rank * El]): int(g["starts"][rank * El]) + l["rows"]])
+
+
+# ---------------------------------------------------------------- buffer discipline of the fused transport (a model, no GPU)
+def _simulate_fused(routes, world, layers, credits, order):
+    """Event model of the fused expert-parallel stack's hand-offs (csrc/moe_ep.cu). Per rank and layer two kernels run in stream order:
+    EXPERT(l) starts when the delivered-row counter of parity l & 1 has reached everything the rank's plan expects up to layer l;
+    COMBINE(l) starts when every rank that holds an expert of this rank's tokens has finished EXPERT(l), and then stores the rows of
+    layer l + 1 into their owners' buffers of parity (l + 1) & 1. routes[l][src][dst] = rows src's tokens send to dst's experts for
+    layer l. With credits, a sender first waits until the destination has finished the expert kernel of the last layer that used the
+    same buffers (layer l - 1 when sending for l + 1). `order` = rank priority of an adversarial scheduler: the first rank that can
+    move always moves. Returns (finished, violations): a violation = rows stored into a buffer whose previous rows were not consumed
+    yet, or an expert kernel released before its own layer's rows were all in."""
+    stage = [0] * world                    # kernels completed per rank: 0 = initial scatter pending, then 1 + 2 * l (+1) ...
+    delivered = [[[0] * layers for _ in range(world)] for _ in range(2)]    # [parity][dst][layer] rows stored (kept per layer to audit)
+    expert_done = [-1] * world
+    violations = []
+
+    def rows_expected(dst, upto_layer, parity):
+        return sum(routes[l][s][dst] for l in range(upto_layer + 1) if l & 1 == parity for s in range(world))
+
+    def send(src, layer):                  # rows of `layer` leave src
+        for dst in range(world):
+            n = routes[layer][src][dst]
+            if not n:
+                continue
+            if layer >= 2 and expert_done[dst] < layer - 2:
+                violations.append(("overwrite", src, dst, layer))
+            delivered[layer & 1][dst][layer] += n
+
+    def can_send(src, layer):
+        if not credits or layer < 2:
+            return True
+        return all(expert_done[dst] >= layer - 2 for dst in range(world) if routes[layer][src][dst])
+
+    progress = True
+    while progress:
+        progress = False
+        for r in order:
+            k = stage[r]
+            if k == 0:                      # initial scatter: rows of layer 0
+                send(r, 0); stage[r] = 1; progress = True; break
+            l, phase = (k - 1) // 2, (k - 1) % 2
+            if l >= layers:
+                continue
+            if phase == 0:                  # EXPERT(l): the counter of its parity only grows and is compared with a running total
+                got = sum(delivered[l & 1][r])
+                if got >= rows_expected(r, l, l & 1):
+                    if sum(delivered[l & 1][r][: l + 1]) < rows_expected(r, l, l & 1):
+                        violations.append(("early release", r, l))
+                    expert_done[r] = l; stage[r] = k + 1; progress = True; break
+            else:                           # COMBINE(l): needs the results of every rank its tokens were routed to
+                need = [d for d in range(world) if routes[l][r][d]]
+                if all(expert_done[d] >= l for d in need) and (l + 1 >= layers or can_send(r, l + 1)):
+                    if l + 1 < layers:
+                        send(r, l + 1)
+                    stage[r] = k + 1; progress = True; break
+    return all(s == 1 + 2 * layers for s in stage), violations
+
+
+def test_fused_transport_buffer_credits():
+    """Routing in which rank 0 sends nothing to rank 1 for two layers and then does: without the buffer credit rank 0 may store rows of
+    layer 2 into rank 1's buffers while rank 1 has not consumed layer 0 (the model catches it: rows overwritten and the counter gate
+    released early); with the credit every schedule finishes without a violation."""
+    world, layers = 2, 5
+    z = lambda: [[0] * world for _ in range(world)]
+    routes = [z() for _ in range(layers)]
+    for l in range(layers):
+        routes[l][1][1] = 16                              # rank 1's tokens stay on rank 1's experts
+        routes[l][0][0] = 16
+    routes[0][1][0] = 0
+    routes[2][0][1] = 8; routes[2][0][0] = 8              # from layer 2 on rank 0's tokens also use rank 1's experts
+    routes[3][0][1] = 8; routes[3][0][0] = 8
+    routes[4][0][1] = 4; routes[4][0][0] = 12
+    done, bad = _simulate_fused(routes, world, layers, credits=False, order=[0, 1])     # rank 0 runs ahead whenever it can
+    assert any(v[0] == "overwrite" for v in bad), "the model must catch the missing credit"
+    for order in ([0, 1], [1, 0]):
+        done, bad = _simulate_fused(routes, world, layers, credits=True, order=order)
+        assert done and not bad, (order, bad)
+    # dense routing (every rank sends to every rank in every layer), four ranks, every rank in turn favoured by the scheduler
+    world, layers = 4, 6
+    routes = [[[3 + ((l + s + d) % 4) for d in range(world)] for s in range(world)] for l in range(layers)]
+    for first in range(world):
+        order = [first] + [r for r in range(world) if r != first]
+        done, bad = _simulate_fused(routes, world, layers, credits=True, order=order)
+        assert done and not bad, (order, bad)

@@ -1,0 +1,172 @@
+"""The stream-ordered device forms (_async / _dev) of the C-ABI, each against the host-staged entry or the checker it must agree with.
+
+These are the forms a serving process uses (device pointers in, nothing staged, nothing read back); the host-staged entries that the
+other GPU tests call go through the same kernels but not through these argument paths. W4 is run at the full size of the benchmark's
+W4 configuration (x bf16 [16, 4096], W int4 [4096, 4096], fp16 scale per 32) against the double self-oracle: the reference has no
+integer-W4 arithmetic, so that parity is unpinned.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from cudapp_b200 import api
+from oracle import oracle as orc
+from tests.test_gpu_ops import make_weights, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    import torch
+    a = np.ascontiguousarray(a)
+    view = {np.dtype(np.uint32): np.int32, np.dtype(np.uint16): np.int16, np.dtype(np.uint64): np.int64}.get(a.dtype)
+    return torch.from_numpy(a.view(view) if view else a).to("cuda:0")
+
+
+def va(t):
+    return C.c_uint64(t.data_ptr())
+
+
+def group_table(t, ids):
+    tab = np.empty((len(ids), 2), np.uint64)
+    for i, e in enumerate(ids):
+        w, s = C.c_uint64(), C.c_uint64()
+        assert api.lib.omega_gpu_fp8_tensor_entry(t, C.c_uint32(int(e)), C.byref(w), C.byref(s)) == 0
+        tab[i] = (w.value, s.value)
+    return tab
+
+
+def test_gemv_grouped_dev_and_async():
+    """grouped GEMV, device forms: the _dev entry takes a row that carries the reference router's 2^64 fold and removes it exactly
+    (src/omega_gpu_fp8_api.h:115-118); the _async entry takes plain rows, shared or one per group, f32 or bf16"""
+    import torch
+    rng = np.random.default_rng(31)
+    E, n, k, groups = 12, 256, 1024, 8
+    w8, sc = make_weights(rng, E, n, k)
+    rc, t = api.fp8_tensor_upload(E, n, k, w8, sc); assert rc == 0, api.last_error()
+    ids = rng.choice(E, groups, replace=False).astype(np.uint32)
+    x1 = rng.normal(0, 1, (1, k)).astype(np.float32)
+    rc, want = api.fp8_gemv_grouped_f32(t, ids, x1); assert rc == 0, api.last_error()
+    d_tab = dev(group_table(t, ids))
+    d_xf = dev((x1 * np.float32(2.0 ** 64)).astype(np.float32))           # exact: a power of two
+    y = np.empty((groups, n), np.float32)
+    info = api.Fp8Info()
+    rc = api.lib.omega_gpu_fp8_gemv_grouped_dev(t, C.c_uint32(groups), va(d_tab), va(d_xf), y.ctypes.data_as(C.c_void_p), C.byref(info))
+    assert rc == 0, api.last_error()
+    assert np.array_equal(y.view(np.uint32), want.view(np.uint32)) and info.groups == groups
+    assert api.lib.omega_gpu_fp8_gemv_grouped_dev(t, C.c_uint32(groups), C.c_uint64(0), va(d_xf), y.ctypes.data_as(C.c_void_p), None) == api.BAD_ARGS
+    # _async: shared f32 row, then one bf16 row per group
+    s = torch.cuda.Stream()
+    d_x1 = dev(x1); d_y = torch.full((groups, n), -999.0, dtype=torch.float32, device="cuda:0")
+    torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_fp8_gemv_grouped_async(t, C.c_uint32(groups), va(d_tab), va(d_x1), C.c_uint32(1), C.c_int(0), va(d_y), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    assert np.array_equal(d_y.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    xg = orc.bf16_bits(rng.normal(0, 1, (groups, k)).astype(np.float32))
+    rc, want_g = api.fp8_gemv_grouped_f32(t, ids, orc.bf16_to_f32(xg)); assert rc == 0, api.last_error()
+    d_xg = dev(xg); d_y.fill_(-999.0); torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_fp8_gemv_grouped_async(t, C.c_uint32(groups), va(d_tab), va(d_xg), C.c_uint32(groups), C.c_int(1), va(d_y), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    assert np.array_equal(d_y.cpu().numpy().view(np.uint32), want_g.view(np.uint32))
+    assert api.lib.omega_gpu_fp8_gemv_grouped_async(t, C.c_uint32(groups), va(d_tab), va(d_xg), C.c_uint32(3), C.c_int(1), va(d_y), C.c_void_p(s.cuda_stream)) == api.BAD_ARGS
+    api.fp8_tensor_free(t)
+
+
+def test_fp8gemm_async_with_and_without_maps():
+    """row-table GEMM, device form (the reference's record entry, src/omega_gpu_fp8gemm_api.h:103): segment records from the device
+    plan; without maps row p reads x row p and writes y row p, with maps it reads x[XMAP[p]] and writes y[YMAP[p]]"""
+    import torch
+    rng = np.random.default_rng(32)
+    E, n, k, T, S = 10, 256, 512, 21, 3
+    w8, sc = make_weights(rng, E, n, k)
+    rc, t = api.fp8_tensor_upload(E, n, k, w8, sc); assert rc == 0, api.last_error()
+    picks = np.stack([rng.choice(E, S, replace=False) for _ in range(T)]).astype(np.uint32)
+    x = rng.uniform(-2, 2, (T, k)).astype(np.float32)
+    g = orc.plan_global(picks, E, ystride=S)
+    R = g["rows"]
+    ids_sorted = np.repeat(np.arange(E, dtype=np.uint32), g["counts"])
+    rc, want = api.fp8gemm(t, ids_sorted, g["xmap"][:R], x); assert rc == 0, api.last_error()    # sorted row p <- x[xmap[p]]
+    # the device plan builds the segment records (directory = the tensor's own entries)
+    d_dir = dev(group_table(t, np.arange(E)))
+    d_ids = dev(picks)
+    d_counts = torch.zeros(E, dtype=torch.int32, device="cuda:0"); d_starts = torch.zeros_like(d_counts)
+    d_xmap = torch.zeros(R + 8, dtype=torch.int32, device="cuda:0"); d_ymap = torch.zeros_like(d_xmap)
+    d_seg = torch.zeros(E * 8, dtype=torch.int32, device="cuda:0"); d_hdr = torch.zeros(8, dtype=torch.int32, device="cuda:0")
+    o = api.MoePlanOut(d_counts.data_ptr(), d_starts.data_ptr(), d_xmap.data_ptr(), d_ymap.data_ptr(), d_seg.data_ptr(), d_dir.data_ptr(), 0, 0, 0, d_hdr.data_ptr())
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_moe_plan_async(C.c_uint32(T), C.c_uint32(S), C.c_uint32(E), C.c_uint32(S), C.c_uint32(0), va(d_ids), C.byref(o), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    hdr = d_hdr.cpu().numpy().view(np.uint32)
+    assert hdr[0] == R and hdr[3] == 0
+    assert np.array_equal(d_counts.cpu().numpy().view(np.uint32), g["counts"]) and np.array_equal(d_starts.cpu().numpy().view(np.uint32), g["starts"])
+    assert np.array_equal(d_xmap.cpu().numpy().view(np.uint32), g["xmap"]) and np.array_equal(d_ymap.cpu().numpy().view(np.uint32), g["ymap"])
+    segs = int(hdr[1])
+    d_x = dev(x)
+    # with maps: y row ymap[p] = token * S + slot
+    d_y = torch.full((T * S, n), -999.0, dtype=torch.float32, device="cuda:0"); torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_fp8gemm_async(t, C.c_uint32(R), C.c_uint32(segs), va(d_seg), va(d_x), C.c_int(0), va(d_y), va(d_xmap), va(d_ymap), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    got = d_y.cpu().numpy()
+    assert np.array_equal(got[g["ymap"][:R]].view(np.uint32), want.view(np.uint32))
+    # without maps: the caller gathers x into sorted order itself
+    d_xs = dev(x[g["xmap"][:R]]); d_y2 = torch.full((R, n), -999.0, dtype=torch.float32, device="cuda:0"); torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_fp8gemm_async(t, C.c_uint32(R), C.c_uint32(segs), va(d_seg), va(d_xs), C.c_int(0), va(d_y2), C.c_uint64(0), C.c_uint64(0), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    assert np.array_equal(d_y2.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    # one map without the other is refused
+    assert api.lib.omega_gpu_fp8gemm_async(t, C.c_uint32(R), C.c_uint32(segs), va(d_seg), va(d_x), C.c_int(0), va(d_y), va(d_xmap), C.c_uint64(0), C.c_void_p(s.cuda_stream)) == api.BAD_ARGS
+    api.fp8_tensor_free(t)
+
+
+def test_topk_async_and_residual_norm_async():
+    import torch
+    rng = np.random.default_rng(33)
+    T, E, K, H = 37, 128, 8, 1024
+    logits = orc.bf16_bits(np.round(rng.normal(0, 1, (T, E)) * 4) / 4)       # coarse values: many ties, the lowest index must win
+    d_lg = dev(logits); d_ids = torch.zeros((T, K), dtype=torch.int32, device="cuda:0"); d_w = torch.zeros((T, K), dtype=torch.float32, device="cuda:0")
+    s = torch.cuda.Stream(); torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_moe_topk_async(C.c_uint32(T), C.c_uint32(E), C.c_uint32(K), C.c_int(1), va(d_lg), va(d_ids), va(d_w), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    rid, rw = orc.topk(orc.bf16_to_f32(logits), K, True)
+    assert np.array_equal(d_ids.cpu().numpy().view(np.uint32), rid) and np.max(np.abs(d_w.cpu().numpy() - rw)) <= 1e-5
+    # residual step: h = bf16->f32(x16), xn = bf16(RMSNorm(h)); then h += m, h16 = bf16(h)
+    x16 = orc.bf16_bits(rng.normal(0, 1.5, (T, H)).astype(np.float32)); m = rng.normal(0, 0.3, (T, H)).astype(np.float32)
+    d_x16 = dev(x16); d_m = dev(m)
+    d_h = torch.zeros((T, H), dtype=torch.float32, device="cuda:0"); d_xn = torch.zeros((T, H), dtype=torch.int16, device="cuda:0"); d_h16 = torch.zeros_like(d_xn)
+    torch.cuda.synchronize()
+    rc = api.lib.omega_gpu_residual_norm_async(C.c_uint32(T), C.c_uint32(H), C.c_float(1e-6), va(d_x16), C.c_uint64(0), va(d_h), va(d_xn), C.c_uint64(0), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    h0 = orc.bf16_to_f32(x16)
+    assert np.array_equal(d_h.cpu().numpy(), h0)
+    assert np.array_equal(d_xn.cpu().numpy().view(np.uint16), orc.bf16_bits(orc.rmsnorm(h0, 1e-6)))
+    rc = api.lib.omega_gpu_residual_norm_async(C.c_uint32(T), C.c_uint32(H), C.c_float(1e-6), C.c_uint64(0), va(d_m), va(d_h), va(d_xn), va(d_h16), C.c_void_p(s.cuda_stream))
+    assert rc == 0, api.last_error()
+    s.synchronize()
+    h1 = h0 + m
+    assert np.array_equal(d_h.cpu().numpy(), h1) and np.array_equal(d_h16.cpu().numpy().view(np.uint16), orc.bf16_bits(h1))
+    assert np.array_equal(d_xn.cpu().numpy().view(np.uint16), orc.bf16_bits(orc.rmsnorm(h1, 1e-6)))
+    assert api.lib.omega_gpu_residual_norm_async(C.c_uint32(0), C.c_uint32(H), C.c_float(1e-6), C.c_uint64(0), va(d_m), va(d_h), va(d_xn), va(d_h16), C.c_void_p(s.cuda_stream)) == api.BAD_ARGS
+
+
+def test_w4_gemm_full_size():
+    """the benchmark's W4 configuration at its own size: 16 x 4096 activations, 4096 x 4096 int4 weights; double self-oracle (parity unpinned:
+    no reference W4), the benchmark's bars on the unrounded f32 result and on the bf16 output"""
+    rng = np.random.default_rng(41)
+    n, k, m = 4096, 4096, 16
+    packed, sc = orc.w4_quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (m, k)).astype(np.float32))
+    rc, t, _ = api.w4_upload(packed, sc); assert rc == 0, api.last_error()
+    rc, y16, y32 = api.w4_gemm_bf16(t, n, xb); assert rc == 0, api.last_error()
+    ref = orc.w4_gemm(packed, sc, orc.bf16_to_f32(xb))
+    assert np.max(np.abs(y32 - ref)) <= 1e-2 and rel_l2(y32, ref) <= 1e-3, (float(np.max(np.abs(y32 - ref))), rel_l2(y32, ref))
+    assert np.array_equal(y16, orc.bf16_bits(y32))
+    api.lib.omega_gpu_w4_free(t)

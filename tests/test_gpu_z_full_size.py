@@ -5,28 +5,54 @@ The decode layer (64 tokens) is compared with the checker on every token. The pr
 large for the checker to follow row by row in seconds, so it is pinned three ways: the routing of all 4096 tokens bit-exact, a seeded
 sample of tokens against the checker (a token's output depends on no other token; the reference samples rows the same way,
 tests/gpu_fp8gemm_test.c:9), and a property over all rows: permuting the tokens permutes the outputs bit for bit.
+
+The 48-layer x 256-token stack (the configuration the throughput metric is quoted on) is followed by the checker on a seeded sample of
+tokens through all 48 layers (each layer's weights are copied back from the GPU one layer at a time).
+
+Every expert has its own weights: they are drawn and quantised on the GPU (the quantiser kernel is itself checked bit for bit in
+test_gpu_ops.py) and the codes and scales the checker uses are copied back from there.
 """
+import ctypes as C
+
 import numpy as np
 import pytest
 
 from cudapp_b200 import api
 from oracle import oracle as orc
-from tests.test_gpu_ops import make_weights, rel_l2
+from tests.test_gpu_ops import rel_l2
 
 pytestmark = pytest.mark.gpu
 E, H, I, K = 128, 2048, 768, 8
 
 
+def gpu_layer_weights(seed, host=True):
+    """One layer's 128 distinct experts, drawn (N(0, 0.02) -> bf16) and quantised on the GPU; returns the two uploaded tensors and,
+    with host=True, the codes and bf16 scales as numpy arrays for the checker."""
+    import torch
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev); g.manual_seed(seed)
+    out = {}
+    for name, n, k in (("gu", 2 * I, H), ("dn", H, I)):
+        w = (torch.randn((E * n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        w8 = torch.empty((E, n, k), dtype=torch.uint8, device=dev); sc = torch.empty((E, n // 128, k // 128), dtype=torch.int16, device=dev)
+        torch.cuda.synchronize()
+        assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * n), C.c_uint32(k), C.c_uint64(w.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0, api.last_error()
+        t = C.c_void_p()
+        assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(n), C.c_uint32(k), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr()), C.byref(t)) == 0, api.last_error()
+        out["t" + name] = t
+        if host:
+            out["w" + name] = w8.cpu().numpy(); out["s" + name] = sc.cpu().numpy().view(np.uint16)
+        del w, w8, sc
+    return out
+
+
 @pytest.fixture(scope="module")
 def full():
-    rng = np.random.default_rng(2027)
-    base = 16   # distinct weight sets; experts e and e + 16 share one (the host-side generation of 128 would take half a minute)
-    wgu, sgu = (np.ascontiguousarray(np.tile(a, (E // base, 1, 1))) for a in make_weights(rng, base, 2 * I, H))
-    wdn, sdn = (np.ascontiguousarray(np.tile(a, (E // base, 1, 1))) for a in make_weights(rng, base, H, I))
-    rc, tgu = api.fp8_tensor_upload(E, 2 * I, H, wgu, sgu); assert rc == 0, api.last_error()
-    rc, tdn = api.fp8_tensor_upload(E, H, I, wdn, sdn); assert rc == 0, api.last_error()
-    yield dict(wgu=wgu, sgu=sgu, wdn=wdn, sdn=sdn, tgu=tgu, tdn=tdn)
-    api.fp8_tensor_free(tgu); api.fp8_tensor_free(tdn)
+    d = gpu_layer_weights(2027)
+    # no two experts share a weight block: a kernel that read expert e + 16 for expert e would be caught
+    assert len({d["wgu"][e, :64, :64].tobytes() for e in range(E)}) == E and len({d["wdn"][e, :64, :64].tobytes() for e in range(E)}) == E
+    yield d
+    api.fp8_tensor_free(d["tgu"]); api.fp8_tensor_free(d["tdn"])
 
 
 def test_decode_layer_64_tokens(full):
@@ -69,3 +95,52 @@ def test_prefill_layer_4096_tokens(full):
     assert np.array_equal(pids, ids[perm])
     assert np.array_equal(p32.view(np.uint32), o32[perm].view(np.uint32))
     api.lib.omega_gpu_moe_layer_free(layer)
+
+
+def test_stack_48_layers_256_tokens():
+    """The whole 48-layer step on 256 tokens. Layers 0, 1 and 47 are checked one at a time to the per-layer bar: the checker computes the
+    layer from the residual stream the GPU itself held before it (stacks over the first 1, 2, 47 and 48 layers give those streams), on a
+    seeded sample of tokens (a token's path depends on no other token). The checker also follows the sample through all 48 layers on its
+    own; there the two paths drift apart by more than one layer's error, because every layer rounds its normalised input to bf16 and a
+    difference of one part in 10^5 now and then flips such a rounding (one part in 256): that end-to-end distance has its own, wider bar."""
+    import torch
+    Ln, T = 48, 256
+    rng = np.random.default_rng(48256)
+    logits = orc.bf16_bits(rng.normal(0, 1, (Ln, T, E)).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    pick = np.sort(rng.choice(T, 6, replace=False))
+    h = orc.bf16_to_f32(xb[pick])
+    layers, tensors, keep = [], [], {}
+    for l in range(Ln):
+        d = gpu_layer_weights(1000 + l)
+        rc, layer = api.moe_layer_create(d["tgu"], d["tdn"], topk=K, max_tokens=T); assert rc == 0, api.last_error()
+        layers.append(layer); tensors += [d["tgu"], d["tdn"]]
+        xn = orc.bf16_bits(orc.rmsnorm(h, 1e-6))
+        mo, _, _ = orc.moe_layer(logits[l][pick], xn, d["wgu"], d["sgu"], d["wdn"], d["sdn"], K)
+        h = h + mo
+        if l in (0, 1, Ln - 1):
+            keep[l] = d
+        del d
+    torch.cuda.empty_cache()
+
+    def run(n_layers):
+        rc, stack = api.moe_stack_create(layers[:n_layers], 1e-6); assert rc == 0, api.last_error()
+        rc, o16, o32 = api.moe_stack_bf16(stack, logits[:n_layers], xb); assert rc == 0, api.last_error()
+        rc, o16b, o32b = api.moe_stack_bf16(stack, logits[:n_layers], xb)        # graph replay: identical bits
+        assert rc == 0 and np.array_equal(o32.view(np.uint32), o32b.view(np.uint32))
+        assert np.isfinite(o32).all() and np.array_equal(o16, orc.bf16_bits(o32))
+        api.lib.omega_gpu_moe_stack_free(stack)
+        return o32
+    stream = {0: orc.bf16_to_f32(xb), 1: run(1), 2: run(2), Ln - 1: run(Ln - 1), Ln: run(Ln)}
+    for l in (0, 1, Ln - 1):       # one layer at a time, from the GPU's own residual stream: the per-layer bar
+        d = keep[l]
+        h_in = stream[l][pick]
+        mo, _, _ = orc.moe_layer(logits[l][pick], orc.bf16_bits(orc.rmsnorm(h_in, 1e-6)), d["wgu"], d["sgu"], d["wdn"], d["sdn"], K)
+        want = h_in + mo; got = stream[l + 1][pick]
+        assert np.max(np.abs(got - want)) <= 1e-2 and rel_l2(got - h_in, mo) <= 1e-3, (l, float(np.max(np.abs(got - want))), rel_l2(got - h_in, mo))
+    got = stream[Ln][pick]            # all 48 layers, checker on its own path: the wider end-to-end bar
+    assert np.max(np.abs(got - h)) <= 5e-2 and rel_l2(got, h) <= 1e-2, (float(np.max(np.abs(got - h))), rel_l2(got, h))
+    for layer in layers:
+        api.lib.omega_gpu_moe_layer_free(layer)
+    for t in tensors:
+        api.fp8_tensor_free(t)
