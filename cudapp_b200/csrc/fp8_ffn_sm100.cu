@@ -24,7 +24,7 @@ struct FfnArgs {
     uint32_t *err;
     // expert parallelism (null / 0 on one GPU): wait until peers have delivered header[0] input rows past *gate_base; down results go to the
     // owning rank's buffer (row y -> rank y / rows_per_rank) and each owner's counter [ret_index] is advanced once per delivered 256-feature slice
-    const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index;
+    const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index; uint32_t wait_limit;
 };
 
 constexpr uint32_t FFN_RING = 64;                 // ring of published down-unit ids; the producer is never more than a few units ahead of the slowest role
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                         tma_load_2d(dst + A_TILE, mw, full_bar(kb), (int)(kb * 128u), wy1);
                     }
                     griddep_wait(); griddep_launch();
-                    if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13))) { *abort_flag = 1; break; }
+                    if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13, a.wait_limit))) { *abort_flag = 1; break; }
                     if (q.mode && !(ok = tile_ready(q.tile, 21))) break;
                     for (uint32_t kb = 0; kb < npre; kb++)
                         for (uint32_t p = 0; p < P; p++)
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
         // ---------------------------------------------------------------- scale loader
         bool ok = true;
         griddep_wait();
-        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 14)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
+        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 14, a.wait_limit)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
         for (uint32_t n = 0; ok; n++) {
             uint32_t u = 0, have = 0;
             if (lane == 0) have = unit_at(n, u) ? 1u : 0u;
@@ -365,7 +365,7 @@ cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, 
     FfnArgs a = {};
     a.gu_scale = m.gu_scale; a.dn_scale = m.dn_scale; a.x_scale = m.x_scale; a.qa = m.qa; a.sa = m.sa; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap;
     a.out = m.out; a.hidden = m.hidden; a.inter = m.inter; a.q_rows = m.q_rows; a.sched = m.sched; a.err = m.err;
-    a.gate = m.gate; a.gate_base = m.gate_base; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index;
+    a.gate = m.gate; a.gate_base = m.gate_base; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index; a.wait_limit = m.wait_limit ? m.wait_limit : (1u << 22);
     const int sms = st().sm_count ? st().sm_count : 148;
     const CUtensorMap *w0 = (const CUtensorMap *)tm_gu, *q0 = (const CUtensorMap *)tm_qx, *w1 = (const CUtensorMap *)tm_dn, *q1 = (const CUtensorMap *)tm_qa;
 #define LAUNCH(PXV, PAV)                                                                                                                \

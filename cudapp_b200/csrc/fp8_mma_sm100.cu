@@ -42,6 +42,7 @@ struct MmaArgs {
     uint32_t rows_per_rank, ret_index;  // ret_index: which counter of the owner's counter block this launch advances
     const unsigned long long *gate_base; // rows delivered through `gate` before this layer (counters only ever grow)
     unsigned long long *bump;           // a base to advance by header[0] (the gate|up GEMM of this layer has consumed those rows)
+    uint32_t wait_limit;                // iterations of the bounded wait on `gate`
 };
 
 template <int P>
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
                 if (phase == 1) {
                     griddep_wait(); griddep_launch();
                     if (a.bump && blockIdx.x == 0) *a.bump += a.header[0];
-                    if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13))) { *abort_flag = 1; break; }
+                    if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13, a.wait_limit))) { *abort_flag = 1; break; }
                 }
                 it = phase == 2 ? STAGES : 0;
                 uint32_t seen = 0;
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
         // ---------------------------------------------------------------- scale loader: next unit's scales while this one runs
         uint32_t n = 0; bool ok = true;
         griddep_wait();   // the row scales below are the previous kernel's output
-        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 14)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
+        if (a.gate) { if (lane == 0 && !gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 14, a.wait_limit)) *abort_flag = 1; __syncwarp(); if (*abort_flag) ok = false; }
         for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
             const uint4 t = a.tiles[u / a.pairs]; const uint32_t j = u % a.pairs, b = n & 1u;
             const uint32_t r0 = a.mode == 0 ? j * 128u : 2u * j * 128u, r1 = a.mode == 0 ? a.inter + j * 128u : (2u * j + 1u) * 128u;
@@ -336,7 +337,7 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
     MmaArgs a = {};
     a.wscale = m.wscale; a.ascale = m.ascale; a.tiles = (const uint4 *)m.tiles; a.header = m.header; a.ymap = m.ymap; a.out = m.out;
     a.q_out = m.q_out; a.s_out = m.s_out; a.q_rows = m.q_rows; a.q_pieces = m.q_pieces;
-    a.gate = m.gate; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index; a.gate_base = m.gate_base; a.bump = m.bump;
+    a.gate = m.gate; a.out_peers = m.out_peers; a.ret_counters = m.ret_counters; a.rows_per_rank = m.rows_per_rank; a.ret_index = m.ret_index; a.gate_base = m.gate_base; a.bump = m.bump; a.wait_limit = m.wait_limit ? m.wait_limit : (1u << 22);
     a.n = m.n; a.k = m.k; a.mode = m.mode; a.inter = m.n / 2u; a.pairs = m.n / 256u; a.out_stride = m.out_stride; a.err = m.err;
     const int sms = st().sm_count ? st().sm_count : 148;
     const CUtensorMap *w = (const CUtensorMap *)tm_w, *q = (const CUtensorMap *)tm_q;

@@ -46,6 +46,7 @@ struct State {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     int gemv_mutant = 0, gemm_mutant = 0;
     uint32_t cta_budget = 0;
+    uint32_t wait_limit = 1u << 22;   // iterations of a bounded cross-GPU wait before it gives up (each iteration sleeps about 100 ns); tests shorten it
     int sealed = 0;
     // grow-only staging buffers for host-staged calls
     void *stage[8] = {nullptr}; size_t stage_bytes[8] = {0};
@@ -109,6 +110,7 @@ struct MmaLaunch {
     uint32_t *err;                     // device word: non-zero = a bounded wait inside the kernel ran out
     // expert parallelism (null / 0 otherwise): wait for `*gate >= header[0]` delivered input rows; mode 1 results go to out_peers[row / rows_per_rank]
     const unsigned long long *gate; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index; const unsigned long long *gate_base; unsigned long long *bump;
+    uint32_t wait_limit;               // iterations of the bounded wait on `gate` (0 = the default)
 };
 bool make_tmap_u8(void *out_map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 uint32_t mma_tile_rows(uint32_t pieces);
@@ -123,6 +125,7 @@ struct FfnLaunch {
     const float *gu_scale, *dn_scale, *x_scale; uint8_t *qa; float *sa; const void *tiles; const uint32_t *header, *ymap; float *out;
     uint32_t hidden, inter, q_rows; uint32_t *sched, *err;   // sched: [0] next down unit, [1 + tile] finished gate|up units; zeroed before the launch
     const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index;   // expert parallelism, as in MmaLaunch
+    uint32_t wait_limit;
 };
 bool ffn_shape_ok(uint32_t hidden, uint32_t inter);
 cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, const void *tm_qa, uint32_t px, uint32_t pa, const FfnLaunch &m, cudaStream_t s, bool pdl);

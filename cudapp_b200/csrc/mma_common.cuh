@@ -42,8 +42,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // bounded wait until a counter that peers advance with system-scope atomics reaches `want`
-__device__ __forceinline__ bool gate_wait(const unsigned long long *gate, unsigned long long want, uint32_t *err, uint32_t code) {
-    for (uint32_t i = 0; i < (1u << 22); i++) {
+__device__ __forceinline__ bool gate_wait(const unsigned long long *gate, unsigned long long want, uint32_t *err, uint32_t code, uint32_t limit = 1u << 22) {
+    for (uint32_t i = 0; i < limit; i++) {
         unsigned long long v;
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(gate) : "memory");
         if (v >= want) { asm volatile("fence.proxy.async;" ::: "memory"); return true; }
@@ -98,6 +98,40 @@ __device__ __forceinline__ float2 dec2(uint32_t v) {
     asm("{ .reg .b16 a; cvt.u16.u32 a, %1; cvt.rn.f16x2.e4m3x2 %0, a; }" : "=r"(h2) : "r"(v));
     asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(f.x), "=f"(f.y) : "r"(h2));
     return f;
+}
+
+__device__ __forceinline__ uint32_t enc4(float a, float b, float c, float d) { return enc2(a, b) | (enc2(c, d) << 16); }
+__device__ __forceinline__ void dec4(uint32_t v, float *o) {
+    const float2 lo = dec2(v & 0xffffu), hi = dec2(v >> 16);
+    o[0] = lo.x; o[1] = lo.y; o[2] = hi.x; o[3] = hi.y;
+}
+// f32 -> bf16 bits, round to nearest even, NaN kept quiet
+__device__ __forceinline__ uint32_t bf16_rne_bits(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
+}
+// THE activation quantiser of this library (src/omega_blackwell_codegen_qg.h:7-19 in the reference), one call per warp and
+// 128-column group, lane = 4 consecutive columns: amax over the group floored at 2^-100, scale = the smallest power of two with
+// amax / scale <= 448, code = e4m3 round-to-nearest-even, saturating. pieces > 1 (this library's exact-activation format): piece
+// p re-encodes the residual the earlier pieces left, scaled by 16^p; every step is exact in f32. Every kernel that produces
+// activation pieces calls this one function, so the stand-alone quantiser, the fused stack step and the expert-parallel stack step
+// cannot drift apart. Returns the scale; codes[p] = this lane's four codes of piece p.
+__device__ __forceinline__ float quant_pieces_warp(const float *v, uint32_t pieces, uint32_t *codes) {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = pq_scale_mma(amax);
+    const float inv = __uint_as_float((254u - (__float_as_uint(s) >> 23)) << 23);   // s is a power of two: exact reciprocal, v * inv == v / s
+    float res[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) res[i] = v[i] * inv;
+    for (uint32_t p = 0; p < pieces; p++) {
+        codes[p] = enc4(res[0], res[1], res[2], res[3]);
+        if (p + 1 == pieces) break;
+        float d[4]; dec4(codes[p], d);
+#pragma unroll
+        for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
+    }
+    return s;
 }
 
 }  // namespace b200

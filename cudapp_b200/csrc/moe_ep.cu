@@ -16,6 +16,7 @@
 // No TMA load reads peer memory anywhere: remote rows are written by plain stores and read locally.
 #include <stdlib.h>
 #include "internal.h"
+#include "mma_common.cuh"
 
 struct OmegaGpuMoeEp {
     uint32_t world, rank, topk, experts, experts_local, hidden, tokens_local_max, cap, region_rows;
@@ -301,7 +302,7 @@ struct OmegaGpuMoeEpStack {
     b200::PlanBatch pg, pl; size_t map_stride, tile_stride;
     uint8_t *comm; size_t comm_bytes, q_par, off_sx, sx_par, off_dn, off_cnt, off_credit;   // peers map this block: pieces x2 | scales x2 | results | counters (x2: by layer parity)
     uint64_t *peer_tab;                  // device [5][world]: pieces, scales, results, counters, buffer credits of every rank
-    float *h; uint32_t *err, *sched; bool one_launch;
+    float *h, *norm_w; uint32_t *err, *sched; bool one_launch;   // norm_w: device [layers][hidden], RMSNorm weight of each layer's input (ones until set)
     void *opened[64]; int n_opened; int connected;
     alignas(128) unsigned char tm_qx[2][128];
     uint32_t launches;
@@ -326,7 +327,8 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         uint32_t parity, uint16_t *__restrict__ h16, uint32_t *err, uint32_t *__restrict__ sched, uint32_t n_sched,
         unsigned long long *bump, const uint32_t *bump_rows,
         uint32_t world, uint32_t rank, const uint64_t *__restrict__ credit_peers, const unsigned long long *credit_local,
-        uint32_t done_parity, uint32_t done_uses_per_step, uint32_t done_uses_before, uint32_t next_uses_per_step, uint32_t next_uses_before) {
+        uint32_t done_parity, uint32_t done_uses_per_step, uint32_t done_uses_before, uint32_t next_uses_per_step, uint32_t next_uses_before,
+        const float *__restrict__ nw, uint32_t wait_limit) {
     __shared__ double red[8];
     __shared__ float s_scale;
     __shared__ uint32_t s_d[32], s_row[32], s_fail;
@@ -353,7 +355,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
             // the counter only grows: this layer's results are complete at (uses so far + 1) x slices per use
             const unsigned long long ret_want = ((unsigned long long)(*step - 1u) * uses_per_step + uses_before + 1ull) * ret_unit;
             bool ok = false;
-            for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+            for (uint32_t i = 0; i < wait_limit && !ok; i++) {
                 unsigned long long v;
                 asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ret_gate) : "memory");
                 ok = v >= ret_want;
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         const unsigned long long want = (unsigned long long)(*step - 1u) * next_uses_per_step + next_uses_before;
         const unsigned long long *c = credit_local + 2u * s_d[tid] + parity;
         bool ok = want == 0ull;
-        for (uint32_t i = 0; i < (1u << 22) && !ok; i++) {
+        for (uint32_t i = 0; i < wait_limit && !ok; i++) {
             unsigned long long v;
             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(c) : "memory");
             ok = v >= want;
@@ -420,34 +422,13 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
         const uint32_t c = kb * 128u + lane * 4u;
         const float4 hv = *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);
-        float v[4] = {hv.x * sc, hv.y * sc, hv.z * sc, hv.w * sc};
+        const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw + c));
+        // the same arithmetic, value for value, as combine_norm_scatter_kernel of the single-GPU stack: xn = bf16(h * s * w), then the shared quantiser
+        float v[4] = {__fmul_rn(__fmul_rn(hv.x, sc), wv.x), __fmul_rn(__fmul_rn(hv.y, sc), wv.y), __fmul_rn(__fmul_rn(hv.z, sc), wv.z), __fmul_rn(__fmul_rn(hv.w, sc), wv.w)};
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const uint32_t b = __float_as_uint(v[i]);
-            const uint32_t r = ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
-            v[i] = __uint_as_float(r << 16);
-        }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        amax = fmaxf(amax, 7.888609052210118e-31f);
-        const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, cc = (M + 0x1fffffu) >> 23;
-        const float qs = __uint_as_float((E + cc - 8u) << 23);
-        float res[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], qs);
+        for (int i = 0; i < 4; i++) v[i] = __uint_as_float(bf16_rne_bits(v[i]) << 16);
         uint32_t codes[4];
-        for (uint32_t p = 0; p < pieces; p++) {
-            uint16_t lo, hi;
-            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(res[1]), "f"(res[0]));
-            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(res[3]), "f"(res[2]));
-            codes[p] = (uint32_t)lo | ((uint32_t)hi << 16);
-            uint32_t l2, h2; float d[4];
-            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.rn.f16x2.e4m3x2 %0, a; cvt.rn.f16x2.e4m3x2 %1, b; }" : "=r"(l2), "=r"(h2) : "r"(codes[p]));
-            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[0]), "=f"(d[1]) : "r"(l2));
-            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[2]), "=f"(d[3]) : "r"(h2));
-#pragma unroll
-            for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
-        }
+        const float qs = quant_pieces_warp(v, pieces, codes);
         for (uint32_t s = 0; s < topk; s++) {
             uint8_t *q = reinterpret_cast<uint8_t *>(q_peers[s_d[s]]) + q_off;
             for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)s_row[s] * hidden + c) = codes[p];
@@ -489,7 +470,7 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
         o_pb[b][0] = take(Ln * E * 4); o_pb[b][1] = take(Ln * E * 4); o_pb[b][2] = take(Ln * S->map_stride * 4); o_pb[b][3] = take(Ln * S->map_stride * 4);
         o_pb[b][4] = take(Ln * S->map_stride * 4); o_pb[b][5] = take(Ln * 32); o_pb[b][6] = take(Ln * S->tile_stride * 16);
     }
-    const size_t o_h = take((size_t)S->tokens_local * H * 4), o_err = take(64), o_sched = take((S->tile_stride + 1) * 4);
+    const size_t o_h = take((size_t)S->tokens_local * H * 4), o_err = take(64), o_sched = take((S->tile_stride + 1) * 4), o_nw = take(Ln * H * 4);
     bool ok = cuda_ok(cudaMalloc(&S->route, off), "cudaMalloc(ep routing)") && cuda_ok(cudaMemset(S->route, 0, off), "memset");
     if (ok) {
         char *f = S->route;
@@ -500,7 +481,8 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
             pb[b]->ymap = (uint32_t *)(f + o_pb[b][3]); pb[b]->pos = (uint32_t *)(f + o_pb[b][4]); pb[b]->header = (uint32_t *)(f + o_pb[b][5]);
             pb[b]->tiles = (uint4 *)(f + o_pb[b][6]); pb[b]->map_stride = S->map_stride; pb[b]->tile_stride = S->tile_stride;
         }
-        S->h = (float *)(f + o_h); S->err = (uint32_t *)(f + o_err); S->sched = (uint32_t *)(f + o_sched);
+        S->h = (float *)(f + o_h); S->err = (uint32_t *)(f + o_err); S->sched = (uint32_t *)(f + o_sched); S->norm_w = (float *)(f + o_nw);
+        { std::vector<float> ones(Ln * H, 1.0f); ok = cuda_ok(cudaMemcpy(S->norm_w, ones.data(), ones.size() * 4, cudaMemcpyHostToDevice), "init norm weights"); }
         S->one_launch = ((v0.x_pieces == 2 && v0.act_pieces == 3) || (v0.x_pieces == 1 && v0.act_pieces == 1) || (v0.x_pieces == 2 && v0.act_pieces == 2)) &&
                         ffn_shape_ok(v0.hidden, v0.inter) && !getenv("B200MOE_TWO_LAUNCH");
         // the block peers write into: activation pieces | their scales | result rows of the local tokens | counters
@@ -562,6 +544,13 @@ int omega_gpu_moe_epstack_connect(OmegaGpuMoeEpStack *S, const uint8_t *handles)
 }
 
 uint32_t omega_gpu_moe_epstack_launches(const OmegaGpuMoeEpStack *S) { return S ? S->launches : 0; }
+int omega_gpu_moe_epstack_set_norm(OmegaGpuMoeEpStack *S, uint32_t layer, const float *norm_w) {
+    if (!S || !norm_w || layer >= S->layers) return OMEGA_GPU_FP8_BAD_ARGS;
+    for (uint32_t i = 0; i < S->hidden; i++) if (!(norm_w[i] == norm_w[i]) || norm_w[i] - norm_w[i] != 0.0f) { set_error("ep stack: norm weight %u of layer %u is not finite", i, layer); return OMEGA_GPU_FP8_BAD_ARGS; }
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    return cuda_ok(cudaMemcpy(S->norm_w + (size_t)layer * S->hidden, norm_w, (size_t)S->hidden * 4, cudaMemcpyHostToDevice), "copy norm weights") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
 uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *S) { return S ? (uint64_t)(uintptr_t)S->h : 0; }
 
 /* one whole step for this rank. logits_all_va: bf16 [layers][tokens][experts] of ALL tokens (gathered by the caller);
@@ -591,7 +580,7 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
     ep_combine_norm_scatter_kernel<<<Tl, 256, 0, s>>>(H, K, S->eps, (const uint16_t *)(uintptr_t)x_va, nullptr, nullptr, S->h, nullptr, 0ull, S->err + 4, 0u, 0u,
                                                       S->ids_g + tok0, S->pg.pos + tok0, S->pg.starts, El, Px, pstride, (size_t)0, (size_t)0, tab, tab + G, tab + 3 * G, 0u, nullptr, S->err,
                                                       S->sched, (uint32_t)S->tile_stride + 1u, nullptr, nullptr,
-                                                      G, S->rank, tab + 4 * G, credit, 0xffffffffu, 0u, 0u, (Ln + 1u) / 2u, 0u); n++;
+                                                      G, S->rank, tab + 4 * G, credit, 0xffffffffu, 0u, 0u, (Ln + 1u) / 2u, 0u, S->norm_w, st().wait_limit); n++;
     for (uint32_t l = 0; l < Ln && ok; l++) {
         LayerView v; layer_view(S->local[l], &v);
         const uint32_t par = l & 1u;
@@ -601,14 +590,14 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
             f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = (const float *)(S->comm + S->off_sx + par * S->sx_par); f.qa = v.qa; f.sa = v.sa;
             f.tiles = S->pl.tiles + (size_t)l * S->tile_stride; f.header = hdr; f.ymap = S->pl.ymap + (size_t)l * S->map_stride; f.out = dn_local;
             f.hidden = H; f.inter = v.inter; f.q_rows = S->row_cap; f.sched = S->sched; f.err = S->err;
-            f.gate = cnt + par; f.gate_base = base + par; f.out_peers = tab + 2 * G; f.ret_counters = tab + 3 * G; f.rows_per_rank = Tl * K; f.ret_index = 2 + par;
+            f.wait_limit = st().wait_limit; f.gate = cnt + par; f.gate_base = base + par; f.out_peers = tab + 2 * G; f.ret_counters = tab + 3 * G; f.rows_per_rank = Tl * K; f.ret_index = 2 + par;
             ok = cuda_ok(launch_ffn(v.tm_gu, S->tm_qx[par], v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, true), "expert ffn launch"); n++;
         } else {
             MmaLaunch g = {};
             g.wscale = v.gu_scale; g.ascale = (const float *)(S->comm + S->off_sx + par * S->sx_par); g.tiles = S->pl.tiles + (size_t)l * S->tile_stride; g.header = hdr;
             g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
             g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = S->err;   // one failure word for the whole step: later kernels see it and do nothing
-            g.gate = cnt + par; g.gate_base = base + par;
+            g.gate = cnt + par; g.gate_base = base + par; g.wait_limit = st().wait_limit;
             ok = cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx[par], Px, g, s, true), "gate|up mma launch"); n++;
             MmaLaunch d = {};
             d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pl.ymap + (size_t)l * S->map_stride; d.out = dn_local; d.q_rows = S->row_cap;
@@ -623,7 +612,8 @@ int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *S, uint64_t logits_all_
                                                                   last ? nullptr : S->pg.starts + (size_t)(l + 1) * E, El, Px, pstride, (par ^ 1u) * S->q_par, (par ^ 1u) * S->sx_par, last ? nullptr : tab, tab + G, tab + 3 * G,
                                                                   par ^ 1u, last ? (uint16_t *)(uintptr_t)out_bf16_va : nullptr, S->err,
                                                                   S->sched, (uint32_t)S->tile_stride + 1u, S->one_launch ? base + par : nullptr, hdr,
-                                                                  G, S->rank, tab + 4 * G, credit, par, (Ln + 1u - par) / 2u, l / 2u, (Ln + par) / 2u, (l + 1u) / 2u);
+                                                                  G, S->rank, tab + 4 * G, credit, par, (Ln + 1u - par) / 2u, l / 2u, (Ln + par) / 2u, (l + 1u) / 2u,
+                                                                  S->norm_w + (size_t)(last ? 0 : l + 1) * H, st().wait_limit);
         n++;
     }
     S->launches = n;
@@ -637,9 +627,32 @@ int omega_gpu_moe_epstack_status(OmegaGpuMoeEpStack *S, void *stream) {
     if (!cuda_ok(cudaMemcpyAsync(&e, S->err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
         !cuda_ok(cudaMemcpyAsync(hdr.data(), S->pl.header, hdr.size() * 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
         !cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "ep stack status")) return OMEGA_GPU_FP8_CHIP_FAIL;
-    if (e) return (int)e;
-    for (size_t l = 0; l < S->layers; l++) { if (hdr[l * 8 + 3]) return 100 + (int)hdr[l * 8 + 3]; if (hdr[l * 8 + 4]) return (int)hdr[l * 8 + 4]; }
+    for (size_t l = 0; l < S->layers && !e; l++) if (hdr[l * 8 + 4]) e = hdr[l * 8 + 4];
+    if (e) {
+        // a bounded wait gave up: the step's outcome is unknown, peers may still be storing into this rank. As the reference does on a
+        // timeout (src/omega_gpu_session.h:27-29), the process latches: every later compute call is refused, nothing is freed.
+        Lock l;
+        set_error("ep stack: a bounded wait inside a kernel ran out (code %u); the process is latched", e);
+        st().latched = true;
+        return (int)e;
+    }
+    for (size_t l = 0; l < S->layers; l++) if (hdr[l * 8 + 3]) return 100 + (int)hdr[l * 8 + 3];
     return 0;
+}
+
+/* TEST ONLY. Shortens (or restores, 0) the iteration limit of the bounded cross-GPU waits of kernels launched from now on. */
+void omega_gpu_moe_test_set_wait_limit(uint32_t iterations) { Lock l; st().wait_limit = iterations ? iterations : (1u << 22); }
+/* TEST ONLY. Makes this rank expect `rows` more delivered input rows than its peers will ever store (layers of even index), so the next
+ * step's first expert kernel waits for a row that never comes: the host-made failure for the timeout test. Synchronous. */
+int omega_gpu_moe_epstack_test_expect_extra(OmegaGpuMoeEpStack *S, uint32_t rows) {
+    if (!S) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    unsigned long long v = 0;
+    unsigned long long *base = (unsigned long long *)(S->err + 8);
+    if (!cuda_ok(cudaMemcpy(&v, base, 8, cudaMemcpyDeviceToHost), "read base")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    v += rows;
+    return cuda_ok(cudaMemcpy(base, &v, 8, cudaMemcpyHostToDevice), "write base") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
 }  // extern "C"

@@ -1,6 +1,7 @@
 // moe_glue.cu: the small operators between the expert GEMMs: SiLU gate, router-weighted combine, and the
 // activation quantiser that feeds the FP8 tensor-core GEMM.
 #include "internal.h"
+#include "mma_common.cuh"
 
 namespace b200 {
 
@@ -53,28 +54,7 @@ cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, con
     return cudaGetLastError();
 }
 
-// Activation quantiser (src/omega_blackwell_codegen_qg.h:7-19): per row and 128-column group, amax floored at
-// 2^-100, scale = the smallest power of two with amax / scale <= 448, code = e4m3 round-to-nearest-even,
-// saturating. pieces > 1 (this library's exact-activation format): piece p re-encodes the residual the earlier
-// pieces left, scaled by 16^p; every step is exact in f32. One warp per (row, group); lane = 4 columns.
-__device__ __forceinline__ float pq_scale_dev(float amax) {
-    amax = fmaxf(amax, 7.888609052210118e-31f /* 2^-100 */);
-    const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, c = (M + 0x1fffffu) >> 23;
-    return __uint_as_float((E + c - 8u) << 23);
-}
-__device__ __forceinline__ uint32_t enc4(float a, float b, float c, float d) {
-    uint16_t lo, hi;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
-    return (uint32_t)lo | ((uint32_t)hi << 16);
-}
-__device__ __forceinline__ void dec4(uint32_t v, float *o) {
-    uint32_t lo, hi;
-    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.rn.f16x2.e4m3x2 %0, a; cvt.rn.f16x2.e4m3x2 %1, b; }" : "=r"(lo) , "=r"(hi) : "r"(v));
-    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(o[0]), "=f"(o[1]) : "r"(lo));
-    asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(o[2]), "=f"(o[3]) : "r"(hi));
-}
-
+// Activation quantiser: quant_pieces_warp (mma_common.cuh) applied to rows of x. One warp per (row, 128-column group); lane = 4 columns.
 __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, size_t piece_stride, const void *__restrict__ x, int x_bf16, size_t x_stride,
                                                         const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
                                                         uint8_t *__restrict__ q, float *__restrict__ sc) {
@@ -103,22 +83,10 @@ __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t 
         for (int u = 0; u < U; u++) {
             if (rr[u] == 0xffffffffu) continue;
             const uint32_t r = rr[u], b = bb[u];
-            float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
-            for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            const float s = pq_scale_dev(amax);
+            uint32_t codes[4];
+            const float s = quant_pieces_warp(v[u], pieces, codes);
             if (lane == 0) sc[(size_t)r * kb + b] = s;
-            const float inv = __uint_as_float((254u - (__float_as_uint(s) >> 23)) << 23);   // s is a power of two: exact reciprocal, v * inv == v / s
-            float res[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) res[i] = v[u][i] * inv;
-            for (uint32_t p = 0; p < pieces; p++) {
-                const uint32_t code = enc4(res[0], res[1], res[2], res[3]);
-                *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)r * k + b * 128u + lane * 4u) = code;
-                if (p + 1 == pieces) break;
-                float d[4]; dec4(code, d);
-#pragma unroll
-                for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
-            }
+            for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)r * k + b * 128u + lane * 4u) = codes[p];
         }
     }
 }

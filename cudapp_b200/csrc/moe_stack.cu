@@ -6,13 +6,14 @@
 #include <stdlib.h>
 #include <vector>
 #include "internal.h"
+#include "mma_common.cuh"
 
 namespace b200 {
 
 // one CTA per token: h (+= m) ; xn = bf16(h * rsqrt(mean(h^2) + eps)). Sum of squares in double, one f32 factor,
 // as the reference host glue does (tests/gpu_decode_graph_test.c:56-60). x16 != nullptr initialises h from bf16.
 __global__ void __launch_bounds__(256) residual_norm_kernel(uint32_t hidden, float eps, const uint16_t *__restrict__ x16, const float *__restrict__ m,
-                                                            float *__restrict__ h, uint16_t *__restrict__ xn, uint16_t *__restrict__ h16) {
+                                                            float *__restrict__ h, uint16_t *__restrict__ xn, uint16_t *__restrict__ h16, const float *__restrict__ nw) {
     __shared__ double red[8];
     __shared__ float s_scale;
     const uint32_t t = blockIdx.x, tid = threadIdx.x;
@@ -34,8 +35,8 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(uint32_t hidden, flo
     const float sc = s_scale;
     for (uint32_t c = tid; c < hidden; c += 256) {
         const size_t i = (size_t)t * hidden + c;
-        const uint32_t b = __float_as_uint(h[i] * sc);
-        xn[i] = (uint16_t)(((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16));
+        const float v = __fmul_rn(h[i], sc);
+        xn[i] = (uint16_t)bf16_rne_bits(nw ? __fmul_rn(v, nw[c]) : v);
     }
 }
 
@@ -49,7 +50,8 @@ __global__ void __launch_bounds__(256) residual_norm_kernel(uint32_t hidden, flo
 __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidden, uint32_t topk, float eps, const uint16_t *__restrict__ x16,
                                                                    const float *__restrict__ w, const float *__restrict__ dn, float *__restrict__ h,
                                                                    const uint32_t *__restrict__ pos, uint32_t pieces, size_t piece_stride, uint8_t *__restrict__ q,
-                                                                   float *__restrict__ sx, uint16_t *__restrict__ h16, uint32_t *__restrict__ sched, uint32_t n_sched) {
+                                                                   float *__restrict__ sx, uint16_t *__restrict__ h16, uint32_t *__restrict__ sched, uint32_t n_sched,
+                                                                   const float *__restrict__ nw) {
     __shared__ double red[8];
     __shared__ float s_scale;
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
@@ -93,34 +95,14 @@ __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidd
     for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
         const uint32_t c = kb * 128u + lane * 4u;
         const float4 hv = *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);   // written by this CTA above
-        float v[4] = {hv.x * sc, hv.y * sc, hv.z * sc, hv.w * sc};
+        const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw + c));
+        // xn = h * s * w (the reference's RMSNorm, src/omega_blackwell_codegen_dec.c:261-286; host form tests/gpu_decode_graph_test.c:56-60);
+        // xn is a bf16 tensor: round first, then quantise the rounded value
+        float v[4] = {__fmul_rn(__fmul_rn(hv.x, sc), wv.x), __fmul_rn(__fmul_rn(hv.y, sc), wv.y), __fmul_rn(__fmul_rn(hv.z, sc), wv.z), __fmul_rn(__fmul_rn(hv.w, sc), wv.w)};
 #pragma unroll
-        for (int i = 0; i < 4; i++) {   // xn is a bf16 tensor: round first, then quantise the rounded value
-            const uint32_t b = __float_as_uint(v[i]);
-            const uint32_t r = ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
-            v[i] = __uint_as_float(r << 16);
-        }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        amax = fmaxf(amax, 7.888609052210118e-31f);
-        const uint32_t mb = __float_as_uint(amax), E = mb >> 23, M = mb & 0x7fffffu, cc = (M + 0x1fffffu) >> 23;
-        const float qs = __uint_as_float((E + cc - 8u) << 23);
-        float res[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) res[i] = __fdiv_rn(v[i], qs);
+        for (int i = 0; i < 4; i++) v[i] = __uint_as_float(bf16_rne_bits(v[i]) << 16);
         uint32_t codes[4];
-        for (uint32_t p = 0; p < pieces; p++) {
-            uint16_t lo, hi;
-            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(res[1]), "f"(res[0]));
-            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(res[3]), "f"(res[2]));
-            codes[p] = (uint32_t)lo | ((uint32_t)hi << 16);
-            uint32_t l2, h2; float d[4];
-            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.rn.f16x2.e4m3x2 %0, a; cvt.rn.f16x2.e4m3x2 %1, b; }" : "=r"(l2), "=r"(h2) : "r"(codes[p]));
-            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[0]), "=f"(d[1]) : "r"(l2));
-            asm("{ .reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b; }" : "=f"(d[2]), "=f"(d[3]) : "r"(h2));
-#pragma unroll
-            for (int i = 0; i < 4; i++) res[i] = (res[i] - d[i]) * 16.0f;
-        }
+        const float qs = quant_pieces_warp(v, pieces, codes);
         for (uint32_t s = 0; s < topk; s++) {
             const uint32_t row = pos[(size_t)t * topk + s];
             for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)row * hidden + c) = codes[p];
@@ -137,6 +119,7 @@ struct OmegaGpuMoeStack {
     float eps;
     uint32_t experts, hidden, max_tokens;
     float *h; uint16_t *xn, *logits, *x, *out16;      // device
+    float *norm_w;                                    // device [layers][hidden]: RMSNorm weight of each layer's input (ones until set)
     cudaGraphExec_t graph; uint32_t graph_tokens; cudaStream_t graph_stream;
     uint64_t g_logits, g_x, g_out32, g_out16;         // addresses the captured graph was built for
     uint32_t launches;
@@ -159,14 +142,14 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
         if (!cuda_ok(launch_topk(Ln * tokens, E, K, (int)v0.norm_topk, logits, S->ids_all, S->wts_all, s), "topk launch")) return false; n++;
         if (!cuda_ok(launch_plan_batch(Ln, tokens, K, E, K, S->tile_rows, S->ids_all, S->pb, s), "plan launch")) return false; n++;
         const size_t pstride = (size_t)S->row_cap * H;
-        auto launch_cns = [&](const uint16_t *x16, const float *w, const float *dn, const uint32_t *pos, uint8_t *q, uint16_t *h16) {
+        auto launch_cns = [&](const uint16_t *x16, const float *w, const float *dn, const uint32_t *pos, uint8_t *q, uint16_t *h16, const float *nw) {
             cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];
             cfg.gridDim = dim3(tokens); cfg.blockDim = dim3(256); cfg.stream = s;
             at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = at; cfg.numAttrs = 0;   // measured: launching this kernel (or the down GEMM) as a programmatic dependent is slower
-            return cudaLaunchKernelEx(&cfg, combine_norm_scatter_kernel, H, K, S->eps, x16, w, dn, S->h, pos, Px, pstride, q, S->sx, h16, S->sched, (uint32_t)S->tile_stride + 1u);
+            return cudaLaunchKernelEx(&cfg, combine_norm_scatter_kernel, H, K, S->eps, x16, w, dn, S->h, pos, Px, pstride, q, S->sx, h16, S->sched, (uint32_t)S->tile_stride + 1u, nw);
         };
-        if (!cuda_ok(launch_cns(x, nullptr, nullptr, S->pb.pos, S->qx, nullptr), "norm launch")) return false; n++;
+        if (!cuda_ok(launch_cns(x, nullptr, nullptr, S->pb.pos, S->qx, nullptr, S->norm_w), "norm launch")) return false; n++;
         for (uint32_t l = 0; l < Ln; l++) {
             LayerView v; layer_view(S->layers[l], &v);
             const uint32_t *hdr = S->pb.header + (size_t)l * 8;
@@ -191,20 +174,20 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
             if (S->prof) cudaEventRecord(S->prof[2 * l + 1], s);
             const bool last = l + 1 == Ln;
             if (!cuda_ok(launch_cns(nullptr, S->wts_all + (size_t)l * tokens * K, v.dn, last ? nullptr : S->pb.pos + (size_t)(l + 1) * S->map_stride,
-                                    last ? nullptr : S->qx, last ? out16 : nullptr), "combine launch")) return false; n++;
+                                    last ? nullptr : S->qx, last ? out16 : nullptr, S->norm_w + (size_t)(last ? 0 : l + 1) * H), "combine launch")) return false; n++;
         }
         if (out32 && !cuda_ok(cudaMemcpyAsync(out32, S->h, (size_t)tokens * H * 4, cudaMemcpyDeviceToDevice, s), "copy h")) return false;
         S->launches = n;
         return cuda_ok(cudaGetLastError(), "stack launch");
     }
-    residual_norm_kernel<<<tokens, 256, 0, s>>>(H, S->eps, x, nullptr, S->h, S->xn, nullptr); n++;
+    residual_norm_kernel<<<tokens, 256, 0, s>>>(H, S->eps, x, nullptr, S->h, S->xn, nullptr, S->norm_w); n++;
     for (uint32_t l = 0; l < Ln; l++) {
         OmegaGpuMoeLayer *L = S->layers[l];
         float *m = layer_out32(L);
         if (!layer_forward(L, tokens, logits + (size_t)l * tokens * E, S->xn, m, nullptr, s)) return false;
         n += omega_gpu_moe_layer_launches(L);
         const bool last = l + 1 == Ln;
-        residual_norm_kernel<<<tokens, 256, 0, s>>>(H, S->eps, nullptr, m, S->h, last ? nullptr : S->xn, last ? out16 : nullptr); n++;
+        residual_norm_kernel<<<tokens, 256, 0, s>>>(H, S->eps, nullptr, m, S->h, last ? nullptr : S->xn, last ? out16 : nullptr, S->norm_w + (size_t)(last ? 0 : l + 1) * H); n++;
     }
     if (out32 && !cuda_ok(cudaMemcpyAsync(out32, S->h, (size_t)tokens * H * 4, cudaMemcpyDeviceToDevice, s), "copy h")) return false;
     S->launches = n;
@@ -232,12 +215,25 @@ static bool stack_run(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *logi
 
 extern "C" {
 
-int omega_gpu_residual_norm_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va, uint64_t xn_va, uint64_t h16_va, void *stream) {
+int omega_gpu_residual_norm_w_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va, uint64_t xn_va, uint64_t h16_va,
+                                    uint64_t norm_w_va, void *stream) {
     if (!tokens || !hidden || !h_va) return OMEGA_GPU_FP8_BAD_ARGS;
     if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
     residual_norm_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>(hidden, eps, (const uint16_t *)(uintptr_t)x16_va, (const float *)(uintptr_t)m_va, (float *)(uintptr_t)h_va,
-                                                                    (uint16_t *)(uintptr_t)xn_va, (uint16_t *)(uintptr_t)h16_va);
+                                                                    (uint16_t *)(uintptr_t)xn_va, (uint16_t *)(uintptr_t)h16_va, (const float *)(uintptr_t)norm_w_va);
     return cuda_ok(cudaGetLastError(), "residual norm launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
+int omega_gpu_residual_norm_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va, uint64_t xn_va, uint64_t h16_va, void *stream) {
+    return omega_gpu_residual_norm_w_async(tokens, hidden, eps, x16_va, m_va, h_va, xn_va, h16_va, 0, stream);
+}
+
+int omega_gpu_moe_stack_set_norm(OmegaGpuMoeStack *S, uint32_t layer, const float *norm_w) {
+    if (!S || !norm_w || layer >= S->layers.size()) return OMEGA_GPU_FP8_BAD_ARGS;
+    for (uint32_t i = 0; i < S->hidden; i++) if (!(norm_w[i] == norm_w[i]) || norm_w[i] - norm_w[i] != 0.0f) { set_error("moe stack: norm weight %u of layer %u is not finite", i, layer); return OMEGA_GPU_FP8_BAD_ARGS; }
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    // the captured step reads this buffer, so new weights take effect at the next step without a new capture
+    return cuda_ok(cudaMemcpy(S->norm_w + (size_t)layer * S->hidden, norm_w, (size_t)S->hidden * 4, cudaMemcpyHostToDevice), "copy norm weights") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
 int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, float eps, OmegaGpuMoeStack **out) {
@@ -257,10 +253,15 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
         S->layers.push_back(layer[i]);
     }
     const size_t T = S->max_tokens, H = S->hidden;
-    const size_t bytes = T * H * 4 + T * H * 2 * 3 + (size_t)layers * T * S->experts * 2;
+    const size_t nw_off = (T * H * 4 + T * H * 2 * 3 + (size_t)layers * T * S->experts * 2 + 255) & ~(size_t)255, bytes = nw_off + (size_t)layers * H * 4;
     char *b = nullptr;
     if (!cuda_ok(cudaMalloc(&b, bytes), "cudaMalloc(stack)")) { delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
     S->h = (float *)b; S->xn = (uint16_t *)(b + T * H * 4); S->x = S->xn + T * H; S->out16 = S->x + T * H; S->logits = S->out16 + T * H;
+    S->norm_w = (float *)(b + nw_off);
+    {
+        std::vector<float> ones((size_t)layers * H, 1.0f);
+        if (!cuda_ok(cudaMemcpy(S->norm_w, ones.data(), ones.size() * 4, cudaMemcpyHostToDevice), "init norm weights")) { cudaFree(b); delete S; return OMEGA_GPU_FP8_CHIP_FAIL; }
+    }
     // fused path when every layer runs the tensor-core engine with the same piece counts
     LayerView v0; layer_view(layer[0], &v0);
     S->fused = v0.engine == OMEGA_GPU_MOE_ENGINE_MMA && H % 128 == 0;

@@ -231,6 +231,13 @@ class FusedEpStack(EpStack):
     def status(self):
         return int(self.api.lib.omega_gpu_moe_epstack_status(self.eps, C.c_void_p(self.torch.cuda.current_stream().cuda_stream)))
 
+    def step_checked(self, step_index, timeout_s=5.0):
+        """step() behind the host-side hand-shake: raises before anything is launched when a peer left, is silent or disagrees"""
+        why = agree(default_store(self.dist), self.rank, self.world, step_index, {"tokens": self.T, "layers": self.Ln, "world": self.world}, timeout_s)
+        if why is not None:
+            raise RuntimeError("expert-parallel step %d not launched: %s" % (step_index, why))
+        self.step()
+
     def close(self):
         """free this rank's exchange object, layers and tensors (every rank must have finished its steps: peers map this memory)"""
         self.torch.cuda.synchronize(); self.dist.barrier()
@@ -242,6 +249,43 @@ class FusedEpStack(EpStack):
             self.api.fp8_tensor_free(t)
         self.layers, self.tensors = [], []
         self.torch.cuda.empty_cache(); self.dist.barrier()
+
+
+def default_store(dist):
+    """the rendezvous key-value store of the default process group (host side, independent of the GPU collectives)"""
+    return dist.distributed_c10d._get_default_store()
+
+
+def leave(store, rank):
+    """A rank that stops between two steps (none of its kernels in flight) says so on the host; its peers see it in their next agree()."""
+    store.set("b200moe/left/%d" % rank, "1")
+
+
+def agree(store, rank, world, step, payload, timeout_s=5.0):
+    """Host-side hand-shake before step `step` is enqueued. Every rank posts `payload` (what it is about to launch: token count, layer
+    count, ...) and reads its peers'. Returns None when every rank answered with the same payload; otherwise a sentence saying which rank
+    left, did not answer in time, or posted something else. Nothing is launched on a disagreement: the kernels of a step wait for rows
+    from every rank, so a step with a missing or mismatched peer could only end in their bounded waits running out."""
+    import datetime
+    import json
+    key = lambda r: "b200moe/agree/%d/%d" % (step, r)
+    gone = lambda: [r for r in range(world) if store.check(["b200moe/left/%d" % r])]
+    if gone():
+        return "rank(s) %s left before step %d" % (gone(), step)
+    store.set(key(rank), json.dumps(payload, sort_keys=True))
+    try:
+        store.wait([key(r) for r in range(world)], datetime.timedelta(seconds=timeout_s))
+    except Exception:
+        if gone():
+            return "rank(s) %s left before step %d" % (gone(), step)
+        missing = [r for r in range(world) if not store.check([key(r)])]
+        return "rank(s) %s did not answer for step %d within %.1f s" % (missing, step, timeout_s)
+    mine = json.dumps(payload, sort_keys=True)
+    for r in range(world):
+        other = store.get(key(r)).decode()
+        if other != mine:
+            return "rank %d posted %s for step %d, this rank %s" % (r, other, step, mine)
+    return None
 
 
 def parity_check(api, torch, dist, rank, world, tokens, engine, layers=2, seed_base=0):

@@ -105,7 +105,7 @@ int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t l
 uint32_t omega_gpu_moe_layer_launches(const OmegaGpuMoeLayer *l);
 
 /* ---- a stack of MoE layers, the MoE part of the reference's whole-token decode graph (src/omega_gpu_decode_graph.c:321-351):
- * h = x; per layer: xn = bf16(RMSNorm(h)) (unit norm weights; sum of squares in double as the reference host glue,
+ * h = x; per layer: xn = bf16(RMSNorm(h) * norm weight of the layer) (sum of squares in double as the reference host glue,
  * tests/gpu_decode_graph_test.c:56-60), h = h + MoE_l(xn, logits_l). Router logits are inputs (one [tokens][E] block per
  * layer). Layers of one stack share one scratch workspace and run as one CUDA graph per token count. */
 typedef struct OmegaGpuMoeStack OmegaGpuMoeStack;
@@ -118,6 +118,10 @@ int omega_gpu_moe_stack_bf16(OmegaGpuMoeStack *s, uint32_t tokens, const uint16_
 int omega_gpu_moe_stack_async(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,
                               uint64_t out_bf16_va, void *stream);
 uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *s);
+/* RMSNorm weight of layer `layer`'s input, f32 [hidden] on the host (copied): xn = bf16(h * rsqrt(mean(h^2) + eps) * norm_w), the
+ * reference's RES COMBINE|NORM with the layer's norm weight (src/omega_blackwell_codegen_dec.c:261-286; host form
+ * tests/gpu_decode_graph_test.c:56-60). Every layer starts with unit weights. Takes effect at the next step. */
+int omega_gpu_moe_stack_set_norm(OmegaGpuMoeStack *s, uint32_t layer, const float *norm_w);
 /* One step launched without the graph, a CUDA event before and after each layer's expert kernel(s): expert_ms[l] = device
  * time of layer l's gate|up + down work (one launch when *launches_per_layer is 1). Tensor-core path only. For measurement. */
 int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint32_t cap, float *expert_ms,
@@ -127,6 +131,9 @@ int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t l
  * h = (x16 ? bf16->f32(x16) : h) + (m ? m : 0); xn = bf16(RMSNorm(h)) when xn_va != 0; h16 = bf16(h) when h16_va != 0 */
 int omega_gpu_residual_norm_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va,
                                   uint64_t xn_va, uint64_t h16_va, void *stream);
+/* the same with the norm weight vector: norm_w_va f32 [hidden] on the device (0 = unit weights); xn = bf16(h * s * w) */
+int omega_gpu_residual_norm_w_async(uint32_t tokens, uint32_t hidden, float eps, uint64_t x16_va, uint64_t m_va, uint64_t h_va,
+                                    uint64_t xn_va, uint64_t h16_va, uint64_t norm_w_va, void *stream);
 
 /* ---- expert parallelism over the GPUs of one node (no counterpart in the reference, which runs one device).
  * Rank r of `world` holds experts [r*E/world, (r+1)*E/world) as an ordinary OmegaGpuMoeLayer over its local tensors
@@ -164,6 +171,15 @@ int omega_gpu_moe_epstack_connect(OmegaGpuMoeEpStack *s, const uint8_t *handles)
 int omega_gpu_moe_epstack_step_async(OmegaGpuMoeEpStack *s, uint64_t logits_all_va, uint64_t x_va, uint64_t out_bf16_va, void *stream);
 int omega_gpu_moe_epstack_status(OmegaGpuMoeEpStack *s, void *stream);
 uint32_t omega_gpu_moe_epstack_launches(const OmegaGpuMoeEpStack *s);
+/* synchronises `stream`; 0, 100 + a routing-plan status, or the code of a bounded wait that ran out inside a kernel (13 / 14 input rows of a
+ * layer, 16 result rows, 17 buffer credit, 1-10, 20-22 the kernel's own pipeline). On such a code the kernels of the step have returned by
+ * themselves, the later ones did nothing, and the process LATCHES: every later compute call returns CHIP_FAIL and nothing is freed,
+ * the reference's contract for a completion of unknown outcome (src/omega_gpu_session.h:27-29, src/omega_gpu_wait.h:20-24). */
+/* TEST ONLY: the iteration limit of those waits (0 = default, about a second), and a host-made failure: expect `rows` input rows more
+ * than any peer will deliver. */
+void omega_gpu_moe_test_set_wait_limit(uint32_t iterations);
+int omega_gpu_moe_epstack_test_expect_extra(OmegaGpuMoeEpStack *s, uint32_t rows);
+int omega_gpu_moe_epstack_set_norm(OmegaGpuMoeEpStack *s, uint32_t layer, const float *norm_w);   /* as omega_gpu_moe_stack_set_norm; every rank sets the same weights */
 uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *s);   /* device address of the f32 residual stream [tokens_local][hidden] */
 /* ---- router front half: RMSNorm of a residual row with the layer's norm weight, router logits against the bf16 gate matrix,
  * softmax top-k (lowest index on ties, ids in descending-logit order), weights renormalised over the selected when norm_topk.

@@ -190,12 +190,14 @@ def combine(w, d):
     return out
 
 
-def rmsnorm(x, eps=1e-6):
+def rmsnorm(x, eps=1e-6, w=None):
+    """x f32 [T][H] -> x * rsqrt(mean(x^2) + eps) * w (w f32 [H], None = ones)"""
     x = np.ascontiguousarray(x, dtype=np.float32)
+    w = None if w is None else np.ascontiguousarray(w, dtype=np.float32)
     out = np.empty_like(x)
     L = lib()
     for t in range(x.shape[0]):
-        L.orc_rmsnorm(_ptr(x[t], F32P), None, C.c_uint32(x.shape[1]), C.c_float(eps), _ptr(out[t], F32P))
+        L.orc_rmsnorm(_ptr(x[t], F32P), _ptr(w, F32P), C.c_uint32(x.shape[1]), C.c_float(eps), _ptr(out[t], F32P))
     return out
 
 

@@ -147,3 +147,39 @@ def test_no_device_fails_loudly():
     work, seg, maps, meta = orc.plan_buffers()
     st, _ = api.omega_moe_plan(cfg, np.zeros(1024, np.uint64), work, seg, maps, meta)
     assert st == 14 and work[0] == np.uint64(0x5A5A5A5A5A5A5A5A)
+
+
+def test_expert_parallel_create_refusals_before_device():
+    """shapes that cannot be sharded are refused on the host before any device work: tokens or experts not divisible by the rank count, a rank
+    outside the world, no layers"""
+    dummy = (C.c_void_p * 2)(C.c_void_p(1), C.c_void_p(1))      # never dereferenced: the refusals come first
+    out = C.c_void_p(123)
+    cr = api.lib.omega_gpu_moe_epstack_create
+    for world, rank, layers, experts, tokens in ((4, 0, 2, 128, 254), (3, 0, 2, 128, 255), (4, 4, 2, 128, 256), (4, 0, 0, 128, 256), (0, 0, 2, 128, 256), (65, 0, 2, 130, 260)):
+        out.value = 123
+        assert cr(C.c_uint32(world), C.c_uint32(rank), C.c_uint32(layers), dummy, C.c_uint32(experts), C.c_uint32(tokens), C.c_float(1e-6), C.byref(out)) == api.BAD_ARGS
+        assert not out.value
+    assert cr(C.c_uint32(2), C.c_uint32(0), C.c_uint32(2), None, C.c_uint32(128), C.c_uint32(256), C.c_float(1e-6), C.byref(out)) == api.BAD_ARGS
+    ep = C.c_void_p(123)
+    ce = api.lib.omega_gpu_moe_ep_create
+    for world, rank, experts, topk, hidden, tl in ((4, 0, 130, 8, 2048, 64), (4, 5, 128, 8, 2048, 64), (4, 0, 128, 0, 2048, 64), (4, 0, 128, 8, 2052, 64), (4, 0, 128, 8, 2048, 0)):
+        ep.value = 123
+        assert ce(C.c_uint32(world), C.c_uint32(rank), C.c_uint32(experts), C.c_uint32(topk), C.c_uint32(hidden), C.c_uint32(tl), C.byref(ep)) == api.BAD_ARGS
+        assert not ep.value
+
+
+REFERENCE = os.environ.get("B200MOE_REFERENCE", os.path.normpath(os.path.join(ROOT, "..", "reference")))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "src")), reason="the reference tree (for its headers) is not on this machine")
+def test_c_caller_compiled_against_the_reference_headers(tmp_path):
+    """tests/abi_against_reference_headers.c includes the reference's own omega_gpu_fp8_api.h / omega_gpu_fp8gemm_api.h / cudapp_native.h and is
+    linked with libb200moe.so: the boundary as a C caller of the reference sees it"""
+    import subprocess
+    exe = str(tmp_path / "abi_ref")
+    libdir = os.path.join(ROOT, "cudapp_b200", "lib")
+    cc = subprocess.run(["gcc", "-std=gnu11", "-Wall", "-Werror", "-I", os.path.join(REFERENCE, "src"), os.path.join(ROOT, "tests", "abi_against_reference_headers.c"),
+                         "-L", libdir, "-lb200moe", "-Wl,-rpath," + libdir, "-o", exe], capture_output=True, text=True)
+    assert cc.returncode == 0, cc.stderr
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0 and "PASS" in run.stdout, run.stdout + run.stderr

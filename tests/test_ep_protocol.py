@@ -183,3 +183,55 @@ def test_fused_transport_buffer_credits():
         order = [first] + [r for r in range(world) if r != first]
         done, bad = _simulate_fused(routes, world, layers, credits=True, order=order)
         assert done and not bad, (order, bad)
+
+
+# ---------------------------------------------------------------- failures made on the host: a peer that disagrees, a peer that left
+def _agree_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    import datetime
+    import torch.distributed as dist
+    from cudapp_b200 import ep
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    store = ep.default_store(dist)
+    out = {}
+    launched = []                                             # stands for "kernels were enqueued"
+    def step(i, payload, timeout=3.0):
+        why = ep.agree(store, rank, world, i, payload, timeout)
+        if why is None:
+            launched.append(i)
+        return why
+    out["ok"] = step(0, {"tokens": 256, "layers": 48})                                       # everybody agrees
+    out["mismatch"] = step(1, {"tokens": 256 if rank == 0 else 128, "layers": 48})           # rank 1 is about to launch another shape
+    out["silent"] = ep.agree(store, rank, 3, 2, {"tokens": 256}, 1.0)                        # a third rank that never joined: it does not answer
+    if rank == 1:
+        ep.leave(store, rank)                                                                # rank 1 stops between steps ...
+        out["left"] = "n/a"
+    else:
+        out["left"] = step(3, {"tokens": 256, "layers": 48})                                 # ... rank 0 learns of it before its next launch
+    out["launched"] = launched
+    ret.put((rank, out))
+    if rank == 0:
+        import time
+        time.sleep(0.5)
+    dist.destroy_process_group()
+
+
+def test_host_side_failures_stop_a_step_before_launch():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_agree_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for r in (0, 1):
+        assert got[r]["ok"] is None and got[r]["launched"] == [0]                            # only the agreed step was launched, on both ranks
+        assert "posted" in got[r]["mismatch"]
+    assert "left" in got[0]["left"] and "[1]" in got[0]["left"]
+    for r in (0, 1):
+        assert "did not answer" in got[r]["silent"] and "[2]" in got[r]["silent"]

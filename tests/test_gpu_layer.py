@@ -4,6 +4,8 @@ The checker strings the reference's operators together exactly as its host glue 
 (tests/gpu_decode_graph_test.c:129-147): top-k, per pick gate|up GEMV -> SiLU gate -> down GEMV, slot-order weighted
 sum. Bars (the benchmark's): routing ids bit-exact, outputs max-abs <= 1e-2 and rel-L2 <= 1e-3 on the f32 result.
 """
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -81,6 +83,22 @@ def test_stack_small(engine):
         h = h + mo
     assert np.max(np.abs(o32 - h)) <= 1e-2 and rel_l2(o32, h) <= 1e-3
     assert np.array_equal(o16, orc.bf16_bits(o32))
+    # each layer's own RMSNorm weight (the reference's RES COMBINE|NORM, src/omega_blackwell_codegen_dec.c:261-286): new weights
+    # take effect at the next step of the same captured graph
+    nws = [rng.uniform(0.5, 1.5, H).astype(np.float32) for _ in range(Ln)]
+    for l in range(Ln):
+        assert api.lib.omega_gpu_moe_stack_set_norm(stack, C.c_uint32(l), nws[l].ctypes.data_as(C.c_void_p)) == 0, api.last_error()
+    assert api.lib.omega_gpu_moe_stack_set_norm(stack, C.c_uint32(Ln), nws[0].ctypes.data_as(C.c_void_p)) == api.BAD_ARGS
+    rc, w16, w32 = api.moe_stack_bf16(stack, logits, xb); assert rc == 0, api.last_error()
+    h = orc.bf16_to_f32(xb)
+    for l in range(Ln):
+        xn = orc.bf16_bits(orc.rmsnorm(h, 1e-6, nws[l]))
+        mo, _, _ = orc.moe_layer(logits[l], xn, ms[l]["wgu"], ms[l]["sgu"], ms[l]["wdn"], ms[l]["sdn"], topk)
+        h = h + mo
+    assert np.max(np.abs(w32 - h)) <= 1e-2 and rel_l2(w32, h) <= 1e-3 and not np.array_equal(w32, o32)
+    ones = np.ones(H, np.float32)
+    for l in range(Ln):
+        assert api.lib.omega_gpu_moe_stack_set_norm(stack, C.c_uint32(l), ones.ctypes.data_as(C.c_void_p)) == 0
     rc, o16b, o32b = api.moe_stack_bf16(stack, logits, xb)          # graph replay: identical bits
     assert rc == 0 and np.array_equal(o32, o32b)
     assert api.lib.omega_gpu_moe_stack_launches(stack) >= Ln * 3
@@ -102,8 +120,13 @@ def test_epstack_world1_equals_stack():
     # the layers' workspace holds 32 tokens; the expert-parallel stack is created for those 32 and run with all of them
     T2 = 32
     logits2 = orc.bf16_bits(rng.normal(0, 1, (Ln, T2, E)).astype(np.float32)); x2 = orc.bf16_bits(rng.normal(0, 1, (T2, H)).astype(np.float32))
+    nws = [rng.uniform(0.5, 1.5, H).astype(np.float32) for _ in range(Ln)]       # each layer's own RMSNorm weight, the same on both stacks
+    for l in range(Ln):
+        assert api.lib.omega_gpu_moe_stack_set_norm(stack, C.c_uint32(l), nws[l].ctypes.data_as(C.c_void_p)) == 0, api.last_error()
     rc, want16, want32 = api.moe_stack_bf16(stack, logits2, x2); assert rc == 0, api.last_error()
     assert api.lib.omega_gpu_moe_epstack_create(C.c_uint32(1), C.c_uint32(0), C.c_uint32(Ln), arr, C.c_uint32(E), C.c_uint32(T2), C.c_float(1e-6), C.byref(eps)) == 0, api.last_error()
+    for l in range(Ln):
+        assert api.lib.omega_gpu_moe_epstack_set_norm(eps, C.c_uint32(l), nws[l].ctypes.data_as(C.c_void_p)) == 0, api.last_error()
     dev = torch.device("cuda", 0)
     d_lg = torch.from_numpy(logits2.view(np.int16)).to(dev); d_x = torch.from_numpy(x2.view(np.int16)).to(dev); d_o = torch.empty((T2, H), dtype=torch.int16, device=dev)
     s = torch.cuda.Stream()
