@@ -42,18 +42,20 @@ def parse():
     ap.add_argument("--engine", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8)
     ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline and the prefill-layer measurement out (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: the 48-layer stack the metric is quoted on (default); prefill: one layer, 4096 tokens, skewed routing, plain FP8 activations")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "w4", "decode_layer"],
+                    help="decode: the 48-layer stack the metric is quoted on (default); prefill: one layer, 4096 tokens, skewed routing, plain FP8 activations; "
+                         "gemv: the single FP8 projection [768, 2048] on cold weights; w4: the W4 GEMM 16 x 4096 x 4096 on cold weights; decode_layer: one layer, 64 tokens")
     ap.add_argument("--tile-rows", type=int, default=0, help="prefill: 0 = library's choice, 32 or 128 = force the row-tile size")
-    ap.add_argument("--skip-prefill", action="store_true", help="decode workload: leave the prefill-layer measurement out of the line")
+    ap.add_argument("--skip-prefill", action="store_true", help="decode workload: leave the side measurements (prefill layer, single projection, W4 GEMM, 64-token layer) out of the line")
     return ap.parse_args()
 
 
 # ---------------------------------------------------------------------------------------------- CPU arm
-def cpu_layer_sample(tokens, steps, warmup, seed=0):
+def cpu_layer_sample(tokens, steps, warmup, seed=0, f32=False):
     """Times the reference's own host GEMV oracle (oracle/_ref, built from the reference sources) or, where that
     build is absent, the checker's restatement of it, on `tokens` tokens through ONE layer with every host thread.
-    Returns (seconds per step, kind, cores)."""
+    f32=True times the checker's f32 restatement of the kernels' own summation order instead (a faster, all-core CPU form
+    of the same math). Returns (seconds per step, kind, cores)."""
     from concurrent.futures import ThreadPoolExecutor
     from oracle import oracle as orc
     cores = len(os.sched_getaffinity(0))
@@ -71,12 +73,16 @@ def cpu_layer_sample(tokens, steps, warmup, seed=0):
     with ThreadPoolExecutor(cores) as ex:
         list(ex.map(make, used))
     R = orc.ref_lib()
-    kind = "reference" if R is not None else "port"
+    kind = "port" if f32 or R is None else "reference"
     L = orc.lib()
     p = lambda a, t: a.ctypes.data_as(t)
 
     def gemv(w8, sc, n, k, xv, y):
-        if R is not None:
+        if f32:
+            y32 = np.empty(n, np.float32)
+            L.orc_gemv_emu(p(w8, orc.U8P), p(sc, orc.U16P), C.c_uint32(n), C.c_uint32(k), p(xv, orc.F32P), p(y32, orc.F32P))
+            y[:] = y32
+        elif R is not None:
             R.omega_fp8_gemv_oracle(p(w8, orc.U8P), p(sc, orc.U16P), C.c_uint32(n), C.c_uint32(k), p(xv, orc.F32P), p(y, orc.F64P), None)
         else:
             L.orc_gemv(p(w8, orc.U8P), p(sc, orc.U16P), C.c_uint32(n), C.c_uint32(k), p(xv, orc.F32P), p(y, orc.F64P), None)
@@ -120,24 +126,62 @@ def run_reference(args, rank):
 
 # ---------------------------------------------------------------------------------------------- GPU arm
 class ClockSampler:
+    """SM clock and throttle reasons DURING a timed region, read-only: NVML queries every 10 ms from a thread (an nvidia-smi process per
+    sample costs about 100 ms, too coarse for a region of a fraction of a second); nvidia-smi is the fallback when NVML cannot be loaded."""
     QUERY = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, index):
-        self.rows = []
+    def __init__(self, index, period_s=0.01):
+        self.sm, self.reason_bits, self.power = [], 0, []
+        self.max_mhz = None
         self.stop = threading.Event()
-        self.index = index
+        self.index, self.period = index, period_s
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = None
+            try:   # the CUDA device index is not the NVML index when only some GPUs of the machine are visible: go by UUID
+                import torch
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(torch.cuda.get_device_properties(index).uuid)).encode())
+            except Exception:
+                self.handle = None
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nvml = None
         self.th = threading.Thread(target=self.run, daemon=True)
+
+    def sample_nvml(self):
+        n = self.nvml
+        self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+        try:
+            self.power.append(n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+        except Exception:
+            pass
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        self.reason_bits |= int(get(self.handle))
+
+    def sample_smi(self):
+        out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        r = [c.strip() for c in out.split(",")]
+        if len(r) >= 7 and r[0].replace(".", "").isdigit():
+            self.sm.append(float(r[0])); self.max_mhz = float(r[1]) if r[1].replace(".", "").isdigit() else self.max_mhz
+            for bit, name in self.REASONS.items():
+                j = 3 + ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"].index(name)
+                if r[j].lower().startswith("active"):
+                    self.reason_bits |= bit
 
     def run(self):
         while not self.stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
+                self.sample_nvml() if self.nvml else self.sample_smi()
             except Exception:
                 pass
-            self.stop.wait(0.1)
+            self.stop.wait(self.period if self.nvml else 0.1)
 
     def __enter__(self):
         self.th.start(); return self
@@ -146,13 +190,9 @@ class ClockSampler:
         self.stop.set(); self.th.join(timeout=6)
 
     def summary(self):
-        if not self.rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for j, n in enumerate(names) if any(r[3 + j].lower().startswith("active") for r in self.rows if len(r) > 3 + j)]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(self.rows[0][1]) if self.rows[0][1].replace(".", "").isdigit() else None,
-                "reasons": reasons, "samples": len(self.rows)}
+        reasons = [name for bit, name in self.REASONS.items() if self.reason_bits & bit]
+        return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_min_mhz": float(np.min(self.sm)) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "power_w_max": float(np.max(self.power)) if self.power else None, "reasons": reasons, "samples": len(self.sm), "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 def measured_peak():
@@ -239,13 +279,14 @@ def run_ours(args, rank, world):
     # streams its own 604 MB of weights, so no launch finds its bytes in L2
     ms_t = (C.c_float * Ln)(); cnt = C.c_uint32(0); per_layer = C.c_uint32(0)
     layer_ms = []
-    for rep in range(4):
+    for rep in range(13):    # the first pass warms up; 12 passes x 48 layers are kept and the median reported
         rc = api.lib.omega_gpu_moe_stack_profile(stack, C.c_uint32(T), C.c_uint64(logits_d.data_ptr()), C.c_uint64(x_d.data_ptr()), C.c_uint32(Ln), ms_t, C.byref(cnt), C.byref(per_layer))
         assert rc == 0, api.last_error()
         if rep:
             layer_ms += [ms_t[i] for i in range(cnt.value)]
     top = "expert_ffn (gate|up + SiLU + pieces -> down, one launch)" if per_layer.value == 1 else "gate|up + down (two launches)"
-    kern_ms = {top: float(np.mean(layer_ms))}
+    kern_ms = {top: float(np.median(layer_ms))}
+    kern_spread = {"p10_ms": float(np.percentile(layer_ms, 10)), "p90_ms": float(np.percentile(layer_ms, 90)), "mean_ms": float(np.mean(layer_ms)), "launches_timed": len(layer_ms)}
     # algorithmic bytes of that work per layer: every distinct expert's codes + scales once, plus the layer's input and output rows
     bf16_to_f32 = api.bf16_to_f32
     ids = np.stack([np.argsort(-bf16_to_f32(logits_h[l].numpy().view(np.uint16)), axis=1, kind="stable")[:, :TOPK] for l in range(min(Ln, 4))])
@@ -260,9 +301,17 @@ def run_ours(args, rank, world):
 
     if args.skip_cpu:
         cpu_sec, kind, cores = float("nan"), "skipped", 0
+        cpu_f32 = None
     else:
         cpu_sec, kind, cores = cpu_layer_sample(args.cpu_sample_tokens, 1, 0)
+        f32_sec, _, _ = cpu_layer_sample(args.cpu_sample_tokens, 1, 0, f32=True)
+        cpu_f32 = {"value": args.cpu_sample_tokens / (f32_sec * Ln), "unit": "tokens/s", "cores": cores, "kind": "port",
+                   "what": "the checker's f32 restatement of the kernels' own arithmetic (orc_gemv_emu), same sample, all host threads"}
     cpu_value = args.cpu_sample_tokens / (cpu_sec * Ln)
+    # what this GPU's HBM gives THIS process right now (the roofline's denominator stays the pool-wide measured figure)
+    cg, rg = C.c_float(0), C.c_float(0)
+    rc = api.lib.omega_gpu_hbm_peak(C.c_uint64(2 << 30), C.c_uint32(10), C.byref(cg), C.byref(rg))
+    hbm_now = {"copy_gbs_this_run": float(cg.value), "read_gbs_this_run": float(rg.value)} if rc == 0 else {"copy_gbs_this_run": None, "read_gbs_this_run": None}
     total_s = ms * 1e-3
     out = {
         "metric": "moe_layer_tokens_per_s", "value": T * args.steps / total_s, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -274,9 +323,12 @@ def run_ours(args, rank, world):
         "e2e": {"value": T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(logits_h.numel() * 2 + x_h.numel() * 2), "d2h_bytes_per_step": int(out_h.numel() * 2)},
         "gpu_launches": int(launches_per_step) * args.steps,
         "roofline": {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind + " copy bandwidth",
-                     "algorithmic_bytes": alg_bytes, "kernel_ms": kern_ms[top], "traffic": traffic, "frac_of_8TBps": achieved / 8000.0},
+                     "algorithmic_bytes": alg_bytes, "kernel_ms": kern_ms[top], "kernel_ms_spread": kern_spread, "traffic": traffic, "frac_of_8TBps": achieved / 8000.0,
+                     "copy_gbs_this_run": hbm_now["copy_gbs_this_run"], "read_gbs_this_run": hbm_now["read_gbs_this_run"],
+                     "frac_of_copy_this_run": (achieved / hbm_now["copy_gbs_this_run"]) if hbm_now["copy_gbs_this_run"] else None},
         "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": kind,
-                         "sample": "%d tokens through 1 of %d layers (x%d extrapolated), double-precision host GEMV oracle per routed row, %d threads" % (args.cpu_sample_tokens, Ln, Ln, cores)},
+                         "sample": "%d tokens through 1 of %d layers (x%d extrapolated), double-precision host GEMV oracle per routed row, %d threads" % (args.cpu_sample_tokens, Ln, Ln, cores),
+                         "f32_all_cores": cpu_f32},
         "clocks": clocks.summary(),
     }
     api.lib.omega_gpu_moe_stack_free(stack)
@@ -289,6 +341,13 @@ def run_ours(args, rank, world):
                               "roofline": pf["roofline"], "gpu_launches": pf["gpu_launches"]}
         except Exception as e:   # the headline line is printed whatever happens to the side measurement
             out["prefill"] = {"error": "%s: %s" % (type(e).__name__, e)}
+        # the three smaller configurations of the benchmark definition, each on cold weights
+        for key, fn in (("gemv", run_gemv), ("w4", run_w4), ("decode_layer", run_decode_layer)):
+            try:
+                r = fn(pa)
+                out[key] = {"workload": r["config"]["workload"], "value": r["value"], "unit": r["unit"], "us_per_call": r["ms_per_step"] * 1e3, "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
+            except Exception as e:
+                out[key] = {"error": "%s: %s" % (type(e).__name__, e)}
     print(json.dumps(out))
 
 
@@ -376,14 +435,185 @@ def run_prefill(args):
         "clocks": clocks.summary()}
 
 
+def _timed_graph(torch, stream, record, replays):
+    """captures record() (launches on `stream`) into a CUDA graph and returns the mean milliseconds of one replay (CUDA events on that stream)"""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        record()                                   # once eagerly: lazy initialisation outside the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=stream):
+            record()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(replays):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / replays
+
+
+def run_gemv(args):
+    """The single FP8 projection: x bf16 [1, 2048] times W e4m3 [768, 2048] with 128 x 128 block scales, through the stream-ordered GEMV
+    entry. One call moves 1.6 MB, less than L2 holds, so a loop over one weight would time the cache: as the reference's own cold gate does
+    (tests/gpu_fp8_api_test.c:841-849) the calls rotate through disjoint weight sets, here 128 of them (201 MB, more than L2), all inside one
+    CUDA graph; bytes / time per call is then an HBM figure. The call is launch-latency-bound: 0.24 us of traffic at the measured bandwidth."""
+    import torch
+    from cudapp_b200 import api
+    torch.cuda.set_device(0); dev = torch.device("cuda", 0)
+    sets, n, k = 128, 768, 2048
+    g = torch.Generator(device=dev); g.manual_seed(0)
+    w = (torch.randn((sets * n, k), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    w8 = torch.empty((sets, n, k), dtype=torch.uint8, device=dev); sc = torch.empty((sets, n // 128, k // 128), dtype=torch.int16, device=dev)
+    torch.cuda.synchronize()
+    assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(sets * n), C.c_uint32(k), C.c_uint64(w.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0, api.last_error()
+    t = C.c_void_p()
+    assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(sets), C.c_uint32(n), C.c_uint32(k), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr()), C.byref(t)) == 0, api.last_error()
+    del w, w8, sc
+    tab = np.empty((sets, 2), np.uint64)
+    for e in range(sets):
+        a, b = C.c_uint64(), C.c_uint64()
+        assert api.lib.omega_gpu_fp8_tensor_entry(t, C.c_uint32(e), C.byref(a), C.byref(b)) == 0
+        tab[e] = (a.value, b.value)
+    d_tab = torch.from_numpy(tab.view(np.int64)).to(dev)
+    rng = np.random.default_rng(0)
+    d_x = torch.from_numpy(api.bf16_bits(rng.normal(0, 1, (1, k)).astype(np.float32)).view(np.int16)).to(dev)
+    d_y = torch.zeros((sets, n), dtype=torch.float32, device=dev)
+    stream = torch.cuda.Stream()
+
+    def record(order=range(sets)):
+        for e in order:
+            rc = api.lib.omega_gpu_fp8_gemv_grouped_async(t, C.c_uint32(1), C.c_uint64(d_tab.data_ptr() + 16 * e), C.c_uint64(d_x.data_ptr()), C.c_uint32(1), C.c_int(1),
+                                                          C.c_uint64(d_y.data_ptr() + 4 * n * e), C.c_void_p(stream.cuda_stream))
+            assert rc == 0, api.last_error()
+    cold_ms = _timed_graph(torch, stream, record, 10) / sets
+    hot_ms = _timed_graph(torch, stream, lambda: record([0] * sets), 10) / sets         # the same weight every call: from L2
+    assert torch.isfinite(d_y).all()
+    api.fp8_tensor_free(t)
+    alg = n * k + (n // 128) * (k // 128) * 4 + k * 2 + n * 2                              # codes + scales + x + y (bf16 output in the definition)
+    peak, kind = measured_peak()
+    ach = alg / (cold_ms * 1e-3) / 1e9
+    return {"metric": "fp8_gemv_calls_per_s", "value": 1.0 / (cold_ms * 1e-3), "unit": "calls/s", "n_gpus": 1, "steps": 10 * sets, "warmup": 3 * sets, "ms_per_step": cold_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "single FP8 projection: x bf16 [1, 2048] x W e4m3 [768, 2048], block scales 128 x 128", "l2": "calls rotate through 128 disjoint weight sets (201 MB) inside one CUDA graph",
+                       "us_per_call_cold": cold_ms * 1e3, "us_per_call_same_weight": hot_ms * 1e3},
+            "gpu_launches": 10 * sets,
+            "roofline": {"bound": "hbm", "kernel": "fp8_rows_kernel (one row per warp)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind + " copy bandwidth",
+                         "algorithmic_bytes": alg, "kernel_ms": cold_ms, "traffic": None, "note": "launch-latency-bound: the call's bytes take 0.24 us at the peak"}}
+
+
+def run_w4(args):
+    """The W4 GEMM of the benchmark definition: x bf16 [16, 4096] times W int4 [4096, 4096] (two per byte, fp16 scale per 32 columns), bf16 out.
+    Cold method as for the single projection: 16 disjoint weight copies (151 MB, more than L2) rotated inside one CUDA graph. No reference
+    counterpart (the reference refuses integer W4), so there is no CPU reference arm for it."""
+    import torch
+    from cudapp_b200 import api
+    torch.cuda.set_device(0); dev = torch.device("cuda", 0)
+    sets, n, k, m = 16, 4096, 4096, 16
+    rng = np.random.default_rng(0)
+    w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    amax = np.abs(w.reshape(n, k // 32, 32)).max(-1)
+    scale = np.where(amax > 0, amax / 7.0, 1.0).astype(np.float16)                          # per row, per 32 columns
+    q = np.clip(np.rint(w.reshape(n, k // 32, 32) / scale.astype(np.float32)[..., None]), -8, 7).astype(np.int8).reshape(n, k)
+    packed = ((q[:, 0::2] & 0xF) | ((q[:, 1::2] & 0xF) << 4)).astype(np.uint8)             # low nibble = even column
+    tensors = []
+    for _ in range(sets):                                                                   # the same values in 16 separate device buffers: the timing needs distinct memory
+        t = C.c_void_p()
+        assert api.lib.omega_gpu_w4_upload(C.c_uint32(n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), scale.view(np.uint16).ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
+        tensors.append(t)
+    d_x = torch.from_numpy(api.bf16_bits(rng.normal(0, 1, (m, k)).astype(np.float32)).view(np.int16)).to(dev)
+    d_y = torch.zeros((sets, m, n), dtype=torch.int16, device=dev)
+    stream = torch.cuda.Stream()
+
+    def record(order=range(sets)):
+        for e in order:
+            rc = api.lib.omega_gpu_w4_gemm_async(tensors[e], C.c_uint32(m), C.c_uint64(d_x.data_ptr()), C.c_uint64(d_y.data_ptr() + 2 * m * n * e), C.c_uint64(0), C.c_void_p(stream.cuda_stream))
+            assert rc == 0, api.last_error()
+    cold_ms = _timed_graph(torch, stream, record, 10) / sets
+    for t in tensors:
+        api.lib.omega_gpu_w4_free(t)
+    alg = n * k // 2 + n * (k // 32) * 2 + m * k * 2 + m * n * 2
+    peak, kind = measured_peak()
+    ach = alg / (cold_ms * 1e-3) / 1e9
+    return {"metric": "w4_gemm_calls_per_s", "value": 1.0 / (cold_ms * 1e-3), "unit": "calls/s", "n_gpus": 1, "steps": 10 * sets, "warmup": 3 * sets, "ms_per_step": cold_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights, fp16 group scales, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "W4 GEMM: x bf16 [16, 4096] x W int4 [4096, 4096], fp16 scale per 32 columns", "l2": "calls rotate through 16 disjoint weight copies (151 MB) inside one CUDA graph",
+                       "tflops": 2.0 * m * n * k / (cold_ms * 1e-3) / 1e12, "parity": "unpinned: the reference has no integer-W4 arithmetic"},
+            "gpu_launches": 10 * sets,
+            "roofline": {"bound": "hbm", "kernel": "w4_gemm_kernel", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind + " copy bandwidth",
+                         "algorithmic_bytes": alg, "kernel_ms": cold_ms, "traffic": None, "note": "this kernel runs on the f32 FMA pipes, not the tensor cores: it is FMA-bound, far from the HBM line"}}
+
+
+def run_decode_layer(args):
+    """One MoE layer on 64 decode tokens (128 experts, top-8): ~126 distinct experts = 0.6 GB of weights per call, more than L2, so every call
+    streams them from HBM. Device-resident inputs, the stream-ordered layer entry, CUDA events."""
+    import torch
+    from cudapp_b200 import api
+    torch.cuda.set_device(0); dev = torch.device("cuda", 0)
+    T = 64
+    g = torch.Generator(device=dev); g.manual_seed(0)
+    wgu = (torch.randn((E * 2 * I, H), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    wdn = (torch.randn((E * H, I), generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    w8 = torch.empty((E, 2 * I, H), dtype=torch.uint8, device=dev); sc = torch.empty((E, 2 * I // 128, H // 128), dtype=torch.int16, device=dev)
+    d8 = torch.empty((E, H, I), dtype=torch.uint8, device=dev); dsc = torch.empty((E, H // 128, I // 128), dtype=torch.int16, device=dev)
+    torch.cuda.synchronize()
+    assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * 2 * I), C.c_uint32(H), C.c_uint64(wgu.data_ptr()), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr())) == 0, api.last_error()
+    assert api.lib.omega_gpu_fp8_quantize_bf16_dev(C.c_uint32(E * H), C.c_uint32(I), C.c_uint64(wdn.data_ptr()), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr())) == 0, api.last_error()
+    tg, td = C.c_void_p(), C.c_void_p()
+    assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(2 * I), C.c_uint32(H), C.c_uint64(w8.data_ptr()), C.c_uint64(sc.data_ptr()), C.byref(tg)) == 0, api.last_error()
+    assert api.lib.omega_gpu_fp8_tensor_upload_dev(C.c_uint32(E), C.c_uint32(H), C.c_uint32(I), C.c_uint64(d8.data_ptr()), C.c_uint64(dsc.data_ptr()), C.byref(td)) == 0, api.last_error()
+    del wgu, wdn, w8, sc, d8, dsc
+    rc, layer = api.moe_layer_create(tg, td, topk=TOPK, max_tokens=T, engine=args.engine)
+    assert rc == 0, api.last_error()
+    rng = np.random.default_rng(0)
+    lg = api.bf16_bits(rng.normal(0, 1, (T, E)).astype(np.float32))
+    logits_d = torch.from_numpy(lg.view(np.int16)).to(dev)
+    x_d = torch.from_numpy(api.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32)).view(np.int16)).to(dev)
+    out32 = torch.empty((T, H), dtype=torch.float32, device=dev); out16 = torch.empty((T, H), dtype=torch.int16, device=dev)
+    stream = torch.cuda.Stream()
+
+    def step():
+        rc = api.lib.omega_gpu_moe_layer_async(layer, C.c_uint32(T), C.c_uint64(logits_d.data_ptr()), C.c_uint64(x_d.data_ptr()), C.c_uint64(out32.data_ptr()),
+                                               C.c_uint64(out16.data_ptr()), C.c_void_p(stream.cuda_stream))
+        assert rc == 0, api.last_error()
+    ms = _timed_graph(torch, stream, step, 20)
+    assert torch.isfinite(out32).all()
+    launches = int(api.lib.omega_gpu_moe_layer_launches(layer))
+    ms_t = (C.c_float * 12)(); names = (C.c_char_p * 12)(); cnt = C.c_uint32(0)
+    kern = {}
+    for rep_ in range(5):
+        rc = api.lib.omega_gpu_moe_layer_profile(layer, C.c_uint32(T), C.c_uint64(logits_d.data_ptr()), C.c_uint64(x_d.data_ptr()), C.c_uint64(out32.data_ptr()), C.c_uint32(12), ms_t, names, C.byref(cnt))
+        assert rc == 0, api.last_error()
+        if rep_:
+            for i in range(cnt.value):
+                kern.setdefault(names[i].decode(), []).append(ms_t[i])
+    kern = {k_: float(np.median(v)) for k_, v in kern.items()}
+    api.lib.omega_gpu_moe_layer_free(layer); api.fp8_tensor_free(tg); api.fp8_tensor_free(td)
+    ids = np.argsort(-api.bf16_to_f32(lg), axis=1, kind="stable")[:, :TOPK]
+    distinct = len(np.unique(ids))
+    alg = distinct * (GU_BYTES + DN_BYTES) + T * E * 2 + 2 * T * H * 2
+    gemm_ms = sum(v for k_, v in kern.items() if "mma" in k_ or "gemm" in k_)
+    peak, kind = measured_peak()
+    ach = alg / (gemm_ms * 1e-3) / 1e9
+    return {"metric": "moe_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": 20, "warmup": 4, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 weights, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "one MoE decode layer, 64 tokens, 128 experts top-8, hidden 2048, inter 768", "tokens_per_step": T, "distinct_experts": distinct,
+                       "l2": "0.6 GB of weights per call: larger than L2", "kernel_ms": kern, "whole_layer_gbs": alg / (ms * 1e-3) / 1e9},
+            "gpu_launches": launches * 20,
+            "roofline": {"bound": "hbm", "kernel": "gate|up + down grouped GEMM (two launches)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                         "peak_kind": kind + " copy bandwidth", "algorithmic_bytes": alg, "kernel_ms": gemm_ms, "traffic": None}}
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
-    elif args.workload == "prefill":
+    elif args.workload in ("prefill", "gemv", "w4", "decode_layer"):
         if rank == 0:
-            print(json.dumps(run_prefill(args)))
+            print(json.dumps({"prefill": run_prefill, "gemv": run_gemv, "w4": run_w4, "decode_layer": run_decode_layer}[args.workload](args)))
     else:
         run_ours(args, rank, world)
 

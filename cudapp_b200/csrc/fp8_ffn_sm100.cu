@@ -35,10 +35,15 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     constexpr int PMAX = PX > PA ? PX : PA, NMAX = MMA_TOK * PMAX;
     constexpr int STAGES = PMAX <= 3 ? 4 : 3;
     constexpr uint32_t STAGE_BYTES = 2 * A_TILE + PMAX * B_PIECE;
-    constexpr uint32_t TMEM_COLS = 4 * NMAX <= 128 ? 128 : 4 * NMAX <= 256 ? 256 : 512;
+    // TMEM partial buffers: one buffer = both 128-feature blocks of a K block (2 x 32 x pieces columns). All 512 columns are taken, so a
+    // gate|up K block (narrower: PX pieces) has up to four buffers and the MMA issuer can run that far ahead of the promotion warps; the
+    // buffers of the two kinds of unit overlap, so the issuer drains the gate|up buffers once, before its first down unit.
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t NBX = 512 / (64 * PX) >= 4 ? 4 : 512 / (64 * PX), NBD = 512 / (64 * PA) >= 4 ? 4 : 512 / (64 * PA);
+    static_assert(NBX >= 2 && NBD >= 2, "two partial buffers at least");
     constexpr uint32_t Q_GROUP_BYTES = PA * MMA_TOK * 128;   // per epilogue group: PA pieces x 32 rows x 128 bytes of output codes
     extern __shared__ uint8_t dyn_smem[];
-    __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 12];
+    __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 16];
     __shared__ uint32_t s_tmem, s_abort;
     __shared__ float s_sc[2][2][KB_MAX][MMA_TOK];
     __shared__ float s_red[2][4][MMA_TOK];
@@ -52,19 +57,19 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     auto full_bar = [&](uint32_t s) { return bar0 + 8u * s; };
     auto empty_bar = [&](uint32_t s) { return bar0 + 8u * (STAGES + s); };
     auto accfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + b); };
-    auto accempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
-    auto scfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 4 + b); };
-    auto scempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 6 + b); };
-    auto group_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 8 + g); };
-    auto turn_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 10 + g); };
+    auto accempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 4 + b); };
+    auto scfull_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 8 + b); };
+    auto scempty_bar = [&](uint32_t b) { return bar0 + 8u * (2 * STAGES + 10 + b); };
+    auto group_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 12 + g); };
+    auto turn_bar = [&](uint32_t g) { return bar0 + 8u * (2 * STAGES + 14 + g); };
     volatile uint32_t *abort_flag = &s_abort;
 
     if (threadIdx.x < 128) s_ret[threadIdx.x >> 6][threadIdx.x & 63u] = 0;
     if (threadIdx.x == 0) {
         s_abort = 0; s_published = 0;
         for (uint32_t s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (uint32_t b = 0; b < 4; b++) { mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128); }
         for (uint32_t b = 0; b < 2; b++) {
-            mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128);
             mbar_init(scfull_bar(b), 32); mbar_init(scempty_bar(b), 128); mbar_init(group_bar(b), 128); mbar_init(turn_bar(b), 128);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -81,6 +86,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     const bool dead = *reinterpret_cast<volatile uint32_t *>(a.err) != 0;   // a failure is already recorded: do nothing
     const uint32_t n_tiles = dead ? 0u : a.header[2], n_gu = n_tiles * PG, n_dn = n_tiles * PD;
     const uint32_t my_gu = blockIdx.x < n_gu ? (n_gu - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;   // gate|up units of this CTA (static round-robin)
+    // The partial buffer of this CTA's it-th K block (its gate|up K blocks come first: it < gu_kbs): buffer index, how often that buffer was
+    // used before (its mbarrier phase) and its first TMEM column. Every role walks the same sequence, so all compute the same slots.
+    const uint32_t gu_kbs = my_gu * KBX;
+    struct Slot { uint32_t buf, use, col, half; };
+    auto acc_slot = [&](uint32_t it) -> Slot {
+        Slot sl;
+        if (it < gu_kbs) { sl.buf = it % NBX; sl.use = it / NBX; sl.col = sl.buf * (64u * PX); sl.half = 32u * PX; }
+        else { const uint32_t j = it - gu_kbs; sl.buf = j % NBD; sl.use = (gu_kbs + NBX - 1u - sl.buf) / NBX + j / NBD; sl.col = sl.buf * (64u * PA); sl.half = 32u * PA; }
+        return sl;
+    };
 
     // The n-th unit of this CTA: gate|up units first (unit id u < n_gu), then the down units the producer publishes.
     // Returns false when the CTA has no n-th unit. Only the producer fetches; the other roles read what it published.
@@ -184,21 +199,26 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                 const Unit q = decode(u);
                 const uint32_t N = q.mode ? (uint32_t)(MMA_TOK * PA) : (uint32_t)(MMA_TOK * PX);
                 const uint32_t idesc = (1u << 4) | ((N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);   // f8f6f4, D f32, A = B = e4m3 K-major, M 128
+                if (it == gu_kbs && it != 0) {   // first down unit: its buffers overlap the gate|up ones, which must all be drained (once per launch)
+                    for (uint32_t b = 0; b < NBX && ok; b++) ok = mbar_wait(accempty_bar(b), (((gu_kbs + NBX - 1u - b) / NBX) & 1u) ^ 1u, abort_flag, a.err, 2);
+                    if (!ok) break;
+                }
                 for (uint32_t kb = 0; kb < q.KB; kb++, it++) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u, buf = it & 1u, bph = (it >> 1) & 1u;
-                    if (!(ok = mbar_wait(accempty_bar(buf), bph ^ 1u, abort_flag, a.err, 2))) break;
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    const Slot sl = acc_slot(it);
+                    if (!(ok = mbar_wait(accempty_bar(sl.buf), (sl.use & 1u) ^ 1u, abort_flag, a.err, 2))) break;
                     if (!(ok = mbar_wait(full_bar(s), ph, abort_flag, a.err, 3))) break;
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * STAGE_BYTES;
                     const uint64_t da0 = umma_desc(sa), da1 = umma_desc(sa + A_TILE), db = umma_desc(sa + 2 * A_TILE);
-                    const uint32_t d0 = tmem + buf * 2u * NMAX, d1 = d0 + NMAX;
+                    const uint32_t d0 = tmem + sl.col, d1 = d0 + sl.half;
 #pragma unroll
                     for (uint32_t ks = 0; ks < 4; ks++) {
                         tc_mma_f8(d0, da0 + 2u * ks, db + 2u * ks, idesc, ks);
                         tc_mma_f8(d1, da1 + 2u * ks, db + 2u * ks, idesc, ks);
                     }
                     tc_commit(empty_bar(s));
-                    tc_commit(accfull_bar(buf));
+                    tc_commit(accfull_bar(sl.buf));
                 }
             }
         }
@@ -251,15 +271,16 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
             auto kloop = [&](auto pc) {
                 constexpr int P = decltype(pc)::value;
                 for (uint32_t kb = 0; kb < q.KB; kb++, it++) {
-                    const uint32_t buf = it & 1u, bph = (it >> 1) & 1u;
-                    if (!(ok = mbar_wait(accfull_bar(buf), bph, abort_flag, a.err, 4))) return;
+                    const Slot sl = acc_slot(it);
+                    const uint32_t buf = sl.buf;
+                    if (!(ok = mbar_wait(accfull_bar(buf), sl.use & 1u, abort_flag, a.err, 4))) return;
                     tc_fence_after();
-                    const uint32_t taddr = tmem + ((q4 * 32u) << 16) + buf * 2u * NMAX;
+                    const uint32_t taddr = tmem + ((q4 * 32u) << 16) + sl.col;
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
                         uint32_t da[MMA_TOK], db[MMA_TOK];
-                        TMEM_LD32(taddr + half * NMAX + (P - 1) * MMA_TOK, da);
-                        if (P > 1) TMEM_LD32(taddr + half * NMAX + (P > 1 ? P - 2 : 0) * MMA_TOK, db);
+                        TMEM_LD32(taddr + half * (P * MMA_TOK) + (P - 1) * MMA_TOK, da);
+                        if (P > 1) TMEM_LD32(taddr + half * (P * MMA_TOK) + (P > 1 ? P - 2 : 0) * MMA_TOK, db);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (P > 1) {
 #pragma unroll
@@ -267,7 +288,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                         }
 #pragma unroll
                         for (int p = P - 3; p >= 0; p--) {
-                            TMEM_LD32(taddr + half * NMAX + p * MMA_TOK, db);
+                            TMEM_LD32(taddr + half * (P * MMA_TOK) + p * MMA_TOK, db);
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                             for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));

@@ -135,8 +135,16 @@ cudaError_t launch_gemv_grouped(const GemvArgs &a, uint32_t cta_budget, uint32_t
     uint32_t want = cta_budget ? cta_budget : (sms * 4u + a.groups_or_segs - 1u) / a.groups_or_segs;
     if (want == 0) want = 1;
     if (gx > want) gx = want;
-    if (grid_x) *grid_x = gx;
     if (warps) *warps = 8;
+    if (gx * a.groups_or_segs < sms && !cta_budget) {
+        // few groups (the single-projection call): four rows per warp would leave most SMs without a CTA; one row per warp gives
+        // four times the CTAs. A row's arithmetic does not depend on how rows are dealt to warps: same bits.
+        gx = (a.n + 7u) / 8u;
+        if (gx > want) gx = want;
+        if (grid_x) *grid_x = gx;
+        return launch_lb<1, 1>(a, dim3(gx, a.groups_or_segs), s);
+    }
+    if (grid_x) *grid_x = gx;
     return launch_lb<4, 1>(a, dim3(gx, a.groups_or_segs), s);
 }
 // Row-table form: MT = 4 activation rows per pass of a segment's weights.

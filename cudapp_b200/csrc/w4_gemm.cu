@@ -111,6 +111,20 @@ void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     if (t->s) cudaFree(t->s);
     free(t);
 }
+static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *dx, uint16_t *d16, float *d32, cudaStream_t s) {
+    const size_t smem = (size_t)W4_MT * t->k * 2;
+    static bool attr = false;
+    if (!attr) { const cudaError_t e = cudaFuncSetAttribute(w4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); if (e != cudaSuccess) return e; attr = true; }
+    uint32_t grid = (t->n / W4_RW + 7) / 8; const uint32_t cap = (uint32_t)(st().sm_count ? st().sm_count : 148); if (grid > cap) grid = cap;
+    w4_gemm_kernel<<<grid, 256, smem, s>>>(m, t->n, t->k, t->w, t->s, dx, d16, d32);
+    return cudaGetLastError();
+}
+int omega_gpu_w4_gemm_async(const OmegaGpuW4Tensor *t, uint32_t m, uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream) {
+    if (!t || !m || !x_bf16_va || (!y_bf16_va && !y_f32_va)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    return cuda_ok(w4_launch(t, m, (const uint16_t *)(uintptr_t)x_bf16_va, (uint16_t *)(uintptr_t)y_bf16_va, (float *)(uintptr_t)y_f32_va, (cudaStream_t)stream), "w4 launch")
+               ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+}
 int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x, uint16_t *y16, float *y32) {
     if (!t || !m || !x || (!y16 && !y32)) return OMEGA_GPU_FP8_BAD_ARGS;
     Lock l;
@@ -119,14 +133,7 @@ int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t
     uint16_t *dx = (uint16_t *)stage(0, xb), *d16 = (uint16_t *)stage(1, yb * 2); float *d32 = (float *)stage(2, yb * 4);
     if (!dx || !d16 || !d32) return OMEGA_GPU_FP8_CHIP_FAIL;
     cudaStream_t s = st().stream;
-    const size_t smem = (size_t)W4_MT * t->k * 2;
-    bool ok = cuda_ok(cudaFuncSetAttribute(w4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "w4 smem") &&
-              cuda_ok(cudaMemcpyAsync(dx, x, xb, cudaMemcpyHostToDevice, s), "copy x");
-    if (ok) {
-        uint32_t grid = (t->n / W4_RW + 7) / 8; const uint32_t cap = (uint32_t)st().sm_count; if (grid > cap) grid = cap;
-        w4_gemm_kernel<<<grid, 256, smem, s>>>(m, t->n, t->k, t->w, t->s, dx, d16, d32);
-        ok = cuda_ok(cudaGetLastError(), "w4 launch");
-    }
+    bool ok = cuda_ok(cudaMemcpyAsync(dx, x, xb, cudaMemcpyHostToDevice, s), "copy x") && cuda_ok(w4_launch(t, m, dx, d16, d32, s), "w4 launch");
     if (ok && y16) ok = cuda_ok(cudaMemcpyAsync(y16, d16, yb * 2, cudaMemcpyDeviceToHost, s), "copy y");
     if (ok && y32) ok = cuda_ok(cudaMemcpyAsync(y32, d32, yb * 4, cudaMemcpyDeviceToHost, s), "copy y");
     ok = ok && cuda_ok(cudaStreamSynchronize(s), "w4 gemm");

@@ -67,6 +67,8 @@ int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uin
 void omega_gpu_w4_free(OmegaGpuW4Tensor *t);
 /* y bf16 [m][n] = x bf16 [m][k] * W^T, f32 accumulation; yf32 (optional) receives the unrounded values */
 int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32);
+/* the same on device buffers, stream-ordered (one of y_bf16_va / y_f32_va may be 0) */
+int omega_gpu_w4_gemm_async(const OmegaGpuW4Tensor *t, uint32_t m, uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream);
 
 /* ---- the MoE layer: top-k -> plan -> gate|up grouped GEMM + SiLU gate -> down grouped GEMM -> weighted combine
  * (the MoE part of src/omega_gpu_decode_graph.c:341-351 for decode, src/omega_gpu_q36_graph.c:1147 for prefill). */
@@ -204,6 +206,10 @@ int omega_gpu_moe_router_f32(OmegaGpuMoeRouter *r, uint32_t rows, const float *x
  * issues iters x 4 tcgen05 MMAs of M 128, N 256, K 32 on operands resident in shared memory). *tflops = best of `repeats` timed
  * launches (CUDA events), *ms_out (optional) that launch's duration. The denominator for "fraction of FP8 tensor peak". */
 int omega_gpu_fp8_tensor_peak(uint32_t iters, uint32_t repeats, float *tflops, float *ms_out);
+/* Measurement aid, no reference counterpart: HBM bandwidth of this GPU as this process sees it. Two buffers of `bytes` each (256 MiB to
+ * 4 GiB, larger than L2) are allocated for the call: *copy_gbs = (bytes read + bytes written) / time of a plain copy kernel, *read_gbs =
+ * bytes / time of a read-only stream; best of `repeats` timed launches each (CUDA events). */
+int omega_gpu_hbm_peak(uint64_t bytes, uint32_t repeats, float *copy_gbs, float *read_gbs);
 
 #ifdef __cplusplus
 }

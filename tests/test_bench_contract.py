@@ -1,5 +1,5 @@
 """Host-side checks of bench.py that need no GPU: the reference arm prints one JSON line with the keys the contract names, and the
-clock summary parses nvidia-smi rows as documented."""
+clock summary reads NVML (a fake one here) as documented."""
 import json
 import os
 import subprocess
@@ -33,12 +33,31 @@ def test_reference_arm_other_ranks_stay_silent():
 
 
 def test_clock_summary():
+    """the sampler against a fake NVML (read-only queries; nothing is ever set): median clock, reasons seen at any sample, sample count"""
+    class FakeNvml:
+        NVML_CLOCK_SM = 1
+        def __init__(self):
+            self.i = 0
+            self.clocks = [1800, 1750, 1700]
+            self.reasons = [0x4, 0x4, 0x0]           # sw_power_cap on two of three samples
+        def nvmlDeviceGetClockInfo(self, h, which):
+            return self.clocks[self.i % 3]
+        def nvmlDeviceGetPowerUsage(self, h):
+            return 900000
+        def nvmlDeviceGetCurrentClocksEventReasons(self, h):
+            r = self.reasons[self.i % 3]; self.i += 1
+            return r
     c = bench.ClockSampler(0)
-    c.rows = [["1800", "1965", "640.1", "Not Active", "Not Active", "Not Active", "Active"], ["1750", "1965", "900.0", "Not Active", "Not Active", "Not Active", "Active"],
-              ["1700", "1965", "910.0", "Not Active", "Not Active", "Not Active", "Not Active"]]
+    c.nvml, c.handle, c.max_mhz = FakeNvml(), object(), 1965.0
+    c.sm, c.power, c.reason_bits = [], [], 0
+    for _ in range(3):
+        c.sample_nvml()
     s = c.summary()
-    assert s["sm_mhz"] == 1750.0 and s["sm_max_mhz"] == 1965.0 and s["reasons"] == ["sw_power_cap"] and s["samples"] == 3
-    c.rows = []
+    assert s["sm_mhz"] == 1750.0 and s["sm_min_mhz"] == 1700.0 and s["sm_max_mhz"] == 1965.0 and s["reasons"] == ["sw_power_cap"] and s["samples"] == 3
+    assert s["power_w_max"] == 900.0
+    c.reason_bits |= 0x40
+    assert "hw_thermal_slowdown" in c.summary()["reasons"]
+    c.sm = []
     assert c.summary()["sm_mhz"] is None
 
 
