@@ -2,13 +2,18 @@
 // columns) times bf16 activations, f32 accumulation, bf16 output. The reference has no integer-W4 arithmetic
 // (docs/models/QUANT.md:62 of the reference: "integer W4 refuses"), so this follows the benchmark definition only:
 // y[m][r] = sum over groups g of scale[r][g] * sum_{c in g} x[m][c] * q[r][c].
-// Weight-streaming kernel: a warp owns RW output rows; lane l owns K groups l, l+32, ... (16 contiguous bytes each,
-// 512 contiguous bytes per warp load); the activation panel sits in shared memory as bf16.
+// Two kernels. The tensor-core kernel takes the shapes it is written for (n a multiple of 128; k 1024, 2048 or 4096); the
+// CUDA-core kernel takes every other shape: a warp owns RW output rows; lane l owns K groups l, l+32, ... (16 contiguous bytes
+// each, 512 contiguous bytes per warp load); the activation panel sits in shared memory as bf16.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdlib.h>
 #include "internal.h"
 
-struct OmegaGpuW4Tensor { uint32_t n, k; uint8_t *w; uint16_t *s; };
+struct OmegaGpuW4Tensor {
+    uint32_t n, k; uint8_t *w; uint16_t *s;
+    float *part; uint32_t *counters;   // scratch of the tensor-core kernel: K-quarter partial sums [4][16][n] f32 and one arrival counter per 128 output rows
+};
 
 namespace b200 {
 
@@ -82,6 +87,92 @@ __global__ void __launch_bounds__(256) w4_gemm_kernel(uint32_t m, uint32_t n, ui
     }
 }
 
+// ---------------------------------------------------------------- tensor-core kernel
+// The activation panel has at most 16 rows per pass: exactly the M of the warp-level mma.sync m16n8k16 (the tcgen05 MMA starts at M 64 and
+// takes its operands from shared or tensor memory, so the int4 -> bf16 expansion would have to go through shared memory; here it stays
+// in registers, and the kernel is a weight stream whose tensor work is a few percent of the memory time either way).
+// int4 values are exact in bf16; a scale group is 32 columns = two k16 MMAs into a fresh accumulator, then acc += scale * partial in f32:
+// the definition's own order of operations (group sums first, then the scale). Work split: grid (n / 128, 4 K quarters), 16 warps, a warp owns
+// 8 output rows (one n8 tile) over its quarter's groups; every weight word a thread needs is requested before the first one is used (the whole
+// matrix is in flight at once). Inside a group the 32 columns are dealt to the MMA's k slots so that thread t of a quad uses exactly the 8
+// nibbles of its own 32-bit word (columns 8t .. 8t+7): k slots {2t, 2t+1, 2t+8, 2t+9} of the first MMA are columns 8t .. 8t+3, of the second
+// 8t+4 .. 8t+7; the activation fragments follow the same dealing, so each product meets its own weight. The four K quarters of an output block
+// meet in a scratch buffer; the CTA that arrives last adds them in quarter order (a fixed order: same bits every run).
+__device__ __forceinline__ void mma_bf16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// byte j of v (two signed nibbles: low = even column) -> two bf16 values. 0x4300 | (nibble ^ 8) is the bf16 number 128 + (q + 8); minus 136 gives q exactly.
+__device__ __forceinline__ uint32_t nib2_bf16(uint32_t v, int j) {
+    const uint32_t b = v >> (8 * j);
+    uint32_t u = (((b & 0xFu) | ((b << 12) & 0xF0000u)) ^ 0x00080008u) | 0x43004300u;
+    __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162 *>(&u);
+    h = __hsub2(h, __floats2bfloat162_rn(136.0f, 136.0f));
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int GQ>   // scale groups per K quarter: k = 128 * GQ
+__global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m, uint32_t n, uint32_t k, const uint8_t *__restrict__ w, const uint16_t *__restrict__ sc,
+                                                        const uint16_t *__restrict__ x, uint16_t *__restrict__ y16, float *__restrict__ y32, float *part, uint32_t *counters) {
+    constexpr uint32_t KQ = GQ * 32u, XS = KQ * 2u + 64u;   // columns per quarter; bytes between panel rows (the 64 keep a quarter-warp's 16-byte reads on separate banks)
+    extern __shared__ __align__(16) uint8_t xq[];
+    __shared__ uint32_t s_last;
+    const uint32_t nb = blockIdx.x, kq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, r = lane >> 2, t = lane & 3u;
+    const uint32_t mt = min(16u, m - m0);
+    // this thread's weight words: output row n0 + r, word t of every group of the quarter; all requested before anything else
+    const uint32_t n0 = nb * 128u + warp * 8u;
+    const uint32_t *wrow = reinterpret_cast<const uint32_t *>(w + (size_t)(n0 + r) * (k / 2u) + (size_t)kq * (KQ / 2u));
+    uint32_t wq[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; g++) wq[g] = __ldcs(wrow + g * 4 + t);
+    // scales of the two output columns this thread's accumulators belong to (n0 + 2t, n0 + 2t + 1)
+    const uint4 *s0p = reinterpret_cast<const uint4 *>(sc + (size_t)(n0 + 2u * t) * (k / 32u) + kq * GQ), *s1p = reinterpret_cast<const uint4 *>(sc + (size_t)(n0 + 2u * t + 1u) * (k / 32u) + kq * GQ);
+    uint4 sv0[GQ / 8], sv1[GQ / 8];
+#pragma unroll
+    for (int i = 0; i < GQ / 8; i++) { sv0[i] = __ldg(s0p + i); sv1[i] = __ldg(s1p + i); }
+    // the quarter of the activation panel: rows m0 .. m0 + 15 (zero past m), columns kq * KQ ..
+    for (uint32_t i = threadIdx.x; i < 16u * (KQ / 8u); i += 512u) {
+        const uint32_t row = i / (KQ / 8u), c8 = i - row * (KQ / 8u);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < mt) v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + row) * k + (size_t)kq * KQ) + c8);
+        *reinterpret_cast<uint4 *>(xq + row * XS + c8 * 16u) = v;
+    }
+    __syncthreads();
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int g = 0; g < GQ; g++) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + r * XS + g * 64 + t * 16u);          // panel row r, columns 8t .. 8t+7 of group g
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + (r + 8u) * XS + g * 64 + t * 16u);   // panel row r + 8
+        float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        mma_bf16_16816(p, xa.x, xb.x, xa.y, xb.y, nib2_bf16(wq[g], 0), nib2_bf16(wq[g], 1));
+        mma_bf16_16816(p, xa.z, xb.z, xa.w, xb.w, nib2_bf16(wq[g], 2), nib2_bf16(wq[g], 3));
+        const uint32_t *u0 = reinterpret_cast<const uint32_t *>(&sv0[g >> 3]), *u1 = reinterpret_cast<const uint32_t *>(&sv1[g >> 3]);
+        const uint32_t h0 = (u0[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu, h1 = (u1[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu;
+        const float sl = __half2float(__ushort_as_half((unsigned short)h0)), sh = __half2float(__ushort_as_half((unsigned short)h1));
+        acc[0] = fmaf(p[0], sl, acc[0]); acc[1] = fmaf(p[1], sh, acc[1]); acc[2] = fmaf(p[2], sl, acc[2]); acc[3] = fmaf(p[3], sh, acc[3]);
+    }
+    // this quarter's share of the block: part[kq][row][n]
+    *reinterpret_cast<float2 *>(part + ((size_t)kq * 16u + r) * n + n0 + 2u * t) = make_float2(acc[0], acc[1]);
+    *reinterpret_cast<float2 *>(part + ((size_t)kq * 16u + r + 8u) * n + n0 + 2u * t) = make_float2(acc[2], acc[3]);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(counters + nb, 1u) == 3u ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < 16u * 128u; i += 512u) {
+        const uint32_t row = i >> 7, col = nb * 128u + (i & 127u);
+        if (row >= mt) continue;
+        float v = __ldcg(part + (size_t)row * n + col);
+#pragma unroll
+        for (uint32_t q = 1; q < 4; q++) v = __fadd_rn(v, __ldcg(part + ((size_t)q * 16u + row) * n + col));
+        const size_t at = (size_t)(m0 + row) * n + col;
+        if (y32) y32[at] = v;
+        if (y16) { const uint32_t b = __float_as_uint(v); y16[at] = (uint16_t)(((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16)); }
+    }
+    if (threadIdx.x == 0) counters[nb] = 0;   // ready for the next launch (launches on one tensor are stream-ordered)
+}
+
 }  // namespace b200
 using namespace b200;
 
@@ -98,9 +189,14 @@ int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uin
     if (!t) return OMEGA_GPU_FP8_BAD_ARGS;
     t->n = n; t->k = k;
     const size_t wb = (size_t)n * k / 2, sb = (size_t)n * (k / 32) * 2;
-    const bool ok = cuda_ok(cudaMalloc(&t->w, wb), "cudaMalloc(w4)") && cuda_ok(cudaMalloc(&t->s, sb), "cudaMalloc(w4 scales)") &&
-                    cuda_ok(cudaMemcpy(t->w, packed, wb, cudaMemcpyHostToDevice), "copy w4") && cuda_ok(cudaMemcpy(t->s, scale_f16, sb, cudaMemcpyHostToDevice), "copy w4 scales");
-    if (!ok) { if (t->w) cudaFree(t->w); if (t->s) cudaFree(t->s); free(t); return OMEGA_GPU_FP8_CHIP_FAIL; }
+    bool ok = cuda_ok(cudaMalloc(&t->w, wb), "cudaMalloc(w4)") && cuda_ok(cudaMalloc(&t->s, sb), "cudaMalloc(w4 scales)") &&
+              cuda_ok(cudaMemcpy(t->w, packed, wb, cudaMemcpyHostToDevice), "copy w4") && cuda_ok(cudaMemcpy(t->s, scale_f16, sb, cudaMemcpyHostToDevice), "copy w4 scales");
+    if (ok && n % 128u == 0 && (k == 1024u || k == 2048u || k == 4096u)) {   // the tensor-core kernel's scratch
+        const size_t pb = (size_t)4 * 16 * n * 4, cb = (size_t)(n / 128u) * 4;
+        ok = cuda_ok(cudaMalloc(&t->part, pb), "cudaMalloc(w4 partials)") && cuda_ok(cudaMalloc(&t->counters, cb), "cudaMalloc(w4 counters)") &&
+             cuda_ok(cudaMemset(t->counters, 0, cb), "memset");
+    }
+    if (!ok) { if (t->w) cudaFree(t->w); if (t->s) cudaFree(t->s); if (t->part) cudaFree(t->part); if (t->counters) cudaFree(t->counters); free(t); return OMEGA_GPU_FP8_CHIP_FAIL; }
     *out = t;
     return OMEGA_GPU_FP8_OK;
 }
@@ -109,9 +205,20 @@ void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     Lock l;
     if (t->w) cudaFree(t->w);
     if (t->s) cudaFree(t->s);
+    if (t->part) cudaFree(t->part);
+    if (t->counters) cudaFree(t->counters);
     free(t);
 }
 static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *dx, uint16_t *d16, float *d32, cudaStream_t s) {
+    if (t->part && !getenv("B200MOE_W4_FMA")) {   // tensor-core kernel: one launch per 16 activation rows (they share the tensor's scratch, in stream order)
+        const dim3 grid(t->n / 128u, 4);
+        for (uint32_t m0 = 0; m0 < m; m0 += 16u) {
+            if (t->k == 4096u) w4_mma_kernel<32><<<grid, 512, 16 * (32 * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters);
+            else if (t->k == 2048u) w4_mma_kernel<16><<<grid, 512, 16 * (16 * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters);
+            else w4_mma_kernel<8><<<grid, 512, 16 * (8 * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters);
+        }
+        return cudaGetLastError();
+    }
     const size_t smem = (size_t)W4_MT * t->k * 2;
     static bool attr = false;
     if (!attr) { const cudaError_t e = cudaFuncSetAttribute(w4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); if (e != cudaSuccess) return e; attr = true; }

@@ -196,18 +196,20 @@ def test_glue_ops():
     assert np.array_equal(api.act_quant_f32(x, 1)[1][:, 0], q1)
 
 
-def test_w4_gemm():
-    """W4 configuration (self-oracle: the reference has no integer-W4 arithmetic)"""
+@pytest.mark.parametrize("n,k,m", [(512, 1024, 16), (256, 2048, 40), (130, 1536, 16)])
+def test_w4_gemm(n, k, m):
+    """W4 configuration (self-oracle: the reference has no integer-W4 arithmetic). The first two shapes take the tensor-core kernel (the second
+    in three passes of 16 activation rows, the last one partly filled), the third the general CUDA-core kernel; same bars for both."""
     rng = np.random.default_rng(4)
-    n, k, m = 512, 1024, 16
     packed, sc = orc.w4_quantize(rng.normal(0, 0.02, (n, k)).astype(np.float32))
     xb = orc.bf16_bits(rng.normal(0, 1, (m, k)).astype(np.float32))
     rc, t, _ = api.w4_upload(packed, sc); assert rc == 0, api.last_error()
     rc, y16, y32 = api.w4_gemm_bf16(t, n, xb); assert rc == 0, api.last_error()
     ref = orc.w4_gemm(packed, sc, orc.bf16_to_f32(xb))
     assert np.max(np.abs(y32 - ref)) <= 1e-2 and rel_l2(y32, ref) < 1e-3
-    assert np.max(np.abs(orc.bf16_to_f32(y16) - ref)) <= 1e-2
-    rc, _, y5 = api.w4_gemm_bf16(t, n, xb[:5]); assert rc == 0 and np.array_equal(y5, y32[:5])
+    assert np.max(np.abs(orc.bf16_to_f32(y16) - ref)) <= 1e-2 and np.array_equal(y16, orc.bf16_bits(y32))
+    rc, _, y5 = api.w4_gemm_bf16(t, n, xb[:5]); assert rc == 0 and np.array_equal(y5, y32[:5])       # fewer rows: the same bits for those rows
+    rc, _, yb = api.w4_gemm_bf16(t, n, xb); assert rc == 0 and np.array_equal(yb.view(np.uint32), y32.view(np.uint32))   # again: the scratch and counters came back clean
     api.lib.omega_gpu_w4_free(t)
 
 
