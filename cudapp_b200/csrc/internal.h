@@ -143,6 +143,8 @@ struct LayerView {
 void layer_view(OmegaGpuMoeLayer *L, LayerView *v);
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src);
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens);
+cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s);
+void router_dims(const OmegaGpuMoeRouter *r, uint32_t *experts, uint32_t *hidden);
 float *layer_out32(OmegaGpuMoeLayer *L);
 uint16_t *layer_stage_x(OmegaGpuMoeLayer *L);
 }  // namespace b200

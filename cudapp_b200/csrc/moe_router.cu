@@ -79,6 +79,18 @@ __global__ void __launch_bounds__(256) router_rows_kernel(uint32_t hidden, uint3
     if (warp == 0) warp_topk(lg, experts, topk, norm, ids + (size_t)row * topk, wts + (size_t)row * topk);
 }
 
+// stream-ordered launch for callers inside the library (the layer stack): xn16 = bf16(RMSNorm(x) * norm weight), ids, weights
+cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s) {
+    const size_t smem = ((size_t)r->hidden + r->experts) * 4;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    router_rows_kernel<<<rows, 256, smem, s>>>(r->hidden, r->experts, topk, norm_topk, eps, 1.0f, x, r->hidden, r->norm_w, r->gate, nullptr, xn16, nullptr, ids, wts);
+    return cudaGetLastError();
+}
+void router_dims(const OmegaGpuMoeRouter *r, uint32_t *experts, uint32_t *hidden) { *experts = r->experts; *hidden = r->hidden; }
+
 }  // namespace b200
 using namespace b200;
 

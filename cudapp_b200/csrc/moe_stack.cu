@@ -116,6 +116,8 @@ using namespace b200;
 
 struct OmegaGpuMoeStack {
     std::vector<OmegaGpuMoeLayer *> layers;
+    std::vector<OmegaGpuMoeRouter *> routers;   // per layer, or null: when every layer has one the stack computes its own routing and takes no logits
+    bool router_mode;
     float eps;
     uint32_t experts, hidden, max_tokens;
     float *h; uint16_t *xn, *logits, *x, *out16;      // device
@@ -136,6 +138,56 @@ namespace b200 {
 static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s) {
     const uint32_t H = S->hidden, E = S->experts, Ln = (uint32_t)S->layers.size();
     uint32_t n = 0;
+    if (S->fused && S->router_mode) {
+        // Router inside the stack (the reference's per-layer order, src/omega_gpu_decode_graph.c:341-351): residual (+ combine of the layer
+        // before) -> router (RMSNorm with the layer's norm weight, gate GEMV, top-k) -> plan -> quantise the normalised rows into the plan's
+        // sorted order -> experts. Five launches per layer instead of two; no logits input.
+        const uint32_t K = S->topk, Px = S->x_pieces, R = tokens * K;
+        LayerView v0; layer_view(S->layers[0], &v0);
+        const size_t pstride = (size_t)S->row_cap * H;
+        auto launch_res = [&](const uint16_t *x16, const float *w, const float *dn, uint16_t *h16) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(tokens); cfg.blockDim = dim3(256); cfg.stream = s;
+            return cudaLaunchKernelEx(&cfg, combine_norm_scatter_kernel, H, K, S->eps, x16, w, dn, S->h, (const uint32_t *)nullptr, Px, pstride, (uint8_t *)nullptr, S->sx, h16, S->sched,
+                                      (uint32_t)S->tile_stride + 1u, (const float *)S->norm_w);
+        };
+        for (uint32_t l = 0; l < Ln; l++) {
+            LayerView v; layer_view(S->layers[l], &v);
+            LayerView vp; if (l) layer_view(S->layers[l - 1], &vp);
+            uint32_t *ids = S->ids_all + (size_t)l * R; float *wts = S->wts_all + (size_t)l * R;
+            if (!cuda_ok(launch_res(l ? nullptr : x, l ? S->wts_all + (size_t)(l - 1) * R : nullptr, l ? vp.dn : nullptr, nullptr), "residual launch")) return false; n++;
+            if (!cuda_ok(launch_router_rows(S->routers[l], tokens, S->h, S->eps, (int)v0.norm_topk, K, S->xn, ids, wts, s), "router launch")) return false; n++;
+            uint32_t *hdr = S->pb.header + (size_t)l * 8;
+            OmegaGpuMoePlanOut o = {};
+            o.counts_va = (uint64_t)(uintptr_t)(S->pb.counts + (size_t)l * E); o.starts_va = (uint64_t)(uintptr_t)(S->pb.starts + (size_t)l * E);
+            o.xmap_va = (uint64_t)(uintptr_t)(S->pb.xmap + (size_t)l * S->map_stride); o.ymap_va = (uint64_t)(uintptr_t)(S->pb.ymap + (size_t)l * S->map_stride);
+            o.header_va = (uint64_t)(uintptr_t)hdr; o.tiles_va = (uint64_t)(uintptr_t)(S->pb.tiles + (size_t)l * S->tile_stride);
+            if (!cuda_ok(launch_plan(tokens, K, E, K, S->tile_rows, ids, o, s), "plan launch")) return false; n++;
+            if (!cuda_ok(launch_act_quant(R, H, Px, S->xn, 1, S->pb.xmap + (size_t)l * S->map_stride, hdr, S->qx, S->sx, s, 0, S->row_cap), "x quant launch")) return false; n++;
+            if (S->prof) cudaEventRecord(S->prof[2 * l], s);
+            if (S->one_launch) {
+                FfnLaunch f = {};
+                f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = S->sx; f.qa = v.qa; f.sa = v.sa; f.tiles = S->pb.tiles + (size_t)l * S->tile_stride; f.header = hdr;
+                f.ymap = S->pb.ymap + (size_t)l * S->map_stride; f.out = v.dn; f.hidden = H; f.inter = v.inter; f.q_rows = S->row_cap; f.sched = S->sched; f.err = hdr + 4;
+                if (!cuda_ok(launch_ffn(v.tm_gu, S->tm_qx, v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, false), "expert ffn launch")) return false; n++;
+            } else {
+                MmaLaunch g = {};
+                g.wscale = v.gu_scale; g.ascale = S->sx; g.tiles = S->pb.tiles + (size_t)l * S->tile_stride; g.header = hdr; g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
+                g.n = 2 * v.inter; g.k = H; g.mode = 0; g.out_stride = v.inter; g.err = hdr + 4;
+                if (!cuda_ok(launch_mma_grouped(v.tm_gu, S->tm_qx, Px, g, s, false), "gate|up mma launch")) return false; n++;
+                MmaLaunch d = {};
+                d.wscale = v.dn_scale; d.ascale = v.sa; d.tiles = g.tiles; d.header = hdr; d.ymap = S->pb.ymap + (size_t)l * S->map_stride; d.out = v.dn; d.q_rows = S->row_cap;
+                d.n = H; d.k = v.inter; d.mode = 1; d.out_stride = H; d.err = g.err;
+                if (!cuda_ok(launch_mma_grouped(v.tm_dn, v.tm_qa, v.act_pieces, d, s, false), "down mma launch")) return false; n++;
+            }
+            if (S->prof) cudaEventRecord(S->prof[2 * l + 1], s);
+        }
+        LayerView vl; layer_view(S->layers[Ln - 1], &vl);
+        if (!cuda_ok(launch_res(nullptr, S->wts_all + (size_t)(Ln - 1) * R, vl.dn, out16), "combine launch")) return false; n++;
+        if (out32 && !cuda_ok(cudaMemcpyAsync(out32, S->h, (size_t)tokens * H * 4, cudaMemcpyDeviceToDevice, s), "copy h")) return false;
+        S->launches = n;
+        return cuda_ok(cudaGetLastError(), "stack launch");
+    }
     if (S->fused) {
         const uint32_t K = S->topk, Px = S->x_pieces;
         LayerView v0; layer_view(S->layers[0], &v0);
@@ -227,6 +279,22 @@ int omega_gpu_residual_norm_async(uint32_t tokens, uint32_t hidden, float eps, u
     return omega_gpu_residual_norm_w_async(tokens, hidden, eps, x16_va, m_va, h_va, xn_va, h16_va, 0, stream);
 }
 
+int omega_gpu_moe_stack_set_router(OmegaGpuMoeStack *S, uint32_t layer, OmegaGpuMoeRouter *router) {
+    if (!S || layer >= S->layers.size()) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (router) {
+        uint32_t e = 0, h = 0; router_dims(router, &e, &h);
+        if (e != S->experts || h != S->hidden) { set_error("moe stack: router of layer %u is %u experts x %u, the stack %u x %u", layer, e, h, S->experts, S->hidden); return OMEGA_GPU_FP8_BAD_ARGS; }
+        if (!S->fused) { set_error("moe stack: the router runs inside the stack on the tensor-core engine only"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    }
+    Lock l;
+    S->routers[layer] = router;
+    bool all = true;
+    for (auto *r : S->routers) all = all && r != nullptr;
+    S->router_mode = all;
+    if (S->graph) { cudaGraphExecDestroy(S->graph); S->graph = nullptr; }   // another sequence of launches: capture again at the next step
+    return OMEGA_GPU_FP8_OK;
+}
+
 int omega_gpu_moe_stack_set_norm(OmegaGpuMoeStack *S, uint32_t layer, const float *norm_w) {
     if (!S || !norm_w || layer >= S->layers.size()) return OMEGA_GPU_FP8_BAD_ARGS;
     for (uint32_t i = 0; i < S->hidden; i++) if (!(norm_w[i] == norm_w[i]) || norm_w[i] - norm_w[i] != 0.0f) { set_error("moe stack: norm weight %u of layer %u is not finite", i, layer); return OMEGA_GPU_FP8_BAD_ARGS; }
@@ -243,7 +311,7 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     OmegaGpuMoeStack *S = new OmegaGpuMoeStack();
-    S->eps = eps; S->graph = nullptr; S->graph_tokens = 0; S->launches = 0; S->prof = nullptr;
+    S->eps = eps; S->graph = nullptr; S->graph_tokens = 0; S->launches = 0; S->prof = nullptr; S->router_mode = false; S->routers.assign(layers, nullptr);
     layer_dims(layer[0], &S->experts, &S->hidden, &S->max_tokens);
     for (uint32_t i = 0; i < layers; i++) {
         uint32_t e, h, mt; layer_dims(layer[i], &e, &h, &mt);
@@ -309,7 +377,7 @@ void omega_gpu_moe_stack_free(OmegaGpuMoeStack *S) {
 uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *S) { return S ? S->launches : 0; }
 
 int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *S, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint32_t cap, float *expert_ms, uint32_t *count, uint32_t *launches_per_layer) {
-    if (!S || !tokens || !logits_va || !x_va || !expert_ms || !count || !cap) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!S || !tokens || (!logits_va && !S->router_mode) || !x_va || !expert_ms || !count || !cap) return OMEGA_GPU_FP8_BAD_ARGS;
     if (tokens > S->max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
     if (!S->fused) { set_error("moe stack profile: only the tensor-core path records per-layer times"); return OMEGA_GPU_FP8_BAD_ARGS; }
     Lock l;
@@ -330,7 +398,7 @@ int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *S, uint32_t tokens, uint64_t l
 }
 
 int omega_gpu_moe_stack_async(OmegaGpuMoeStack *S, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va, uint64_t out_bf16_va, void *stream) {
-    if (!S || !tokens || !logits_va || !x_va || (!out_f32_va && !out_bf16_va)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!S || !tokens || (!logits_va && !S->router_mode) || !x_va || (!out_f32_va && !out_bf16_va)) return OMEGA_GPU_FP8_BAD_ARGS;
     if (tokens > S->max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
     Lock l;
     if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
@@ -339,13 +407,13 @@ int omega_gpu_moe_stack_async(OmegaGpuMoeStack *S, uint32_t tokens, uint64_t log
 }
 
 int omega_gpu_moe_stack_bf16(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *logits, const uint16_t *x, uint16_t *out_bf16, float *out_f32) {
-    if (!S || !tokens || !logits || !x || (!out_bf16 && !out_f32)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!S || !tokens || (!logits && !S->router_mode) || !x || (!out_bf16 && !out_f32)) return OMEGA_GPU_FP8_BAD_ARGS;
     if (tokens > S->max_tokens) return OMEGA_GPU_FP8_TOO_LARGE;
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     cudaStream_t s = st().stream;
     const size_t xb = (size_t)tokens * S->hidden * 2, lb = S->layers.size() * (size_t)tokens * S->experts * 2;
-    bool ok = cuda_ok(cudaMemcpyAsync(S->logits, logits, lb, cudaMemcpyHostToDevice, s), "copy logits") &&
+    bool ok = (S->router_mode || cuda_ok(cudaMemcpyAsync(S->logits, logits, lb, cudaMemcpyHostToDevice, s), "copy logits")) &&
               cuda_ok(cudaMemcpyAsync(S->x, x, xb, cudaMemcpyHostToDevice, s), "copy x") &&
               stack_run(S, tokens, S->logits, S->x, nullptr, S->out16, s);
     if (ok && out_bf16) ok = cuda_ok(cudaMemcpyAsync(out_bf16, S->out16, xb, cudaMemcpyDeviceToHost, s), "copy out");

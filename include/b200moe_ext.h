@@ -111,6 +111,7 @@ uint32_t omega_gpu_moe_layer_launches(const OmegaGpuMoeLayer *l);
  * tests/gpu_decode_graph_test.c:56-60), h = h + MoE_l(xn, logits_l). Router logits are inputs (one [tokens][E] block per
  * layer). Layers of one stack share one scratch workspace and run as one CUDA graph per token count. */
 typedef struct OmegaGpuMoeStack OmegaGpuMoeStack;
+typedef struct OmegaGpuMoeRouter OmegaGpuMoeRouter;   /* the router front half, further down */
 int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, float eps, OmegaGpuMoeStack **out);
 void omega_gpu_moe_stack_free(OmegaGpuMoeStack *s);
 /* host buffers: logits bf16 [layers][tokens][E], x bf16 [tokens][H] -> out bf16 [tokens][H] (final h), out_f32 optional */
@@ -124,6 +125,13 @@ uint32_t omega_gpu_moe_stack_launches(const OmegaGpuMoeStack *s);
  * reference's RES COMBINE|NORM with the layer's norm weight (src/omega_blackwell_codegen_dec.c:261-286; host form
  * tests/gpu_decode_graph_test.c:56-60). Every layer starts with unit weights. Takes effect at the next step. */
 int omega_gpu_moe_stack_set_norm(OmegaGpuMoeStack *s, uint32_t layer, const float *norm_w);
+/* Router inside the stack, the reference's own per-layer order (src/omega_gpu_decode_graph.c:341-351: router -> experts -> RES COMBINE|NORM).
+ * Once EVERY layer has a router (omega_gpu_moe_router_create: the layer's gate matrix and the norm weight of its input), the stack takes no
+ * logits (pass NULL / 0): per layer it adds the combine of the layer before to the residual stream, runs the router on it (RMSNorm with
+ * the router's norm weight -> bf16 xn, logits, top-k), plans, quantises xn into the plan's sorted rows and runs the experts. The routers
+ * stay owned by the caller and must outlive the stack; router NULL takes a layer's router away again (the stack then wants logits).
+ * Tensor-core engine only. Weights set with omega_gpu_moe_stack_set_norm are not used in this mode (the router carries the norm weight). */
+int omega_gpu_moe_stack_set_router(OmegaGpuMoeStack *s, uint32_t layer, OmegaGpuMoeRouter *router);
 /* One step launched without the graph, a CUDA event before and after each layer's expert kernel(s): expert_ms[l] = device
  * time of layer l's gate|up + down work (one launch when *launches_per_layer is 1). Tensor-core path only. For measurement. */
 int omega_gpu_moe_stack_profile(OmegaGpuMoeStack *s, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint32_t cap, float *expert_ms,
@@ -189,7 +197,6 @@ uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *s);   /* device addre
  * src/omega_blackwell_codegen_router.h:15-33) for any number of rows in one launch. The reference's group tables (directory
  * entries of the selected experts) are not produced: this library's routing plan reads the ids themselves.
  * gate_bf16: [experts][hidden] bf16 bits (the checkpoint's mlp.gate.weight), norm_w: f32 [hidden]; both are copied. */
-typedef struct OmegaGpuMoeRouter OmegaGpuMoeRouter;
 int omega_gpu_moe_router_create(uint32_t experts, uint32_t hidden, const uint16_t *gate_bf16, const float *norm_w, OmegaGpuMoeRouter **out);
 void omega_gpu_moe_router_free(OmegaGpuMoeRouter *r);
 /* device buffers, stream-ordered. x_va: f32 rows, x_stride_bytes apart (0 = dense; a multiple of 16). Outputs: xn_va f32

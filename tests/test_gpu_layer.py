@@ -244,3 +244,53 @@ def test_router_then_layer_routed():
     assert np.max(np.abs(o32 - ref)) <= 1e-2 and rel_l2(o32, ref) <= 1e-3, (float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref))
     api.lib.omega_gpu_moe_router_free(r)
     free_layer(m)
+
+
+def test_stack_with_router_inside():
+    """The stack computes its own routing: per layer residual (+ combine of the layer before) -> router (RMSNorm with the layer's norm weight,
+    bf16 gate GEMV, top-k) -> plan -> experts, the reference's order (src/omega_gpu_decode_graph.c:341-351); no logits input. The checker follows
+    layer by layer with its double-precision router; where a token's margin between the last selected and the first unselected logit is
+    below 1e-4 the selection may legitimately differ (the reference router test's own rule, tests/gpu_router_test.c:95-111), so such a token is
+    left out of the comparison from that layer on."""
+    rng = np.random.default_rng(77)
+    E, H, I, topk, T, Ln = 16, 512, 256, 4, 24, 3
+    ms = [build_layer(rng, E, H, I, 32, api.ENGINE_MMA, topk) for _ in range(Ln)]
+    rc, stack = api.moe_stack_create([m["layer"] for m in ms], 1e-6); assert rc == 0, api.last_error()
+    gates = [orc.bf16_bits(rng.uniform(-0.05, 0.05, (E, H)).astype(np.float32)) for _ in range(Ln)]
+    nws = [rng.uniform(0.8, 1.2, H).astype(np.float32) for _ in range(Ln)]
+    routers = []
+    for l in range(Ln):
+        rc, r = api.moe_router_create(gates[l], nws[l]); assert rc == 0, api.last_error()
+        routers.append(r)
+    xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    o16 = np.empty((T, H), np.uint16); o32 = np.empty((T, H), np.float32)
+    run = lambda: api.lib.omega_gpu_moe_stack_bf16(stack, C.c_uint32(T), None, xb.ctypes.data_as(C.c_void_p), o16.ctypes.data_as(C.c_void_p), o32.ctypes.data_as(C.c_void_p))
+    assert run() == api.BAD_ARGS                                           # no routers yet: the stack wants logits
+    for l in range(Ln - 1):
+        assert api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(l), routers[l]) == 0, api.last_error()
+    assert run() == api.BAD_ARGS                                           # one layer still without a router
+    assert api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(Ln - 1), routers[Ln - 1]) == 0, api.last_error()
+    assert api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(Ln), routers[0]) == api.BAD_ARGS
+    assert run() == 0, api.last_error()
+    h = orc.bf16_to_f32(xb)
+    keep = np.ones(T, bool)
+    for l in range(Ln):
+        xn64, lg, ids, w, margin = orc.router(h, nws[l], gates[l], 1e-6, topk, True)
+        keep &= margin >= 1e-4
+        xn = orc.bf16_bits(orc.rmsnorm(h, 1e-6, nws[l]))
+        mo, _, _ = orc.moe_layer(None, xn, ms[l]["wgu"], ms[l]["sgu"], ms[l]["wdn"], ms[l]["sdn"], topk, routing=(ids, w.astype(np.float32)))
+        h = h + mo
+    assert keep.sum() >= T - 3
+    assert np.max(np.abs(o32[keep] - h[keep])) <= 1e-2 and rel_l2(o32[keep], h[keep]) <= 1e-3, (float(np.max(np.abs(o32[keep] - h[keep]))), rel_l2(o32[keep], h[keep]))
+    assert np.array_equal(o16, orc.bf16_bits(o32))
+    first = o32.copy()
+    assert run() == 0 and np.array_equal(first.view(np.uint32), o32.view(np.uint32))       # graph replay: identical bits
+    assert api.lib.omega_gpu_moe_stack_launches(stack) == 5 * Ln + 1
+    # taking a router away puts the stack back on given logits
+    assert api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(0), None) == 0
+    assert run() == api.BAD_ARGS
+    api.lib.omega_gpu_moe_stack_free(stack)
+    for r in routers:
+        api.lib.omega_gpu_moe_router_free(r)
+    for m in ms:
+        free_layer(m)
