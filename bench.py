@@ -331,6 +331,37 @@ def run_ours(args, rank, world):
                          "f32_all_cores": cpu_f32},
         "clocks": clocks.summary(),
     }
+    # the same step with the router inside the stack (no logits input: per layer RMSNorm + gate GEMV + top-k + plan on the device), beside the headline
+    try:
+        routers = []
+        for l in range(Ln):
+            gate = api.bf16_bits(np.random.default_rng(1000 + l).uniform(-0.05, 0.05, (E, H)).astype(np.float32))
+            rc, r = api.moe_router_create(gate, np.ones(H, np.float32)); assert rc == 0, api.last_error()
+            routers.append(r)
+            assert api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(l), r) == 0, api.last_error()
+
+        def step_router():
+            rc = api.lib.omega_gpu_moe_stack_async(stack, C.c_uint32(T), C.c_uint64(0), C.c_uint64(x_d.data_ptr()), C.c_uint64(out32_d.data_ptr()), C.c_uint64(out16_d.data_ptr()), C.c_void_p(stream.cuda_stream))
+            assert rc == 0, api.last_error()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                step_router()
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record(stream)
+            for _ in range(10):
+                step_router()
+            r1.record(stream)
+            torch.cuda.synchronize()
+        assert torch.isfinite(out32_d).all()
+        out["router_inside"] = {"ms_per_step": r0.elapsed_time(r1) / 10, "tokens_per_s": T / (r0.elapsed_time(r1) / 10 * 1e-3), "launches_per_step": int(api.lib.omega_gpu_moe_stack_launches(stack)),
+                                "what": "the same 48-layer step with RMSNorm + router gate GEMV + top-k + routing plan computed per layer inside the stack (no logits input)"}
+        for l in range(Ln):
+            api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(l), None)
+        for r in routers:
+            api.lib.omega_gpu_moe_router_free(r)
+    except Exception as e:
+        out["router_inside"] = {"error": "%s: %s" % (type(e).__name__, e)}
     api.lib.omega_gpu_moe_stack_free(stack)
     if not args.skip_prefill and not args.skip_cpu:
         # the prefill configuration beside the headline: one layer, 4096 tokens, compute-bound grouped GEMMs against the FP8 tensor peak
