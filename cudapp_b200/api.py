@@ -37,7 +37,7 @@ class Fp8GemmInfo(C.Structure):
 
 class MoeConfig(C.Structure):
     _fields_ = [("topk", C.c_uint32), ("max_tokens", C.c_uint32), ("engine", C.c_uint32), ("x_pieces", C.c_uint32), ("act_pieces", C.c_uint32),
-                ("norm_topk", C.c_uint32), ("first_expert", C.c_uint32), ("local_experts", C.c_uint32), ("tile_rows", C.c_uint32)]
+                ("norm_topk", C.c_uint32), ("first_expert", C.c_uint32), ("local_experts", C.c_uint32), ("tile_rows", C.c_uint32), ("shared_expert", C.c_uint32)]
 
 
 class MoePlanOut(C.Structure):
@@ -216,8 +216,8 @@ def w4_gemm_bf16(t, n, x_bf16):
 
 
 # ---------------------------------------------------------------- layer and stack
-def moe_layer_create(gate_up, down, topk=8, max_tokens=256, engine=ENGINE_AUTO, x_pieces=0, act_pieces=0, norm_topk=True, tile_rows=0):
-    cfg = MoeConfig(topk, max_tokens, engine, x_pieces, act_pieces, 1 if norm_topk else 0, 0, 0, tile_rows)
+def moe_layer_create(gate_up, down, topk=8, max_tokens=256, engine=ENGINE_AUTO, x_pieces=0, act_pieces=0, norm_topk=True, tile_rows=0, shared_expert=False):
+    cfg = MoeConfig(topk, max_tokens, engine, x_pieces, act_pieces, 1 if norm_topk else 0, 0, 0, tile_rows, 1 if shared_expert else 0)
     h = VP()
     rc = lib.omega_gpu_moe_layer_create(gate_up, down, C.byref(cfg), C.byref(h))
     return rc, (h if rc == 0 else None)

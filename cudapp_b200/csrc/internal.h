@@ -82,7 +82,8 @@ struct GemvArgs {
 cudaError_t launch_gemv_grouped(const GemvArgs &a, uint32_t cta_budget, uint32_t *grid_x, uint32_t *warps, cudaStream_t s);
 cudaError_t launch_gemm_rows(const GemvArgs &a, uint32_t *grid_x, uint32_t *mt, cudaStream_t s);
 
-cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s);
+// slots: entries per token in ids / wts (0 = topk); topk + 1 appends the shared expert (id = experts, weight 1)
+cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s, uint32_t slots = 0);
 // scratch (optional, zero-filled once, plan_scratch_words(picks, experts) u32): lets a plan of 4096 picks or more run as three launches over many SMs
 cudaError_t launch_plan(uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
                         const OmegaGpuMoePlanOut &o, cudaStream_t s, uint32_t *scratch = nullptr, size_t scratch_words = 0);
@@ -136,14 +137,15 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
 bool layer_forward_routed(OmegaGpuMoeLayer *L, uint32_t rows, const uint32_t *ids, const void *x, size_t x_stride_bytes, float *dn, cudaStream_t s);
 // what the stack needs from a layer to drive the tensor-core kernels itself
 struct LayerView {
-    uint32_t engine, topk, experts, hidden, inter, x_pieces, act_pieces, tile_rows, max_tokens, row_cap, norm_topk;
+    uint32_t engine, topk, experts, hidden, inter, x_pieces, act_pieces, tile_rows, max_tokens, row_cap, norm_topk;   // topk = slots per token, experts = what the tensors hold
+    uint32_t shared;   // 1: the last expert is the shared one, slot topk - 1 of every token
     const float *gu_scale, *dn_scale; const void *tm_gu, *tm_dn, *tm_qa;
     uint8_t *qa; float *sa, *dn;
 };
 void layer_view(OmegaGpuMoeLayer *L, LayerView *v);
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src);
 void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, uint32_t *max_tokens);
-cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s);
+cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s, uint32_t slots = 0);
 void router_dims(const OmegaGpuMoeRouter *r, uint32_t *experts, uint32_t *hidden);
 float *layer_out32(OmegaGpuMoeLayer *L);
 uint16_t *layer_stage_x(OmegaGpuMoeLayer *L);

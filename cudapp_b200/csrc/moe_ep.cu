@@ -451,6 +451,7 @@ int omega_gpu_moe_epstack_create(uint32_t world, uint32_t rank, uint32_t layers,
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     LayerView v0; layer_view(local[0], &v0);
+    if (v0.shared) { set_error("ep stack: layers with a shared expert are not sharded by this stack"); return OMEGA_GPU_FP8_BAD_ARGS; }
     if (v0.engine != OMEGA_GPU_MOE_ENGINE_MMA || v0.experts != experts / world || v0.max_tokens < tokens || v0.topk > 32) { set_error("ep stack: local layers must run the tensor-core engine over experts/world experts with max_tokens >= tokens"); return OMEGA_GPU_FP8_BAD_ARGS; }
     OmegaGpuMoeEpStack *S = new OmegaGpuMoeEpStack();
     S->world = world; S->rank = rank; S->layers = layers; S->topk = v0.topk; S->experts = experts; S->experts_local = experts / world; S->hidden = v0.hidden;

@@ -67,7 +67,8 @@ static void workspace_release(Workspace *w) {
 struct OmegaGpuMoeLayer {
     const OmegaGpuFp8Tensor *gu, *dn;
     OmegaGpuMoeConfig cfg;
-    uint32_t experts, hidden, inter;
+    uint32_t experts, hidden, inter;   // experts: what the tensors hold (the shared expert included)
+    uint32_t shared, routed_topk;      // shared 1: cfg.topk counts the slots (routed_topk + 1) and the router chooses among experts - 1
     uint64_t *dir_gu, *dir_dn;   // device {w_va, s_va} per expert
     b200::Workspace *ws;
     uint32_t launches, marks;    // kernels of the last forward; profile marks of the last forward (a mark may cover several launches)
@@ -94,7 +95,7 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
             !cuda_ok(cudaMemcpyAsync(w->wts, wts_in, (size_t)R * 4, cudaMemcpyDeviceToDevice, s), "copy weights")) return false;
         MARK("routing_copy");
     } else {
-        if (!cuda_ok(launch_topk(tokens, E, K, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s), "topk launch")) return false;
+        if (!cuda_ok(launch_topk(tokens, E - L->shared, L->routed_topk, (int)L->cfg.norm_topk, logits, w->ids, w->wts, s, K), "topk launch")) return false;
         MARK("topk");
     }
     OmegaGpuMoePlanOut o = {};
@@ -206,7 +207,7 @@ static bool layer_build_maps(OmegaGpuMoeLayer *L) {
 // dst drops its own workspace and uses src's (same shape, at least as many tokens); calls on them must then be stream-ordered
 bool layer_share_workspace(OmegaGpuMoeLayer *dst, OmegaGpuMoeLayer *src) {
     if (dst->ws == src->ws) return true;
-    if (dst->experts != src->experts || dst->hidden != src->hidden || dst->inter != src->inter || dst->cfg.topk != src->cfg.topk ||
+    if (dst->experts != src->experts || dst->hidden != src->hidden || dst->inter != src->inter || dst->cfg.topk != src->cfg.topk || dst->shared != src->shared ||
         dst->cfg.max_tokens > src->cfg.max_tokens) return false;
     workspace_release(dst->ws);
     dst->ws = src->ws; src->ws->refs++;
@@ -216,7 +217,7 @@ void layer_dims(const OmegaGpuMoeLayer *L, uint32_t *experts, uint32_t *hidden, 
 void layer_view(OmegaGpuMoeLayer *L, LayerView *v) {
     v->engine = L->cfg.engine; v->topk = L->cfg.topk; v->experts = L->experts; v->hidden = L->hidden; v->inter = L->inter;
     v->x_pieces = L->cfg.x_pieces; v->act_pieces = L->cfg.act_pieces; v->tile_rows = L->tile_rows; v->max_tokens = L->ws->max_tokens;
-    v->row_cap = L->ws->max_tokens * L->ws->topk + 8; v->norm_topk = L->cfg.norm_topk;
+    v->row_cap = L->ws->max_tokens * L->ws->topk + 8; v->norm_topk = L->cfg.norm_topk; v->shared = L->shared;
     v->gu_scale = L->gu->s; v->dn_scale = L->dn->s; v->tm_gu = L->tm_gu; v->tm_dn = L->tm_dn; v->tm_qa = L->tm_qa;
     v->qa = L->ws->qa; v->sa = L->ws->sa; v->dn = L->ws->dn;
 }
@@ -232,13 +233,15 @@ int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuF
     if (out) *out = nullptr;
     if (!gate_up || !down || !cfg || !out) return OMEGA_GPU_FP8_BAD_ARGS;
     if (gate_up->experts != down->experts || gate_up->n != 2 * down->k || gate_up->k != down->n) { set_error("moe layer: gate|up [E][2I][H] and down [E][H][I] do not match"); return OMEGA_GPU_FP8_BAD_ARGS; }
-    if (cfg->topk == 0 || cfg->topk > 32 || cfg->topk > gate_up->experts || cfg->max_tokens == 0 || gate_up->experts > 1024) return OMEGA_GPU_FP8_BAD_ARGS;
-    if ((uint64_t)cfg->max_tokens * cfg->topk > (1u << 24)) return OMEGA_GPU_FP8_TOO_LARGE;
+    if (cfg->topk == 0 || cfg->topk > 31 || cfg->topk > gate_up->experts || cfg->max_tokens == 0 || gate_up->experts > 1024 || cfg->shared_expert > 1) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (cfg->shared_expert && (gate_up->experts < 2 || cfg->topk > gate_up->experts - 1)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if ((uint64_t)cfg->max_tokens * (cfg->topk + cfg->shared_expert) > (1u << 24)) return OMEGA_GPU_FP8_TOO_LARGE;
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     OmegaGpuMoeLayer *L = (OmegaGpuMoeLayer *)calloc(1, sizeof *L);
     if (!L) return OMEGA_GPU_FP8_BAD_ARGS;
     L->gu = gate_up; L->dn = down; L->cfg = *cfg; L->experts = gate_up->experts; L->hidden = gate_up->k; L->inter = down->k;
+    L->shared = cfg->shared_expert; L->routed_topk = cfg->topk; L->cfg.topk = cfg->topk + cfg->shared_expert;   // from here on topk = slots per token
     if (!L->cfg.x_pieces) L->cfg.x_pieces = 2;
     if (!L->cfg.act_pieces) L->cfg.act_pieces = 3;
     if (L->cfg.x_pieces > 4 || L->cfg.act_pieces > 4) { free(L); return OMEGA_GPU_FP8_BAD_ARGS; }
@@ -259,7 +262,7 @@ int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuF
     }
     bool ok = cuda_ok(cudaMalloc(&L->dir_gu, (size_t)E * 32), "cudaMalloc(directory)");
     if (ok) { L->dir_dn = L->dir_gu + 2 * E; ok = cuda_ok(cudaMemcpy(L->dir_gu, dir.data(), (size_t)E * 32, cudaMemcpyHostToDevice), "copy directory"); }
-    if (ok) { L->ws = workspace_create(cfg->max_tokens, cfg->topk, E, L->hidden, L->inter); ok = L->ws != nullptr; }
+    if (ok) { L->ws = workspace_create(cfg->max_tokens, L->cfg.topk, E, L->hidden, L->inter); ok = L->ws != nullptr; }
     if (ok) ok = layer_build_maps(L);
     if (!ok) { if (L->dir_gu) cudaFree(L->dir_gu); free(L); return OMEGA_GPU_FP8_CHIP_FAIL; }
     *out = L;
@@ -322,7 +325,7 @@ int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     Workspace *w = L->ws; cudaStream_t s = st().stream;
-    const size_t lb = (size_t)tokens * L->experts * 2, xb = (size_t)tokens * L->hidden * 2, rb = (size_t)tokens * L->cfg.topk * 4;
+    const size_t lb = (size_t)tokens * (L->experts - L->shared) * 2, xb = (size_t)tokens * L->hidden * 2, rb = (size_t)tokens * L->cfg.topk * 4;
     bool ok = cuda_ok(cudaMemcpyAsync(w->logits, logits, lb, cudaMemcpyHostToDevice, s), "copy logits") &&
               cuda_ok(cudaMemcpyAsync(w->x, x, xb, cudaMemcpyHostToDevice, s), "copy x") &&
               layer_forward(L, tokens, w->logits, w->x, w->out32, w->out16, s);

@@ -14,7 +14,9 @@
 namespace b200 {
 
 // ------------------------------------------------------------------ top-k: one warp per token
-__global__ void __launch_bounds__(256) topk_kernel(uint32_t tokens, uint32_t experts, uint32_t topk, int norm,
+// slots = entries per token in ids / wts: topk, or topk + 1 when a shared expert follows the routed picks (its id = experts, weight 1:
+// the reference's ninth group, src/omega_gpu_q36_graph.h:7-21; a caller with a shared-expert gate supplies the weight through the router)
+__global__ void __launch_bounds__(256) topk_kernel(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, uint32_t slots,
                                                    const uint16_t *__restrict__ logits, uint32_t *__restrict__ ids, float *__restrict__ wts) {
     extern __shared__ float sm[];
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -22,12 +24,13 @@ __global__ void __launch_bounds__(256) topk_kernel(uint32_t tokens, uint32_t exp
     float *l = sm + (size_t)warp * experts;
     for (uint32_t e = lane; e < experts; e += 32) l[e] = __uint_as_float((uint32_t)logits[(size_t)t * experts + e] << 16);
     __syncwarp();
-    warp_topk(l, experts, topk, norm, ids + (size_t)t * topk, wts + (size_t)t * topk);
+    warp_topk(l, experts, topk, norm, ids + (size_t)t * slots, wts + (size_t)t * slots);
+    if (slots > topk && lane == 0) { ids[(size_t)t * slots + topk] = experts; wts[(size_t)t * slots + topk] = 1.0f; }
 }
 
-cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s) {
+cudaError_t launch_topk(uint32_t tokens, uint32_t experts, uint32_t topk, int norm, const uint16_t *logits, uint32_t *ids, float *wts, cudaStream_t s, uint32_t slots) {
     const uint32_t warps = experts <= 512 ? 8u : 4u;
-    topk_kernel<<<(tokens + warps - 1) / warps, warps * 32, (size_t)warps * experts * 4, s>>>(tokens, experts, topk, norm, logits, ids, wts);
+    topk_kernel<<<(tokens + warps - 1) / warps, warps * 32, (size_t)warps * experts * 4, s>>>(tokens, experts, topk, norm, slots ? slots : topk, logits, ids, wts);
     return cudaGetLastError();
 }
 
@@ -366,26 +369,34 @@ uint32_t omega_moe_plan(uint64_t *result, const void *cfg_, uint64_t cfg_n, cons
     uint64_t *work = (uint64_t *)work_, *seg = (uint64_t *)seg_, *maps = (uint64_t *)maps_, *meta = (uint64_t *)meta_;
     const uint64_t T = c[1], S = c[2], E = c[3];
     if (c[0] != 1 || T > 128 || S > 8 || E == 0 || E > 256 || c[4] != E || c[5] > 1152 || c[6] > 257 || c[7] > 1160) { *result = 1; return OMEGA_OK; }
-    // the grouping itself runs on the GPU over the u32 picks; ids that do not fit 32 bits are invalid by definition
-    uint32_t id32[1024], counts[256], starts[256], xmap[1024 + 8], ymap[1024 + 8], hdr[8];
-    for (uint64_t i = 0; i < T * S; i++) { if (ids[i] > 0xffffffffull) { *result = 2; return OMEGA_OK; } id32[i] = (uint32_t)ids[i]; }
+    // The grouping runs on the GPU over u32 picks, the shared expert's rows included: every token gets one more pick, slot S, for expert E
+    // (the unit's shared id), so the device plan itself puts them last (E is the largest id) in token order with destination t * (S + 1) + S
+    // (om/moe/moe_plan.om:112-117). An id that does not fit 32 bits, or a routed pick at or past E that is not the "absent" mark, is invalid.
+    const uint64_t S1 = S + 1;
+    uint32_t id32[128 * 9], counts[257], starts[257], xmap[128 * 9 + 8], ymap[128 * 9 + 8], hdr[8];
+    for (uint64_t t = 0; t < T; t++) {
+        for (uint64_t sl = 0; sl < S; sl++) {
+            const uint64_t v = ids[t * S + sl];
+            if (v > 0xffffffffull || (v >= E && v != 0xffffffffull)) { *result = 2; return OMEGA_OK; }
+            id32[t * S1 + sl] = (uint32_t)v;
+        }
+        id32[t * S1 + S] = (uint32_t)E;
+    }
     {
         Lock l;
-        if (plan_staged((uint32_t)T, (uint32_t)S, (uint32_t)E, (uint32_t)S + 1, id32, counts, starts, xmap, ymap, hdr) != OMEGA_GPU_FP8_OK) return 14; /* trap: no device */
+        if (plan_staged((uint32_t)T, (uint32_t)S1, (uint32_t)E + 1u, (uint32_t)S1, id32, counts, starts, xmap, ymap, hdr) != OMEGA_GPU_FP8_OK) return 14; /* trap: no device */
     }
     if (hdr[3] != 0) { *result = 2; return OMEGA_OK; }
-    const uint64_t routed = hdr[0], nw = routed + T, ns = hdr[1] + (T ? 1 : 0);
+    const uint64_t nw = hdr[0], routed = nw - T, ns = hdr[1];
     if (nw > c[5] || ns > c[6] || nw + 8 > c[7]) { *result = 3; return OMEGA_OK; }
     uint64_t z = 0;
-    for (uint64_t e = 0; e < E; e++) if (counts[e]) {
-        seg[z * 4] = e; seg[z * 4 + 1] = starts[e]; seg[z * 4 + 2] = counts[e]; seg[z * 4 + 3] = 0; z++;
+    for (uint64_t e = 0; e <= E; e++) if (counts[e]) {
+        seg[z * 4] = e; seg[z * 4 + 1] = starts[e]; seg[z * 4 + 2] = counts[e]; seg[z * 4 + 3] = e == E ? 1 : 0; z++;
         for (uint64_t p = starts[e]; p < (uint64_t)starts[e] + counts[e]; p++) {
-            uint64_t *r = work + p * 9; const uint64_t t = xmap[p], s = ymap[p] - t * (S + 1);
-            r[0] = e; r[1] = t; r[2] = t; r[3] = s; r[4] = s; r[5] = starts[e]; r[6] = counts[e]; r[7] = ymap[p]; r[8] = s;
+            uint64_t *r = work + p * 9; const uint64_t t = xmap[p], sl = ymap[p] - t * S1;
+            r[0] = e; r[1] = t; r[2] = t; r[3] = sl; r[4] = sl; r[5] = starts[e]; r[6] = counts[e]; r[7] = ymap[p]; r[8] = sl;
         }
     }
-    if (T) { seg[z * 4] = E; seg[z * 4 + 1] = routed; seg[z * 4 + 2] = T; seg[z * 4 + 3] = 1; }
-    for (uint64_t t = 0; t < T; t++) { uint64_t *r = work + (routed + t) * 9; r[0] = E; r[1] = t; r[2] = t; r[3] = S; r[4] = S; r[5] = routed; r[6] = T; r[7] = t * (S + 1) + S; r[8] = S; }
     for (uint64_t p = 0; p < nw; p++) { maps[p] = work[p * 9 + 1]; maps[1160 + p] = work[p * 9 + 7]; }
     for (uint64_t p = 0; p < 8; p++) { maps[nw + p] = 0; maps[1160 + nw + p] = 0; }
     meta[0] = nw; meta[1] = ns; meta[2] = routed; meta[3] = T; meta[4] = 1; meta[5] = meta[6] = meta[7] = 0;

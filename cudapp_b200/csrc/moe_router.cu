@@ -15,6 +15,7 @@ struct OmegaGpuMoeRouter {
     uint32_t experts, hidden;
     uint16_t *gate;      // device [experts][hidden] bf16
     float *norm_w;       // device [hidden]
+    uint16_t *shared_gate;   // device [hidden] bf16 or null: the shared expert's gate vector (weight of the extra slot = sigmoid(gate . xn))
 };
 
 namespace b200 {
@@ -28,7 +29,8 @@ __device__ __forceinline__ uint32_t bf16_rne_bits(float f) {
 __global__ void __launch_bounds__(256) router_rows_kernel(uint32_t hidden, uint32_t experts, uint32_t topk, int norm, float eps, float out_scale,
                                                           const float *__restrict__ x, size_t x_stride, const float *__restrict__ norm_w,
                                                           const uint16_t *__restrict__ gate, float *__restrict__ xn_out, uint16_t *__restrict__ xn16_out,
-                                                          float *__restrict__ logits_out, uint32_t *__restrict__ ids, float *__restrict__ wts) {
+                                                          float *__restrict__ logits_out, uint32_t *__restrict__ ids, float *__restrict__ wts,
+                                                          uint32_t slots, const uint16_t *__restrict__ shared_gate) {
     extern __shared__ __align__(16) float sm[];
     float *xn = sm, *lg = sm + hidden;
     __shared__ double red[8];
@@ -76,17 +78,27 @@ __global__ void __launch_bounds__(256) router_rows_kernel(uint32_t hidden, uint3
     }
     __syncthreads();
     // ---- phase 3: selection and weights
-    if (warp == 0) warp_topk(lg, experts, topk, norm, ids + (size_t)row * topk, wts + (size_t)row * topk);
+    if (warp == 0) warp_topk(lg, experts, topk, norm, ids + (size_t)row * slots, wts + (size_t)row * slots);
+    // ---- the shared expert's slot (slots = topk + 1): id = experts; weight = sigmoid(shared gate . xn), the reference's ninth group
+    //      (src/omega_gpu_q36_graph.h:20), or 1 when the layer has no such gate
+    if (slots > topk && warp == 1) {
+        float acc = 0.0f;
+        if (shared_gate) {
+            for (uint32_t c = lane; c < hidden; c += 32u) acc = fmaf(__uint_as_float((uint32_t)shared_gate[c] << 16), xn[c], acc);
+            for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        }
+        if (lane == 0) { ids[(size_t)row * slots + topk] = experts; wts[(size_t)row * slots + topk] = shared_gate ? __fdiv_rn(1.0f, 1.0f + expf(-acc)) : 1.0f; }
+    }
 }
 
 // stream-ordered launch for callers inside the library (the layer stack): xn16 = bf16(RMSNorm(x) * norm weight), ids, weights
-cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s) {
+cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s, uint32_t slots) {
     const size_t smem = ((size_t)r->hidden + r->experts) * 4;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    router_rows_kernel<<<rows, 256, smem, s>>>(r->hidden, r->experts, topk, norm_topk, eps, 1.0f, x, r->hidden, r->norm_w, r->gate, nullptr, xn16, nullptr, ids, wts);
+    router_rows_kernel<<<rows, 256, smem, s>>>(r->hidden, r->experts, topk, norm_topk, eps, 1.0f, x, r->hidden, r->norm_w, r->gate, nullptr, xn16, nullptr, ids, wts, slots ? slots : topk, r->shared_gate);
     return cudaGetLastError();
 }
 void router_dims(const OmegaGpuMoeRouter *r, uint32_t *experts, uint32_t *hidden) { *experts = r->experts; *hidden = r->hidden; }
@@ -102,7 +114,7 @@ int omega_gpu_moe_router_create(uint32_t experts, uint32_t hidden, const uint16_
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     OmegaGpuMoeRouter *r = new OmegaGpuMoeRouter();
-    r->experts = experts; r->hidden = hidden; r->gate = nullptr; r->norm_w = nullptr;
+    r->experts = experts; r->hidden = hidden; r->gate = nullptr; r->norm_w = nullptr; r->shared_gate = nullptr;
     const size_t gb = (size_t)experts * hidden * 2, nb = (size_t)hidden * 4;
     const bool ok = cuda_ok(cudaMalloc(&r->gate, gb), "cudaMalloc(router gate)") && cuda_ok(cudaMalloc(&r->norm_w, nb), "cudaMalloc(router norm)") &&
                     cuda_ok(cudaMemcpy(r->gate, gate_bf16, gb, cudaMemcpyHostToDevice), "copy router gate") &&
@@ -117,7 +129,16 @@ void omega_gpu_moe_router_free(OmegaGpuMoeRouter *r) {
     Lock l;
     if (r->gate) cudaFree(r->gate);
     if (r->norm_w) cudaFree(r->norm_w);
+    if (r->shared_gate) cudaFree(r->shared_gate);
     delete r;
+}
+
+int omega_gpu_moe_router_set_shared_gate(OmegaGpuMoeRouter *r, const uint16_t *gate_bf16) {
+    if (!r || !gate_bf16) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    if (!r->shared_gate && !cuda_ok(cudaMalloc(&r->shared_gate, (size_t)r->hidden * 2), "cudaMalloc(shared gate)")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    return cuda_ok(cudaMemcpy(r->shared_gate, gate_bf16, (size_t)r->hidden * 2, cudaMemcpyHostToDevice), "copy shared gate") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
 int omega_gpu_moe_router_rows_async(OmegaGpuMoeRouter *r, uint32_t rows, uint64_t x_va, uint32_t x_stride_bytes, float eps, int norm_topk, float out_scale,
@@ -132,7 +153,7 @@ int omega_gpu_moe_router_rows_async(OmegaGpuMoeRouter *r, uint32_t rows, uint64_
     }
     router_rows_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>(r->hidden, r->experts, topk, norm_topk, eps, out_scale, (const float *)(uintptr_t)x_va, x_stride_bytes / 4u,
                                                                   r->norm_w, r->gate, (float *)(uintptr_t)xn_va, (uint16_t *)(uintptr_t)xn_bf16_va, (float *)(uintptr_t)logits_va,
-                                                                  (uint32_t *)(uintptr_t)ids_va, (float *)(uintptr_t)wts_va);
+                                                                  (uint32_t *)(uintptr_t)ids_va, (float *)(uintptr_t)wts_va, topk + (r->shared_gate ? 1u : 0u), r->shared_gate);
     return cuda_ok(cudaGetLastError(), "router launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
@@ -141,10 +162,10 @@ int omega_gpu_moe_router_f32(OmegaGpuMoeRouter *r, uint32_t rows, const float *x
     if (!r || !rows || !x || !ids || !wts || !topk || topk > 32 || topk > r->experts) return OMEGA_GPU_FP8_BAD_ARGS;
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
-    const size_t xb = (size_t)rows * r->hidden * 4, lb = (size_t)rows * r->experts * 4, kb = (size_t)rows * topk * 4;
+    const size_t xb = (size_t)rows * r->hidden * 4, lb = (size_t)rows * r->experts * 4, kb = (size_t)rows * (topk + (r->shared_gate ? 1u : 0u)) * 4;   // ids / wts rows: topk (+ 1 with a shared gate)
     float *dx = (float *)stage(0, xb), *dxn = (float *)stage(1, xb), *dl = (float *)stage(2, lb + 2 * kb);
     if (!dx || !dxn || !dl) return OMEGA_GPU_FP8_CHIP_FAIL;
-    uint32_t *di = (uint32_t *)(dl + (size_t)rows * r->experts); float *dw = (float *)(di + (size_t)rows * topk);
+    uint32_t *di = (uint32_t *)(dl + (size_t)rows * r->experts); float *dw = (float *)(di + kb / 4);
     cudaStream_t s = st().stream;
     bool ok = cuda_ok(cudaMemcpyAsync(dx, x, xb, cudaMemcpyHostToDevice, s), "copy x");
     if (ok) {

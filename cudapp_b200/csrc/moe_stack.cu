@@ -119,7 +119,7 @@ struct OmegaGpuMoeStack {
     std::vector<OmegaGpuMoeRouter *> routers;   // per layer, or null: when every layer has one the stack computes its own routing and takes no logits
     bool router_mode;
     float eps;
-    uint32_t experts, hidden, max_tokens;
+    uint32_t experts, hidden, max_tokens, shared;   // experts: what the tensors hold; shared 1: the last of them is the shared expert, logits cover experts - 1
     float *h; uint16_t *xn, *logits, *x, *out16;      // device
     float *norm_w;                                    // device [layers][hidden]: RMSNorm weight of each layer's input (ones until set)
     cudaGraphExec_t graph; uint32_t graph_tokens; cudaStream_t graph_stream;
@@ -156,7 +156,7 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
             LayerView vp; if (l) layer_view(S->layers[l - 1], &vp);
             uint32_t *ids = S->ids_all + (size_t)l * R; float *wts = S->wts_all + (size_t)l * R;
             if (!cuda_ok(launch_res(l ? nullptr : x, l ? S->wts_all + (size_t)(l - 1) * R : nullptr, l ? vp.dn : nullptr, nullptr), "residual launch")) return false; n++;
-            if (!cuda_ok(launch_router_rows(S->routers[l], tokens, S->h, S->eps, (int)v0.norm_topk, K, S->xn, ids, wts, s), "router launch")) return false; n++;
+            if (!cuda_ok(launch_router_rows(S->routers[l], tokens, S->h, S->eps, (int)v0.norm_topk, K - v0.shared, S->xn, ids, wts, s, K), "router launch")) return false; n++;
             uint32_t *hdr = S->pb.header + (size_t)l * 8;
             OmegaGpuMoePlanOut o = {};
             o.counts_va = (uint64_t)(uintptr_t)(S->pb.counts + (size_t)l * E); o.starts_va = (uint64_t)(uintptr_t)(S->pb.starts + (size_t)l * E);
@@ -191,7 +191,7 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
     if (S->fused) {
         const uint32_t K = S->topk, Px = S->x_pieces;
         LayerView v0; layer_view(S->layers[0], &v0);
-        if (!cuda_ok(launch_topk(Ln * tokens, E, K, (int)v0.norm_topk, logits, S->ids_all, S->wts_all, s), "topk launch")) return false; n++;
+        if (!cuda_ok(launch_topk(Ln * tokens, E - v0.shared, K - v0.shared, (int)v0.norm_topk, logits, S->ids_all, S->wts_all, s, K), "topk launch")) return false; n++;
         if (!cuda_ok(launch_plan_batch(Ln, tokens, K, E, K, S->tile_rows, S->ids_all, S->pb, s), "plan launch")) return false; n++;
         const size_t pstride = (size_t)S->row_cap * H;
         auto launch_cns = [&](const uint16_t *x16, const float *w, const float *dn, const uint32_t *pos, uint8_t *q, uint16_t *h16, const float *nw) {
@@ -236,7 +236,7 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
     for (uint32_t l = 0; l < Ln; l++) {
         OmegaGpuMoeLayer *L = S->layers[l];
         float *m = layer_out32(L);
-        if (!layer_forward(L, tokens, logits + (size_t)l * tokens * E, S->xn, m, nullptr, s)) return false;
+        if (!layer_forward(L, tokens, logits + (size_t)l * tokens * (E - S->shared), S->xn, m, nullptr, s)) return false;
         n += omega_gpu_moe_layer_launches(L);
         const bool last = l + 1 == Ln;
         residual_norm_kernel<<<tokens, 256, 0, s>>>(H, S->eps, nullptr, m, S->h, last ? nullptr : S->xn, last ? out16 : nullptr, S->norm_w + (size_t)(last ? 0 : l + 1) * H); n++;
@@ -283,7 +283,7 @@ int omega_gpu_moe_stack_set_router(OmegaGpuMoeStack *S, uint32_t layer, OmegaGpu
     if (!S || layer >= S->layers.size()) return OMEGA_GPU_FP8_BAD_ARGS;
     if (router) {
         uint32_t e = 0, h = 0; router_dims(router, &e, &h);
-        if (e != S->experts || h != S->hidden) { set_error("moe stack: router of layer %u is %u experts x %u, the stack %u x %u", layer, e, h, S->experts, S->hidden); return OMEGA_GPU_FP8_BAD_ARGS; }
+        if (e != S->experts - S->shared || h != S->hidden) { set_error("moe stack: router of layer %u is %u experts x %u, the stack routes over %u x %u", layer, e, h, S->experts - S->shared, S->hidden); return OMEGA_GPU_FP8_BAD_ARGS; }
         if (!S->fused) { set_error("moe stack: the router runs inside the stack on the tensor-core engine only"); return OMEGA_GPU_FP8_BAD_ARGS; }
     }
     Lock l;
@@ -313,6 +313,7 @@ int omega_gpu_moe_stack_create(uint32_t layers, OmegaGpuMoeLayer *const *layer, 
     OmegaGpuMoeStack *S = new OmegaGpuMoeStack();
     S->eps = eps; S->graph = nullptr; S->graph_tokens = 0; S->launches = 0; S->prof = nullptr; S->router_mode = false; S->routers.assign(layers, nullptr);
     layer_dims(layer[0], &S->experts, &S->hidden, &S->max_tokens);
+    { LayerView vs; layer_view(layer[0], &vs); S->shared = vs.shared; }
     for (uint32_t i = 0; i < layers; i++) {
         uint32_t e, h, mt; layer_dims(layer[i], &e, &h, &mt);
         if (e != S->experts || h != S->hidden || mt != S->max_tokens || !layer_share_workspace(layer[i], layer[0])) {
@@ -412,7 +413,7 @@ int omega_gpu_moe_stack_bf16(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     cudaStream_t s = st().stream;
-    const size_t xb = (size_t)tokens * S->hidden * 2, lb = S->layers.size() * (size_t)tokens * S->experts * 2;
+    const size_t xb = (size_t)tokens * S->hidden * 2, lb = S->layers.size() * (size_t)tokens * (S->experts - S->shared) * 2;
     bool ok = (S->router_mode || cuda_ok(cudaMemcpyAsync(S->logits, logits, lb, cudaMemcpyHostToDevice, s), "copy logits")) &&
               cuda_ok(cudaMemcpyAsync(S->x, x, xb, cudaMemcpyHostToDevice, s), "copy x") &&
               stack_run(S, tokens, S->logits, S->x, nullptr, S->out16, s);

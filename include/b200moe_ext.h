@@ -84,6 +84,11 @@ typedef struct {
     uint32_t first_expert, local_experts; /* expert-parallel shard held here; 0, 0 = all */
     uint32_t tile_rows;   /* tensor-core engine, rows per routed-row tile: 0 = chosen per call (128 once a call brings 64 rows per expert on average and
                              x_pieces = act_pieces = 1, else 32), 32 = always 32, 128 = always 128 (refused unless x_pieces = act_pieces = 1, k <= 2048) */
+    uint32_t shared_expert; /* 1: the two tensors hold one expert more than the router routes over, the LAST one being the shared expert every token
+                             goes through (the reference's ninth group: src/omega_gpu_q36_graph.h:7-21, :53-55, :87). A token then has topk + 1
+                             slots: logits are [tokens][experts - 1], ids / wts are [tokens][topk + 1], slot topk holds id experts - 1; its weight is 1
+                             from the logits entries, or what the caller / the router's shared gate supplies through the routed entry. The routing
+                             plan puts the shared rows in the last segment (om/moe/moe_plan.om:112-117) and the combine runs over topk + 1 slots. */
 } OmegaGpuMoeConfig;
 /* gate_up: [E][2I][H] (gate rows first), down: [E][H][I]; both stay owned by the caller and must outlive the layer */
 int omega_gpu_moe_layer_create(const OmegaGpuFp8Tensor *gate_up, const OmegaGpuFp8Tensor *down, const OmegaGpuMoeConfig *cfg,
@@ -199,6 +204,10 @@ uint64_t omega_gpu_moe_epstack_h(const OmegaGpuMoeEpStack *s);   /* device addre
  * gate_bf16: [experts][hidden] bf16 bits (the checkpoint's mlp.gate.weight), norm_w: f32 [hidden]; both are copied. */
 int omega_gpu_moe_router_create(uint32_t experts, uint32_t hidden, const uint16_t *gate_bf16, const float *norm_w, OmegaGpuMoeRouter **out);
 void omega_gpu_moe_router_free(OmegaGpuMoeRouter *r);
+/* The shared expert's gate vector, bf16 [hidden] (copied). Once set, every row gets one more slot after its topk routed ones: id = experts
+ * (the shared expert's index in a tensor of experts + 1), weight = sigmoid(gate . xn) (src/omega_gpu_q36_graph.h:20); ids_va / wts_va of the
+ * calls below are then [rows][topk + 1]. */
+int omega_gpu_moe_router_set_shared_gate(OmegaGpuMoeRouter *r, const uint16_t *gate_bf16);
 /* device buffers, stream-ordered. x_va: f32 rows, x_stride_bytes apart (0 = dense; a multiple of 16). Outputs: xn_va f32
  * [rows][hidden] = RMSNorm(x) * out_scale (0 = skip), xn_bf16_va bf16 [rows][hidden] = RMSNorm(x) rounded to nearest even (0 = skip;
  * the input rows of omega_gpu_moe_layer_async), logits_va f32 [rows][experts] (0 = skip), ids_va u32 [rows][topk], wts_va f32 [rows][topk]. */

@@ -294,3 +294,55 @@ def test_stack_with_router_inside():
         api.lib.omega_gpu_moe_router_free(r)
     for m in ms:
         free_layer(m)
+
+
+@pytest.mark.parametrize("engine", [api.ENGINE_FMA, api.ENGINE_MMA])
+def test_layer_with_shared_expert(engine):
+    """The reference's ninth group (src/omega_gpu_q36_graph.h:7-21, :53-55): tensors of experts + 1, the last one the shared expert that every
+    token goes through in one more slot after its routed picks; the plan puts those rows in the last segment and the combine runs over
+    topk + 1 slots in slot order. From logits the shared slot has weight 1."""
+    rng = np.random.default_rng(91)
+    Er, H, I, topk, T = 16, 512, 256, 4, 24
+    wgu, sgu = make_weights(rng, Er + 1, 2 * I, H); wdn, sdn = make_weights(rng, Er + 1, H, I)
+    rc, tgu = api.fp8_tensor_upload(Er + 1, 2 * I, H, wgu, sgu); assert rc == 0, api.last_error()
+    rc, tdn = api.fp8_tensor_upload(Er + 1, H, I, wdn, sdn); assert rc == 0, api.last_error()
+    rc, layer = api.moe_layer_create(tgu, tdn, topk=topk, max_tokens=32, engine=engine, shared_expert=True); assert rc == 0, api.last_error()
+    logits = orc.bf16_bits(rng.normal(0, 1, (T, Er)).astype(np.float32)); xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    rc, o16, o32, ids, w = api.moe_layer_bf16(layer, logits, xb, topk + 1); assert rc == 0, api.last_error()
+    rid, rw = orc.topk(orc.bf16_to_f32(logits), topk, True)
+    assert np.array_equal(ids[:, :topk], rid) and np.all(ids[:, topk] == Er) and np.all(w[:, topk] == 1.0) and np.max(np.abs(w[:, :topk] - rw)) <= 1e-5
+    ids5 = np.concatenate([rid, np.full((T, 1), Er, np.uint32)], 1); w5 = np.concatenate([rw.astype(np.float32), np.ones((T, 1), np.float32)], 1)
+    ref, _, _ = orc.moe_layer(None, xb, wgu, sgu, wdn, sdn, topk + 1, routing=(ids5, w5))
+    assert np.max(np.abs(o32 - ref)) <= 1e-2 and rel_l2(o32, ref) <= 1e-3, (float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref))
+    # without the shared expert's contribution the result is far off: the slot is really computed
+    ref_routed, _, _ = orc.moe_layer(None, xb, wgu, sgu, wdn, sdn, topk, routing=(rid, rw.astype(np.float32)))
+    assert rel_l2(o32, ref_routed) > 0.1
+    # a stack of two such layers with the router inside; the routers carry the shared expert's gate: slot weight = sigmoid(gate . xn)
+    if engine == api.ENGINE_MMA:
+        rc, layer2 = api.moe_layer_create(tgu, tdn, topk=topk, max_tokens=32, engine=engine, shared_expert=True); assert rc == 0, api.last_error()
+        rc, stack = api.moe_stack_create([layer, layer2], 1e-6); assert rc == 0, api.last_error()
+        gates = [orc.bf16_bits(rng.uniform(-0.05, 0.05, (Er, H)).astype(np.float32)) for _ in range(2)]
+        sgate = [orc.bf16_bits(rng.uniform(-0.05, 0.05, H).astype(np.float32)) for _ in range(2)]
+        nws = [rng.uniform(0.8, 1.2, H).astype(np.float32) for _ in range(2)]
+        routers = []
+        for l in range(2):
+            rc, r = api.moe_router_create(gates[l], nws[l]); assert rc == 0, api.last_error()
+            assert api.lib.omega_gpu_moe_router_set_shared_gate(r, sgate[l].ctypes.data_as(C.c_void_p)) == 0, api.last_error()
+            assert api.lib.omega_gpu_moe_stack_set_router(stack, C.c_uint32(l), r) == 0, api.last_error()
+            routers.append(r)
+        s16 = np.empty((T, H), np.uint16); s32 = np.empty((T, H), np.float32)
+        assert api.lib.omega_gpu_moe_stack_bf16(stack, C.c_uint32(T), None, xb.ctypes.data_as(C.c_void_p), s16.ctypes.data_as(C.c_void_p), s32.ctypes.data_as(C.c_void_p)) == 0, api.last_error()
+        h = orc.bf16_to_f32(xb); keep = np.ones(T, bool)
+        for l in range(2):
+            xn64, lg, lids, lw, margin = orc.router(h, nws[l], gates[l], 1e-6, topk, True)
+            keep &= margin >= 1e-4
+            sw = 1.0 / (1.0 + np.exp(-(xn64 @ orc.bf16_to_f32(sgate[l]).astype(np.float64))))
+            i5 = np.concatenate([lids, np.full((T, 1), Er, np.uint32)], 1); w5 = np.concatenate([lw, sw[:, None]], 1).astype(np.float32)
+            mo, _, _ = orc.moe_layer(None, orc.bf16_bits(orc.rmsnorm(h, 1e-6, nws[l])), wgu, sgu, wdn, sdn, topk + 1, routing=(i5, w5))
+            h = h + mo
+        assert keep.sum() >= T - 3 and np.max(np.abs(s32[keep] - h[keep])) <= 1e-2 and rel_l2(s32[keep], h[keep]) <= 1e-3
+        api.lib.omega_gpu_moe_stack_free(stack)
+        for r in routers:
+            api.lib.omega_gpu_moe_router_free(r)
+        api.lib.omega_gpu_moe_layer_free(layer2)
+    api.lib.omega_gpu_moe_layer_free(layer); api.fp8_tensor_free(tgu); api.fp8_tensor_free(tdn)
