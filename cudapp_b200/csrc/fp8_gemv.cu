@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(256) fp8_rows_kernel(const GemvArgs a) {
 #pragma unroll
                 for (int j = 0; j < R; j++) acc[j][m] = 0.0f;
             }
-#pragma unroll 2
+#pragma unroll(R == 1 && MT == 1 ? 4 : 2)   // one row per warp: all four 16-byte weight loads of a 2048-wide row in flight
             for (uint32_t st = 0; st < steps; st++) {
                 const uint32_t c0 = st * 32u * LB + lane * LB;
                 float wv[R][LB];
