@@ -368,10 +368,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
             mbar_arrive(scempty_bar(b));
         }
         if (a.out_peers && ok) {
-            __threadfence_system();
+            // the group's result stores are ordered before its barrier; the publishing threads fence once at system scope (cumulative) and count
             mbar_arrive(group_bar(g));
-            if (mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15) && et < 64u && s_ret[g][et])
+            if (mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15) && et < 64u && s_ret[g][et]) {
+                __threadfence_system();
                 atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[et]) + a.ret_index, (unsigned long long)s_ret[g][et]);
+            }
         }
     }
     if (*abort_flag) { for (int i = 0; i < 64; i++) __nanosleep(1000); }

@@ -291,11 +291,12 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             mbar_arrive(scempty_bar(b));   // this unit's scales and destination rows may be overwritten
         }
         if (a.out_peers && ok) {
-            // all result rows of this group are stored: make them visible system-wide, then advance each owner's counter once
-            __threadfence_system();
+            // all result rows of this group are stored and ordered before the group's barrier: the publishing threads fence once at system scope
+            // (a fence is cumulative) and advance each owner's counter once
             mbar_arrive(group_bar(g));
             if (mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15)) {
                 const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                if (et < 64u && s_ret[g][et]) __threadfence_system();
                 if (et < 64u && s_ret[g][et]) atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[et]) + a.ret_index, (unsigned long long)s_ret[g][et]);
             }
         }

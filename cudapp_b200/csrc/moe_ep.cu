@@ -435,9 +435,13 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
             if (lane == 0) reinterpret_cast<float *>(sx_peers[s_d[s]] + sx_off)[(size_t)s_row[s] * kb_total + kb] = qs;
         }
     }
-    __threadfence_system();
+    // publish: every thread's stores are ordered before the barrier; the few publishing threads then fence at system scope (a fence is
+    // cumulative: it covers what the barrier made visible to them) and count the row in. One fence by one warp, not one per thread.
     __syncthreads();
-    if (tid < topk) atomicAdd_system(reinterpret_cast<unsigned long long *>(cnt_peers[s_d[tid]]) + parity, 1ull);
+    if (tid < topk) {
+        __threadfence_system();
+        atomicAdd_system(reinterpret_cast<unsigned long long *>(cnt_peers[s_d[tid]]) + parity, 1ull);
+    }
 }
 
 }  // namespace b200
