@@ -11,7 +11,8 @@
 #include "internal.h"
 
 struct OmegaGpuW4Tensor {
-    uint32_t n, k; uint8_t *w; uint16_t *s;
+    uint32_t n, k; uint8_t *w; uint16_t *s;   // s: fp16 scales (int4 format) or, viewed as bytes, E8M0 scales (MXFP4 format)
+    uint32_t fmt;                              // 0: signed int4 + fp16 scale per 32; 1: MXFP4 = E2M1 + E8M0 scale per 32
     float *part; uint32_t *counters;   // scratch of the tensor-core kernel: K-quarter partial sums [4][16][n] f32 and one arrival counter per 128 output rows
 };
 
@@ -111,7 +112,25 @@ __device__ __forceinline__ uint32_t nib2_bf16(uint32_t v, int j) {
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-template <int GQ>   // scale groups per K quarter: k = 128 * GQ
+// Eight E2M1 nibbles of v -> four bf16 pairs (b[j] = the two nibbles of byte j, low nibble = even column = low half). The seven magnitudes
+// 0.5, 1, 1.5, 2, 3, 4, 6 are exact in bf16; a byte-permute looks the low and the high byte of each up in 8-entry tables, the sign bit moves to bit 15
+// (the reference's scalar decoder: native/models/mxfp4.om, docs/models/MXFP4.md:4-9; signed zero kept).
+__device__ __forceinline__ void e2m1x8_bf16(uint32_t v, uint32_t *b) {
+    const uint32_t m = v & 0x77777777u;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const uint32_t sel = h ? (m >> 16) : (m & 0xffffu), sg = h ? (v >> 16) : (v & 0xffffu);
+        uint32_t lo, hi, p01, p23;
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"(0xC0800000u), "r"(0xC0804000u), "r"(sel));   // low bytes of bf16(0, .5, 1, 1.5 | 2, 3, 4, 6)
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(0x3F3F3F00u), "r"(0x40404040u), "r"(sel));   // high bytes
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(p01) : "r"(lo), "r"(hi), "r"(0x5140u));
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(p23) : "r"(lo), "r"(hi), "r"(0x7362u));
+        b[2 * h] = p01 | ((sg & 0x8u) << 12) | ((sg & 0x80u) << 24);
+        b[2 * h + 1] = p23 | ((sg & 0x800u) << 4) | ((sg & 0x8000u) << 16);
+    }
+}
+
+template <int GQ, int FMT>   // scale groups per K quarter: k = 128 * GQ; FMT 0: int4 + fp16 scales, 1: E2M1 + E8M0 scales (MXFP4)
 __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m, uint32_t n, uint32_t k, const uint8_t *__restrict__ w, const uint16_t *__restrict__ sc,
                                                         const uint16_t *__restrict__ x, uint16_t *__restrict__ y16, float *__restrict__ y32, float *part, uint32_t *counters) {
     constexpr uint32_t KQ = GQ * 32u, XS = KQ * 2u + 64u;   // columns per quarter; bytes between panel rows (the 64 keep a quarter-warp's 16-byte reads on separate banks)
@@ -125,11 +144,18 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
     uint32_t wq[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; g++) wq[g] = __ldcs(wrow + g * 4 + t);
-    // scales of the two output columns this thread's accumulators belong to (n0 + 2t, n0 + 2t + 1)
-    const uint4 *s0p = reinterpret_cast<const uint4 *>(sc + (size_t)(n0 + 2u * t) * (k / 32u) + kq * GQ), *s1p = reinterpret_cast<const uint4 *>(sc + (size_t)(n0 + 2u * t + 1u) * (k / 32u) + kq * GQ);
-    uint4 sv0[GQ / 8], sv1[GQ / 8];
+    // scales of the two output columns this thread's accumulators belong to (n0 + 2t, n0 + 2t + 1): GQ values each, fp16 (FMT 0) or E8M0 bytes (FMT 1)
+    constexpr int SB = FMT ? 1 : 2, SV = GQ * SB / 16 > 0 ? GQ * SB / 16 : 1;   // bytes per scale; 16-byte vectors per row (GQ = 8 bytes of E8M0: half a vector, loaded as 8 bytes)
+    const uint8_t *scb = reinterpret_cast<const uint8_t *>(sc);
+    const uint8_t *s0b = scb + ((size_t)(n0 + 2u * t) * (k / 32u) + kq * GQ) * SB, *s1b = scb + ((size_t)(n0 + 2u * t + 1u) * (k / 32u) + kq * GQ) * SB;
+    uint4 sv0[SV], sv1[SV];
+    if (GQ * SB >= 16) {
 #pragma unroll
-    for (int i = 0; i < GQ / 8; i++) { sv0[i] = __ldg(s0p + i); sv1[i] = __ldg(s1p + i); }
+        for (int i = 0; i < SV; i++) { sv0[i] = __ldg(reinterpret_cast<const uint4 *>(s0b) + i); sv1[i] = __ldg(reinterpret_cast<const uint4 *>(s1b) + i); }
+    } else {
+        const uint2 a0 = __ldg(reinterpret_cast<const uint2 *>(s0b)), a1 = __ldg(reinterpret_cast<const uint2 *>(s1b));
+        sv0[0] = make_uint4(a0.x, a0.y, 0, 0); sv1[0] = make_uint4(a1.x, a1.y, 0, 0);
+    }
     // the quarter of the activation panel: rows m0 .. m0 + 15 (zero past m), columns kq * KQ ..
     for (uint32_t i = threadIdx.x; i < 16u * (KQ / 8u); i += 512u) {
         const uint32_t row = i / (KQ / 8u), c8 = i - row * (KQ / 8u);
@@ -144,11 +170,20 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
         const uint4 xa = *reinterpret_cast<const uint4 *>(xq + r * XS + g * 64 + t * 16u);          // panel row r, columns 8t .. 8t+7 of group g
         const uint4 xb = *reinterpret_cast<const uint4 *>(xq + (r + 8u) * XS + g * 64 + t * 16u);   // panel row r + 8
         float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        mma_bf16_16816(p, xa.x, xb.x, xa.y, xb.y, nib2_bf16(wq[g], 0), nib2_bf16(wq[g], 1));
-        mma_bf16_16816(p, xa.z, xb.z, xa.w, xb.w, nib2_bf16(wq[g], 2), nib2_bf16(wq[g], 3));
-        const uint32_t *u0 = reinterpret_cast<const uint32_t *>(&sv0[g >> 3]), *u1 = reinterpret_cast<const uint32_t *>(&sv1[g >> 3]);
-        const uint32_t h0 = (u0[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu, h1 = (u1[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu;
-        const float sl = __half2float(__ushort_as_half((unsigned short)h0)), sh = __half2float(__ushort_as_half((unsigned short)h1));
+        uint32_t bq[4];
+        if (FMT) e2m1x8_bf16(wq[g], bq);
+        else { bq[0] = nib2_bf16(wq[g], 0); bq[1] = nib2_bf16(wq[g], 1); bq[2] = nib2_bf16(wq[g], 2); bq[3] = nib2_bf16(wq[g], 3); }
+        mma_bf16_16816(p, xa.x, xb.x, xa.y, xb.y, bq[0], bq[1]);
+        mma_bf16_16816(p, xa.z, xb.z, xa.w, xb.w, bq[2], bq[3]);
+        float sl, sh;
+        if (FMT) {   // E8M0: 2^(byte - 127); byte 0 is 2^-127, a subnormal f32
+            const uint32_t e0 = (reinterpret_cast<const uint32_t *>(&sv0[g >> 4])[(g & 15) >> 2] >> (8 * (g & 3))) & 0xffu, e1 = (reinterpret_cast<const uint32_t *>(&sv1[g >> 4])[(g & 15) >> 2] >> (8 * (g & 3))) & 0xffu;
+            sl = __uint_as_float(e0 ? e0 << 23 : 0x00400000u); sh = __uint_as_float(e1 ? e1 << 23 : 0x00400000u);
+        } else {
+            const uint32_t *u0 = reinterpret_cast<const uint32_t *>(&sv0[g >> 3]), *u1 = reinterpret_cast<const uint32_t *>(&sv1[g >> 3]);
+            const uint32_t h0 = (u0[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu, h1 = (u1[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu;
+            sl = __half2float(__ushort_as_half((unsigned short)h0)); sh = __half2float(__ushort_as_half((unsigned short)h1));
+        }
         acc[0] = fmaf(p[0], sl, acc[0]); acc[1] = fmaf(p[1], sh, acc[1]); acc[2] = fmaf(p[2], sl, acc[2]); acc[3] = fmaf(p[3], sh, acc[3]);
     }
     // this quarter's share of the block: part[kq][row][n]
@@ -200,6 +235,27 @@ int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uin
     *out = t;
     return OMEGA_GPU_FP8_OK;
 }
+/* MXFP4 weights (E2M1 nibbles, low nibble = even column, E8M0 scale per 32 columns: the format of docs/models/MXFP4.md in the reference, whose
+ * scalar decoder native/models/mxfp4.om defines every element's value). The tensor runs through omega_gpu_w4_gemm_bf16 / _async like an int4 one. */
+int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_e8m0, OmegaGpuW4Tensor **out) {
+    if (out) *out = nullptr;
+    if (!out || !packed || !scale_e8m0 || !n || !k) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (n % 128u || !(k == 1024u || k == 2048u || k == 4096u)) { set_error("mxfp4 upload: n must be a multiple of 128 and k 1024, 2048 or 4096"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    for (size_t i = 0; i < (size_t)n * (k / 32); i++) if (scale_e8m0[i] == 0xffu) { set_error("mxfp4 upload: scale 255 (a NaN block) at group %zu", i); return OMEGA_GPU_FP8_NAN_WEIGHT; }
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    OmegaGpuW4Tensor *t = (OmegaGpuW4Tensor *)calloc(1, sizeof *t);
+    if (!t) return OMEGA_GPU_FP8_BAD_ARGS;
+    t->n = n; t->k = k; t->fmt = 1;
+    const size_t wb = (size_t)n * k / 2, sb = (size_t)n * (k / 32), pb = (size_t)4 * 16 * n * 4, cb = (size_t)(n / 128u) * 4;
+    const bool ok = cuda_ok(cudaMalloc(&t->w, wb), "cudaMalloc(mxfp4)") && cuda_ok(cudaMalloc((void **)&t->s, sb), "cudaMalloc(mxfp4 scales)") &&
+                    cuda_ok(cudaMemcpy(t->w, packed, wb, cudaMemcpyHostToDevice), "copy mxfp4") && cuda_ok(cudaMemcpy(t->s, scale_e8m0, sb, cudaMemcpyHostToDevice), "copy mxfp4 scales") &&
+                    cuda_ok(cudaMalloc(&t->part, pb), "cudaMalloc(mxfp4 partials)") && cuda_ok(cudaMalloc(&t->counters, cb), "cudaMalloc(mxfp4 counters)") &&
+                    cuda_ok(cudaMemset(t->counters, 0, cb), "memset");
+    if (!ok) { if (t->w) cudaFree(t->w); if (t->s) cudaFree(t->s); if (t->part) cudaFree(t->part); if (t->counters) cudaFree(t->counters); free(t); return OMEGA_GPU_FP8_CHIP_FAIL; }
+    *out = t;
+    return OMEGA_GPU_FP8_OK;
+}
 void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     if (!t) return;
     Lock l;
@@ -210,12 +266,13 @@ void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     free(t);
 }
 static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *dx, uint16_t *d16, float *d32, cudaStream_t s) {
-    if (t->part && !getenv("B200MOE_W4_FMA")) {   // tensor-core kernel: one launch per 16 activation rows (they share the tensor's scratch, in stream order)
+    if (t->part && (t->fmt || !getenv("B200MOE_W4_FMA"))) {   // tensor-core kernel: one launch per 16 activation rows (they share the tensor's scratch, in stream order)
         const dim3 grid(t->n / 128u, 4);
         for (uint32_t m0 = 0; m0 < m; m0 += 16u) {
-            if (t->k == 4096u) w4_mma_kernel<32><<<grid, 512, 16 * (32 * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters);
-            else if (t->k == 2048u) w4_mma_kernel<16><<<grid, 512, 16 * (16 * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters);
-            else w4_mma_kernel<8><<<grid, 512, 16 * (8 * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters);
+#define W4_LAUNCH(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters)
+            if (t->fmt) { if (t->k == 4096u) W4_LAUNCH(32, 1); else if (t->k == 2048u) W4_LAUNCH(16, 1); else W4_LAUNCH(8, 1); }
+            else { if (t->k == 4096u) W4_LAUNCH(32, 0); else if (t->k == 2048u) W4_LAUNCH(16, 0); else W4_LAUNCH(8, 0); }
+#undef W4_LAUNCH
         }
         return cudaGetLastError();
     }

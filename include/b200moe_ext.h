@@ -65,6 +65,12 @@ int omega_gpu_act_quant_f32(uint32_t rows, uint32_t k, uint32_t pieces, const fl
 typedef struct OmegaGpuW4Tensor OmegaGpuW4Tensor;
 int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint16_t *scale_f16, OmegaGpuW4Tensor **out);
 void omega_gpu_w4_free(OmegaGpuW4Tensor *t);
+/* ---- MXFP4 weights: E2M1 nibbles (two per byte along K, low nibble = even column) with one E8M0 scale byte per 32 columns, the format of the
+ * reference's docs/models/MXFP4.md; every element's value is what its scalar decoder native/models/mxfp4.om returns (checked against that unit's
+ * own verification oracle). packed [n][k/2], scale_e8m0 [n][k/32]; scale 255 (a NaN block) is refused with NAN_WEIGHT. n a multiple of 128,
+ * k 1024, 2048 or 4096. The tensor is used with omega_gpu_w4_gemm_bf16 / _async and freed with omega_gpu_w4_free. The reference has no MXFP4 GEMM
+ * ("a scalar primitive, not a GEMM"), so the product y = x W^T is defined here: per group the sum of x * element, times 2^(scale - 127), f32. */
+int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_e8m0, OmegaGpuW4Tensor **out);
 /* y bf16 [m][n] = x bf16 [m][k] * W^T, f32 accumulation; yf32 (optional) receives the unrounded values */
 int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32);
 /* the same on device buffers, stream-ordered (one of y_bf16_va / y_f32_va may be 0) */

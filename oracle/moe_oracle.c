@@ -499,6 +499,41 @@ void orc_w4_gemm_rows(const uint8_t *packed, const uint16_t *scale_f16, uint32_t
     }
 }
 
+/* ------------------------------------------------------------------ MXFP4 (E2M1 nibble + E8M0 scale per 32 elements) */
+
+/* One MXFP4 element as exact IEEE binary32 bits: what the reference's scalar decoder returns (native/models/mxfp4.om; contract
+ * docs/models/MXFP4.md:4-9; its verification oracle tests/models/mxfp4-check.py:30-35: ldexp(FP4_VALUES[nibble], scale - 127), values the
+ * format cannot hold finitely become signed infinity, signed zero kept, small results become subnormals). nib 0..15 (bit 3 = sign, bits 2..1
+ * exponent, bit 0 mantissa), scale 0..254 biased by 127; 255 is the reserved NaN block and is refused by the callers. Integer arithmetic only. */
+uint32_t orc_mxfp4_bits(uint32_t nib, uint32_t scale) {
+    const uint32_t sign = (nib & 8u) << 28, m = nib & 7u;
+    if (m == 0) return sign;
+    /* value = mag * 2^(scale - 127) with mag in {0.5, 1, 1.5, 2, 3, 4, 6} = (2 + man) * 2^(exp - 2) for exp >= 1, and 0.5 = 2^-1 for m = 1 */
+    int e; uint32_t frac;   /* value = (1 + frac / 2) * 2^e */
+    if (m == 1) { e = -1; frac = 0; } else { e = (int)(m >> 1) - 1; frac = m & 1u; }
+    e += (int)scale - 127;
+    if (e > 127) return sign | 0x7f800000u;
+    if (e >= -126) return sign | ((uint32_t)(e + 127) << 23) | (frac << 22);
+    /* subnormal: (1 + frac / 2) * 2^e = (2 + frac) * 2^(e - 1); one unit is 2^-149 */
+    const int sh = e - 1 + 149;
+    if (sh < 0) return sign;   /* cannot occur: the smallest element is 0.5 * 2^-127 = 2^-128 = 2^21 units */
+    return sign | ((2u + frac) << sh);
+}
+/* y[m][r] = sum over groups of 2^(scale - 127) * sum_c x[m][c] * e2m1(nibble[r][c]) in double; low nibble = even column (gpt-oss order). rows [r0, r1) */
+void orc_mxfp4_gemm_rows(const uint8_t *packed, const uint8_t *scale_e8m0, uint32_t k, uint32_t r0, uint32_t r1,
+                         uint32_t n, const float *x, uint32_t m_rows, double *y) {
+    for (uint32_t r = r0; r < r1; r++) for (uint32_t m = 0; m < m_rows; m++) {
+        double acc = 0.0;
+        for (uint32_t c = 0; c < k; c++) {
+            const uint8_t b = packed[((size_t)r * k + c) / 2];
+            const uint32_t bits = orc_mxfp4_bits((c & 1u) ? (b >> 4) : (b & 15u), scale_e8m0[(size_t)r * (k / 32) + c / 32]);
+            float w; memcpy(&w, &bits, 4);
+            acc += (double)x[(size_t)m * k + c] * (double)w;
+        }
+        y[(size_t)m * n + r] = acc;
+    }
+}
+
 /* ------------------------------------------------------------------ one MoE layer, the reference host glue */
 
 /* For sorted row p (expert e, token t, slot s): gu = GEMV(W_gu[e], x[t]) (double dot, stored f32, as a

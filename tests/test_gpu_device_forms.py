@@ -170,3 +170,27 @@ def test_w4_gemm_full_size():
     assert np.max(np.abs(y32 - ref)) <= 1e-2 and rel_l2(y32, ref) <= 1e-3, (float(np.max(np.abs(y32 - ref))), rel_l2(y32, ref))
     assert np.array_equal(y16, orc.bf16_bits(y32))
     api.lib.omega_gpu_w4_free(t)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 16), (128, 2048, 21), (4096, 4096, 16)])
+def test_mxfp4_gemm(n, k, m):
+    """MXFP4 weights (E2M1 + E8M0 per 32: docs/models/MXFP4.md of the reference) times bf16 activations against the double checker, whose element
+    decoder equals the reference's own verification oracle record for record (tests/test_oracle_pin.py). Every nibble value and a wide range of
+    scales occur, among them scale 0 (2^-127) and large ones; the NaN scale is refused at upload."""
+    rng = np.random.default_rng(n + k)
+    packed = rng.integers(0, 256, (n, k // 2)).astype(np.uint8)
+    scale = rng.integers(110, 135, (n, k // 32)).astype(np.uint8)
+    scale[0, 0] = 0; scale[1, 1] = 1; scale[n - 1, k // 32 - 1] = 140
+    xb = orc.bf16_bits(rng.normal(0, 1, (m, k)).astype(np.float32))
+    t = C.c_void_p()
+    bad = scale.copy(); bad[3, 2] = 255
+    assert api.lib.omega_gpu_mxfp4_upload(C.c_uint32(n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), bad.ctypes.data_as(C.c_void_p), C.byref(t)) == api.NAN_WEIGHT and not t.value
+    assert api.lib.omega_gpu_mxfp4_upload(C.c_uint32(n), C.c_uint32(k + 32), packed.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p), C.byref(t)) == api.BAD_ARGS
+    assert api.lib.omega_gpu_mxfp4_upload(C.c_uint32(n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
+    rc, y16, y32 = api.w4_gemm_bf16(t, n, xb); assert rc == 0, api.last_error()
+    ref = orc.mxfp4_gemm(packed, scale, orc.bf16_to_f32(xb))
+    mag = orc.mxfp4_gemm(packed & 0x77, scale, np.abs(orc.bf16_to_f32(xb)))                 # sum of |terms|: the reference's own error measure for a dot product
+    assert np.all(np.abs(y32 - ref) <= 1e-5 * mag + 1e-30), float(np.max(np.abs(y32 - ref) / (mag + 1e-30)))
+    assert rel_l2(y32, ref) <= 1e-3 and np.array_equal(y16, orc.bf16_bits(y32))
+    rc, _, yb = api.w4_gemm_bf16(t, n, xb); assert rc == 0 and np.array_equal(yb.view(np.uint32), y32.view(np.uint32))
+    api.lib.omega_gpu_w4_free(t)

@@ -402,3 +402,34 @@ def test_combine_against_reference():
         assert np.array_equal(dec, ref)                                        # equal as numbers everywhere ...
         nz = ref != 0
         assert np.array_equal(dec.view(np.uint32)[nz], ref.view(np.uint32)[nz])   # ... and as bits wherever the sum is not an exact zero
+
+
+# ------------------------------------------------------------------ MXFP4 element decoder (native/models/mxfp4.om; oracle tests/models/mxfp4-check.py)
+MXFP4_ORACLE_SHA256 = "665ce3b50c419456c447dc8eabf300d79f20d38dfdbd6e5b3fd6b97308f0bf04"   # docs/models/MXFP4.md: oracle_sha256 of the 130 560 records
+
+
+def mxfp4_all_records():
+    import struct
+    return b"".join(struct.pack("<I", orc.mxfp4_bits((p >> (4 * l)) & 15, s)) for s in range(255) for p in range(256) for l in range(2))
+
+
+def test_mxfp4_decoder_against_published_digest():
+    """every (scale, byte, lane) record of the reference's own check, in its order: the digest the reference publishes for its oracle's output"""
+    import hashlib
+    assert hashlib.sha256(mxfp4_all_records()).hexdigest() == MXFP4_ORACLE_SHA256
+    for nib, scale, want in ((2, 127, 1.0), (7, 127, 6.0), (9, 127, -0.5), (1, 128, 1.0), (7, 254, np.inf), (15, 254, -np.inf), (8, 5, -0.0)):
+        got = np.array([orc.mxfp4_bits(nib, scale)], np.uint32).view(np.float32)[0]
+        assert got == np.float32(want) and np.signbit(got) == np.signbit(np.float32(want))
+    assert orc.mxfp4_bits(1, 0) == 1 << 21                                     # 0.5 * 2^-127 = 2^-128: a subnormal, not flushed
+
+
+MXCHECK = os.path.join(os.environ.get("B200MOE_REFERENCE", os.path.normpath(os.path.join(os.path.dirname(__file__), "..", "..", "reference"))), "tests", "models", "mxfp4-check.py")
+
+
+@pytest.mark.skipif(not os.path.exists(MXCHECK), reason="the reference tree is not on this machine")
+def test_mxfp4_decoder_against_reference_oracle():
+    """the same records against the reference's verification oracle itself (imported from its test script where the tree is present)"""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("mxfp4_check", MXCHECK); m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)
+    want = b"".join(m.oracle(p, l, s) for s in range(255) for p in range(256) for l in range(2))
+    assert want == mxfp4_all_records()
