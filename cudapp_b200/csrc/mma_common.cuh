@@ -134,4 +134,44 @@ __device__ __forceinline__ float quant_pieces_warp(const float *v, uint32_t piec
     return s;
 }
 
+// Router-weighted sum of one token's K result rows at columns c .. c + 3, in slot order, multiply then add, never fused: the reference's combine
+// (src/omega_blackwell_codegen_dec.c:226-255). All K row loads are issued before the first one is used: with a run-time slot count the loop
+// serialises K dependent memory round trips per thread (measured: 14 us per layer for this step at 8 slots, against 4 with the loads in flight).
+// VOLATILE: rows written by peer GPUs are read past L1.
+template <int K, bool VOLATILE>
+__device__ __forceinline__ float4 combine_slots_k(const float *__restrict__ w, const float *__restrict__ dn, size_t first_row, uint32_t hidden, uint32_t c) {
+    float ws[K]; float4 d[K];
+#pragma unroll
+    for (int s = 0; s < K; s++) {
+        ws[s] = __ldg(w + first_row + s);
+        const float4 *p = reinterpret_cast<const float4 *>(dn + (first_row + s) * hidden + c);
+        d[s] = VOLATILE ? __ldcv(p) : __ldg(p);
+    }
+    float4 m = make_float4(__fmul_rn(ws[0], d[0].x), __fmul_rn(ws[0], d[0].y), __fmul_rn(ws[0], d[0].z), __fmul_rn(ws[0], d[0].w));
+#pragma unroll
+    for (int s = 1; s < K; s++)
+        m = make_float4(__fadd_rn(m.x, __fmul_rn(ws[s], d[s].x)), __fadd_rn(m.y, __fmul_rn(ws[s], d[s].y)), __fadd_rn(m.z, __fmul_rn(ws[s], d[s].z)), __fadd_rn(m.w, __fmul_rn(ws[s], d[s].w)));
+    return m;
+}
+template <bool VOLATILE>
+__device__ __forceinline__ float4 combine_slots(uint32_t topk, const float *__restrict__ w, const float *__restrict__ dn, size_t first_row, uint32_t hidden, uint32_t c) {
+    switch (topk) {
+        case 8: return combine_slots_k<8, VOLATILE>(w, dn, first_row, hidden, c);
+        case 9: return combine_slots_k<9, VOLATILE>(w, dn, first_row, hidden, c);
+        case 4: return combine_slots_k<4, VOLATILE>(w, dn, first_row, hidden, c);
+        case 5: return combine_slots_k<5, VOLATILE>(w, dn, first_row, hidden, c);
+        case 2: return combine_slots_k<2, VOLATILE>(w, dn, first_row, hidden, c);
+        default: break;
+    }
+    float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t s = 0; s < topk; s++) {
+        const float ws = __ldg(w + first_row + s);
+        const float4 *p = reinterpret_cast<const float4 *>(dn + (first_row + s) * hidden + c);
+        const float4 d = VOLATILE ? __ldcv(p) : __ldg(p);
+        const float4 q = make_float4(__fmul_rn(ws, d.x), __fmul_rn(ws, d.y), __fmul_rn(ws, d.z), __fmul_rn(ws, d.w));
+        m = s == 0 ? q : make_float4(__fadd_rn(m.x, q.x), __fadd_rn(m.y, q.y), __fadd_rn(m.z, q.z), __fadd_rn(m.w, q.w));
+    }
+    return m;
+}
+
 }  // namespace b200

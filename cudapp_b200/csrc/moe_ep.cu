@@ -395,13 +395,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         if (x16) { const uint2 u = *reinterpret_cast<const uint2 *>(x16 + i); v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u)); }
         else v = *reinterpret_cast<const float4 *>(h + i);
         if (dn) {
-            float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t s = 0; s < topk; s++) {
-                const float ws = __ldg(w + (size_t)t * topk + s);
-                const float4 d = __ldcv(reinterpret_cast<const float4 *>(dn + ((size_t)t * topk + s) * hidden + c));   // written by peers: no stale cache line
-                const float4 p = make_float4(__fmul_rn(ws, d.x), __fmul_rn(ws, d.y), __fmul_rn(ws, d.z), __fmul_rn(ws, d.w));
-                m = s == 0 ? p : make_float4(__fadd_rn(m.x, p.x), __fadd_rn(m.y, p.y), __fadd_rn(m.z, p.z), __fadd_rn(m.w, p.w));
-            }
+            const float4 m = combine_slots<true>(topk, w, dn, (size_t)t * topk, hidden, c);
             v = make_float4(__fadd_rn(v.x, m.x), __fadd_rn(v.y, m.y), __fadd_rn(v.z, m.z), __fadd_rn(v.w, m.w));
         }
         *reinterpret_cast<float4 *>(h + i) = v;

@@ -31,14 +31,7 @@ __global__ void __launch_bounds__(256) combine_kernel(uint32_t tokens, uint32_t 
                                                       const float *__restrict__ d, float *__restrict__ out, uint16_t *__restrict__ out_bf16) {
     const uint32_t t = blockIdx.x;
     for (uint32_t c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
-        float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t s = 0; s < slots; s++) {
-            const float ws = __ldg(w + (size_t)t * slots + s);
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(d + ((size_t)t * slots + s) * hidden + c));
-            const float4 p = make_float4(__fmul_rn(ws, v.x), __fmul_rn(ws, v.y), __fmul_rn(ws, v.z), __fmul_rn(ws, v.w));
-            if (s == 0) m = p;
-            else m = make_float4(__fadd_rn(m.x, p.x), __fadd_rn(m.y, p.y), __fadd_rn(m.z, p.z), __fadd_rn(m.w, p.w));
-        }
+        const float4 m = combine_slots<false>(slots, w, d, (size_t)t * slots, hidden, c);
         if (out) *reinterpret_cast<float4 *>(out + (size_t)t * hidden + c) = m;
         if (out_bf16) {
             const uint32_t lo = __float_as_uint(m.x), hi = __float_as_uint(m.y), lo2 = __float_as_uint(m.z), hi2 = __float_as_uint(m.w);

@@ -54,26 +54,30 @@ __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidd
                                                                    const float *__restrict__ nw) {
     __shared__ double red[8];
     __shared__ float s_scale;
+    __shared__ uint32_t s_pos[32];
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
+    // the next layer's sorted rows of this token's picks and the norm weights come from step start, not from the kernel before: fetch them
+    // before the dependency wait
+    if (q && tid < topk) s_pos[tid] = pos[(size_t)t * topk + tid];
+    float4 keep[4], wkeep[4];   // this thread's columns (tid * 4 + 1024 j) of h and of the norm weight: the quantiser below uses the same mapping
+    const bool kept = hidden <= 4096u;
+    if (q && kept) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const uint32_t c = tid * 4u + 1024u * j; if (c < hidden) wkeep[j] = __ldg(reinterpret_cast<const float4 *>(nw + c)); }
+    }
     // launched as a programmatic dependent: everything read below is the previous kernel's output
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // work-list words of the expert kernel that follows (its previous launch has completed: this kernel depends on it)
     if (sched && blockIdx.x == 0) for (uint32_t i = tid; i < n_sched; i += 256) sched[i] = 0;
     double sq = 0.0;
-    for (uint32_t c = tid * 4; c < hidden; c += 1024) {
+    auto add_row = [&](uint32_t c) -> float4 {
         const size_t i = (size_t)t * hidden + c;
         float4 v;
         if (x16) { const uint2 u = *reinterpret_cast<const uint2 *>(x16 + i); v = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u)); }
         else v = *reinterpret_cast<const float4 *>(h + i);
         if (dn) {
-            float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t s = 0; s < topk; s++) {
-                const float ws = __ldg(w + (size_t)t * topk + s);
-                const float4 d = __ldg(reinterpret_cast<const float4 *>(dn + ((size_t)t * topk + s) * hidden + c));
-                const float4 p = make_float4(__fmul_rn(ws, d.x), __fmul_rn(ws, d.y), __fmul_rn(ws, d.z), __fmul_rn(ws, d.w));
-                m = s == 0 ? p : make_float4(__fadd_rn(m.x, p.x), __fadd_rn(m.y, p.y), __fadd_rn(m.z, p.z), __fadd_rn(m.w, p.w));
-            }
+            const float4 m = combine_slots<false>(topk, w, dn, (size_t)t * topk, hidden, c);
             v = make_float4(__fadd_rn(v.x, m.x), __fadd_rn(v.y, m.y), __fadd_rn(v.z, m.z), __fadd_rn(v.w, m.w));
         }
         *reinterpret_cast<float4 *>(h + i) = v;
@@ -83,6 +87,13 @@ __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidd
             *reinterpret_cast<uint2 *>(h16 + i) = pk;
         }
         sq += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+        return v;
+    };
+    if (kept) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const uint32_t c = tid * 4u + 1024u * j; if (c < hidden) keep[j] = add_row(c); }
+    } else {
+        for (uint32_t c = tid * 4; c < hidden; c += 1024) add_row(c);
     }
     if (!q) return;
     for (int o = 16; o; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
@@ -91,11 +102,10 @@ __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidd
     if (tid == 0) { double acc = 0; for (int i = 0; i < 8; i++) acc += red[i]; s_scale = (float)(1.0 / sqrt(acc / (double)hidden + (double)eps)); }
     __syncthreads();
     const float sc = s_scale;
-    // one warp per 128-column block, lane = 4 columns (the quantiser's own mapping)
-    for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
+    // one warp per 128-column block, lane = 4 columns (the quantiser's own mapping): block warp + 8 j = columns tid * 4 + 1024 j, the ones this
+    // thread summed above
+    auto emit = [&](uint32_t kb, const float4 hv, const float4 wv) {
         const uint32_t c = kb * 128u + lane * 4u;
-        const float4 hv = *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);   // written by this CTA above
-        const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw + c));
         // xn = h * s * w (the reference's RMSNorm, src/omega_blackwell_codegen_dec.c:261-286; host form tests/gpu_decode_graph_test.c:56-60);
         // xn is a bf16 tensor: round first, then quantise the rounded value
         float v[4] = {__fmul_rn(__fmul_rn(hv.x, sc), wv.x), __fmul_rn(__fmul_rn(hv.y, sc), wv.y), __fmul_rn(__fmul_rn(hv.z, sc), wv.z), __fmul_rn(__fmul_rn(hv.w, sc), wv.w)};
@@ -104,9 +114,18 @@ __global__ void __launch_bounds__(256) combine_norm_scatter_kernel(uint32_t hidd
         uint32_t codes[4];
         const float qs = quant_pieces_warp(v, pieces, codes);
         for (uint32_t s = 0; s < topk; s++) {
-            const uint32_t row = pos[(size_t)t * topk + s];
+            const uint32_t row = s_pos[s];
             for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)row * hidden + c) = codes[p];
             if (lane == 0) sx[(size_t)row * kb_total + kb] = qs;
+        }
+    };
+    if (kept) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const uint32_t kb = (tid >> 5) + 8u * j; if (kb < kb_total) emit(kb, keep[j], wkeep[j]); }
+    } else {
+        for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
+            const uint32_t c = kb * 128u + lane * 4u;
+            emit(kb, *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c), __ldg(reinterpret_cast<const float4 *>(nw + c)));
         }
     }
 }
