@@ -267,9 +267,12 @@ int omega_gpu_moe_ep_combine_async(OmegaGpuMoeEp *ep, uint32_t tokens_local, uin
 /* 0, or the code of a bounded wait that ran out (11 dispatch flags, 12 return flags); synchronises the stream */
 int omega_gpu_moe_ep_status(OmegaGpuMoeEp *ep, void *stream) {
     if (!ep) return OMEGA_GPU_FP8_BAD_ARGS;
-    uint32_t v = 0;
-    if (!cuda_ok(cudaMemcpyAsync(&v, ep->err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") || !cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "ep status")) return OMEGA_GPU_FP8_CHIP_FAIL;
-    return (int)v;
+    // the transport's word, then the word the local tensor-core kernels record an expired wait in (word 4 of the plan header)
+    uint32_t v = 0, k = 0;
+    if (!cuda_ok(cudaMemcpyAsync(&v, ep->err, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
+        !cuda_ok(cudaMemcpyAsync(&k, ep->hdr + 4, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
+        !cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "ep status")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    return (int)(v ? v : k);
 }
 
 }  // extern "C"

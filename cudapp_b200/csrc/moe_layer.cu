@@ -340,4 +340,16 @@ int omega_gpu_moe_layer_bf16(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_
     return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 
+// Status of the stream-ordered entries (which never block): waits for `stream`, then returns 0, 100 + the routing plan's refusal, or the
+// code of a bounded wait that ran out inside a tensor-core kernel (that word is sticky: the process latches, as the blocking entry does).
+int omega_gpu_moe_layer_status(OmegaGpuMoeLayer *L, void *stream) {
+    if (!L) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    uint32_t hdr[8] = {0};
+    if (!cuda_ok(cudaMemcpyAsync(hdr, L->ws->header, 32, cudaMemcpyDeviceToHost, (cudaStream_t)stream), "copy status") ||
+        !cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "moe layer status")) return OMEGA_GPU_FP8_CHIP_FAIL;
+    if (hdr[4]) { set_error("moe layer: a bounded wait inside the tensor-core kernel ran out (code %u)", hdr[4]); st().latched = true; return (int)hdr[4]; }
+    return hdr[3] ? 100 + (int)hdr[3] : 0;
+}
+
 }  // extern "C"

@@ -98,7 +98,9 @@ __device__ __forceinline__ bool plan_tables(uint32_t experts, uint32_t tile_rows
         if (o.seg_a_va) reinterpret_cast<Seg32 *>(o.seg_a_va)[z] = zero;
         if (o.seg_b_va) reinterpret_cast<Seg32 *>(o.seg_b_va)[z] = zero;
     }
-    if (tid == 0) { hdr[0] = rows_total; hdr[1] = segs_total; hdr[2] = tiles_total; hdr[3] = 0; hdr[4] = hdr[5] = hdr[6] = hdr[7] = 0; }
+    // word 4 belongs to the kernels that consume the plan (an expired bounded wait is recorded there): it is zero from the owner's allocation and
+    // stays set once written, so a later plan does not erase a timeout that nobody has read yet
+    if (tid == 0) { hdr[0] = rows_total; hdr[1] = segs_total; hdr[2] = tiles_total; hdr[3] = 0; hdr[5] = hdr[6] = hdr[7] = 0; }
     uint32_t *xmap = reinterpret_cast<uint32_t *>(o.xmap_va), *ymap = reinterpret_cast<uint32_t *>(o.ymap_va);
     if (tid < 8) { xmap[rows_total + tid] = 0; ymap[rows_total + tid] = 0; }
     __syncthreads();

@@ -35,7 +35,8 @@ int omega_gpu_moe_topk_async(uint32_t tokens, uint32_t experts, uint32_t topk, i
  * xmap[rows+8] = token, ymap[rows+8] = token*ystride+slot (8 zero pads), seg: 32-byte records for the non-empty
  * experts in ascending id built from the two directories ({w_va, s_va} per expert), records past the last
  * non-empty expert up to `experts` zeroed; tiles: one {expert, row0, cnt} u32 x4 entry per `tile_rows` slice of
- * a segment (tile_rows 0 = none); header u32[8] = {rows, segments, tiles, status, 0...}; status 2 = id out of range. */
+ * a segment (tile_rows 0 = none); header u32[8] = {rows, segments, tiles, status, w, 0, 0, 0}; status 2 = id out of range; word w is
+ * left as it is (the kernels that consume a plan record an expired bounded wait there: zero it once, when the buffer is made). */
 typedef struct {
     uint64_t counts_va, starts_va, xmap_va, ymap_va;
     uint64_t seg_a_va, dir_a_va; /* first projection's segment records and {w_va, s_va} directory (may be 0) */
@@ -110,6 +111,9 @@ int omega_gpu_moe_layer_async(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t log
  * omega_gpu_moe_router_rows_async), x_va the bf16 input rows; an id outside the layer's experts makes the plan refuse (header status) */
 int omega_gpu_moe_layer_routed_async(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t ids_va, uint64_t wts_va, uint64_t x_va, uint64_t out_f32_va,
                                      uint64_t out_bf16_va, void *stream);
+/* status of the two stream-ordered entries above: waits for `stream`; 0, 100 + the routing plan's status, or the code of a bounded wait
+ * that ran out inside a kernel (sticky; the process is latched, as by the blocking entry) */
+int omega_gpu_moe_layer_status(OmegaGpuMoeLayer *l, void *stream);
 /* One forward on the library's stream with a CUDA event between consecutive launches: ms[i] = device time of the i-th
  * kernel (launch order), names[i] = its static name; *count entries (at most cap). For measurement. */
 int omega_gpu_moe_layer_profile(OmegaGpuMoeLayer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va,

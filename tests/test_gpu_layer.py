@@ -232,7 +232,7 @@ def test_router_then_layer_routed():
     assert rc == 0, api.last_error()
     rc = api.lib.omega_gpu_moe_layer_routed_async(m["layer"], C.c_uint32(T), u64(ids), u64(wts), u64(xn16), u64(out32), C.c_uint64(0), stream)
     assert rc == 0, api.last_error()
-    torch.cuda.synchronize()
+    assert api.lib.omega_gpu_moe_layer_status(m["layer"], stream) == 0, api.last_error()   # plan accepted, no wait ran out
     ids_h = ids.cpu().numpy().view(np.uint32); wts_h = wts.cpu().numpy(); xn_h = xn16.cpu().numpy().view(np.uint16); o32 = out32.cpu().numpy()
     oxn, olg, oids, ow, margin = orc.router(x, nw, gate, 1e-6, topk, True)
     sure = margin >= 1e-4
@@ -242,6 +242,14 @@ def test_router_then_layer_routed():
     assert np.max(np.abs(xn_h.astype(np.int32) - want)) <= 1 and np.mean(xn_h.astype(np.int32) != want) < 1e-2
     ref, _, _ = orc.moe_layer(None, xn_h, m["wgu"], m["sgu"], m["wdn"], m["sdn"], topk, routing=(ids_h, wts_h))
     assert np.max(np.abs(o32 - ref)) <= 1e-2 and rel_l2(o32, ref) <= 1e-3, (float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref))
+    # an id outside the layer's experts: the plan refuses (no rows, so the kernels that follow do nothing) and the status entry says so;
+    # the next good call clears it
+    bad = ids.clone(); bad[0, 0] = 100000
+    rc = api.lib.omega_gpu_moe_layer_routed_async(m["layer"], C.c_uint32(T), u64(bad), u64(wts), u64(xn16), u64(out32), C.c_uint64(0), stream)
+    assert rc == 0 and api.lib.omega_gpu_moe_layer_status(m["layer"], stream) == 102
+    rc = api.lib.omega_gpu_moe_layer_routed_async(m["layer"], C.c_uint32(T), u64(ids), u64(wts), u64(xn16), u64(out32), C.c_uint64(0), stream)
+    assert rc == 0 and api.lib.omega_gpu_moe_layer_status(m["layer"], stream) == 0
+    assert np.array_equal(out32.cpu().numpy(), o32)
     api.lib.omega_gpu_moe_router_free(r)
     free_layer(m)
 
