@@ -27,10 +27,11 @@ struct FfnArgs {
     const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index; uint32_t wait_limit;
 };
 
+constexpr int FFN_THREADS = 32 * 12;              // warp group 0: TMA, MMA, scale loader, one idle warp; warp groups 1 and 2: the two promotion / epilogue groups
 constexpr uint32_t FFN_RING = 64;                 // ring of published down-unit ids; the producer is never more than a few units ahead of the slowest role
 
 template <int PX, int PA>
-__global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_constant__ CUtensorMap tm_gu, const __grid_constant__ CUtensorMap tm_qx,
+__global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_constant__ CUtensorMap tm_gu, const __grid_constant__ CUtensorMap tm_qx,
                                                                    const __grid_constant__ CUtensorMap tm_dn, const __grid_constant__ CUtensorMap tm_qa, const FfnArgs a) {
     constexpr int PMAX = PX > PA ? PX : PA, NMAX = MMA_TOK * PMAX;
     constexpr int STAGES = PMAX <= 3 ? 4 : 3;
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     extern __shared__ uint8_t dyn_smem[];
     __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 16];
     __shared__ uint32_t s_tmem, s_abort;
-    __shared__ float s_sc[2][2][KB_MAX][MMA_TOK];
+    __shared__ __align__(16) float s_sc[2][2][KB_MAX][MMA_TOK];
     __shared__ float s_red[2][4][MMA_TOK];
     __shared__ uint32_t s_ymap[2][MMA_TOK];
     __shared__ volatile uint32_t s_units[FFN_RING];   // down units this CTA took, in order (slot = index % FFN_RING); 0xffffffff = no more
@@ -82,6 +83,9 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
+    // Registers go where the promotion needs them: the three single-thread roles give theirs up, the promotion threads hold a whole K block of
+    // partial sums at once, so a K block costs one TMEM round trip (two with three pieces) instead of one per piece pair.
+    // 128 x 56 + 256 x 224 = 384 x 168 registers. Each warp group changes its own count inside its own branch.
     const uint32_t H = a.hidden, I = a.inter, KBX = H / 128u, KBA = I / 128u, PG = I / 128u, PD = H / 256u;
     const bool dead = *reinterpret_cast<volatile uint32_t *>(a.err) != 0;   // a failure is already recorded: do nothing
     const uint32_t n_tiles = dead ? 0u : a.header[2], n_gu = n_tiles * PG, n_dn = n_tiles * PD;
@@ -132,6 +136,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
         return false;
     };
 
+    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (and scheduler of the down units)
         if (lane == 0) {
@@ -251,9 +256,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
             }
             mbar_arrive(scfull_bar(b));
         }
-    } else {
+    } else if (warp >= 4) {
         // ---------------------------------------------------------------- promotion + epilogue: two groups of 4 warps take alternate units
-        const uint32_t g = (warp - 3u) >> 2, q4 = warp & 3u, row = q4 * 32u + lane, et = (warp - 3u - 4u * g) * 32u + lane;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+        const uint32_t g = (warp - 4u) >> 2, q4 = warp & 3u, row = q4 * 32u + lane, et = row;
         uint32_t it = 0, gsync = 0, turns = 0; bool ok = true;
         for (uint32_t n = 0; ok; n++) {
             uint32_t u = 0, have = 0;
@@ -268,6 +274,15 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
             float acc0[MMA_TOK], acc1[MMA_TOK];
 #pragma unroll
             for (int i = 0; i < MMA_TOK; i++) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
+            // promotion of one half (one 128-feature block) of a K block: pieces folded last to first (x 1/16 each), then acc += Sw * Sa * partial
+            auto promote = [&](uint32_t (&v)[MMA_TOK], const float *sc, float (&acc)[MMA_TOK]) {
+#pragma unroll
+                for (int i = 0; i < MMA_TOK; i += 4) {
+                    const float4 c = *reinterpret_cast<const float4 *>(sc + i);
+                    acc[i] = fmaf(__uint_as_float(v[i]), c.x, acc[i]); acc[i + 1] = fmaf(__uint_as_float(v[i + 1]), c.y, acc[i + 1]);
+                    acc[i + 2] = fmaf(__uint_as_float(v[i + 2]), c.z, acc[i + 2]); acc[i + 3] = fmaf(__uint_as_float(v[i + 3]), c.w, acc[i + 3]);
+                }
+            };
             auto kloop = [&](auto pc) {
                 constexpr int P = decltype(pc)::value;
                 for (uint32_t kb = 0; kb < q.KB; kb++, it++) {
@@ -276,29 +291,48 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_ffn_kernel(const __grid_co
                     if (!(ok = mbar_wait(accfull_bar(buf), sl.use & 1u, abort_flag, a.err, 4))) return;
                     tc_fence_after();
                     const uint32_t taddr = tmem + ((q4 * 32u) << 16) + sl.col;
+                    if constexpr (P <= 2) {
+                        // both halves in one round trip; the buffer goes back to the MMA issuer as soon as the loads have landed
+                        uint32_t h0[P][MMA_TOK], h1[P][MMA_TOK];
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        uint32_t da[MMA_TOK], db[MMA_TOK];
-                        TMEM_LD32(taddr + half * (P * MMA_TOK) + (P - 1) * MMA_TOK, da);
-                        if (P > 1) TMEM_LD32(taddr + half * (P * MMA_TOK) + (P > 1 ? P - 2 : 0) * MMA_TOK, db);
+                        for (int p = P - 1; p >= 0; p--) { TMEM_LD32(taddr + p * MMA_TOK, h0[p]); TMEM_LD32(taddr + P * MMA_TOK + p * MMA_TOK, h1[p]); }
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        tc_fence_before(); mbar_arrive(accempty_bar(buf));
                         if (P > 1) {
 #pragma unroll
-                            for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));
+                            for (int i = 0; i < MMA_TOK; i++) {
+                                h0[0][i] = __float_as_uint(fmaf(__uint_as_float(h0[P - 1][i]), 0.0625f, __uint_as_float(h0[0][i])));
+                                h1[0][i] = __float_as_uint(fmaf(__uint_as_float(h1[P - 1][i]), 0.0625f, __uint_as_float(h1[0][i])));
+                            }
                         }
+                        promote(h0[0], &s_sc[b][0][kb][0], acc0);
+                        promote(h1[0], &s_sc[b][1][kb][0], acc1);
+                    } else {
+                        // one half per round trip; the second half's loads fly while the first is promoted
+                        uint32_t r[P][MMA_TOK], da[MMA_TOK];
 #pragma unroll
-                        for (int p = P - 3; p >= 0; p--) {
-                            TMEM_LD32(taddr + half * (P * MMA_TOK) + p * MMA_TOK, db);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                            for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));
-                        }
-                        if (half == 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }
+                        for (int p = P - 1; p >= 0; p--) TMEM_LD32(taddr + p * MMA_TOK, r[p]);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int i = 0; i < MMA_TOK; i++) {
-                            const float sc = s_sc[b][half][kb][i];
-                            if (half) acc1[i] = fmaf(__uint_as_float(da[i]), sc, acc1[i]); else acc0[i] = fmaf(__uint_as_float(da[i]), sc, acc0[i]);
+                            float v = __uint_as_float(r[P - 1][i]);
+#pragma unroll
+                            for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(r[p][i]));
+                            da[i] = __float_as_uint(v);
                         }
+#pragma unroll
+                        for (int p = P - 1; p >= 0; p--) TMEM_LD32(taddr + P * MMA_TOK + p * MMA_TOK, r[p]);
+                        promote(da, &s_sc[b][0][kb][0], acc0);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        tc_fence_before(); mbar_arrive(accempty_bar(buf));
+#pragma unroll
+                        for (int i = 0; i < MMA_TOK; i++) {
+                            float v = __uint_as_float(r[P - 1][i]);
+#pragma unroll
+                            for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(r[p][i]));
+                            da[i] = __float_as_uint(v);
+                        }
+                        promote(da, &s_sc[b][1][kb][0], acc1);
                     }
                 }
             };
@@ -398,7 +432,7 @@ cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, 
         static bool attr = false;                                                                                                       \
         if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_ffn_kernel<PXV, PAV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
         cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];                                                                         \
-        cfg.gridDim = dim3(sms); cfg.blockDim = dim3(MMA_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
+        cfg.gridDim = dim3(sms); cfg.blockDim = dim3(FFN_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;           \
         cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;                                                                                     \
         cudaError_t le = cudaLaunchKernelEx(&cfg, fp8_ffn_kernel<PXV, PAV>, *w0, *q0, *w1, *q1, a);                                     \
