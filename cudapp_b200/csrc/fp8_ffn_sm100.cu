@@ -27,7 +27,8 @@ struct FfnArgs {
     const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index; uint32_t wait_limit;
 };
 
-constexpr int FFN_THREADS = 32 * 12;              // warp group 0: TMA, MMA, scale loader, one idle warp; warp groups 1 and 2: the two promotion / epilogue groups
+constexpr int FFN_THREADS = 32 * 12;              // warp group 0: TMA, MMA, scale loader, scheduler of the down units; warp groups 1 and 2: the two promotion / epilogue groups
+constexpr uint32_t FFN_AHEAD = 6;                 // the scheduler takes the next down unit when the producer has this many K blocks left to issue
 constexpr uint32_t FFN_RING = 64;                 // ring of published down-unit ids; the producer is never more than a few units ahead of the slowest role
 
 template <int PX, int PA>
@@ -50,7 +51,8 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
     __shared__ float s_red[2][4][MMA_TOK];
     __shared__ uint32_t s_ymap[2][MMA_TOK];
     __shared__ volatile uint32_t s_units[FFN_RING];   // down units this CTA took, in order (slot = index % FFN_RING); 0xffffffff = no more
-    __shared__ volatile uint32_t s_published;
+    __shared__ uint4 s_tile[FFN_RING];                // their tile records; an entry is published once its tile's gate|up units have all finished
+    __shared__ volatile uint32_t s_published, s_prog; // entries published by the scheduler; K blocks the producer has issued
     __shared__ uint32_t s_ret[2][64];             // [epilogue group][rank]: result slices stored into that rank's buffer (expert parallel)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t smem_base = (smem_u32(dyn_smem) + 1023u) & ~1023u;
@@ -67,7 +69,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
 
     if (threadIdx.x < 128) s_ret[threadIdx.x >> 6][threadIdx.x & 63u] = 0;
     if (threadIdx.x == 0) {
-        s_abort = 0; s_published = 0;
+        s_abort = 0; s_published = 0; s_prog = 0;
         for (uint32_t s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (uint32_t b = 0; b < 4; b++) { mbar_init(accfull_bar(b), 1); mbar_init(accempty_bar(b), 128); }
         for (uint32_t b = 0; b < 2; b++) {
@@ -110,11 +112,14 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
             if (spin > SPIN_LIMIT || *abort_flag) { if (!*abort_flag) { *abort_flag = 1; atomicCAS(a.err, 0u, 20u); } return false; }
             __nanosleep(20);
         }
+        __threadfence_block();   // the entry (and, through the scheduler's acquire, the tile's pieces and scales) is read after the count
         const uint32_t v = s_units[i % FFN_RING];
         if (v == 0xffffffffu) return false;
         u = n_gu + v;
         return true;
     };
+    // tile record of this CTA's n-th unit (after unit_at(n) returned true)
+    auto tile_at = [&](uint32_t n, uint32_t tile) -> uint4 { return n < my_gu ? a.tiles[tile] : s_tile[(n - my_gu) % FFN_RING]; };
     struct Unit { uint32_t mode, tile, j, KB, r0, r1; };
     auto decode = [&](uint32_t u) -> Unit {
         Unit q;
@@ -140,24 +145,15 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (and scheduler of the down units)
         if (lane == 0) {
-            uint32_t it = 0, n = 0, taken = 0; bool ok = true, first = true, drained = false;
+            uint32_t it = 0, n = 0; bool ok = true, first = true;
             while (ok) {
                 uint32_t u;
-                if (n < my_gu) u = blockIdx.x + n * gridDim.x;
-                else {
-                    if (drained) break;
-                    if (first) { first = false; griddep_wait(); griddep_launch(); }   // the work-list counter is cleared by the kernel this one depends on
-                    const uint32_t v = n_dn ? atomicAdd(a.sched, 1u) : 0xffffffffu;
-                    const bool have = v < n_dn;
-                    s_units[taken % FFN_RING] = have ? v : 0xffffffffu;
-                    __threadfence_block();
-                    s_published = ++taken;
-                    if (!have) { drained = true; break; }
-                    u = n_gu + v;
-                }
-                n++;
+                if (n >= my_gu && first) { first = false; griddep_wait(); griddep_launch(); }   // no gate|up unit here: the down units come from the scheduler, which waits for the same grid
+                if (!unit_at(n, u)) break;
                 const Unit q = decode(u);
-                const uint4 t = a.tiles[q.tile];
+                const uint4 t = tile_at(n, q.tile);
+                if (q.mode) asm volatile("fence.proxy.async;" ::: "memory");   // the tile's pieces were written by other SMs: the scheduler acquired them, this thread reads them through TMA
+                n++;
                 const CUtensorMap *mw = q.mode ? &tm_dn : &tm_gu, *mq = q.mode ? &tm_qa : &tm_qx;
                 const uint32_t wn = q.mode ? H : 2u * I, P = q.mode ? (uint32_t)PA : (uint32_t)PX, bytes = 2 * A_TILE + P * B_PIECE;
                 const int wy0 = (int)(t.x * wn + q.r0), wy1 = (int)(t.x * wn + q.r1);
@@ -174,12 +170,11 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
                     }
                     griddep_wait(); griddep_launch();
                     if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13, a.wait_limit))) { *abort_flag = 1; break; }
-                    if (q.mode && !(ok = tile_ready(q.tile, 21))) break;
                     for (uint32_t kb = 0; kb < npre; kb++)
                         for (uint32_t p = 0; p < P; p++)
                             tma_load_2d(smem_base + kb * STAGE_BYTES + 2 * A_TILE + p * B_PIECE, mq, full_bar(kb), (int)(kb * 128u), (int)(p * a.q_rows + t.y));
-                    it = npre; kb0 = npre;
-                } else if (q.mode && !(ok = tile_ready(q.tile, 21))) break;
+                    it = npre; kb0 = npre; s_prog = it;
+                }
                 for (uint32_t kb = kb0; kb < q.KB && ok; kb++, it++) {
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
@@ -189,10 +184,10 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
                     tma_load_2d(dst + A_TILE, mw, full_bar(s), (int)(kb * 128u), wy1);
                     for (uint32_t p = 0; p < P; p++)
                         tma_load_2d(dst + 2 * A_TILE + p * B_PIECE, mq, full_bar(s), (int)(kb * 128u), (int)(p * a.q_rows + t.y));
+                    s_prog = it + 1;
                 }
             }
             if (first) { griddep_wait(); griddep_launch(); }   // a CTA without work still takes part in the launch chain
-            if (!drained) { s_units[taken % FFN_RING] = 0xffffffffu; __threadfence_block(); s_published = taken + 1; }   // let the other roles finish
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -236,16 +231,13 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
             uint32_t u = 0, have = 0;
             if (lane == 0) have = unit_at(n, u) ? 1u : 0u;
             have = __shfl_sync(0xffffffffu, have, 0); u = __shfl_sync(0xffffffffu, u, 0);
+            __syncwarp();
             if (!have) break;
             const Unit q = decode(u);
-            const uint4 t = a.tiles[q.tile]; const uint32_t b = n & 1u;
+            const uint4 t = tile_at(n, q.tile); const uint32_t b = n & 1u;
             if (!(ok = mbar_wait(scempty_bar(b), ((n >> 1) & 1u) ^ 1u, abort_flag, a.err, 7))) break;
-            if (q.mode) {   // the row scales of a down unit are written by this launch's gate|up units
-                uint32_t rdy = 1;
-                if (lane == 0) rdy = tile_ready(q.tile, 22) ? 1u : 0u;
-                if (!__shfl_sync(0xffffffffu, rdy, 0)) break;
-                s_ymap[b][lane] = lane < t.z ? a.ymap[t.y + lane] : 0u;
-            }
+            // the row scales of a down unit are written by this launch's gate|up units: its entry is published only after they have finished
+            if (q.mode) s_ymap[b][lane] = lane < t.z ? a.ymap[t.y + lane] : 0u;
             const float *ws = q.mode ? a.dn_scale : a.gu_scale, *as = q.mode ? a.sa : a.x_scale;
             const uint32_t nb = (q.mode ? H : 2u * I) / 128u;
             const float *w0 = ws + ((size_t)t.x * nb + q.r0 / 128u) * q.KB, *w1 = ws + ((size_t)t.x * nb + q.r1 / 128u) * q.KB;
@@ -255,6 +247,32 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
                 s_sc[b][1][kb][lane] = __ldg(w1 + kb) * cs;
             }
             mbar_arrive(scfull_bar(b));
+        }
+    } else if (warp == 3) {
+        // ---------------------------------------------------------------- scheduler of the down units: takes the next ticket of the layer's work list a
+        // few K blocks before the producer runs out of work, fetches the tile record, waits until the tile's gate|up units have published their pieces
+        // and only then publishes the entry, so that no other role pays these round trips
+        if (lane == 0) {
+            griddep_wait();   // the work-list words are cleared by the kernel this one depends on
+            for (uint32_t i = 0;; i++) {
+                const uint32_t need = gu_kbs + i * KBA;   // K blocks the producer has issued when it asks for entry i
+                bool ok = true;
+                for (uint32_t spin = 0; s_prog + FFN_AHEAD < need; spin++) {
+                    if (spin > SPIN_LIMIT || *abort_flag) { ok = false; break; }
+                    __nanosleep(64);
+                }
+                uint32_t v = 0xffffffffu;
+                if (ok && n_dn) { v = atomicAdd(a.sched, 1u); if (v >= n_dn) v = 0xffffffffu; }
+                if (v != 0xffffffffu) {
+                    const uint32_t tile = v / PD;
+                    const uint4 t = a.tiles[tile];
+                    if (tile_ready(tile, 21)) s_tile[i % FFN_RING] = t; else v = 0xffffffffu;
+                }
+                s_units[i % FFN_RING] = v;
+                __threadfence_block();
+                s_published = i + 1;
+                if (v == 0xffffffffu) break;
+            }
         }
     } else if (warp >= 4) {
         // ---------------------------------------------------------------- promotion + epilogue: two groups of 4 warps take alternate units
@@ -269,7 +287,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
             const Unit q = decode(u);
             if ((n & 1u) != g) { it += q.KB; continue; }
             if (n > 0 && !(ok = mbar_wait(turn_bar(g), turns++ & 1u, abort_flag, a.err, 9))) break;
-            const uint4 t = a.tiles[q.tile]; const uint32_t cnt = t.z, b = n & 1u;
+            const uint4 t = tile_at(n, q.tile); const uint32_t cnt = t.z, b = n & 1u;
             if (!(ok = mbar_wait(scfull_bar(b), (n >> 1) & 1u, abort_flag, a.err, 8))) break;
             float acc0[MMA_TOK], acc1[MMA_TOK];
 #pragma unroll
