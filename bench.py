@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--engine", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8)
     ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline and the prefill-layer measurement out (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "w4", "mxfp4", "decode_layer"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "w4", "mxfp4", "nvfp4", "decode_layer"],
                     help="decode: the 48-layer stack the metric is quoted on (default); prefill: one layer, 4096 tokens, skewed routing, plain FP8 activations; "
                          "gemv: the single FP8 projection [768, 2048] on cold weights; w4: the W4 GEMM 16 x 4096 x 4096 on cold weights; decode_layer: one layer, 64 tokens")
     ap.add_argument("--tile-rows", type=int, default=0, help="prefill: 0 = library's choice, 32 or 128 = force the row-tile size")
@@ -373,7 +373,7 @@ def run_ours(args, rank, world):
         except Exception as e:   # the headline line is printed whatever happens to the side measurement
             out["prefill"] = {"error": "%s: %s" % (type(e).__name__, e)}
         # the three smaller configurations of the benchmark definition, each on cold weights
-        for key, fn in (("gemv", run_gemv), ("w4", run_w4), ("mxfp4", run_mxfp4), ("decode_layer", run_decode_layer)):
+        for key, fn in (("gemv", run_gemv), ("w4", run_w4), ("mxfp4", run_mxfp4), ("nvfp4", run_nvfp4), ("decode_layer", run_decode_layer)):
             try:
                 r = fn(pa)
                 out[key] = {"workload": r["config"]["workload"], "value": r["value"], "unit": r["unit"], "us_per_call": r["ms_per_step"] * 1e3, "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
@@ -539,8 +539,12 @@ def run_mxfp4(args):
     return run_w4(args, mxfp4=True)
 
 
-def run_w4(args, mxfp4=False):
-    """(mxfp4=True: the same shape with MXFP4 weights, E2M1 + E8M0 per 32, the reference's docs/models/MXFP4.md format.)
+def run_nvfp4(args):
+    return run_w4(args, mxfp4=True, nvfp4=True)
+
+
+def run_w4(args, mxfp4=False, nvfp4=False):
+    """(nvfp4=True: E2M1 + unsigned E4M3 scale per 16, the reference's native/models/nvfp4.om.) (mxfp4=True: the same shape with MXFP4 weights, E2M1 + E8M0 per 32, the reference's docs/models/MXFP4.md format.)
     The W4 GEMM of the benchmark definition: x bf16 [16, 4096] times W int4 [4096, 4096] (two per byte, fp16 scale per 32 columns), bf16 out.
     Cold method as for the single projection: 16 disjoint weight copies (151 MB, more than L2) rotated inside one CUDA graph. No reference
     counterpart (the reference refuses integer W4), so there is no CPU reference arm for it."""
@@ -557,10 +561,13 @@ def run_w4(args, mxfp4=False):
     tensors = []
     if mxfp4:
         packed = rng.integers(0, 256, (n, k // 2)).astype(np.uint8); scale8 = rng.integers(118, 124, (n, k // 32)).astype(np.uint8)
+        if nvfp4:
+            scale8 = rng.integers(40, 72, (n, k // 16)).astype(np.uint8)
     for _ in range(sets):                                                                   # the same values in 16 separate device buffers: the timing needs distinct memory
         t = C.c_void_p()
         if mxfp4:
-            assert api.lib.omega_gpu_mxfp4_upload(C.c_uint32(n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), scale8.ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
+            up = api.lib.omega_gpu_nvfp4_upload if nvfp4 else api.lib.omega_gpu_mxfp4_upload
+            assert up(C.c_uint32(n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), scale8.ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
             tensors.append(t)
             continue
         assert api.lib.omega_gpu_w4_upload(C.c_uint32(n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), scale.view(np.uint16).ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
@@ -576,13 +583,13 @@ def run_w4(args, mxfp4=False):
     cold_ms = _timed_graph(torch, stream, record, 10) / sets
     for t in tensors:
         api.lib.omega_gpu_w4_free(t)
-    alg = n * k // 2 + n * (k // 32) * (1 if mxfp4 else 2) + m * k * 2 + m * n * 2
+    alg = n * k // 2 + n * (k // 32) * (2 if nvfp4 or not mxfp4 else 1) + m * k * 2 + m * n * 2
     peak, kind = measured_peak()
     ach = alg / (cold_ms * 1e-3) / 1e9
     return {"metric": "w4_gemm_calls_per_s", "value": 1.0 / (cold_ms * 1e-3), "unit": "calls/s", "n_gpus": 1, "steps": 10 * sets, "warmup": 3 * sets, "ms_per_step": cold_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights, fp16 group scales, f32 accumulate", "data": "synthetic",
-            "config": {"workload": "MXFP4 GEMM: x bf16 [16, 4096] x W e2m1 [4096, 4096], E8M0 scale per 32 columns" if mxfp4 else "W4 GEMM: x bf16 [16, 4096] x W int4 [4096, 4096], fp16 scale per 32 columns", "l2": "calls rotate through 16 disjoint weight copies (151 MB) inside one CUDA graph",
-                       "tflops": 2.0 * m * n * k / (cold_ms * 1e-3) / 1e12, "parity": "element decoder pinned to the reference's mxfp4 oracle; the GEMM itself has no reference counterpart" if mxfp4 else "unpinned: the reference has no integer-W4 arithmetic"},
+            "config": {"workload": "NVFP4 GEMM: x bf16 [16, 4096] x W e2m1 [4096, 4096], unsigned E4M3 scale per 16 columns" if nvfp4 else "MXFP4 GEMM: x bf16 [16, 4096] x W e2m1 [4096, 4096], E8M0 scale per 32 columns" if mxfp4 else "W4 GEMM: x bf16 [16, 4096] x W int4 [4096, 4096], fp16 scale per 32 columns", "l2": "calls rotate through 16 disjoint weight copies (151 MB) inside one CUDA graph",
+                       "tflops": 2.0 * m * n * k / (cold_ms * 1e-3) / 1e12, "parity": "element x scale decoder pinned to the reference's nvfp4 oracle; the bf16 x NVFP4 GEMM itself has no reference counterpart" if nvfp4 else "element decoder pinned to the reference's mxfp4 oracle; the GEMM itself has no reference counterpart" if mxfp4 else "unpinned: the reference has no integer-W4 arithmetic"},
             "gpu_launches": 10 * sets,
             "roofline": {"bound": "hbm", "kernel": "w4_mma_kernel", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind + " copy bandwidth",
                          "algorithmic_bytes": alg, "kernel_ms": cold_ms, "traffic": None, "note": "latency- and issue-bound: int4 / e2m1 expanded to bf16 in registers, mma.sync m16n8k16, four K quarters joined per output block"}}
@@ -653,9 +660,9 @@ def main():
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
-    elif args.workload in ("prefill", "gemv", "w4", "mxfp4", "decode_layer"):
+    elif args.workload in ("prefill", "gemv", "w4", "mxfp4", "nvfp4", "decode_layer"):
         if rank == 0:
-            print(json.dumps({"prefill": run_prefill, "gemv": run_gemv, "w4": run_w4, "mxfp4": run_mxfp4, "decode_layer": run_decode_layer}[args.workload](args)))
+            print(json.dumps({"prefill": run_prefill, "gemv": run_gemv, "w4": run_w4, "mxfp4": run_mxfp4, "nvfp4": run_nvfp4, "decode_layer": run_decode_layer}[args.workload](args)))
     else:
         run_ours(args, rank, world)
 

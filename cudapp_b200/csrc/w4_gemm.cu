@@ -130,7 +130,10 @@ __device__ __forceinline__ void e2m1x8_bf16(uint32_t v, uint32_t *b) {
     }
 }
 
-template <int GQ, int FMT>   // scale groups per K quarter: k = 128 * GQ; FMT 0: int4 + fp16 scales, 1: E2M1 + E8M0 scales (MXFP4)
+// FMT 2 (NVFP4: E2M1 + one unsigned E4M3 scale per 16 columns): a 32-column group holds two scale groups, so its two MMAs must be columns 0..15 and
+// 16..31. Thread t of a quad then feeds columns 4t .. 4t+3 to the first MMA and 16+4t .. 16+4t+3 to the second: the two 16-bit halves it needs sit in
+// the words of quad threads t/2 and 2 + t/2 (one shuffle each); each MMA goes into its own fresh accumulator and is scaled by its own scale.
+template <int GQ, int FMT>   // 32-column groups per K quarter: k = 128 * GQ; FMT 0: int4 + fp16 scales, 1: E2M1 + E8M0 scales (MXFP4), 2: E2M1 + UE4M3 per 16 (NVFP4)
 __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m, uint32_t n, uint32_t k, const uint8_t *__restrict__ w, const uint16_t *__restrict__ sc,
                                                         const uint16_t *__restrict__ x, uint16_t *__restrict__ y16, float *__restrict__ y32, float *part, uint32_t *counters) {
     constexpr uint32_t KQ = GQ * 32u, XS = KQ * 2u + 64u;   // columns per quarter; bytes between panel rows (the 64 keep a quarter-warp's 16-byte reads on separate banks)
@@ -145,9 +148,9 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
 #pragma unroll
     for (int g = 0; g < GQ; g++) wq[g] = __ldcs(wrow + g * 4 + t);
     // scales of the two output columns this thread's accumulators belong to (n0 + 2t, n0 + 2t + 1): GQ values each, fp16 (FMT 0) or E8M0 bytes (FMT 1)
-    constexpr int SB = FMT ? 1 : 2, SV = GQ * SB / 16 > 0 ? GQ * SB / 16 : 1;   // bytes per scale; 16-byte vectors per row (GQ = 8 bytes of E8M0: half a vector, loaded as 8 bytes)
+    constexpr int SB = FMT == 1 ? 1 : 2, SV = GQ * SB / 16 > 0 ? GQ * SB / 16 : 1;   // bytes per scale; 16-byte vectors per row (GQ = 8 bytes of E8M0: half a vector, loaded as 8 bytes)
     const uint8_t *scb = reinterpret_cast<const uint8_t *>(sc);
-    const uint8_t *s0b = scb + ((size_t)(n0 + 2u * t) * (k / 32u) + kq * GQ) * SB, *s1b = scb + ((size_t)(n0 + 2u * t + 1u) * (k / 32u) + kq * GQ) * SB;
+    const uint8_t *s0b = scb + ((size_t)(n0 + 2u * t) * (k / 32u) + kq * GQ) * SB, *s1b = scb + ((size_t)(n0 + 2u * t + 1u) * (k / 32u) + kq * GQ) * SB;   // FMT 2: two scale bytes per 32 columns
     uint4 sv0[SV], sv1[SV];
     if (GQ * SB >= 16) {
 #pragma unroll
@@ -167,10 +170,28 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int g = 0; g < GQ; g++) {
-        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + r * XS + g * 64 + t * 16u);          // panel row r, columns 8t .. 8t+7 of group g
-        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + (r + 8u) * XS + g * 64 + t * 16u);   // panel row r + 8
         float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         uint32_t bq[4];
+        if (FMT == 2) {
+            const uint32_t wa = __shfl_sync(0xffffffffu, wq[g], (lane & ~3u) | (t >> 1)), wb = __shfl_sync(0xffffffffu, wq[g], (lane & ~3u) | 2u | (t >> 1));
+            const uint32_t v = (t & 1u) ? ((wa >> 16) | (wb & 0xffff0000u)) : ((wa & 0xffffu) | (wb << 16));   // nibbles 0..3: columns 4t..4t+3, nibbles 4..7: columns 16+4t..
+            e2m1x8_bf16(v, bq);
+            const uint2 xa = *reinterpret_cast<const uint2 *>(xq + r * XS + g * 64 + t * 8u), xb = *reinterpret_cast<const uint2 *>(xq + (r + 8u) * XS + g * 64 + t * 8u);
+            const uint2 xc = *reinterpret_cast<const uint2 *>(xq + r * XS + g * 64 + 32u + t * 8u), xd = *reinterpret_cast<const uint2 *>(xq + (r + 8u) * XS + g * 64 + 32u + t * 8u);
+            float p2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma_bf16_16816(p, xa.x, xb.x, xa.y, xb.y, bq[0], bq[1]);
+            mma_bf16_16816(p2, xc.x, xd.x, xc.y, xd.y, bq[2], bq[3]);
+            const uint32_t *u0 = reinterpret_cast<const uint32_t *>(&sv0[g >> 3]), *u1 = reinterpret_cast<const uint32_t *>(&sv1[g >> 3]);
+            const uint32_t h0 = (u0[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu, h1 = (u1[(g & 7) >> 1] >> (16 * (g & 1))) & 0xffffu;
+            // unsigned E4M3: (8 + m) * 2^(e - 10) for e > 0 (binary32 exponent field e + 120), m * 2^-9 for e = 0
+            auto ue4m3 = [](uint32_t c) -> float { return (c >> 3) ? __uint_as_float((((c >> 3) + 120u) << 23) | ((c & 7u) << 20)) : (float)(c & 7u) * 0.001953125f; };
+            const float a0 = ue4m3(h0 & 0xffu), a1 = ue4m3(h0 >> 8), c0 = ue4m3(h1 & 0xffu), c1 = ue4m3(h1 >> 8);
+            acc[0] = fmaf(p[0], a0, acc[0]); acc[1] = fmaf(p[1], c0, acc[1]); acc[2] = fmaf(p[2], a0, acc[2]); acc[3] = fmaf(p[3], c0, acc[3]);
+            acc[0] = fmaf(p2[0], a1, acc[0]); acc[1] = fmaf(p2[1], c1, acc[1]); acc[2] = fmaf(p2[2], a1, acc[2]); acc[3] = fmaf(p2[3], c1, acc[3]);
+            continue;
+        }
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + r * XS + g * 64 + t * 16u);          // panel row r, columns 8t .. 8t+7 of group g
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + (r + 8u) * XS + g * 64 + t * 16u);   // panel row r + 8
         if (FMT) e2m1x8_bf16(wq[g], bq);
         else { bq[0] = nib2_bf16(wq[g], 0); bq[1] = nib2_bf16(wq[g], 1); bq[2] = nib2_bf16(wq[g], 2); bq[3] = nib2_bf16(wq[g], 3); }
         mma_bf16_16816(p, xa.x, xb.x, xa.y, xb.y, bq[0], bq[1]);
@@ -256,6 +277,30 @@ int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const 
     *out = t;
     return OMEGA_GPU_FP8_OK;
 }
+/* NVFP4 weights (E2M1 nibbles, low nibble = even column, one unsigned E4M3 scale per 16 columns, no second-level scale: the reference's
+ * native/models/nvfp4.om, docs/models/MXFMT.md). Scale codes 0..126 only: 127 is NaN and 128..255 carry a sign bit, both refused as that unit does. */
+int omega_gpu_nvfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_ue4m3, OmegaGpuW4Tensor **out) {
+    if (out) *out = nullptr;
+    if (!out || !packed || !scale_ue4m3 || !n || !k) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (n % 128u || !(k == 1024u || k == 2048u || k == 4096u)) { set_error("nvfp4 upload: n must be a multiple of 128 and k 1024, 2048 or 4096"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    for (size_t i = 0; i < (size_t)n * (k / 16); i++) {
+        if (scale_ue4m3[i] == 0x7fu) { set_error("nvfp4 upload: scale 127 (NaN) at group %zu", i); return OMEGA_GPU_FP8_NAN_WEIGHT; }
+        if (scale_ue4m3[i] > 0x7fu) { set_error("nvfp4 upload: scale code %u at group %zu has the sign bit set", (unsigned)scale_ue4m3[i], i); return OMEGA_GPU_FP8_BAD_ARGS; }
+    }
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    OmegaGpuW4Tensor *t = (OmegaGpuW4Tensor *)calloc(1, sizeof *t);
+    if (!t) return OMEGA_GPU_FP8_BAD_ARGS;
+    t->n = n; t->k = k; t->fmt = 2;
+    const size_t wb = (size_t)n * k / 2, sb = (size_t)n * (k / 16), pb = (size_t)4 * 16 * n * 4, cb = (size_t)(n / 128u) * 4;
+    const bool ok = cuda_ok(cudaMalloc(&t->w, wb), "cudaMalloc(nvfp4)") && cuda_ok(cudaMalloc((void **)&t->s, sb), "cudaMalloc(nvfp4 scales)") &&
+                    cuda_ok(cudaMemcpy(t->w, packed, wb, cudaMemcpyHostToDevice), "copy nvfp4") && cuda_ok(cudaMemcpy(t->s, scale_ue4m3, sb, cudaMemcpyHostToDevice), "copy nvfp4 scales") &&
+                    cuda_ok(cudaMalloc(&t->part, pb), "cudaMalloc(nvfp4 partials)") && cuda_ok(cudaMalloc(&t->counters, cb), "cudaMalloc(nvfp4 counters)") &&
+                    cuda_ok(cudaMemset(t->counters, 0, cb), "memset");
+    if (!ok) { if (t->w) cudaFree(t->w); if (t->s) cudaFree(t->s); if (t->part) cudaFree(t->part); if (t->counters) cudaFree(t->counters); free(t); return OMEGA_GPU_FP8_CHIP_FAIL; }
+    *out = t;
+    return OMEGA_GPU_FP8_OK;
+}
 void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     if (!t) return;
     Lock l;
@@ -270,7 +315,8 @@ static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16
         const dim3 grid(t->n / 128u, 4);
         for (uint32_t m0 = 0; m0 < m; m0 += 16u) {
 #define W4_LAUNCH(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters)
-            if (t->fmt) { if (t->k == 4096u) W4_LAUNCH(32, 1); else if (t->k == 2048u) W4_LAUNCH(16, 1); else W4_LAUNCH(8, 1); }
+            if (t->fmt == 2) { if (t->k == 4096u) W4_LAUNCH(32, 2); else if (t->k == 2048u) W4_LAUNCH(16, 2); else W4_LAUNCH(8, 2); }
+            else if (t->fmt) { if (t->k == 4096u) W4_LAUNCH(32, 1); else if (t->k == 2048u) W4_LAUNCH(16, 1); else W4_LAUNCH(8, 1); }
             else { if (t->k == 4096u) W4_LAUNCH(32, 0); else if (t->k == 2048u) W4_LAUNCH(16, 0); else W4_LAUNCH(8, 0); }
 #undef W4_LAUNCH
         }

@@ -72,6 +72,11 @@ void omega_gpu_w4_free(OmegaGpuW4Tensor *t);
  * k 1024, 2048 or 4096. The tensor is used with omega_gpu_w4_gemm_bf16 / _async and freed with omega_gpu_w4_free. The reference has no MXFP4 GEMM
  * ("a scalar primitive, not a GEMM"), so the product y = x W^T is defined here: per group the sum of x * element, times 2^(scale - 127), f32. */
 int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_e8m0, OmegaGpuW4Tensor **out);
+/* NVFP4 weights: E2M1 nibbles [n][k/2] (low nibble = even column) and one unsigned E4M3 scale per 16 columns [n][k/16], the reference's
+ * native/models/nvfp4.om (docs/models/MXFMT.md); an element's value is what its nvfp4bits returns; no second-level per-tensor scale, as there.
+ * Scale 127 (NaN) -> NAN_WEIGHT, a scale with the sign bit set -> BAD_ARGS (that unit refuses both); n % 128 == 0, k 1024, 2048 or 4096.
+ * The tensor runs through omega_gpu_w4_gemm_bf16 / _async. */
+int omega_gpu_nvfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_ue4m3, OmegaGpuW4Tensor **out);
 /* y bf16 [m][n] = x bf16 [m][k] * W^T, f32 accumulation; yf32 (optional) receives the unrounded values */
 int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32);
 /* the same on device buffers, stream-ordered (one of y_bf16_va / y_f32_va may be 0) */

@@ -534,6 +534,39 @@ void orc_mxfp4_gemm_rows(const uint8_t *packed, const uint8_t *scale_e8m0, uint3
     }
 }
 
+/* ------------------------------------------------------------------ NVFP4 (E2M1 nibble + unsigned E4M3 scale per 16 elements) */
+
+/* One NVFP4 element times its block scale as exact IEEE binary32 bits: what the reference's scalar decoder returns (native/models/nvfp4.om,
+ * nvfp4bits; contract docs/models/MXFMT.md: "nvfp4bits nib scale gives the exact binary32 bits of element x scale"; its verification oracle
+ * tests/models/mxfmt-check.py:287-300 compares with the ml_dtypes product float4_e2m1fn x float8_e4m3fn and with exact rationals).
+ * nib 0..15 (bit 3 = sign), scale 0..126: an E4M3 code with the sign bit clear; 127 (NaN) and 128..255 (sign set) are refused by that unit
+ * (trap 5): here they return 0xffffffff, which no valid pair produces. Signed zero kept. Integer arithmetic and one exact ldexp. */
+uint32_t orc_nvfp4_bits(uint32_t nib, uint32_t scale) {
+    if (nib > 15u || scale > 126u) return 0xffffffffu;
+    const uint32_t sign = (nib & 8u) << 28, m = nib & 7u;
+    const uint32_t twice = m < 4u ? m : (2u + (m & 1u)) << ((m >> 1) - 1u);        /* 2 x {0, .5, 1, 1.5, 2, 3, 4, 6} */
+    const uint32_t se = scale >> 3, sig = se ? ((scale & 7u) | 8u) : (scale & 7u);   /* scale = sig * 2^(se ? se - 10 : -9) */
+    if (twice == 0 || sig == 0) return sign;
+    const float v = ldexpf((float)(twice * sig), (se ? (int)se - 10 : -9) - 1);     /* at most 12 * 15 = 180: exact, and never subnormal */
+    uint32_t bits; memcpy(&bits, &v, 4);
+    return sign | bits;
+}
+/* y[m][r] = sum over columns of x[m][c] * (element[r][c] * scale[r][c / 16]) in double, columns in order; low nibble = even column
+ * (native/models/nvfp4.om: "element 2i is the low nibble of byte i"). rows [r0, r1) */
+void orc_nvfp4_gemm_rows(const uint8_t *packed, const uint8_t *scale_ue4m3, uint32_t k, uint32_t r0, uint32_t r1,
+                         uint32_t n, const float *x, uint32_t m_rows, double *y) {
+    for (uint32_t r = r0; r < r1; r++) for (uint32_t m = 0; m < m_rows; m++) {
+        double acc = 0.0;
+        for (uint32_t c = 0; c < k; c++) {
+            const uint8_t b = packed[((size_t)r * k + c) / 2];
+            const uint32_t bits = orc_nvfp4_bits((c & 1u) ? (b >> 4) : (b & 15u), scale_ue4m3[(size_t)r * (k / 16) + c / 16]);
+            float w; memcpy(&w, &bits, 4);
+            acc += (double)x[(size_t)m * k + c] * (double)w;
+        }
+        y[(size_t)m * n + r] = acc;
+    }
+}
+
 /* ------------------------------------------------------------------ one MoE layer, the reference host glue */
 
 /* For sorted row p (expert e, token t, slot s): gu = GEMV(W_gu[e], x[t]) (double dot, stored f32, as a

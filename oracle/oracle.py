@@ -305,6 +305,29 @@ def mxfp4_gemm(packed, scale_e8m0, x, threads=None):
     return y
 
 
+def nvfp4_bits(nib, scale):
+    L = lib(); L.orc_nvfp4_bits.restype = C.c_uint32
+    return int(L.orc_nvfp4_bits(C.c_uint32(int(nib)), C.c_uint32(int(scale))))
+
+
+def nvfp4_gemm(packed, scale_ue4m3, x, threads=None):
+    """packed u8 [n][k/2] (low nibble = even column), scale u8 [n][k/16] (E4M3 codes 0..126), x f32 [m][k] -> y f64 [m][n]"""
+    import concurrent.futures as cf
+    packed = np.ascontiguousarray(packed, dtype=np.uint8); sc = np.ascontiguousarray(scale_ue4m3, dtype=np.uint8); x = np.ascontiguousarray(x, dtype=np.float32)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    m = x.shape[0]
+    y = np.empty((m, n), np.float64)
+    L = lib()
+    threads = threads or min(os.cpu_count() or 1, 32)
+    step = max(1, (n + threads - 1) // threads)
+
+    def run(r0):
+        L.orc_nvfp4_gemm_rows(_ptr(packed, U8P), _ptr(sc, U8P), C.c_uint32(k), C.c_uint32(r0), C.c_uint32(min(n, r0 + step)), C.c_uint32(n), _ptr(x, F32P), C.c_uint32(m), _ptr(y, F64P))
+    with cf.ThreadPoolExecutor(threads) as ex:
+        list(ex.map(run, range(0, n, step)))
+    return y
+
+
 def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, threads=None, x_pieces=0, act_pieces=0):
     """Gate|up GEMV, SwiGLU and down GEMV for every sorted row (the reference host glue); ctypes releases
     the GIL, so rows are spread over `threads` host threads. Returns dn f32 [n_dest][hidden]."""

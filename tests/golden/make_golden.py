@@ -91,6 +91,16 @@ def main():
     ref = np.empty((6, 256), np.float32)
     MC.ref_mc(p(down, F32P), p(inv, U32P), p(wt, F32P), C.c_uint32(6), C.c_uint32(256), C.c_uint32(8), p(ref, F32P))
     out["mc_out"] = ref
+    # NVFP4 element x scale: the exact rationals of the reference's verification script (tests/models/mxfmt-check.py: e2m1, ue4m3), as binary32 bits
+    import importlib.util
+    from tests.test_oracle_pin import MXFMT
+    spec = importlib.util.spec_from_file_location("mxfmt_check", MXFMT); mx = importlib.util.module_from_spec(spec); spec.loader.exec_module(mx)
+    tab = np.empty((16, 127), np.uint32)
+    for n in range(16):
+        for c in range(127):
+            v = mx.e2m1(n) * mx.ue4m3(c)
+            tab[n, c] = mx.frac_to_f32bits(abs(v)) | ((n & 8) << 28)        # the sign of a zero product is the element's
+    out["nvfp4_bits"] = tab
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **out)
     print("wrote", os.path.join(HERE, "reference_vectors.npz"), {k_: v_.shape for k_, v_ in out.items()})
 

@@ -81,3 +81,9 @@ def test_combine_prefill_form():
     """slot-order multiply-then-add combine against mc_ref of the reference's prefill host-kernel test"""
     down, inv, wt = mc_case(31, 6, 256, 8)
     assert np.array_equal(orc.combine_mc(down, inv, wt).view(np.uint32), G["mc_out"].view(np.uint32))
+
+
+def test_nvfp4_decode_table():
+    """every NVFP4 element x scale pair against the table made from the reference's verification script"""
+    mine = np.array([orc.nvfp4_bits(n, c) for n in range(16) for c in range(127)], np.uint32).reshape(16, 127)
+    assert np.array_equal(mine, G["nvfp4_bits"])

@@ -194,3 +194,30 @@ def test_mxfp4_gemm(n, k, m):
     assert rel_l2(y32, ref) <= 1e-3 and np.array_equal(y16, orc.bf16_bits(y32))
     rc, _, yb = api.w4_gemm_bf16(t, n, xb); assert rc == 0 and np.array_equal(yb.view(np.uint32), y32.view(np.uint32))
     api.lib.omega_gpu_w4_free(t)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 16), (128, 2048, 21), (4096, 4096, 16)])
+def test_nvfp4_gemm(n, k, m):
+    """NVFP4 weights (E2M1 + one unsigned E4M3 scale per 16 columns: native/models/nvfp4.om of the reference) times bf16 activations against the
+    double checker, whose element x scale decoder equals the reference's verification oracle for every pair (tests/test_oracle_pin.py). Every nibble
+    and every valid scale code occur (zero and subnormal scales among them); NaN and sign-set scales are refused at upload."""
+    rng = np.random.default_rng(n + k + 1)
+    packed = rng.integers(0, 256, (n, k // 2)).astype(np.uint8)
+    scale = rng.integers(0, 127, (n, k // 16)).astype(np.uint8)
+    scale[0, 0] = 0; scale[1, 1] = 1; scale[n - 1, k // 16 - 1] = 126
+    xb = orc.bf16_bits(rng.normal(0, 1, (m, k)).astype(np.float32))
+    t = C.c_void_p()
+    up = lambda kk, sc: api.lib.omega_gpu_nvfp4_upload(C.c_uint32(n), C.c_uint32(kk), packed.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p), C.byref(t))
+    bad = scale.copy(); bad[3, 2] = 127
+    assert up(k, bad) == api.NAN_WEIGHT and not t.value
+    bad[3, 2] = 0x88
+    assert up(k, bad) == api.BAD_ARGS and not t.value
+    assert up(k + 32, scale) == api.BAD_ARGS
+    assert up(k, scale) == 0, api.last_error()
+    rc, y16, y32 = api.w4_gemm_bf16(t, n, xb); assert rc == 0, api.last_error()
+    ref = orc.nvfp4_gemm(packed, scale, orc.bf16_to_f32(xb))
+    mag = orc.nvfp4_gemm(packed & 0x77, scale, np.abs(orc.bf16_to_f32(xb)))                 # sum of |terms|
+    assert np.all(np.abs(y32 - ref) <= 1e-5 * mag + 1e-30), float(np.max(np.abs(y32 - ref) / (mag + 1e-30)))
+    assert rel_l2(y32, ref) <= 1e-3 and np.array_equal(y16, orc.bf16_bits(y32))
+    rc, _, yb = api.w4_gemm_bf16(t, n, xb); assert rc == 0 and np.array_equal(yb.view(np.uint32), y32.view(np.uint32))
+    api.lib.omega_gpu_w4_free(t)

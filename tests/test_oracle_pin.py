@@ -433,3 +433,40 @@ def test_mxfp4_decoder_against_reference_oracle():
     spec = importlib.util.spec_from_file_location("mxfp4_check", MXCHECK); m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)
     want = b"".join(m.oracle(p, l, s) for s in range(255) for p in range(256) for l in range(2))
     assert want == mxfp4_all_records()
+
+
+# ------------------------------------------------------------------ NVFP4 element x scale decoder (native/models/nvfp4.om; oracle tests/models/mxfmt-check.py:278-300)
+def nvfp4_all_pairs():
+    """bits of every element x valid scale pair, element-major: the order of the reference's own decode check"""
+    return np.array([orc.nvfp4_bits(n, c) for n in range(16) for c in range(127)], np.uint32)
+
+
+def test_nvfp4_decoder_against_ml_dtypes():
+    """the comparison the reference's check makes (tests/models/mxfmt-check.py:289-295): the binary32 product of the ml_dtypes values, exact"""
+    ml = pytest.importorskip("ml_dtypes")
+    nib = np.repeat(np.arange(16, dtype=np.uint8), 127); sc = np.tile(np.arange(127, dtype=np.uint8), 16)
+    f4 = nib.view(ml.float4_e2m1fn).astype(np.float64); f8 = sc.view(ml.float8_e4m3fn).astype(np.float64)
+    prod = (f4 * f8).astype(np.float32)
+    assert np.all(prod.astype(np.float64) == f4 * f8)                          # exact in binary32
+    assert np.array_equal(nvfp4_all_pairs(), prod.view(np.uint32))             # signed zeros included
+    for bad in (127, 128, 255):                                                # NaN scale and sign-set scales: refused by the unit (trap 5)
+        assert orc.nvfp4_bits(3, bad) == 0xffffffff
+    assert orc.nvfp4_bits(7, 126) == np.array([6.0 * 448.0], np.float32).view(np.uint32)[0]
+    assert orc.nvfp4_bits(1, 1) == np.array([2.0 ** -10], np.float32).view(np.uint32)[0]
+
+
+MXFMT = os.path.join(os.path.dirname(MXCHECK), "mxfmt-check.py")
+
+
+@pytest.mark.skipif(not os.path.exists(MXFMT), reason="the reference tree is not on this machine")
+def test_nvfp4_decoder_against_reference_oracle():
+    """every pair against the exact rationals of the reference's verification script itself (its e2m1 and ue4m3 functions)"""
+    pytest.importorskip("ml_dtypes")                                           # the script imports it at load
+    import importlib.util
+    from fractions import Fraction
+    spec = importlib.util.spec_from_file_location("mxfmt_check", MXFMT); m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)
+    got = nvfp4_all_pairs().view(np.float32).reshape(16, 127)
+    for n in range(16):
+        for c in range(127):
+            assert Fraction(float(got[n, c])) == m.e2m1(n) * m.ue4m3(c), (n, c)
+            assert bool(np.signbit(got[n, c])) == bool(n & 8)
