@@ -292,66 +292,13 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
             float acc0[MMA_TOK], acc1[MMA_TOK];
 #pragma unroll
             for (int i = 0; i < MMA_TOK; i++) { acc0[i] = 0.0f; acc1[i] = 0.0f; }
-            // promotion of one half (one 128-feature block) of a K block: pieces folded last to first (x 1/16 each), then acc += Sw * Sa * partial
-            auto promote = [&](uint32_t (&v)[MMA_TOK], const float *sc, float (&acc)[MMA_TOK]) {
-#pragma unroll
-                for (int i = 0; i < MMA_TOK; i += 4) {
-                    const float4 c = *reinterpret_cast<const float4 *>(sc + i);
-                    acc[i] = fmaf(__uint_as_float(v[i]), c.x, acc[i]); acc[i + 1] = fmaf(__uint_as_float(v[i + 1]), c.y, acc[i + 1]);
-                    acc[i + 2] = fmaf(__uint_as_float(v[i + 2]), c.z, acc[i + 2]); acc[i + 3] = fmaf(__uint_as_float(v[i + 3]), c.w, acc[i + 3]);
-                }
-            };
             auto kloop = [&](auto pc) {
                 constexpr int P = decltype(pc)::value;
                 for (uint32_t kb = 0; kb < q.KB; kb++, it++) {
                     const Slot sl = acc_slot(it);
-                    const uint32_t buf = sl.buf;
-                    if (!(ok = mbar_wait(accfull_bar(buf), sl.use & 1u, abort_flag, a.err, 4))) return;
+                    if (!(ok = mbar_wait(accfull_bar(sl.buf), sl.use & 1u, abort_flag, a.err, 4))) return;
                     tc_fence_after();
-                    const uint32_t taddr = tmem + ((q4 * 32u) << 16) + sl.col;
-                    if constexpr (P <= 2) {
-                        // both halves in one round trip; the buffer goes back to the MMA issuer as soon as the loads have landed
-                        uint32_t h0[P][MMA_TOK], h1[P][MMA_TOK];
-#pragma unroll
-                        for (int p = P - 1; p >= 0; p--) { TMEM_LD32(taddr + p * MMA_TOK, h0[p]); TMEM_LD32(taddr + P * MMA_TOK + p * MMA_TOK, h1[p]); }
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        tc_fence_before(); mbar_arrive(accempty_bar(buf));
-                        if (P > 1) {
-#pragma unroll
-                            for (int i = 0; i < MMA_TOK; i++) {
-                                h0[0][i] = __float_as_uint(fmaf(__uint_as_float(h0[P - 1][i]), 0.0625f, __uint_as_float(h0[0][i])));
-                                h1[0][i] = __float_as_uint(fmaf(__uint_as_float(h1[P - 1][i]), 0.0625f, __uint_as_float(h1[0][i])));
-                            }
-                        }
-                        promote(h0[0], &s_sc[b][0][kb][0], acc0);
-                        promote(h1[0], &s_sc[b][1][kb][0], acc1);
-                    } else {
-                        // one half per round trip; the second half's loads fly while the first is promoted
-                        uint32_t r[P][MMA_TOK], da[MMA_TOK];
-#pragma unroll
-                        for (int p = P - 1; p >= 0; p--) TMEM_LD32(taddr + p * MMA_TOK, r[p]);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (int i = 0; i < MMA_TOK; i++) {
-                            float v = __uint_as_float(r[P - 1][i]);
-#pragma unroll
-                            for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(r[p][i]));
-                            da[i] = __float_as_uint(v);
-                        }
-#pragma unroll
-                        for (int p = P - 1; p >= 0; p--) TMEM_LD32(taddr + P * MMA_TOK + p * MMA_TOK, r[p]);
-                        promote(da, &s_sc[b][0][kb][0], acc0);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        tc_fence_before(); mbar_arrive(accempty_bar(buf));
-#pragma unroll
-                        for (int i = 0; i < MMA_TOK; i++) {
-                            float v = __uint_as_float(r[P - 1][i]);
-#pragma unroll
-                            for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(r[p][i]));
-                            da[i] = __float_as_uint(v);
-                        }
-                        promote(da, &s_sc[b][1][kb][0], acc1);
-                    }
+                    promote_kblock<P>(tmem + ((q4 * 32u) << 16) + sl.col, accempty_bar(sl.buf), &s_sc[b][0][kb][0], &s_sc[b][1][kb][0], acc0, acc1);
                 }
             };
             if (q.mode) kloop(std::integral_constant<int, PA>{}); else kloop(std::integral_constant<int, PX>{});

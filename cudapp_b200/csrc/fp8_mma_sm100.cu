@@ -45,8 +45,10 @@ struct MmaArgs {
     uint32_t wait_limit;                // iterations of the bounded wait on `gate`
 };
 
+constexpr int GRP_THREADS = 32 * 12;   // warp group 0: TMA, MMA, scale loader, one idle warp; warp groups 1 and 2: the two promotion / epilogue groups
+
 template <int P>
-__global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
+__global__ void __launch_bounds__(GRP_THREADS, 1) fp8_mma_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_q, const MmaArgs a) {
     constexpr int N = MMA_TOK * P;                                   // accumulator columns per weight tile
     constexpr int STAGES = P <= 3 ? 4 : 3;
     constexpr uint32_t STAGE_BYTES = 2 * A_TILE + P * B_PIECE;
@@ -55,7 +57,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     extern __shared__ uint8_t dyn_smem[];
     __shared__ __align__(8) uint64_t s_bar[2 * STAGES + 12];
     __shared__ uint32_t s_tmem, s_abort;
-    __shared__ float s_sc[2][2][KB_MAX][MMA_TOK]; // [scale buffer][weight tile][k block][row] = weight scale x row scale
+    __shared__ __align__(16) float s_sc[2][2][KB_MAX][MMA_TOK]; // [scale buffer][weight tile][k block][row] = weight scale x row scale
     __shared__ float s_red[2][4][MMA_TOK];        // [epilogue group][warp][row]: amax exchange
     __shared__ uint32_t s_ymap[2][MMA_TOK];       // [scale buffer][row]: destination rows (mode 1)
     __shared__ uint32_t s_ret[2][64];             // [epilogue group][rank]: result slices stored into that rank's buffer (expert parallel)
@@ -92,6 +94,8 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
     const uint32_t tmem = s_tmem;
     const uint32_t KB = a.k / 128u, n_tiles = a.header[2], total = *reinterpret_cast<volatile uint32_t *>(a.err) ? 0u : n_tiles * a.pairs;   // after a recorded failure: no work
 
+    // registers go where the promotion needs them (128 x 56 + 256 x 224 = 384 x 168); each warp group changes its own count inside its own branch
+    if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory");
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
@@ -174,9 +178,10 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             }
             mbar_arrive(scfull_bar(b));
         }
-    } else {
+    } else if (warp >= 4) {
         // ---------------------------------------------------------------- promotion + epilogue: two groups of 4 warps take alternate units
-        const uint32_t g = (warp - 3u) >> 2, q = warp & 3u, row = q * 32u + lane;   // q: the TMEM lane quarter this warp may read
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+        const uint32_t g = (warp - 4u) >> 2, q = warp & 3u, row = q * 32u + lane;   // q: the TMEM lane quarter this warp may read
         uint32_t n = 0, gsync = 0, turns = 0; bool ok = true;
         for (uint32_t u = blockIdx.x; u < total && ok; u += gridDim.x, n++) {
             if ((n & 1u) != g) continue;
@@ -193,32 +198,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
                 const uint32_t it = n * KB + kb, buf = it & 1u, bph = (it >> 1) & 1u;
                 if (!(ok = mbar_wait(accfull_bar(buf), bph, abort_flag, a.err, 4))) break;
                 tc_fence_after();
-                const uint32_t taddr = tmem + ((q * 32u) << 16) + buf * 2u * N;
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    // pieces folded highest first (Horner, x 1/16) with at most two 32-column chunks in registers
-                    uint32_t da[MMA_TOK], db[MMA_TOK];
-                    TMEM_LD32(taddr + half * N + (P - 1) * MMA_TOK, da);
-                    if (P > 1) TMEM_LD32(taddr + half * N + (P - 2) * MMA_TOK, db);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (P > 1) {
-#pragma unroll
-                        for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));
-                    }
-#pragma unroll
-                    for (int p = P - 3; p >= 0; p--) {
-                        TMEM_LD32(taddr + half * N + p * MMA_TOK, db);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (int i = 0; i < MMA_TOK; i++) da[i] = __float_as_uint(fmaf(__uint_as_float(da[i]), 0.0625f, __uint_as_float(db[i])));
-                    }
-                    if (half == 1) { tc_fence_before(); mbar_arrive(accempty_bar(buf)); }   // the partial is in registers
-#pragma unroll
-                    for (int i = 0; i < MMA_TOK; i++) {
-                        const float sc = s_sc[b][half][kb][i];
-                        if (half) acc1[i] = fmaf(__uint_as_float(da[i]), sc, acc1[i]); else acc0[i] = fmaf(__uint_as_float(da[i]), sc, acc0[i]);
-                    }
-                }
+                promote_kblock<P>(tmem + ((q * 32u) << 16) + buf * 2u * N, accempty_bar(buf), &s_sc[b][0][kb][0], &s_sc[b][1][kb][0], acc0, acc1);
             }
             if (!ok) break;
             mbar_arrive(turn_bar(g ^ 1u));   // the other group may start on the next unit's partials
@@ -259,7 +239,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
                 mbar_arrive(group_bar(g));
                 if (!(ok = mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 6))) break;
                 // copy out: every (piece, row) is 128 consecutive bytes in memory; 16 bytes per thread per step
-                const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                const uint32_t et = row;
                 for (uint32_t c = et; c < a.q_pieces * MMA_TOK * 8u; c += 128u) {
                     const uint32_t r = c >> 3, p = r / MMA_TOK, i = r - p * MMA_TOK;
                     if (i < cnt) *reinterpret_cast<uint4 *>(a.q_out + ((size_t)p * a.q_rows + t.y + i) * a.inter + j * 128u + (c & 7u) * 16u) = *reinterpret_cast<const uint4 *>(sq + (size_t)c * 16u);
@@ -285,7 +265,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
                         float *o = reinterpret_cast<float *>(a.out_peers[owner]) + (size_t)(y - owner * a.rows_per_rank) * a.out_stride;
                         o[r0 + row] = acc0[i]; o[r1 + row] = acc1[i];
                     }
-                const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                const uint32_t et = row;
                 if (et < cnt) atomicAdd(&s_ret[g][s_ymap[b][et] / a.rows_per_rank], 1u);   // published once, after the last unit
             }
             mbar_arrive(scempty_bar(b));   // this unit's scales and destination rows may be overwritten
@@ -295,7 +275,7 @@ __global__ void __launch_bounds__(MMA_THREADS, 1) fp8_mma_grouped_kernel(const _
             // (a fence is cumulative) and advance each owner's counter once
             mbar_arrive(group_bar(g));
             if (mbar_wait(group_bar(g), gsync++ & 1u, abort_flag, a.err, 15)) {
-                const uint32_t et = (warp - 3u - 4u * g) * 32u + lane;
+                const uint32_t et = row;
                 if (et < 64u && s_ret[g][et]) __threadfence_system();
                 if (et < 64u && s_ret[g][et]) atomicAdd_system(reinterpret_cast<unsigned long long *>(a.ret_counters[et]) + a.ret_index, (unsigned long long)s_ret[g][et]);
             }
@@ -348,7 +328,7 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
         static bool attr = false;                                                                                                       \
         if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
         cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];                                                                         \
-        cfg.gridDim = dim3(sms); cfg.blockDim = dim3(MMA_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
+        cfg.gridDim = dim3(sms); cfg.blockDim = dim3(GRP_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;           \
         cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;                                                                                     \
         cudaError_t le = cudaLaunchKernelEx(&cfg, fp8_mma_grouped_kernel<PV>, *w, *q, a);                                              \

@@ -72,6 +72,76 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
                    "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]) \
                  : "r"(taddr))
 
+// acc += Sw * Sa * partial for the 32 routed rows of one half (one 128-feature block) of a K block: the reference's promotion
+// (src/omega_blackwell_codegen_qg.h:24-26); sc = 32 floats in shared memory, 16-byte aligned
+__device__ __forceinline__ void promote_half(const uint32_t (&v)[MMA_TOK], const float *sc, float (&acc)[MMA_TOK]) {
+#pragma unroll
+    for (int i = 0; i < MMA_TOK; i += 4) {
+        const float4 c = *reinterpret_cast<const float4 *>(sc + i);
+        acc[i] = fmaf(__uint_as_float(v[i]), c.x, acc[i]); acc[i + 1] = fmaf(__uint_as_float(v[i + 1]), c.y, acc[i + 1]);
+        acc[i + 2] = fmaf(__uint_as_float(v[i + 2]), c.z, acc[i + 2]); acc[i + 3] = fmaf(__uint_as_float(v[i + 3]), c.w, acc[i + 3]);
+    }
+}
+// pieces of one half folded last to first (x 1/16 each): r[P-1] / 16 + r[P-2], ... ; the result replaces r[0]
+template <int P>
+__device__ __forceinline__ void fold_pieces(uint32_t (&r)[P][MMA_TOK]) {
+#pragma unroll
+    for (int i = 0; i < MMA_TOK; i++) {
+        float v = __uint_as_float(r[P - 1][i]);
+#pragma unroll
+        for (int p = P - 2; p >= 0; p--) v = fmaf(v, 0.0625f, __uint_as_float(r[p][i]));
+        r[0][i] = __float_as_uint(v);
+    }
+}
+// One K block's partial sums of a promotion thread (its TMEM lane, 2 halves x P pieces x 32 columns at taddr) into the two accumulators.
+// The TMEM loads are what costs time (a few hundred cycles per dependent round trip), so as much as the registers hold is requested at once:
+// both halves in one round trip for P <= 2; one half per round trip for P = 3, the second half in flight while the first is promoted; two pieces
+// per round trip for P = 4. The partial buffer goes back to the MMA issuer (accempty) as soon as its last load has landed.
+template <int P>
+__device__ __forceinline__ void promote_kblock(uint32_t taddr, uint32_t accempty, const float *sc0, const float *sc1, float (&acc0)[MMA_TOK], float (&acc1)[MMA_TOK]) {
+    if constexpr (P <= 2) {
+        uint32_t h0[P][MMA_TOK], h1[P][MMA_TOK];
+#pragma unroll
+        for (int p = P - 1; p >= 0; p--) { TMEM_LD32(taddr + p * MMA_TOK, h0[p]); TMEM_LD32(taddr + P * MMA_TOK + p * MMA_TOK, h1[p]); }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tc_fence_before(); mbar_arrive(accempty);
+        fold_pieces<P>(h0); fold_pieces<P>(h1);
+        promote_half(h0[0], sc0, acc0);
+        promote_half(h1[0], sc1, acc1);
+    } else if constexpr (P == 3) {
+        uint32_t r[P][MMA_TOK], da[MMA_TOK];
+#pragma unroll
+        for (int p = P - 1; p >= 0; p--) TMEM_LD32(taddr + p * MMA_TOK, r[p]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        fold_pieces<P>(r);
+#pragma unroll
+        for (int i = 0; i < MMA_TOK; i++) da[i] = r[0][i];
+#pragma unroll
+        for (int p = P - 1; p >= 0; p--) TMEM_LD32(taddr + P * MMA_TOK + p * MMA_TOK, r[p]);
+        promote_half(da, sc0, acc0);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        tc_fence_before(); mbar_arrive(accempty);
+        fold_pieces<P>(r);
+        promote_half(r[0], sc1, acc1);
+    } else {
+        static_assert(P == 4, "at most four pieces");
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            uint32_t hi[2][MMA_TOK], lo[2][MMA_TOK];
+            TMEM_LD32(taddr + half * P * MMA_TOK + 3 * MMA_TOK, hi[1]); TMEM_LD32(taddr + half * P * MMA_TOK + 2 * MMA_TOK, hi[0]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            TMEM_LD32(taddr + half * P * MMA_TOK + MMA_TOK, lo[1]); TMEM_LD32(taddr + half * P * MMA_TOK, lo[0]);
+            fold_pieces<2>(hi);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (half == 1) { tc_fence_before(); mbar_arrive(accempty); }
+#pragma unroll
+            for (int i = 0; i < MMA_TOK; i++)
+                lo[0][i] = __float_as_uint(fmaf(fmaf(__uint_as_float(hi[0][i]), 0.0625f, __uint_as_float(lo[1][i])), 0.0625f, __uint_as_float(lo[0][i])));
+            if (half) promote_half(lo[0], sc1, acc1); else promote_half(lo[0], sc0, acc0);
+        }
+    }
+}
+
 #define TMEM_LD16(taddr, r, o)                                                                                                           \
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"                   \
                  : "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7]),      \

@@ -12,7 +12,7 @@ namespace b200 {
 struct Workspace {
     uint32_t max_tokens, topk, experts, hidden, inter;
     int refs;
-    uint32_t *ids, *counts, *starts, *xmap, *ymap, *header, *plan_scratch;
+    uint32_t *ids, *counts, *starts, *xmap, *ymap, *header, *plan_scratch, *sched; uint32_t sched_words;   // sched: work list of the one-launch expert kernel
     size_t plan_scratch_words;
     float *wts;
     Seg32 *seg_gu, *seg_dn;
@@ -42,7 +42,7 @@ static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t 
                  o_qx = take(Rp * 4 * hidden), o_qa = take(Rp * 4 * inter), o_sx = take(Rp * (hidden / 128) * 4), o_sa = take(Rp * (inter / 128) * 4),
                  o_lg = take((size_t)max_tokens * experts * 2), o_x = take((size_t)max_tokens * hidden * 2), o_o16 = take((size_t)max_tokens * hidden * 2),
                  o_o32 = take((size_t)max_tokens * hidden * 4), o_ps = take(plan_scratch_words((uint32_t)R, experts) * 4),
-                 o_qt = take((size_t)max_tokens * 4 * hidden), o_stt = take((size_t)max_tokens * (hidden / 128) * 4);
+                 o_qt = take((size_t)max_tokens * 4 * hidden), o_stt = take((size_t)max_tokens * (hidden / 128) * 4), o_sched = take((max_tiles + 1) * 4);
     if (!cuda_ok(cudaMalloc(&w->base, off), "cudaMalloc(workspace)")) { free(w); return nullptr; }
     if (!cuda_ok(cudaMemset(w->base, 0, off), "cudaMemset(workspace)")) { cudaFree(w->base); free(w); return nullptr; }
     char *b = w->base;
@@ -51,7 +51,7 @@ static Workspace *workspace_create(uint32_t max_tokens, uint32_t topk, uint32_t 
     w->seg_gu = (Seg32 *)(b + o_sgu); w->seg_dn = (Seg32 *)(b + o_sdn); w->tiles = (uint4 *)(b + o_tiles);
     w->gu = (float *)(b + o_gu); w->act = (float *)(b + o_act); w->dn = (float *)(b + o_dn);
     w->qx = (uint8_t *)(b + o_qx); w->qa = (uint8_t *)(b + o_qa); w->sx = (float *)(b + o_sx); w->sa = (float *)(b + o_sa);
-    w->qt = (uint8_t *)(b + o_qt); w->stt = (float *)(b + o_stt);
+    w->qt = (uint8_t *)(b + o_qt); w->stt = (float *)(b + o_stt); w->sched = (uint32_t *)(b + o_sched); w->sched_words = (uint32_t)(max_tiles + 1);
     w->plan_scratch = (uint32_t *)(b + o_ps); w->plan_scratch_words = plan_scratch_words((uint32_t)R, experts);
     w->logits = (uint16_t *)(b + o_lg); w->x = (uint16_t *)(b + o_x); w->out16 = (uint16_t *)(b + o_o16); w->out32 = (float *)(b + o_o32);
     return w;
@@ -122,6 +122,19 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
             extra_q = 1;
         } else if (!cuda_ok(launch_act_quant(R, H, Px, x, 1, w->xmap, w->header, w->qx, w->sx, s, 0, Rp), "x quant launch")) return false;
         MARK("x_quant");
+        // decode-shaped calls: the whole expert FFN in one launch (gate|up units, then down units from a work list cleared just before)
+        static const bool two_launches = getenv("B200MOE_TWO_LAUNCH") != nullptr;
+        if (!wide && !two_launches && ffn_shape_ok(H, I) && ((Px == 2 && Pa == 3) || (Px == 1 && Pa == 1) || (Px == 2 && Pa == 2))) {
+            FfnLaunch f = {};
+            f.gu_scale = L->gu->s; f.dn_scale = L->dn->s; f.x_scale = w->sx; f.qa = w->qa; f.sa = w->sa; f.tiles = w->tiles; f.header = w->header; f.ymap = w->ymap;
+            f.out = w->dn; f.hidden = H; f.inter = I; f.q_rows = Rp; f.sched = w->sched; f.err = w->header + 4;
+            if (!cuda_ok(cudaMemsetAsync(w->sched, 0, (size_t)w->sched_words * 4, s), "clear work list") ||
+                !cuda_ok(launch_ffn(L->tm_gu, L->tm_qx, L->tm_dn, L->tm_qa, Px, Pa, f, s, false), "expert ffn launch")) return false;
+            MARK("expert_ffn_mma");
+            if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
+            L->launches = n + extra + extra_q; L->marks = n;
+            return true;
+        }
         MmaLaunch g = {};
         g.wscale = L->gu->s; g.ascale = w->sx; g.tiles = w->tiles; g.header = w->header; g.ymap = nullptr; g.out = nullptr;
         g.q_out = w->qa; g.s_out = w->sa; g.q_rows = Rp; g.q_pieces = Pa;
