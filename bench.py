@@ -651,7 +651,7 @@ def run_decode_layer(args):
             "config": {"workload": "one MoE decode layer, 64 tokens, 128 experts top-8, hidden 2048, inter 768", "tokens_per_step": T, "distinct_experts": distinct,
                        "l2": "0.6 GB of weights per call: larger than L2", "kernel_ms": kern, "whole_layer_gbs": alg / (ms * 1e-3) / 1e9},
             "gpu_launches": launches * 20,
-            "roofline": {"bound": "hbm", "kernel": "gate|up + down grouped GEMM (two launches)", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+            "roofline": {"bound": "hbm", "kernel": "expert FFN (gate|up + down), one launch unless B200MOE_TWO_LAUNCH is set", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                          "peak_kind": kind + " copy bandwidth", "algorithmic_bytes": alg, "kernel_ms": gemm_ms, "traffic": None}}
 
 

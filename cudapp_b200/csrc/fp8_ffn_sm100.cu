@@ -395,7 +395,12 @@ cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, 
         constexpr int PM = (PXV) > (PAV) ? (PXV) : (PAV);                                                                               \
         const size_t smem = (size_t)(PM <= 3 ? 4 : 3) * (2 * A_TILE + PM * B_PIECE) + 2 * (PAV) * MMA_TOK * 128 + 1024;                             \
         static bool attr = false;                                                                                                       \
-        if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_ffn_kernel<PXV, PAV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
+        if (!attr) {                                                                                                                    \
+            /* the register hand-over inside the kernel (56 / 224) balances only if every thread starts with 168: refuse anything else */ \
+            cudaFuncAttributes fa; cudaError_t e = cudaFuncGetAttributes(&fa, fp8_ffn_kernel<PXV, PAV>); if (e != cudaSuccess) return e;                 \
+            if (fa.numRegs != 168) { set_error("expert kernel: %d registers per thread at launch, 168 expected", fa.numRegs); return cudaErrorInvalidConfiguration; } \
+            e = cudaFuncSetAttribute(fp8_ffn_kernel<PXV, PAV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; \
+        }                                                                                                                               \
         cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];                                                                         \
         cfg.gridDim = dim3(sms); cfg.blockDim = dim3(FFN_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;           \

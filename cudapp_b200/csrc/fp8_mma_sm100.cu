@@ -326,7 +326,12 @@ cudaError_t launch_mma_grouped(const void *tm_w, const void *tm_q, uint32_t piec
     do {                                                                                                                                \
         const size_t smem = (size_t)((PV) <= 3 ? 4 : 3) * (2 * A_TILE + (PV) * B_PIECE) + Q_STAGE_BYTES + 1024;                                        \
         static bool attr = false;                                                                                                       \
-        if (!attr) { cudaError_t e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; } \
+        if (!attr) {                                                                                                                    \
+            /* the register hand-over inside the kernel (56 / 224) balances only if every thread starts with 168: refuse anything else */ \
+            cudaFuncAttributes fa; cudaError_t e = cudaFuncGetAttributes(&fa, fp8_mma_grouped_kernel<PV>); if (e != cudaSuccess) return e;                 \
+            if (fa.numRegs != 168) { set_error("grouped kernel: %d registers per thread at launch, 168 expected", fa.numRegs); return cudaErrorInvalidConfiguration; } \
+            e = cudaFuncSetAttribute(fp8_mma_grouped_kernel<PV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; attr = true; \
+        }                                                                                                                               \
         cudaLaunchConfig_t cfg = {}; cudaLaunchAttribute at[1];                                                                         \
         cfg.gridDim = dim3(sms); cfg.blockDim = dim3(GRP_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;                        \
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;           \
