@@ -12,9 +12,10 @@
 // scaled by 16^p; P = 2 represents a bf16 value exactly, P = 3 gives 12 significant bits of an f32), each piece a
 // separate MMA column; columns are folded back (Horner, factor 1/16) when the accumulator is read.
 //
-// One persistent CTA per SM, 11 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane each, the
-// tcgen05 model), warp 2 = scale loader, warps 3-10 = two promotion/epilogue groups of four warps (one TMEM lane quarter
-// each) that take alternate units. A unit of work is (row tile, pair of
+// One persistent CTA per SM, 12 warps in three warp groups: warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane each, the
+// tcgen05 model), warp 2 = scale loader, warp 3 idle; warps 4-11 = two promotion/epilogue groups of four warps (one TMEM lane quarter
+// each) that take alternate units. After the set-up the first warp group gives registers to the other two (setmaxnreg 56 / 224), so that a
+// promotion thread can hold a whole K block of partial sums and fetch it from TMEM in one round trip. A unit of work is (row tile, pair of
 // 128-feature blocks): gate block j with up block j (SiLU gate fused in the epilogue) or two adjacent down blocks.
 // Per 128-wide K block: 2 x 4 MMAs (K = 32 each) into a double-buffered TMEM partial, tcgen05.commit, then the
 // epilogue warps tcgen05.ld the partial and add scale * partial into register accumulators while the next block's

@@ -11,7 +11,6 @@ constexpr int MMA_TOK = 32;                     // routed rows per tile; accumul
 constexpr uint32_t A_TILE = 128 * 128, B_PIECE = MMA_TOK * 128;
 constexpr int KB_MAX = 32;                      // k <= 4096 on this engine
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
-constexpr int MMA_THREADS = 32 * 11;            // TMA, MMA, scale loader, 2 x 4 epilogue warps
 constexpr uint32_t Q_STAGE_BYTES = 2 * 4 * MMA_TOK * 128;   // per epilogue group: up to 4 pieces x 32 rows x 128 bytes of output codes
 
 // ------------------------------------------------------------------ PTX wrappers
