@@ -55,6 +55,21 @@ def test_layer_small(engine, tokens):
     free_layer(m)
 
 
+@pytest.mark.parametrize("E,H,I,topk,T", [(8, 4096, 1536, 4, 40), (16, 1024, 640, 6, 100), (12, 256, 128, 2, 33)])
+def test_layer_other_shapes(E, H, I, topk, T):
+    """the one-launch expert kernel at the edges of its shape range: the longest rows (32 K blocks), an odd number of K blocks in the down
+    projection (5), a single K block; with more and with fewer units than CTAs"""
+    rng = np.random.default_rng(E + H + I)
+    m = build_layer(rng, E, H, I, T, api.ENGINE_MMA, topk)
+    logits = orc.bf16_bits(rng.normal(0, 1, (T, E)).astype(np.float32))
+    xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    check_layer(m, logits, xb, topk)
+    rc, _, o32b, _, _ = api.moe_layer_bf16(m["layer"], logits, xb, topk)          # a second call: same bits (work-list words cleared between calls)
+    rc2, _, o32c, _, _ = api.moe_layer_bf16(m["layer"], logits, xb, topk)
+    assert rc == 0 and rc2 == 0 and np.array_equal(o32b.view(np.uint32), o32c.view(np.uint32))
+    free_layer(m)
+
+
 @pytest.mark.parametrize("engine", [api.ENGINE_FMA, api.ENGINE_MMA])
 def test_layer_decode_shape(engine):
     """the decode configuration's architecture (hidden 2048, expert intermediate 768, top-8) on 32 experts, 64 tokens"""
