@@ -25,66 +25,98 @@ __device__ __forceinline__ uint32_t bf16_rne_bits(float f) {
     return ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16);
 }
 
-// dynamic shared: xn f32 [hidden] | logits f32 [experts]
-__global__ void __launch_bounds__(256) router_rows_kernel(uint32_t hidden, uint32_t experts, uint32_t topk, int norm, float eps, float out_scale,
+// dynamic shared: xn f32 [ROUTER_TOK][hidden] | logits f32 [ROUTER_TOK][experts]
+// A CTA takes ROUTER_TOK consecutive rows: every gate word it loads is multiplied into all of them (the gate matrix is read once per ROUTER_TOK rows
+// instead of once per row), each row keeping its own accumulation chain in the order a one-row CTA would use, so the values do not depend on the grouping.
+constexpr uint32_t ROUTER_TOK = 1;   // measured: 4 rows per CTA (64 CTAs for 256 rows) is slower, the kernel is bound by load latency, not by L2 traffic
+__global__ void __launch_bounds__(256) router_rows_kernel(uint32_t rows, uint32_t hidden, uint32_t experts, uint32_t topk, int norm, float eps, float out_scale,
                                                           const float *__restrict__ x, size_t x_stride, const float *__restrict__ norm_w,
                                                           const uint16_t *__restrict__ gate, float *__restrict__ xn_out, uint16_t *__restrict__ xn16_out,
                                                           float *__restrict__ logits_out, uint32_t *__restrict__ ids, float *__restrict__ wts,
                                                           uint32_t slots, const uint16_t *__restrict__ shared_gate) {
     extern __shared__ __align__(16) float sm[];
-    float *xn = sm, *lg = sm + hidden;
+    float *xn = sm, *lg = sm + (size_t)ROUTER_TOK * hidden;
     __shared__ double red[8];
     __shared__ float s_r;
-    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const float *xr = x + (size_t)row * x_stride;
-    // ---- phase 1: RMSNorm (sum of squares in double, one f32 factor, then (x * r) * w)
-    double ss = 0.0;
-    for (uint32_t i = tid * 4u; i < hidden; i += 1024u) {
-        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
-        ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
-    }
-    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    if (tid == 0) { double t = 0.0; for (int i = 0; i < 8; i++) t += red[i]; s_r = (float)(1.0 / sqrt(t / (double)hidden + (double)eps)); }
-    __syncthreads();
-    const float r = s_r;
-    for (uint32_t i = tid * 4u; i < hidden; i += 1024u) {
-        const float4 v = *reinterpret_cast<const float4 *>(xr + i), w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
-        const float4 o = make_float4(v.x * r * w.x, v.y * r * w.y, v.z * r * w.z, v.w * r * w.w);
-        *reinterpret_cast<float4 *>(xn + i) = o;
-        if (xn_out) *reinterpret_cast<float4 *>(xn_out + (size_t)row * hidden + i) = make_float4(o.x * out_scale, o.y * out_scale, o.z * out_scale, o.w * out_scale);
-        if (xn16_out) {
-            uint2 pk; pk.x = bf16_rne_bits(o.x) | (bf16_rne_bits(o.y) << 16); pk.y = bf16_rne_bits(o.z) | (bf16_rne_bits(o.w) << 16);
-            *reinterpret_cast<uint2 *>(xn16_out + (size_t)row * hidden + i) = pk;
+    const uint32_t row0 = blockIdx.x * ROUTER_TOK, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t ntok = rows - row0 < ROUTER_TOK ? rows - row0 : ROUTER_TOK;
+    // ---- phase 1, row by row: RMSNorm (sum of squares in double, one f32 factor, then (x * r) * w)
+    for (uint32_t k = 0; k < ROUTER_TOK; k++) {
+        float *xk = xn + (size_t)k * hidden;
+        if (k >= ntok) { for (uint32_t i = tid * 4u; i < hidden; i += 1024u) *reinterpret_cast<float4 *>(xk + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f); continue; }
+        const uint32_t row = row0 + k;
+        const float *xr = x + (size_t)row * x_stride;
+        double ss = 0.0;
+        for (uint32_t i = tid * 4u; i < hidden; i += 1024u) {
+            const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+            ss += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+        }
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (tid == 0) { double t = 0.0; for (int i = 0; i < 8; i++) t += red[i]; s_r = (float)(1.0 / sqrt(t / (double)hidden + (double)eps)); }
+        __syncthreads();
+        const float r = s_r;
+        for (uint32_t i = tid * 4u; i < hidden; i += 1024u) {
+            const float4 v = *reinterpret_cast<const float4 *>(xr + i), w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
+            const float4 o = make_float4(v.x * r * w.x, v.y * r * w.y, v.z * r * w.z, v.w * r * w.w);
+            *reinterpret_cast<float4 *>(xk + i) = o;
+            if (xn_out) *reinterpret_cast<float4 *>(xn_out + (size_t)row * hidden + i) = make_float4(o.x * out_scale, o.y * out_scale, o.z * out_scale, o.w * out_scale);
+            if (xn16_out) {
+                uint2 pk; pk.x = bf16_rne_bits(o.x) | (bf16_rne_bits(o.y) << 16); pk.y = bf16_rne_bits(o.z) | (bf16_rne_bits(o.w) << 16);
+                *reinterpret_cast<uint2 *>(xn16_out + (size_t)row * hidden + i) = pk;
+            }
         }
     }
     __syncthreads();
-    // ---- phase 2: logits; warp w takes experts w, w + 8, ...; a lane multiplies 8 consecutive bf16 weights per 16-byte load
+    // ---- phase 2: logits; warp w takes experts w, w + 8, ...; a lane multiplies 8 consecutive bf16 weights per 16-byte load into every row's sum
     const uint32_t words = hidden / 8u;
-    for (uint32_t e = warp; e < experts; e += 8u) {
-        const uint4 *g = reinterpret_cast<const uint4 *>(gate + (size_t)e * hidden);
-        float acc = 0.0f;
+    // two experts per pass (e and e + 8): twice the loads in flight per lane, each sum still in its own order
+    for (uint32_t e = warp; e < experts; e += 16u) {
+        const bool two = e + 8u < experts;
+        const uint4 *g0 = reinterpret_cast<const uint4 *>(gate + (size_t)e * hidden), *g1 = reinterpret_cast<const uint4 *>(gate + (size_t)(two ? e + 8u : e) * hidden);
+        float acc0[ROUTER_TOK], acc1[ROUTER_TOK];
+#pragma unroll
+        for (uint32_t k = 0; k < ROUTER_TOK; k++) { acc0[k] = 0.0f; acc1[k] = 0.0f; }
+#pragma unroll 4
         for (uint32_t c = lane; c < words; c += 32u) {
-            const uint4 u = __ldg(g + c);
-            const float4 a = *reinterpret_cast<const float4 *>(xn + c * 8u), b = *reinterpret_cast<const float4 *>(xn + c * 8u + 4u);
-            acc = fmaf(__uint_as_float(u.x << 16), a.x, acc); acc = fmaf(__uint_as_float(u.x & 0xffff0000u), a.y, acc);
-            acc = fmaf(__uint_as_float(u.y << 16), a.z, acc); acc = fmaf(__uint_as_float(u.y & 0xffff0000u), a.w, acc);
-            acc = fmaf(__uint_as_float(u.z << 16), b.x, acc); acc = fmaf(__uint_as_float(u.z & 0xffff0000u), b.y, acc);
-            acc = fmaf(__uint_as_float(u.w << 16), b.z, acc); acc = fmaf(__uint_as_float(u.w & 0xffff0000u), b.w, acc);
+            const uint4 u = __ldg(g0 + c), v = __ldg(g1 + c);
+#pragma unroll
+            for (uint32_t k = 0; k < ROUTER_TOK; k++) {
+                const float *xk = xn + (size_t)k * hidden + c * 8u;
+                const float4 a = *reinterpret_cast<const float4 *>(xk), b = *reinterpret_cast<const float4 *>(xk + 4u);
+                float s0 = acc0[k], s1 = acc1[k];
+                s0 = fmaf(__uint_as_float(u.x << 16), a.x, s0); s1 = fmaf(__uint_as_float(v.x << 16), a.x, s1);
+                s0 = fmaf(__uint_as_float(u.x & 0xffff0000u), a.y, s0); s1 = fmaf(__uint_as_float(v.x & 0xffff0000u), a.y, s1);
+                s0 = fmaf(__uint_as_float(u.y << 16), a.z, s0); s1 = fmaf(__uint_as_float(v.y << 16), a.z, s1);
+                s0 = fmaf(__uint_as_float(u.y & 0xffff0000u), a.w, s0); s1 = fmaf(__uint_as_float(v.y & 0xffff0000u), a.w, s1);
+                s0 = fmaf(__uint_as_float(u.z << 16), b.x, s0); s1 = fmaf(__uint_as_float(v.z << 16), b.x, s1);
+                s0 = fmaf(__uint_as_float(u.z & 0xffff0000u), b.y, s0); s1 = fmaf(__uint_as_float(v.z & 0xffff0000u), b.y, s1);
+                s0 = fmaf(__uint_as_float(u.w << 16), b.z, s0); s1 = fmaf(__uint_as_float(v.w << 16), b.z, s1);
+                s0 = fmaf(__uint_as_float(u.w & 0xffff0000u), b.w, s0); s1 = fmaf(__uint_as_float(v.w & 0xffff0000u), b.w, s1);
+                acc0[k] = s0; acc1[k] = s1;
+            }
         }
-        for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) { lg[e] = acc; if (logits_out) logits_out[(size_t)row * experts + e] = acc; }
+#pragma unroll
+        for (uint32_t k = 0; k < ROUTER_TOK; k++) {
+            float s0 = acc0[k], s1 = acc1[k];
+            for (int o = 16; o; o >>= 1) { s0 += __shfl_xor_sync(0xffffffffu, s0, o); s1 += __shfl_xor_sync(0xffffffffu, s1, o); }
+            if (lane == 0 && k < ntok) {
+                lg[(size_t)k * experts + e] = s0; if (logits_out) logits_out[(size_t)(row0 + k) * experts + e] = s0;
+                if (two) { lg[(size_t)k * experts + e + 8u] = s1; if (logits_out) logits_out[(size_t)(row0 + k) * experts + e + 8u] = s1; }
+            }
+        }
     }
     __syncthreads();
-    // ---- phase 3: selection and weights
-    if (warp == 0) warp_topk(lg, experts, topk, norm, ids + (size_t)row * slots, wts + (size_t)row * slots);
+    // ---- phase 3: selection and weights, one warp per row
+    if (warp < ntok) warp_topk(lg + (size_t)warp * experts, experts, topk, norm, ids + (size_t)(row0 + warp) * slots, wts + (size_t)(row0 + warp) * slots);
     // ---- the shared expert's slot (slots = topk + 1): id = experts; weight = sigmoid(shared gate . xn), the reference's ninth group
-    //      (src/omega_gpu_q36_graph.h:20), or 1 when the layer has no such gate
-    if (slots > topk && warp == 1) {
+    //      (src/omega_gpu_q36_graph.h:20), or 1 when the layer has no such gate; warps 4 .. 7, one per row
+    if (slots > topk && warp >= ROUTER_TOK && warp - ROUTER_TOK < ntok) {
+        const uint32_t k = warp - ROUTER_TOK, row = row0 + k;
         float acc = 0.0f;
         if (shared_gate) {
-            for (uint32_t c = lane; c < hidden; c += 32u) acc = fmaf(__uint_as_float((uint32_t)shared_gate[c] << 16), xn[c], acc);
+            for (uint32_t c = lane; c < hidden; c += 32u) acc = fmaf(__uint_as_float((uint32_t)shared_gate[c] << 16), xn[(size_t)k * hidden + c], acc);
             for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         }
         if (lane == 0) { ids[(size_t)row * slots + topk] = experts; wts[(size_t)row * slots + topk] = shared_gate ? __fdiv_rn(1.0f, 1.0f + expf(-acc)) : 1.0f; }
@@ -93,12 +125,12 @@ __global__ void __launch_bounds__(256) router_rows_kernel(uint32_t hidden, uint3
 
 // stream-ordered launch for callers inside the library (the layer stack): xn16 = bf16(RMSNorm(x) * norm weight), ids, weights
 cudaError_t launch_router_rows(const OmegaGpuMoeRouter *r, uint32_t rows, const float *x, float eps, int norm_topk, uint32_t topk, uint16_t *xn16, uint32_t *ids, float *wts, cudaStream_t s, uint32_t slots) {
-    const size_t smem = ((size_t)r->hidden + r->experts) * 4;
+    const size_t smem = (size_t)ROUTER_TOK * ((size_t)r->hidden + r->experts) * 4;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    router_rows_kernel<<<rows, 256, smem, s>>>(r->hidden, r->experts, topk, norm_topk, eps, 1.0f, x, r->hidden, r->norm_w, r->gate, nullptr, xn16, nullptr, ids, wts, slots ? slots : topk, r->shared_gate);
+    router_rows_kernel<<<(rows + ROUTER_TOK - 1) / ROUTER_TOK, 256, smem, s>>>(rows, r->hidden, r->experts, topk, norm_topk, eps, 1.0f, x, r->hidden, r->norm_w, r->gate, nullptr, xn16, nullptr, ids, wts, slots ? slots : topk, r->shared_gate);
     return cudaGetLastError();
 }
 void router_dims(const OmegaGpuMoeRouter *r, uint32_t *experts, uint32_t *hidden) { *experts = r->experts; *hidden = r->hidden; }
@@ -147,11 +179,11 @@ int omega_gpu_moe_router_rows_async(OmegaGpuMoeRouter *r, uint32_t rows, uint64_
     if (!x_stride_bytes) x_stride_bytes = r->hidden * 4u;
     if (x_stride_bytes % 16u || x_stride_bytes < r->hidden * 4u || (x_va & 15u)) { set_error("router: residual rows must be 16-byte aligned f32 rows of at least `hidden` values"); return OMEGA_GPU_FP8_BAD_ARGS; }
     if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
-    const size_t smem = ((size_t)r->hidden + r->experts) * 4;
+    const size_t smem = (size_t)ROUTER_TOK * ((size_t)r->hidden + r->experts) * 4;
     if (smem > 48 * 1024) {
         if (!cuda_ok(cudaFuncSetAttribute(router_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "router attribute")) return OMEGA_GPU_FP8_CHIP_FAIL;
     }
-    router_rows_kernel<<<rows, 256, smem, (cudaStream_t)stream>>>(r->hidden, r->experts, topk, norm_topk, eps, out_scale, (const float *)(uintptr_t)x_va, x_stride_bytes / 4u,
+    router_rows_kernel<<<(rows + ROUTER_TOK - 1) / ROUTER_TOK, 256, smem, (cudaStream_t)stream>>>(rows, r->hidden, r->experts, topk, norm_topk, eps, out_scale, (const float *)(uintptr_t)x_va, x_stride_bytes / 4u,
                                                                   r->norm_w, r->gate, (float *)(uintptr_t)xn_va, (uint16_t *)(uintptr_t)xn_bf16_va, (float *)(uintptr_t)logits_va,
                                                                   (uint32_t *)(uintptr_t)ids_va, (float *)(uintptr_t)wts_va, topk + (r->shared_gate ? 1u : 0u), r->shared_gate);
     return cuda_ok(cudaGetLastError(), "router launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
