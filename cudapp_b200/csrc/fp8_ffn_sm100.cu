@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
         // ---------------------------------------------------------------- TMA producer (and scheduler of the down units)
         if (lane == 0) {
             uint32_t it = 0, n = 0; bool ok = true, first = true;
+            const uint64_t pol_w = l2_policy_evict_first();   // weights are read once: keep them from displacing the rows that are read again (measured: 3 % of the step)
             while (ok) {
                 uint32_t u;
                 if (n >= my_gu && first) { first = false; griddep_wait(); griddep_launch(); }   // no gate|up unit here: the down units come from the scheduler, which waits for the same grid
@@ -165,8 +166,8 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
                     for (uint32_t kb = 0; kb < npre; kb++) {
                         const uint32_t dst = smem_base + kb * STAGE_BYTES;
                         mbar_expect_tx(full_bar(kb), bytes);
-                        tma_load_2d(dst, mw, full_bar(kb), (int)(kb * 128u), wy0);
-                        tma_load_2d(dst + A_TILE, mw, full_bar(kb), (int)(kb * 128u), wy1);
+                        tma_load_2d_hint(dst, mw, full_bar(kb), (int)(kb * 128u), wy0, pol_w);
+                        tma_load_2d_hint(dst + A_TILE, mw, full_bar(kb), (int)(kb * 128u), wy1, pol_w);
                     }
                     griddep_wait(); griddep_launch();
                     if (a.gate && !(ok = gate_wait(a.gate, *a.gate_base + a.header[0], a.err, 13, a.wait_limit))) { *abort_flag = 1; break; }
@@ -180,8 +181,8 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) fp8_ffn_kernel(const __grid_co
                     if (!(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
                     const uint32_t dst = smem_base + s * STAGE_BYTES;
                     mbar_expect_tx(full_bar(s), bytes);
-                    tma_load_2d(dst, mw, full_bar(s), (int)(kb * 128u), wy0);
-                    tma_load_2d(dst + A_TILE, mw, full_bar(s), (int)(kb * 128u), wy1);
+                    tma_load_2d_hint(dst, mw, full_bar(s), (int)(kb * 128u), wy0, pol_w);
+                    tma_load_2d_hint(dst + A_TILE, mw, full_bar(s), (int)(kb * 128u), wy1, pol_w);
                     for (uint32_t p = 0; p < P; p++)
                         tma_load_2d(dst + 2 * A_TILE + p * B_PIECE, mq, full_bar(s), (int)(kb * 128u), (int)(p * a.q_rows + t.y));
                     s_prog = it + 1;

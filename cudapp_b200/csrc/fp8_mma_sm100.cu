@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(GRP_THREADS, 1) fp8_mma_grouped_kernel(const _
             // The weights do not depend on the previous kernel, the activation pieces do: fill the pipeline with weight tiles
             // first, then wait for the producer grid, then add the activation tiles of those same stages.
             uint32_t it = 0; bool ok = true;
+            const uint64_t pol_w = l2_policy_evict_first();   // weights are read once per launch
             for (int phase = 0; phase < 3 && ok; phase++) {
                 if (phase == 1) {
                     griddep_wait(); griddep_launch();
@@ -125,8 +126,8 @@ __global__ void __launch_bounds__(GRP_THREADS, 1) fp8_mma_grouped_kernel(const _
                         if (phase == 2 && !(ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, a.err, 1))) break;
                         if (phase != 1) {
                             mbar_expect_tx(full_bar(s), STAGE_BYTES);
-                            tma_load_2d(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0);
-                            tma_load_2d(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1);
+                            tma_load_2d_hint(dst, &tm_w, full_bar(s), (int)(kb * 128u), wy0, pol_w);
+                            tma_load_2d_hint(dst + A_TILE, &tm_w, full_bar(s), (int)(kb * 128u), wy1, pol_w);
                         }
                         if (phase != 0) {
 #pragma unroll
