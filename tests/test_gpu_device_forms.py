@@ -221,3 +221,12 @@ def test_nvfp4_gemm(n, k, m):
     assert rel_l2(y32, ref) <= 1e-3 and np.array_equal(y16, orc.bf16_bits(y32))
     rc, _, yb = api.w4_gemm_bf16(t, n, xb); assert rc == 0 and np.array_equal(yb.view(np.uint32), y32.view(np.uint32))
     api.lib.omega_gpu_w4_free(t)
+
+
+def test_hbm_probe():
+    """the in-process bandwidth probe bench.py reports beside the roofline: plausible figures for an HBM3e part, sizes outside its range refused"""
+    cg, rg = C.c_float(0), C.c_float(0)
+    assert api.lib.omega_gpu_hbm_peak(C.c_uint64(1 << 20), C.c_uint32(2), C.byref(cg), C.byref(rg)) == api.BAD_ARGS      # below 256 MiB: L2 would serve it
+    assert api.lib.omega_gpu_hbm_peak(C.c_uint64(256 << 20), C.c_uint32(0), C.byref(cg), C.byref(rg)) == api.BAD_ARGS
+    assert api.lib.omega_gpu_hbm_peak(C.c_uint64(256 << 20), C.c_uint32(3), C.byref(cg), C.byref(rg)) == 0, api.last_error()
+    assert 1000.0 < cg.value < 10000.0 and 1000.0 < rg.value < 10000.0, (cg.value, rg.value)
