@@ -589,7 +589,7 @@ def run_w4(args, mxfp4=False, nvfp4=False):
     return {"metric": "w4_gemm_calls_per_s", "value": 1.0 / (cold_ms * 1e-3), "unit": "calls/s", "n_gpus": 1, "steps": 10 * sets, "warmup": 3 * sets, "ms_per_step": cold_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights, fp16 group scales, f32 accumulate", "data": "synthetic",
             "config": {"workload": "NVFP4 GEMM: x bf16 [16, 4096] x W e2m1 [4096, 4096], unsigned E4M3 scale per 16 columns" if nvfp4 else "MXFP4 GEMM: x bf16 [16, 4096] x W e2m1 [4096, 4096], E8M0 scale per 32 columns" if mxfp4 else "W4 GEMM: x bf16 [16, 4096] x W int4 [4096, 4096], fp16 scale per 32 columns", "l2": "calls rotate through 16 disjoint weight copies (151 MB) inside one CUDA graph",
-                       "tflops": 2.0 * m * n * k / (cold_ms * 1e-3) / 1e12, "parity": "element x scale decoder pinned to the reference's nvfp4 oracle; the bf16 x NVFP4 GEMM itself has no reference counterpart" if nvfp4 else "element decoder pinned to the reference's mxfp4 oracle; the GEMM itself has no reference counterpart" if mxfp4 else "unpinned: the reference has no integer-W4 arithmetic"},
+                       "tflops": 2.0 * m * n * k / (cold_ms * 1e-3) / 1e12, "parity": "element x scale decoder pinned to the reference's nvfp4 oracle; GEMM checked against the reference's block-scaled product definition (mxmm) with quantised activations" if nvfp4 else "element decoder pinned to the reference's mxfp4 oracle; GEMM checked against the reference's block-scaled product definition (mxmm) with quantised activations" if mxfp4 else "unpinned: the reference has no integer-W4 arithmetic"},
             "gpu_launches": 10 * sets,
             "roofline": {"bound": "hbm", "kernel": "w4_mma_kernel", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_kind": kind + " copy bandwidth",
                          "algorithmic_bytes": alg, "kernel_ms": cold_ms, "traffic": None, "note": "latency- and issue-bound: int4 / e2m1 expanded to bf16 in registers, mma.sync m16n8k16, four K quarters joined per output block"}}

@@ -567,6 +567,49 @@ void orc_nvfp4_gemm_rows(const uint8_t *packed, const uint8_t *scale_ue4m3, uint
     }
 }
 
+/* ------------------------------------------------------------------ block-scaled product C = A B^T of two quantised operands */
+
+/* The reference's definition of a block-scaled GEMM (native/models/mxdot.om `mxmm`, contract docs/models/MXFMT.md: "Each block term is exact ...
+ * Block terms are added left to right in binary64"; its verification oracle tests/models/mxfmt-check.py:392-411, `mx_reference`).
+ * fmt 0: NVFP4 (E2M1 nibbles, low nibble first, unsigned E4M3 scale per 16); fmt 1: MXFP4 (E2M1, E8M0 scale per 32); fmt 2: MXFP8 (E4M3 bytes,
+ * E8M0 per 32). A is m x k, B is n x k, both K-contiguous; scales [rows][k / block]. C[i][j] = sum over blocks, in order, of
+ * (sum_e a_e b_e) * sa * sb, every term exact in binary64 (the inner sums are small integers over 4, or under 2^53 units for E4M3), only the
+ * running sum rounds. mag (optional) = sum of |terms|. Returns 0, or 5 where the unit traps: fmt > 2, k = 0 or not a multiple of the block,
+ * a NaN element (E4M3 0x7f / 0xff) or scale (E8M0 255, UE4M3 above 126). */
+static double mx_elem(uint32_t fmt, const uint8_t *a, size_t i) {
+    if (fmt == 2) return (double)orc_e4m3_decode(a[i]);
+    const uint32_t nib = (a[i >> 1] >> (4u * (i & 1u))) & 15u, m = nib & 7u;
+    const double v = m < 4u ? 0.5 * m : (double)((2u + (m & 1u)) << ((m >> 1) - 1u)) * 0.5;   /* 0 .5 1 1.5 2 3 4 6 */
+    return (nib & 8u) ? -v : v;
+}
+static int mx_scale(uint32_t fmt, uint32_t code, double *out) {
+    if (fmt == 0) { if (code > 126u) return 5; *out = (double)orc_e4m3_decode((uint8_t)code); return 0; }
+    if (code == 255u) return 5;
+    *out = ldexp(1.0, (int)code - 127);
+    return 0;
+}
+int orc_mxmm(uint32_t fmt, uint32_t m, uint32_t n, uint32_t k, const uint8_t *A, const uint8_t *SA, const uint8_t *B, const uint8_t *SB, double *C, double *mag) {
+    if (fmt > 2u) return 5;
+    const uint32_t bs = fmt == 0 ? 16u : 32u;
+    if (k == 0 || k % bs) return 5;
+    const uint32_t kb = k / bs;
+    if (fmt == 2) for (size_t i = 0; i < (size_t)k * m; i++) if ((A[i] & 127u) == 127u) return 5;
+    if (fmt == 2) for (size_t i = 0; i < (size_t)k * n; i++) if ((B[i] & 127u) == 127u) return 5;
+    for (uint32_t i = 0; i < m; i++) for (uint32_t j = 0; j < n; j++) {
+        double acc = 0.0, ab = 0.0;
+        for (uint32_t t = 0; t < kb; t++) {
+            double sa, sb, inner = 0.0;
+            if (mx_scale(fmt, SA[(size_t)i * kb + t], &sa) || mx_scale(fmt, SB[(size_t)j * kb + t], &sb)) return 5;
+            for (uint32_t e = 0; e < bs; e++) inner += mx_elem(fmt, A, ((size_t)i * kb + t) * bs + e) * mx_elem(fmt, B, ((size_t)j * kb + t) * bs + e);
+            const double term = inner * sa * sb;
+            acc += term; ab += fabs(term);
+        }
+        C[(size_t)i * n + j] = acc;
+        if (mag) mag[(size_t)i * n + j] = ab;
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ one MoE layer, the reference host glue */
 
 /* For sorted row p (expert e, token t, slot s): gu = GEMV(W_gu[e], x[t]) (double dot, stored f32, as a

@@ -328,6 +328,16 @@ def nvfp4_gemm(packed, scale_ue4m3, x, threads=None):
     return y
 
 
+def mxmm(fmt, m, n, k, A, SA, B, SB):
+    """block-scaled C = A B^T of the reference's mxdot unit (fmt 0 NVFP4, 1 MXFP4, 2 MXFP8): returns (rc, C f64 [m][n], sum of |terms| [m][n])"""
+    A = np.ascontiguousarray(A, dtype=np.uint8); B = np.ascontiguousarray(B, dtype=np.uint8)
+    SA = np.ascontiguousarray(SA, dtype=np.uint8); SB = np.ascontiguousarray(SB, dtype=np.uint8)
+    Cm = np.zeros((m, n), np.float64); mag = np.zeros((m, n), np.float64)
+    L = lib(); L.orc_mxmm.restype = C.c_int
+    rc = L.orc_mxmm(C.c_uint32(fmt), C.c_uint32(m), C.c_uint32(n), C.c_uint32(k), _ptr(A, U8P), _ptr(SA, U8P), _ptr(B, U8P), _ptr(SB, U8P), _ptr(Cm, F64P), _ptr(mag, F64P))
+    return int(rc), Cm, mag
+
+
 def expert_rows(wgu, sgu, wdn, sdn, x, row_expert, row_token, row_dest, n_dest, threads=None, x_pieces=0, act_pieces=0):
     """Gate|up GEMV, SwiGLU and down GEMV for every sorted row (the reference host glue); ctypes releases
     the GIL, so rows are spread over `threads` host threads. Returns dn f32 [n_dest][hidden]."""

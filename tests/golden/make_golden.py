@@ -101,6 +101,16 @@ def main():
             v = mx.e2m1(n) * mx.ue4m3(c)
             tab[n, c] = mx.frac_to_f32bits(abs(v)) | ((n & 8) << 28)        # the sign of a zero product is the element's
     out["nvfp4_bits"] = tab
+    # block-scaled products: inputs from the reference script's generator, results from its rational oracle (left-to-right binary64 sums)
+    from tests.test_oracle_pin import mx_cases
+    hdr, blobs, res = [], [], []
+    for (fmt, mm, nn, k, A, SA, B, SB) in mx_cases(mx, rounds=2, seed=2027):
+        kb = k // mx.BS[fmt]; eb = k // 2 if fmt < 2 else k
+        _, seq, babs, _ = mx.mx_reference(fmt, mm, nn, k, A, SA, B, SB)
+        hdr.append((fmt, mm, nn, k))
+        blobs.append(np.concatenate([A[:eb * mm], SA[:kb * mm], B[:eb * nn], SB[:kb * nn]]))
+        res.append(np.array([float(v) for v in seq], np.float64))
+    out.update(mx_hdr=np.array(hdr, np.uint32), mx_blob=np.concatenate(blobs), mx_res=np.concatenate(res))
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **out)
     print("wrote", os.path.join(HERE, "reference_vectors.npz"), {k_: v_.shape for k_, v_ in out.items()})
 

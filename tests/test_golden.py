@@ -87,3 +87,19 @@ def test_nvfp4_decode_table():
     """every NVFP4 element x scale pair against the table made from the reference's verification script"""
     mine = np.array([orc.nvfp4_bits(n, c) for n in range(16) for c in range(127)], np.uint32).reshape(16, 127)
     assert np.array_equal(mine, G["nvfp4_bits"])
+
+
+def test_block_scaled_products():
+    """C = A B^T of two block-scaled operands (NVFP4, MXFP4, MXFP8) against results of the reference's rational oracle, bit for bit"""
+    pos = rpos = 0
+    for fmt, m, n, k in G["mx_hdr"].tolist():
+        bs = 16 if fmt == 0 else 32
+        kb, eb = k // bs, (k // 2 if fmt < 2 else k)
+        A = G["mx_blob"][pos:pos + eb * m]; pos += eb * m
+        SA = G["mx_blob"][pos:pos + kb * m]; pos += kb * m
+        B = G["mx_blob"][pos:pos + eb * n]; pos += eb * n
+        SB = G["mx_blob"][pos:pos + kb * n]; pos += kb * n
+        rc, got, _ = orc.mxmm(fmt, m, n, k, A, SA, B, SB)
+        assert rc == 0 and np.array_equal(got.reshape(-1).view(np.uint64), G["mx_res"][rpos:rpos + m * n].view(np.uint64))
+        rpos += m * n
+    assert pos == len(G["mx_blob"]) and rpos == len(G["mx_res"])

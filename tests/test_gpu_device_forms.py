@@ -230,3 +230,35 @@ def test_hbm_probe():
     assert api.lib.omega_gpu_hbm_peak(C.c_uint64(256 << 20), C.c_uint32(0), C.byref(cg), C.byref(rg)) == api.BAD_ARGS
     assert api.lib.omega_gpu_hbm_peak(C.c_uint64(256 << 20), C.c_uint32(3), C.byref(cg), C.byref(rg)) == 0, api.last_error()
     assert 1000.0 < cg.value < 10000.0 and 1000.0 < rg.value < 10000.0, (cg.value, rg.value)
+
+
+@pytest.mark.parametrize("fmt", [0, 1])
+def test_fp4_gemm_against_block_scaled_product(fmt):
+    """Both operands quantised: the reference's own definition of a block-scaled GEMM (native/models/mxdot.om `mxmm`: exact block terms, added left to
+    right in binary64; the checker's restatement is pinned to the reference's rational oracle in tests/test_oracle_pin.py). An FP4 element times its block
+    scale is exact in bf16, so the quantised activations go to the 4-bit GEMM as bf16 rows without loss; every block term is then exact in the kernel too
+    (sums of small integers times powers of two, or times a 4-bit significand) and only the f32 running sum over blocks rounds: the reference's rule for an
+    f32-accumulating kernel, |delta| < 1e-5 x sum of |terms| (tests/gpu_fp8_api_test.c:51)."""
+    rng = np.random.default_rng(40 + fmt)
+    m, n, k = 16, 256, 1024
+    bs = 16 if fmt == 0 else 32
+    A = rng.integers(0, 256, (m, k // 2)).astype(np.uint8); B = rng.integers(0, 256, (n, k // 2)).astype(np.uint8)
+    if fmt == 0:
+        SA = rng.integers(20, 100, (m, k // bs)).astype(np.uint8); SB = rng.integers(0, 127, (n, k // bs)).astype(np.uint8)
+        dec = orc.nvfp4_bits
+    else:
+        SA = rng.integers(117, 137, (m, k // bs)).astype(np.uint8); SB = rng.integers(100, 150, (n, k // bs)).astype(np.uint8)
+        dec = orc.mxfp4_bits
+    nib = np.stack([A & 15, A >> 4], -1).reshape(m, k)                                   # low nibble = even column
+    x = np.array([[dec(int(nib[i, c]), int(SA[i, c // bs])) for c in range(k)] for i in range(m)], np.uint32).view(np.float32)
+    xb = orc.bf16_bits(x)
+    assert np.array_equal(orc.bf16_to_f32(xb).view(np.uint32), x.view(np.uint32))        # element x scale is exact in bf16
+    t = C.c_void_p()
+    up = api.lib.omega_gpu_nvfp4_upload if fmt == 0 else api.lib.omega_gpu_mxfp4_upload
+    assert up(C.c_uint32(n), C.c_uint32(k), B.ctypes.data_as(C.c_void_p), SB.ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
+    rc, y16, y32 = api.w4_gemm_bf16(t, n, xb); assert rc == 0, api.last_error()
+    rc, ref, mag = orc.mxmm(fmt, m, n, k, A, SA, B, SB)
+    assert rc == 0
+    assert np.all(np.abs(y32 - ref) <= 1e-5 * mag + 1e-30), float(np.max(np.abs(y32 - ref) / (mag + 1e-30)))
+    assert np.array_equal(y16, orc.bf16_bits(y32))
+    api.lib.omega_gpu_w4_free(t)

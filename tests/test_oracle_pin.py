@@ -470,3 +470,40 @@ def test_nvfp4_decoder_against_reference_oracle():
         for c in range(127):
             assert Fraction(float(got[n, c])) == m.e2m1(n) * m.ue4m3(c), (n, c)
             assert bool(np.signbit(got[n, c])) == bool(n & 8)
+
+
+# ------------------------------------------------------------------ block-scaled product of two quantised operands (native/models/mxdot.om; oracle tests/models/mxfmt-check.py:392-411)
+MX_SHAPES = ((1, 1, 1), (4, 4, 8), (16, 16, 1), (2, 3, 4), (1, 1, 64))   # (m, n, k in blocks)
+
+
+def mx_cases(m, rounds=4, seed=1026):
+    """seeded cases from the reference script's own generator: all three formats, narrow and wide scale ranges"""
+    rng = np.random.default_rng(seed)
+    for rnd in range(rounds):
+        for fmt in (0, 1, 2):
+            for (mm, nn, kblocks) in MX_SHAPES:
+                yield m.mx_case(rng, fmt, mm, nn, kblocks * m.BS[fmt], wide=(rnd % 2 == 0))[1]
+
+
+@pytest.mark.skipif(not os.path.exists(MXFMT), reason="the reference tree is not on this machine")
+def test_mxmm_against_reference_oracle():
+    """every entry bit-equal to the left-to-right binary64 sum of exact block terms that the reference's verification script computes with rationals,
+    and the sum of |terms| equal to its value; then the refusals of the unit"""
+    pytest.importorskip("ml_dtypes")
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("mxfmt_check", MXFMT); m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)
+    dots = 0
+    for (fmt, mm, nn, k, A, SA, B, SB) in mx_cases(m):
+        exact, seq, babs, kb = m.mx_reference(fmt, mm, nn, k, A, SA, B, SB)
+        rc, got, mag = orc.mxmm(fmt, mm, nn, k, A, SA, B, SB)
+        assert rc == 0
+        assert got.reshape(-1).tolist() == [float(v) for v in seq]                 # bit-equal (== on floats; no NaN occurs)
+        assert np.allclose(mag.reshape(-1), [float(v) for v in babs], rtol=1e-15, atol=0)
+        dots += mm * nn
+    assert dots >= 3000
+    z = np.zeros(64, np.uint8)
+    assert orc.mxmm(3, 1, 1, 32, z, z, z, z)[0] == 5 and orc.mxmm(0, 1, 1, 0, z, z, z, z)[0] == 5 and orc.mxmm(1, 1, 1, 48, z, z, z, z)[0] == 5
+    bad = z.copy(); bad[0] = 255
+    assert orc.mxmm(1, 1, 1, 32, z, bad, z, z)[0] == 5 and orc.mxmm(2, 1, 1, 32, z, z, z, bad)[0] == 5     # E8M0 255
+    bad[0] = 127
+    assert orc.mxmm(0, 1, 1, 16, z, bad, z, z)[0] == 5 and orc.mxmm(2, 1, 1, 32, bad, z, z, z)[0] == 5     # UE4M3 NaN scale, E4M3 NaN element
