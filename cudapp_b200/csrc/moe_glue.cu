@@ -51,6 +51,8 @@ cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, con
 __global__ void __launch_bounds__(256) act_quant_kernel(uint32_t rows, uint32_t k, uint32_t pieces, size_t piece_stride, const void *__restrict__ x, int x_bf16, size_t x_stride,
                                                         const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
                                                         uint8_t *__restrict__ q, float *__restrict__ sc) {
+    // a kernel launched as a programmatic dependent of this one (the expert kernel: it fetches weights and waits for this grid before it reads a row) may start now
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31u, kb = k / 128u;
     const uint32_t nrows = rows_dev ? min(rows, *rows_dev) : rows;
     const uint32_t tasks = nrows * kb, stride = gridDim.x * (blockDim.x >> 5);   // rows <= 2^24 and kb <= 32 on every caller's path
@@ -101,6 +103,7 @@ cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const v
 __global__ void __launch_bounds__(256) gather_rows_kernel(uint32_t rows, uint32_t k, uint32_t pieces, size_t src_piece_stride, size_t dst_piece_stride,
                                                           const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ rows_dev,
                                                           const uint8_t *__restrict__ q_src, const float *__restrict__ s_src, uint8_t *__restrict__ q_dst, float *__restrict__ s_dst) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // as in act_quant_kernel
     const uint32_t lane = threadIdx.x & 31u, kb = k / 128u, words = k / 16u;
     const uint32_t nrows = rows_dev ? min(rows, *rows_dev) : rows;
     const uint32_t tasks = nrows * pieces, stride = gridDim.x * (blockDim.x >> 5);

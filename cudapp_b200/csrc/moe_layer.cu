@@ -114,6 +114,7 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
         // activations as e4m3 pieces in sorted-row order, then the two tensor-core grouped GEMMs
         const uint32_t Px = L->cfg.x_pieces, Pa = L->cfg.act_pieces, Rp = w->max_tokens * w->topk + 8;
         uint32_t extra_q = 0;
+        if (!cuda_ok(cudaMemsetAsync(w->sched, 0, (size_t)w->sched_words * 4, s), "clear work list")) return false;   // the one-launch expert kernel's tickets and tile counters
         if (K >= 4u && tokens >= 512u) {
             // many picks per token: quantise every token row once, then copy codes and scales into sorted-row order (the same bytes as
             // quantising each sorted row, a fraction of the arithmetic)
@@ -128,8 +129,8 @@ bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits,
             FfnLaunch f = {};
             f.gu_scale = L->gu->s; f.dn_scale = L->dn->s; f.x_scale = w->sx; f.qa = w->qa; f.sa = w->sa; f.tiles = w->tiles; f.header = w->header; f.ymap = w->ymap;
             f.out = w->dn; f.hidden = H; f.inter = I; f.q_rows = Rp; f.sched = w->sched; f.err = w->header + 4;
-            if (!cuda_ok(cudaMemsetAsync(w->sched, 0, (size_t)w->sched_words * 4, s), "clear work list") ||
-                !cuda_ok(launch_ffn(L->tm_gu, L->tm_qx, L->tm_dn, L->tm_qa, Px, Pa, f, s, false), "expert ffn launch")) return false;
+            // programmatic dependent of the quantiser before it (the work list was cleared ahead of that kernel): set-up and first weight tiles overlap it
+            if (!cuda_ok(launch_ffn(L->tm_gu, L->tm_qx, L->tm_dn, L->tm_qa, Px, Pa, f, s, true), "expert ffn launch")) return false;
             MARK("expert_ffn_mma");
             if (!cuda_ok(launch_combine(tokens, K, H, w->wts, w->dn, out32, out16, s), "combine launch")) return false; MARK("combine");
             L->launches = n + extra + extra_q; L->marks = n;

@@ -188,7 +188,7 @@ static bool stack_record(OmegaGpuMoeStack *S, uint32_t tokens, const uint16_t *l
                 FfnLaunch f = {};
                 f.gu_scale = v.gu_scale; f.dn_scale = v.dn_scale; f.x_scale = S->sx; f.qa = v.qa; f.sa = v.sa; f.tiles = S->pb.tiles + (size_t)l * S->tile_stride; f.header = hdr;
                 f.ymap = S->pb.ymap + (size_t)l * S->map_stride; f.out = v.dn; f.hidden = H; f.inter = v.inter; f.q_rows = S->row_cap; f.sched = S->sched; f.err = hdr + 4;
-                if (!cuda_ok(launch_ffn(v.tm_gu, S->tm_qx, v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, false), "expert ffn launch")) return false; n++;
+                if (!cuda_ok(launch_ffn(v.tm_gu, S->tm_qx, v.tm_dn, v.tm_qa, Px, v.act_pieces, f, s, true /* dependent of the quantiser just launched */), "expert ffn launch")) return false; n++;
             } else {
                 MmaLaunch g = {};
                 g.wscale = v.gu_scale; g.ascale = S->sx; g.tiles = S->pb.tiles + (size_t)l * S->tile_stride; g.header = hdr; g.q_out = v.qa; g.s_out = v.sa; g.q_rows = S->row_cap; g.q_pieces = v.act_pieces;
