@@ -229,6 +229,46 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
     if (threadIdx.x == 0) counters[nb] = 0;   // ready for the next launch (launches on one tensor are stream-ordered)
 }
 
+// NVFP4 block quantiser (the reference's native/models/nvfp4.om: nvfp4nib = nvfp4scale + nvfp4enc per element). One thread per 16-element block of a
+// bf16 row: amax over the magnitudes, scale = e4m3 (nearest even, saturating) of the binary32 quotient amax / 6, then every element's nibble by comparing
+// its magnitude with scale x {1, 3, 5, 7, 10, 14, 20} / 4 (exact binary32 products), a tie going to the even code, above 6 saturating. NaN sets *bad.
+__global__ void __launch_bounds__(256) nvfp4_quantize_kernel(size_t blocks, const uint16_t *__restrict__ w, uint8_t *__restrict__ packed, uint8_t *__restrict__ scales, int *bad) {
+    const size_t b = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (b >= blocks) return;
+    const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(w + b * 16)), hi = __ldg(reinterpret_cast<const uint4 *>(w + b * 16) + 1);
+    const uint32_t v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    uint32_t amax = 0; bool nan = false;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t a0 = (v[i] & 0x7fffu) << 16, a1 = v[i] & 0x7fff0000u;
+        nan |= a0 > 0x7f800000u || a1 > 0x7f800000u;
+        amax = max(amax, max(a0, a1));
+    }
+    if (nan) { atomicExch(bad, 1); return; }
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(__fdiv_rn(__uint_as_float(amax), 6.0f)));
+    const uint32_t sc = r & 0x7fu, se = sc >> 3, sig = se ? ((sc & 7u) | 8u) : (sc & 7u);
+    const float unit = __uint_as_float((uint32_t)((se ? (int)se - 10 : -9) - 2 + 127) << 23);   // 2^(exponent of the scale - 2)
+    const float t0 = (float)(sig * 1u) * unit, t1 = (float)(sig * 3u) * unit, t2 = (float)(sig * 5u) * unit, t3 = (float)(sig * 7u) * unit,
+                t4 = (float)(sig * 10u) * unit, t5 = (float)(sig * 14u) * unit, t6 = (float)(sig * 20u) * unit;
+    auto enc = [&](uint32_t bits) -> uint32_t {   // bits: a binary32 pattern
+        const uint32_t sign = (bits >> 28) & 8u;
+        if (sig == 0) return sign;
+        const float a = __uint_as_float(bits & 0x7fffffffu);
+        // codes 0..7; thresholds between k and k + 1; a tie stays at k when k is even, goes to k + 1 when k is odd
+        uint32_t c = (a > t0) + (a >= t1) + (a > t2) + (a >= t3) + (a > t4) + (a >= t5) + (a > t6);
+        return sign | c;
+    };
+    uint32_t out[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t byte = enc(v[i] << 16) | (enc(v[i] & 0xffff0000u) << 4);   // element 2i in the low nibble
+        out[i >> 2] |= byte << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2 *>(packed + b * 8) = make_uint2(out[0], out[1]);
+    scales[b] = (uint8_t)sc;
+}
+
 }  // namespace b200
 using namespace b200;
 
@@ -300,6 +340,29 @@ int omega_gpu_nvfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const 
     if (!ok) { if (t->w) cudaFree(t->w); if (t->s) cudaFree(t->s); if (t->part) cudaFree(t->part); if (t->counters) cudaFree(t->counters); free(t); return OMEGA_GPU_FP8_CHIP_FAIL; }
     *out = t;
     return OMEGA_GPU_FP8_OK;
+}
+/* bf16 rows [rows][k] (k a multiple of 16) -> NVFP4: packed [rows][k / 2] and scales [rows][k / 16], bit for bit what the reference's block encoder
+ * (native/models/nvfp4.om nvfp4nib) gives for the same values; a NaN anywhere refuses the call (NAN_WEIGHT), infinities saturate as there. */
+int omega_gpu_nvfp4_quantize_bf16(uint32_t rows, uint32_t k, const uint16_t *w_bf16, uint8_t *packed, uint8_t *scale_ue4m3) {
+    if (!w_bf16 || !packed || !scale_ue4m3 || !rows || !k || k % 16u) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const size_t cnt = (size_t)rows * k, blocks = cnt / 16;
+    uint16_t *dw = (uint16_t *)stage(0, cnt * 2); uint8_t *dp = (uint8_t *)stage(1, cnt / 2); uint8_t *ds = (uint8_t *)stage(2, blocks + 16);
+    if (!dw || !dp || !ds) return OMEGA_GPU_FP8_CHIP_FAIL;
+    int *bad = (int *)(ds + ((blocks + 7) & ~(size_t)7));
+    cudaStream_t s = st().stream;
+    int hbad = 0;
+    bool ok = cuda_ok(cudaMemcpyAsync(dw, w_bf16, cnt * 2, cudaMemcpyHostToDevice, s), "copy weights") && cuda_ok(cudaMemsetAsync(bad, 0, 4, s), "memset");
+    if (ok) {
+        nvfp4_quantize_kernel<<<(unsigned)((blocks + 255) / 256), 256, 0, s>>>(blocks, dw, dp, ds, bad);
+        ok = cuda_ok(cudaGetLastError(), "nvfp4 quantize launch") && cuda_ok(cudaMemcpyAsync(&hbad, bad, 4, cudaMemcpyDeviceToHost, s), "copy flag") &&
+             cuda_ok(cudaStreamSynchronize(s), "nvfp4 quantize");
+    }
+    if (!ok) return OMEGA_GPU_FP8_CHIP_FAIL;
+    if (hbad) { set_error("nvfp4 quantize: NaN value"); return OMEGA_GPU_FP8_NAN_WEIGHT; }
+    ok = cuda_ok(cudaMemcpy(packed, dp, cnt / 2, cudaMemcpyDeviceToHost), "copy codes") && cuda_ok(cudaMemcpy(scale_ue4m3, ds, blocks, cudaMemcpyDeviceToHost), "copy scales");
+    return ok ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     if (!t) return;

@@ -78,6 +78,10 @@ int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const 
  * Scale 127 (NaN) -> NAN_WEIGHT, a scale with the sign bit set -> BAD_ARGS (that unit refuses both); n % 128 == 0, k 1024, 2048 or 4096.
  * The tensor runs through omega_gpu_w4_gemm_bf16 / _async. */
 int omega_gpu_nvfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_ue4m3, OmegaGpuW4Tensor **out);
+/* bf16 rows [rows][k] (host, k % 16 == 0) -> NVFP4 codes and scales on the GPU, bit for bit what the reference's block encoder gives (native/models/nvfp4.om
+ * nvfp4nib: scale = e4m3(amax / 6) nearest even and saturating, element = nearest even E2M1 of x / scale, above 6 and infinity saturate). A NaN value refuses
+ * the call with NAN_WEIGHT and writes nothing. packed [rows][k / 2] (element 2i in the low nibble), scale_ue4m3 [rows][k / 16]. */
+int omega_gpu_nvfp4_quantize_bf16(uint32_t rows, uint32_t k, const uint16_t *w_bf16, uint8_t *packed, uint8_t *scale_ue4m3);
 /* y bf16 [m][n] = x bf16 [m][k] * W^T, f32 accumulation; yf32 (optional) receives the unrounded values */
 int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32);
 /* the same on device buffers, stream-ordered (one of y_bf16_va / y_f32_va may be 0) */

@@ -567,6 +567,57 @@ void orc_nvfp4_gemm_rows(const uint8_t *packed, const uint8_t *scale_ue4m3, uint
     }
 }
 
+/* NVFP4 encoder of the reference (native/models/nvfp4.om: nvfp4enc, nvfp4scale, nvfp4nib; contract docs/models/MXFMT.md; checked there against a
+ * binary64 quotient oracle, exact rationals around every threshold and ml_dtypes, tests/models/mxfmt-check.py:302-352).
+ * orc_nvfp4_enc: the nearest-even E2M1 nibble of x / scale, found by comparing |x| with scale x {1, 3, 5, 7, 10, 14, 20} / 4 (each exact in
+ * binary32); above 6 and infinity saturate to 6; scale 0 gives a signed zero; 0xff where the unit traps (NaN input, scale above 126).
+ * orc_nvfp4_scale: the block scale, e4m3 (round to nearest even, saturating at 448) of the binary32 quotient amax / 6; 0xff for a NaN amax.
+ * orc_nvfp4_block: 16 binary32 values -> scale code and 8 packed bytes (element 2i in the low nibble of byte i); 0xff if any value is NaN. */
+uint32_t orc_nvfp4_enc(uint32_t bits, uint32_t scale) {
+    static const uint32_t mid[7] = {1, 3, 5, 7, 10, 14, 20};
+    if (scale > 126u) return 0xffu;
+    const uint32_t sign = (bits >> 28) & 8u, a = bits & 0x7fffffffu;
+    if (a > 0x7f800000u) return 0xffu;
+    const uint32_t se = scale >> 3, sig = se ? ((scale & 7u) | 8u) : (scale & 7u);
+    if (sig == 0) return sign;
+    const int ex = (se ? (int)se - 10 : -9) - 2;
+    float av; memcpy(&av, &a, 4);
+    uint32_t c = 0;
+    for (uint32_t k = 0; k < 7; k++) {
+        const float t = ldexpf((float)(sig * mid[k]), ex);   /* at most 15 * 20 = 300: exact */
+        if (av < t) break;
+        if (av > t) { c = k + 1; continue; }
+        if (k & 1u) c = k + 1;                               /* a tie goes to the even code */
+        break;
+    }
+    return sign | c;
+}
+uint32_t orc_nvfp4_scale(uint32_t amax_bits) {
+    if (amax_bits > 0x7f800000u) return 0xffu;
+    float a; memcpy(&a, &amax_bits, 4);
+    const volatile float q = a / 6.0f;                       /* one binary32 division, as the unit does */
+    return (uint32_t)orc_e4m3_encode(q) & 0x7fu;
+}
+uint32_t orc_nvfp4_block(const uint32_t *x, uint8_t *q) {
+    uint32_t amax = 0;
+    for (int i = 0; i < 16; i++) { const uint32_t a = x[i] & 0x7fffffffu; if (a > 0x7f800000u) return 0xffu; if (a > amax) amax = a; }
+    const uint32_t sc = orc_nvfp4_scale(amax);
+    for (int j = 0; j < 8; j++) q[j] = (uint8_t)(orc_nvfp4_enc(x[2 * j], sc) | (orc_nvfp4_enc(x[2 * j + 1], sc) << 4));
+    return sc;
+}
+void orc_nvfp4_enc_many(const uint32_t *bits, size_t n, uint32_t scale, uint8_t *out) { for (size_t i = 0; i < n; i++) out[i] = (uint8_t)orc_nvfp4_enc(bits[i], scale); }
+void orc_nvfp4_scale_many(const uint32_t *amax, size_t n, uint8_t *out) { for (size_t i = 0; i < n; i++) out[i] = (uint8_t)orc_nvfp4_scale(amax[i]); }
+/* rows x k binary32 values (k a multiple of 16) -> packed [rows][k / 2] and scales [rows][k / 16]; returns the number of blocks refused (NaN) */
+size_t orc_nvfp4_quantize(const uint32_t *x, size_t rows, size_t k, uint8_t *packed, uint8_t *scales) {
+    size_t bad = 0;
+    for (size_t r = 0; r < rows; r++) for (size_t b = 0; b < k / 16; b++) {
+        const uint32_t sc = orc_nvfp4_block(x + r * k + b * 16, packed + r * (k / 2) + b * 8);
+        scales[r * (k / 16) + b] = (uint8_t)sc;
+        if (sc == 0xffu) bad++;
+    }
+    return bad;
+}
+
 /* ------------------------------------------------------------------ block-scaled product C = A B^T of two quantised operands */
 
 /* The reference's definition of a block-scaled GEMM (native/models/mxdot.om `mxmm`, contract docs/models/MXFMT.md: "Each block term is exact ...

@@ -328,6 +328,30 @@ def nvfp4_gemm(packed, scale_ue4m3, x, threads=None):
     return y
 
 
+def nvfp4_enc(bits, scale):
+    """E2M1 nibbles of binary32 bit patterns `bits` (u32 array) under one scale code; 0xff where the reference's unit traps"""
+    bits = np.ascontiguousarray(bits, dtype=np.uint32); out = np.empty(bits.size, np.uint8)
+    lib().orc_nvfp4_enc_many(_ptr(bits, U32P), C.c_size_t(bits.size), C.c_uint32(int(scale)), _ptr(out, U8P))
+    return out
+
+
+def nvfp4_scale(amax_bits):
+    amax_bits = np.ascontiguousarray(amax_bits, dtype=np.uint32); out = np.empty(amax_bits.size, np.uint8)
+    lib().orc_nvfp4_scale_many(_ptr(amax_bits, U32P), C.c_size_t(amax_bits.size), _ptr(out, U8P))
+    return out
+
+
+def nvfp4_quantize(x):
+    """x f32 [rows][k] -> (packed u8 [rows][k/2], scales u8 [rows][k/16]) by the reference's block rule; raises on a NaN value"""
+    x = np.ascontiguousarray(x, dtype=np.float32); rows, k = x.shape
+    packed = np.empty((rows, k // 2), np.uint8); scales = np.empty((rows, k // 16), np.uint8)
+    L = lib(); L.orc_nvfp4_quantize.restype = C.c_size_t
+    bad = L.orc_nvfp4_quantize(_ptr(x.view(np.uint32), U32P), C.c_size_t(rows), C.c_size_t(k), _ptr(packed, U8P), _ptr(scales, U8P))
+    if bad:
+        raise ValueError("nvfp4_quantize: %d blocks hold a NaN" % bad)
+    return packed, scales
+
+
 def mxmm(fmt, m, n, k, A, SA, B, SB):
     """block-scaled C = A B^T of the reference's mxdot unit (fmt 0 NVFP4, 1 MXFP4, 2 MXFP8): returns (rc, C f64 [m][n], sum of |terms| [m][n])"""
     A = np.ascontiguousarray(A, dtype=np.uint8); B = np.ascontiguousarray(B, dtype=np.uint8)

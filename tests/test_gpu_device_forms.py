@@ -262,3 +262,28 @@ def test_fp4_gemm_against_block_scaled_product(fmt):
     assert np.all(np.abs(y32 - ref) <= 1e-5 * mag + 1e-30), float(np.max(np.abs(y32 - ref) / (mag + 1e-30)))
     assert np.array_equal(y16, orc.bf16_bits(y32))
     api.lib.omega_gpu_w4_free(t)
+
+
+def test_nvfp4_quantiser_bit_exact():
+    """the GPU block quantiser against the checker's restatement of the reference's encoder (pinned in tests/test_oracle_pin.py): magnitudes over forty binades,
+    zero blocks, infinities (saturate), every block's scale and nibbles bit for bit; a NaN refuses the call"""
+    rng = np.random.default_rng(7)
+    rows, k = 128, 1024
+    mag = rng.uniform(-30, 10, (rows, k))
+    x = (rng.choice([-1.0, 1.0], (rows, k)) * np.exp2(mag) * rng.uniform(1, 2, (rows, k))).astype(np.float32)
+    x[::7, :64] = 0.0; x[1::11, 3] = np.inf; x[2::13, 40] = -np.inf
+    xb = orc.bf16_bits(x); xr = orc.bf16_to_f32(xb)
+    packed = np.zeros((rows, k // 2), np.uint8); scales = np.zeros((rows, k // 16), np.uint8)
+    q = lambda w: api.lib.omega_gpu_nvfp4_quantize_bf16(C.c_uint32(rows), C.c_uint32(k), w.ctypes.data_as(C.c_void_p), packed.ctypes.data_as(C.c_void_p), scales.ctypes.data_as(C.c_void_p))
+    assert q(xb) == 0, api.last_error()
+    wp, ws = orc.nvfp4_quantize(xr)
+    assert np.array_equal(scales, ws) and np.array_equal(packed, wp)
+    bad = xb.copy(); bad[5, 17] = 0x7fc0
+    before = packed.copy()
+    assert q(bad) == api.NAN_WEIGHT and np.array_equal(packed, before)
+    assert api.lib.omega_gpu_nvfp4_quantize_bf16(C.c_uint32(rows), C.c_uint32(k + 8), xb.ctypes.data_as(C.c_void_p), packed.ctypes.data_as(C.c_void_p), scales.ctypes.data_as(C.c_void_p)) == api.BAD_ARGS
+    # what was quantised is a valid tensor for the GEMM entries (no scale code above 126 comes out of the encoder)
+    n = rows
+    t = C.c_void_p()
+    assert api.lib.omega_gpu_nvfp4_upload(C.c_uint32(n), C.c_uint32(k), packed[:n].ctypes.data_as(C.c_void_p), scales[:n].ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
+    api.lib.omega_gpu_w4_free(t)

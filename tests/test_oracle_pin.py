@@ -507,3 +507,46 @@ def test_mxmm_against_reference_oracle():
     assert orc.mxmm(1, 1, 1, 32, z, bad, z, z)[0] == 5 and orc.mxmm(2, 1, 1, 32, z, z, z, bad)[0] == 5     # E8M0 255
     bad[0] = 127
     assert orc.mxmm(0, 1, 1, 16, z, bad, z, z)[0] == 5 and orc.mxmm(2, 1, 1, 32, bad, z, z, z)[0] == 5     # UE4M3 NaN scale, E4M3 NaN element
+
+
+# ------------------------------------------------------------------ NVFP4 encoder (native/models/nvfp4.om: nvfp4enc, nvfp4scale; checked as tests/models/mxfmt-check.py:302-352 checks the unit)
+def test_nvfp4_encoder_against_quotient_oracle_and_ml_dtypes():
+    """every non-NaN bfloat16 value under every valid scale against the binary64 quotient placed among the E2M1 midpoints (ties to the even code, above 6
+    saturating); +-1 ulp around every threshold against exact rationals; round trip of every element; the block scale against ml_dtypes' e4m3 cast"""
+    ml = pytest.importorskip("ml_dtypes")
+    from fractions import Fraction
+    F4 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+    bf = np.arange(65536, dtype=np.uint32) << 16
+    bf = bf[(bf & 0x7FFFFFFF) <= 0x7F800000]
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    sval = np.arange(127, dtype=np.uint8).view(ml.float8_e4m3fn).astype(np.float64)
+    x = bf.view(np.float32).astype(np.float64); neg = (bf >> 31).astype(np.uint32)
+    for s in range(127):
+        got = orc.nvfp4_enc(bf, s)
+        if sval[s] == 0:
+            want = neg << 3
+        else:
+            q = np.abs(x) / sval[s]
+            c = np.searchsorted(mids, q, side="left").astype(np.uint32)
+            c = np.minimum(np.where(np.isin(q, mids) & (c % 2 == 1), c + 1, c), 7)
+            want = (neg << 3) | c
+        assert np.array_equal(got, want.astype(np.uint8)), s
+    f32 = lambda v: np.array([v], np.float32).view(np.uint32)[0]
+    for s in range(1, 127):
+        sv = Fraction(float(sval[s])); pts = []
+        for m in (Fraction(1, 4), Fraction(3, 4), Fraction(5, 4), Fraction(7, 4), Fraction(5, 2), Fraction(7, 2), Fraction(5), Fraction(6), Fraction(7)):
+            b = int(f32(float(m * sv))); pts += [b - 1, b, b + 1]
+        got = orc.nvfp4_enc(np.array(pts, np.uint32), s)
+        for b, g in zip(pts, got):
+            xq = Fraction(float(np.array([b], np.uint32).view(np.float32)[0])) / sv
+            assert int(g) == min(range(8), key=lambda k: (abs(xq - Fraction(F4[k])), k % 2)), (s, hex(b))
+        dec = np.array([orc.nvfp4_bits(n, s) for n in range(16)], np.uint32)
+        assert orc.nvfp4_enc(dec, s).tolist() == list(range(16))                  # round trip
+    assert orc.nvfp4_enc(np.array([0x7fc00000], np.uint32), 5)[0] == 0xff and orc.nvfp4_enc(np.array([0], np.uint32), 127)[0] == 0xff   # NaN input, NaN scale: the unit traps
+    rng = np.random.default_rng(20261026)
+    am = np.concatenate([(np.arange(65536, dtype=np.uint32) << 16)[:0x7F81], rng.integers(0, 0x7F800001, 200000, dtype=np.uint32)]).astype(np.uint32)
+    q = (am.view(np.float32) / np.float32(6.0)).astype(np.float32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        c = q.astype(ml.float8_e4m3fn).view(np.uint8).astype(np.uint32)
+    c = np.where((c & 127) == 0x7F, 0x7E, c)                                       # saturating mode: what overflows becomes the largest finite code
+    assert np.array_equal(orc.nvfp4_scale(am), c.astype(np.uint8))
