@@ -14,6 +14,7 @@ struct OmegaGpuW4Tensor {
     uint32_t n, k; uint8_t *w; uint16_t *s;   // s: fp16 scales (int4 format) or, viewed as bytes, E8M0 scales (MXFP4 format)
     uint32_t fmt;                              // 0: signed int4 + fp16 scale per 32; 1: MXFP4 = E2M1 + E8M0 scale per 32
     float *part; uint32_t *counters;   // scratch of the tensor-core kernel: K-quarter partial sums [4][16][n] f32 and one arrival counter per 128 output rows
+    float *gpart; uint32_t *gcounters; uint32_t gtiles, gn;   // the same for the grouped form: per row tile [4][16][gn]; set by omega_gpu_w4_reserve_grouped
 };
 
 namespace b200 {
@@ -135,12 +136,22 @@ __device__ __forceinline__ void e2m1x8_bf16(uint32_t v, uint32_t *b) {
 // the words of quad threads t/2 and 2 + t/2 (one shuffle each); each MMA goes into its own fresh accumulator and is scaled by its own scale.
 template <int GQ, int FMT>   // 32-column groups per K quarter: k = 128 * GQ; FMT 0: int4 + fp16 scales, 1: E2M1 + E8M0 scales (MXFP4), 2: E2M1 + UE4M3 per 16 (NVFP4)
 __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m, uint32_t n, uint32_t k, const uint8_t *__restrict__ w, const uint16_t *__restrict__ sc,
-                                                        const uint16_t *__restrict__ x, uint16_t *__restrict__ y16, float *__restrict__ y32, float *part, uint32_t *counters) {
+                                                        const uint16_t *__restrict__ x, uint16_t *__restrict__ y16, float *__restrict__ y32, float *part, uint32_t *counters,
+                                                        const uint4 *__restrict__ tiles, const uint32_t *__restrict__ header, const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ ymap) {
     constexpr uint32_t KQ = GQ * 32u, XS = KQ * 2u + 64u;   // columns per quarter; bytes between panel rows (the 64 keep a quarter-warp's 16-byte reads on separate banks)
     extern __shared__ __align__(16) uint8_t xq[];
     __shared__ uint32_t s_last;
     const uint32_t nb = blockIdx.x, kq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, r = lane >> 2, t = lane & 3u;
-    const uint32_t mt = min(16u, m - m0);
+    // grouped form (tiles != null): blockIdx.z is a row tile {expert, first sorted row, rows <= 16} of a routing plan; the tensor holds the experts' matrices
+    // one after the other (n rows each); activation row i of the tile is x[xmap[row0 + i]] (or row0 + i), its result goes to row ymap[row0 + i] (or row0 + i)
+    uint32_t mt = 0, row0 = m0;
+    if (tiles) {
+        if (blockIdx.z >= header[2]) return;
+        const uint4 tl = tiles[blockIdx.z];
+        w += (size_t)tl.x * n * (k / 2u); sc = reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(sc) + (size_t)tl.x * n * (k / 32u) * (FMT == 1 ? 1u : 2u));
+        row0 = tl.y; mt = min(16u, tl.z);
+        part += (size_t)blockIdx.z * 4u * 16u * n; counters += (size_t)blockIdx.z * (n / 128u);
+    } else mt = min(16u, m - m0);
     // this thread's weight words: output row n0 + r, word t of every group of the quarter; all requested before anything else
     const uint32_t n0 = nb * 128u + warp * 8u;
     const uint32_t *wrow = reinterpret_cast<const uint32_t *>(w + (size_t)(n0 + r) * (k / 2u) + (size_t)kq * (KQ / 2u));
@@ -163,7 +174,7 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
     for (uint32_t i = threadIdx.x; i < 16u * (KQ / 8u); i += 512u) {
         const uint32_t row = i / (KQ / 8u), c8 = i - row * (KQ / 8u);
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < mt) v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(m0 + row) * k + (size_t)kq * KQ) + c8);
+        if (row < mt) v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)(xmap ? xmap[row0 + row] : row0 + row) * k + (size_t)kq * KQ) + c8);
         *reinterpret_cast<uint4 *>(xq + row * XS + c8 * 16u) = v;
     }
     __syncthreads();
@@ -222,7 +233,7 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
         float v = __ldcg(part + (size_t)row * n + col);
 #pragma unroll
         for (uint32_t q = 1; q < 4; q++) v = __fadd_rn(v, __ldcg(part + ((size_t)q * 16u + row) * n + col));
-        const size_t at = (size_t)(m0 + row) * n + col;
+        const size_t at = (size_t)(ymap ? ymap[row0 + row] : row0 + row) * n + col;
         if (y32) y32[at] = v;
         if (y16) { const uint32_t b = __float_as_uint(v); y16[at] = (uint16_t)(((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16)); }
     }
@@ -371,13 +382,15 @@ void omega_gpu_w4_free(OmegaGpuW4Tensor *t) {
     if (t->s) cudaFree(t->s);
     if (t->part) cudaFree(t->part);
     if (t->counters) cudaFree(t->counters);
+    if (t->gpart) cudaFree(t->gpart);
+    if (t->gcounters) cudaFree(t->gcounters);
     free(t);
 }
 static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *dx, uint16_t *d16, float *d32, cudaStream_t s) {
     if (t->part && (t->fmt || !getenv("B200MOE_W4_FMA"))) {   // tensor-core kernel: one launch per 16 activation rows (they share the tensor's scratch, in stream order)
         const dim3 grid(t->n / 128u, 4);
         for (uint32_t m0 = 0; m0 < m; m0 += 16u) {
-#define W4_LAUNCH(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters)
+#define W4_LAUNCH(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters, nullptr, nullptr, nullptr, nullptr)
             if (t->fmt == 2) { if (t->k == 4096u) W4_LAUNCH(32, 2); else if (t->k == 2048u) W4_LAUNCH(16, 2); else W4_LAUNCH(8, 2); }
             else if (t->fmt) { if (t->k == 4096u) W4_LAUNCH(32, 1); else if (t->k == 2048u) W4_LAUNCH(16, 1); else W4_LAUNCH(8, 1); }
             else { if (t->k == 4096u) W4_LAUNCH(32, 0); else if (t->k == 2048u) W4_LAUNCH(16, 0); else W4_LAUNCH(8, 0); }
@@ -391,6 +404,38 @@ static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16
     uint32_t grid = (t->n / W4_RW + 7) / 8; const uint32_t cap = (uint32_t)(st().sm_count ? st().sm_count : 148); if (grid > cap) grid = cap;
     w4_gemm_kernel<<<grid, 256, smem, s>>>(m, t->n, t->k, t->w, t->s, dx, d16, d32);
     return cudaGetLastError();
+}
+/* Grouped form: the tensor holds `experts` matrices of n_per_expert rows one after the other (uploaded as one tensor of experts x n_per_expert rows);
+ * the rows to multiply come sorted by expert with a tile table of a routing plan made with tile_rows = 16 (omega_gpu_moe_plan_async: tiles {expert, first
+ * row, rows}, header[2] = tiles). reserve allocates the per-tile scratch once (blocking); the async entry queues one launch and allocates nothing. */
+int omega_gpu_w4_reserve_grouped(OmegaGpuW4Tensor *t, uint32_t n_per_expert, uint32_t max_tiles) {
+    if (!t || !n_per_expert || !max_tiles || n_per_expert % 128u || t->n % n_per_expert || !(t->k == 1024u || t->k == 2048u || t->k == 4096u)) return OMEGA_GPU_FP8_BAD_ARGS;
+    Lock l;
+    if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
+    if (t->gpart) { cudaFree(t->gpart); t->gpart = nullptr; }
+    if (t->gcounters) { cudaFree(t->gcounters); t->gcounters = nullptr; }
+    const size_t pb = (size_t)max_tiles * 4 * 16 * n_per_expert * 4, cb = (size_t)max_tiles * (n_per_expert / 128u) * 4;
+    const bool ok = cuda_ok(cudaMalloc(&t->gpart, pb), "cudaMalloc(w4 grouped partials)") && cuda_ok(cudaMalloc(&t->gcounters, cb), "cudaMalloc(w4 grouped counters)") &&
+                    cuda_ok(cudaMemset(t->gcounters, 0, cb), "memset");
+    if (!ok) { if (t->gpart) cudaFree(t->gpart); if (t->gcounters) cudaFree(t->gcounters); t->gpart = nullptr; t->gcounters = nullptr; return OMEGA_GPU_FP8_CHIP_FAIL; }
+    t->gtiles = max_tiles; t->gn = n_per_expert;
+    return OMEGA_GPU_FP8_OK;
+}
+int omega_gpu_w4_gemm_grouped_async(const OmegaGpuW4Tensor *t, uint64_t tiles_va, uint64_t header_va, uint64_t xmap_va, uint64_t ymap_va,
+                                    uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream) {
+    if (!t || !tiles_va || !header_va || !x_bf16_va || (!y_bf16_va && !y_f32_va)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!t->gpart || !t->gtiles) { set_error("w4 grouped gemm: call omega_gpu_w4_reserve_grouped first"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
+    const dim3 grid(t->gn / 128u, 4, t->gtiles);
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint16_t *dx = (const uint16_t *)(uintptr_t)x_bf16_va; uint16_t *d16 = (uint16_t *)(uintptr_t)y_bf16_va; float *d32 = (float *)(uintptr_t)y_f32_va;
+#define W4_GROUPED(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(0u, 0u, t->gn, t->k, t->w, t->s, dx, d16, d32, t->gpart, t->gcounters, \
+        (const uint4 *)(uintptr_t)tiles_va, (const uint32_t *)(uintptr_t)header_va, (const uint32_t *)(uintptr_t)xmap_va, (const uint32_t *)(uintptr_t)ymap_va)
+    if (t->fmt == 2) { if (t->k == 4096u) W4_GROUPED(32, 2); else if (t->k == 2048u) W4_GROUPED(16, 2); else W4_GROUPED(8, 2); }
+    else if (t->fmt) { if (t->k == 4096u) W4_GROUPED(32, 1); else if (t->k == 2048u) W4_GROUPED(16, 1); else W4_GROUPED(8, 1); }
+    else { if (t->k == 4096u) W4_GROUPED(32, 0); else if (t->k == 2048u) W4_GROUPED(16, 0); else W4_GROUPED(8, 0); }
+#undef W4_GROUPED
+    return cuda_ok(cudaGetLastError(), "w4 grouped launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 int omega_gpu_w4_gemm_async(const OmegaGpuW4Tensor *t, uint32_t m, uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream) {
     if (!t || !m || !x_bf16_va || (!y_bf16_va && !y_f32_va)) return OMEGA_GPU_FP8_BAD_ARGS;

@@ -86,6 +86,14 @@ int omega_gpu_nvfp4_quantize_bf16(uint32_t rows, uint32_t k, const uint16_t *w_b
 int omega_gpu_w4_gemm_bf16(const OmegaGpuW4Tensor *t, uint32_t m, const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32);
 /* the same on device buffers, stream-ordered (one of y_bf16_va / y_f32_va may be 0) */
 int omega_gpu_w4_gemm_async(const OmegaGpuW4Tensor *t, uint32_t m, uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream);
+/* Grouped by expert (4-bit expert weights): the tensor was uploaded as experts x n_per_expert rows (expert e's matrix = rows [e n, (e + 1) n)). The rows to
+ * multiply are described by a routing plan made with tile_rows = 16 (omega_gpu_moe_plan_async): tiles u32 x4 {expert, first sorted row, rows <= 16, -},
+ * header[2] = number of tiles. Activation row i of a tile is x[xmap[first + i]] (xmap_va 0: x[first + i]), bf16 [.][k]; its result row (n_per_expert wide) is
+ * y[ymap[first + i]] (ymap_va 0: y[first + i]). omega_gpu_w4_reserve_grouped allocates the per-tile scratch once for at most max_tiles tiles (blocking);
+ * the async entry queues one launch of max_tiles x n / 128 x 4 CTAs (tiles past header[2] return at once) and allocates nothing. */
+int omega_gpu_w4_reserve_grouped(OmegaGpuW4Tensor *t, uint32_t n_per_expert, uint32_t max_tiles);
+int omega_gpu_w4_gemm_grouped_async(const OmegaGpuW4Tensor *t, uint64_t tiles_va, uint64_t header_va, uint64_t xmap_va, uint64_t ymap_va,
+                                    uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream);
 
 /* ---- the MoE layer: top-k -> plan -> gate|up grouped GEMM + SiLU gate -> down grouped GEMM -> weighted combine
  * (the MoE part of src/omega_gpu_decode_graph.c:341-351 for decode, src/omega_gpu_q36_graph.c:1147 for prefill). */

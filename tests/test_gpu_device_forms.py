@@ -287,3 +287,59 @@ def test_nvfp4_quantiser_bit_exact():
     t = C.c_void_p()
     assert api.lib.omega_gpu_nvfp4_upload(C.c_uint32(n), C.c_uint32(k), packed[:n].ctypes.data_as(C.c_void_p), scales[:n].ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
     api.lib.omega_gpu_w4_free(t)
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 2])
+def test_w4_grouped_gemm_by_expert(fmt):
+    """4-bit expert weights: the grouped form (one launch over a routing plan's 16-row tiles, rows gathered by xmap, results scattered by ymap) gives,
+    for every routed pick, the bits the plain entry gives for that expert's own matrix on that token's row. Formats: int4 + fp16 scales, MXFP4, NVFP4."""
+    import torch
+    rng = np.random.default_rng(90 + fmt)
+    E, n, k, T, S = 8, 256, 1024, 50, 4
+    packed = rng.integers(0, 256, (E * n, k // 2)).astype(np.uint8)
+    if fmt == 0:
+        scale = rng.uniform(0.001, 0.01, (E * n, k // 32)).astype(np.float16).view(np.uint16); up = api.lib.omega_gpu_w4_upload
+    elif fmt == 1:
+        scale = rng.integers(118, 124, (E * n, k // 32)).astype(np.uint8); up = api.lib.omega_gpu_mxfp4_upload
+    else:
+        scale = rng.integers(30, 80, (E * n, k // 16)).astype(np.uint8); up = api.lib.omega_gpu_nvfp4_upload
+    picks = np.stack([rng.choice(E, S, replace=False) for _ in range(T)]).astype(np.uint32)
+    picks[3, 1] = 0xFFFFFFFF                                                         # an absent pick: no row
+    xb = orc.bf16_bits(rng.normal(0, 1, (T, k)).astype(np.float32))
+    # reference: every expert's own tensor through the plain entry, all token rows
+    per = k // 32 if fmt < 2 else k // 16
+    want = np.zeros((E, T, n), np.float32)
+    for e in range(E):
+        te = C.c_void_p()
+        assert up(C.c_uint32(n), C.c_uint32(k), packed[e * n:(e + 1) * n].ctypes.data_as(C.c_void_p), np.ascontiguousarray(scale[e * n:(e + 1) * n]).ctypes.data_as(C.c_void_p), C.byref(te)) == 0, api.last_error()
+        rc, _, y = api.w4_gemm_bf16(te, n, xb); assert rc == 0, api.last_error()
+        want[e] = y
+        api.lib.omega_gpu_w4_free(te)
+    t = C.c_void_p()
+    assert up(C.c_uint32(E * n), C.c_uint32(k), packed.ctypes.data_as(C.c_void_p), scale.ctypes.data_as(C.c_void_p), C.byref(t)) == 0, api.last_error()
+    R = T * S
+    max_tiles = R // 16 + E + 8
+    assert api.lib.omega_gpu_w4_gemm_grouped_async(t, C.c_uint64(1), C.c_uint64(1), C.c_uint64(0), C.c_uint64(0), C.c_uint64(1), C.c_uint64(0), C.c_uint64(1), None) == api.BAD_ARGS   # not reserved
+    assert api.lib.omega_gpu_w4_reserve_grouped(t, C.c_uint32(n + 1), C.c_uint32(max_tiles)) == api.BAD_ARGS
+    assert api.lib.omega_gpu_w4_reserve_grouped(t, C.c_uint32(n), C.c_uint32(max_tiles)) == 0, api.last_error()
+    d_ids = dev(picks)
+    d_counts = torch.zeros(E, dtype=torch.int32, device="cuda:0"); d_starts = torch.zeros_like(d_counts)
+    d_xmap = torch.zeros(R + 8, dtype=torch.int32, device="cuda:0"); d_ymap = torch.zeros_like(d_xmap)
+    d_tiles = torch.zeros(max_tiles * 4, dtype=torch.int32, device="cuda:0"); d_hdr = torch.zeros(8, dtype=torch.int32, device="cuda:0")
+    o = api.MoePlanOut(d_counts.data_ptr(), d_starts.data_ptr(), d_xmap.data_ptr(), d_ymap.data_ptr(), 0, 0, 0, 0, d_tiles.data_ptr(), d_hdr.data_ptr())
+    s = torch.cuda.Stream(); torch.cuda.synchronize()
+    assert api.lib.omega_gpu_moe_plan_async(C.c_uint32(T), C.c_uint32(S), C.c_uint32(E), C.c_uint32(S), C.c_uint32(16), va(d_ids), C.byref(o), C.c_void_p(s.cuda_stream)) == 0, api.last_error()
+    d_x = dev(xb); d_y = torch.full((R, n), -999.0, dtype=torch.float32, device="cuda:0"); torch.cuda.synchronize()
+    assert api.lib.omega_gpu_w4_gemm_grouped_async(t, va(d_tiles), va(d_hdr), va(d_xmap), va(d_ymap), va(d_x), C.c_uint64(0), va(d_y), C.c_void_p(s.cuda_stream)) == 0, api.last_error()
+    s.synchronize()
+    got = d_y.cpu().numpy().reshape(T, S, n)
+    hdr = d_hdr.cpu().numpy().view(np.uint32)
+    assert hdr[3] == 0 and hdr[0] == R - 1 and 0 < hdr[2] <= max_tiles
+    for tk in range(T):
+        for sl in range(S):
+            e = picks[tk, sl]
+            if e == 0xFFFFFFFF:
+                assert np.all(got[tk, sl] == -999.0)                               # untouched
+            else:
+                assert np.array_equal(got[tk, sl].view(np.uint32), want[e, tk].view(np.uint32)), (tk, sl)
+    api.lib.omega_gpu_w4_free(t)
