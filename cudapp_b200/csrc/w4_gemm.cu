@@ -159,16 +159,23 @@ __global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m,
 #pragma unroll
     for (int g = 0; g < GQ; g++) wq[g] = __ldcs(wrow + g * 4 + t);
     // scales of the two output columns this thread's accumulators belong to (n0 + 2t, n0 + 2t + 1): GQ values each, fp16 (FMT 0) or E8M0 bytes (FMT 1)
-    constexpr int SB = FMT == 1 ? 1 : 2, SV = GQ * SB / 16 > 0 ? GQ * SB / 16 : 1;   // bytes per scale; 16-byte vectors per row (GQ = 8 bytes of E8M0: half a vector, loaded as 8 bytes)
+    constexpr int SB = FMT == 1 ? 1 : 2, SV = (GQ * SB + 15) / 16;   // bytes per scale; 16-byte vectors per row (GQ = 8 bytes of E8M0: half a vector, loaded as 8 bytes)
     const uint8_t *scb = reinterpret_cast<const uint8_t *>(sc);
     const uint8_t *s0b = scb + ((size_t)(n0 + 2u * t) * (k / 32u) + kq * GQ) * SB, *s1b = scb + ((size_t)(n0 + 2u * t + 1u) * (k / 32u) + kq * GQ) * SB;   // FMT 2: two scale bytes per 32 columns
     uint4 sv0[SV], sv1[SV];
-    if (GQ * SB >= 16) {
+    if (GQ * SB % 16 == 0) {
 #pragma unroll
         for (int i = 0; i < SV; i++) { sv0[i] = __ldg(reinterpret_cast<const uint4 *>(s0b) + i); sv1[i] = __ldg(reinterpret_cast<const uint4 *>(s1b) + i); }
-    } else {
+    } else if (GQ * SB == 8) {
         const uint2 a0 = __ldg(reinterpret_cast<const uint2 *>(s0b)), a1 = __ldg(reinterpret_cast<const uint2 *>(s1b));
         sv0[0] = make_uint4(a0.x, a0.y, 0, 0); sv1[0] = make_uint4(a1.x, a1.y, 0, 0);
+    } else {   // k = 768: 6 or 12 scale bytes per quarter, two-byte aligned
+        sv0[0] = make_uint4(0, 0, 0, 0); sv1[0] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < GQ * SB / 2; i++) {
+            reinterpret_cast<uint16_t *>(&sv0[0])[i] = __ldg(reinterpret_cast<const uint16_t *>(s0b) + i);
+            reinterpret_cast<uint16_t *>(&sv1[0])[i] = __ldg(reinterpret_cast<const uint16_t *>(s1b) + i);
+        }
     }
     // the quarter of the activation panel: rows m0 .. m0 + 15 (zero past m), columns kq * KQ ..
     for (uint32_t i = threadIdx.x; i < 16u * (KQ / 8u); i += 512u) {
@@ -298,7 +305,7 @@ int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uin
     const size_t wb = (size_t)n * k / 2, sb = (size_t)n * (k / 32) * 2;
     bool ok = cuda_ok(cudaMalloc(&t->w, wb), "cudaMalloc(w4)") && cuda_ok(cudaMalloc(&t->s, sb), "cudaMalloc(w4 scales)") &&
               cuda_ok(cudaMemcpy(t->w, packed, wb, cudaMemcpyHostToDevice), "copy w4") && cuda_ok(cudaMemcpy(t->s, scale_f16, sb, cudaMemcpyHostToDevice), "copy w4 scales");
-    if (ok && n % 128u == 0 && (k == 1024u || k == 2048u || k == 4096u)) {   // the tensor-core kernel's scratch
+    if (ok && n % 128u == 0 && (k == 768u || k == 1024u || k == 2048u || k == 4096u)) {   // the tensor-core kernel's scratch
         const size_t pb = (size_t)4 * 16 * n * 4, cb = (size_t)(n / 128u) * 4;
         ok = cuda_ok(cudaMalloc(&t->part, pb), "cudaMalloc(w4 partials)") && cuda_ok(cudaMalloc(&t->counters, cb), "cudaMalloc(w4 counters)") &&
              cuda_ok(cudaMemset(t->counters, 0, cb), "memset");
@@ -312,7 +319,7 @@ int omega_gpu_w4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uin
 int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_e8m0, OmegaGpuW4Tensor **out) {
     if (out) *out = nullptr;
     if (!out || !packed || !scale_e8m0 || !n || !k) return OMEGA_GPU_FP8_BAD_ARGS;
-    if (n % 128u || !(k == 1024u || k == 2048u || k == 4096u)) { set_error("mxfp4 upload: n must be a multiple of 128 and k 1024, 2048 or 4096"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (n % 128u || !(k == 768u || k == 1024u || k == 2048u || k == 4096u)) { set_error("mxfp4 upload: n must be a multiple of 128 and k 768, 1024, 2048 or 4096"); return OMEGA_GPU_FP8_BAD_ARGS; }
     for (size_t i = 0; i < (size_t)n * (k / 32); i++) if (scale_e8m0[i] == 0xffu) { set_error("mxfp4 upload: scale 255 (a NaN block) at group %zu", i); return OMEGA_GPU_FP8_NAN_WEIGHT; }
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
@@ -333,7 +340,7 @@ int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const 
 int omega_gpu_nvfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_ue4m3, OmegaGpuW4Tensor **out) {
     if (out) *out = nullptr;
     if (!out || !packed || !scale_ue4m3 || !n || !k) return OMEGA_GPU_FP8_BAD_ARGS;
-    if (n % 128u || !(k == 1024u || k == 2048u || k == 4096u)) { set_error("nvfp4 upload: n must be a multiple of 128 and k 1024, 2048 or 4096"); return OMEGA_GPU_FP8_BAD_ARGS; }
+    if (n % 128u || !(k == 768u || k == 1024u || k == 2048u || k == 4096u)) { set_error("nvfp4 upload: n must be a multiple of 128 and k 768, 1024, 2048 or 4096"); return OMEGA_GPU_FP8_BAD_ARGS; }
     for (size_t i = 0; i < (size_t)n * (k / 16); i++) {
         if (scale_ue4m3[i] == 0x7fu) { set_error("nvfp4 upload: scale 127 (NaN) at group %zu", i); return OMEGA_GPU_FP8_NAN_WEIGHT; }
         if (scale_ue4m3[i] > 0x7fu) { set_error("nvfp4 upload: scale code %u at group %zu has the sign bit set", (unsigned)scale_ue4m3[i], i); return OMEGA_GPU_FP8_BAD_ARGS; }
@@ -391,9 +398,9 @@ static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16
         const dim3 grid(t->n / 128u, 4);
         for (uint32_t m0 = 0; m0 < m; m0 += 16u) {
 #define W4_LAUNCH(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(m0, m, t->n, t->k, t->w, t->s, dx, d16, d32, t->part, t->counters, nullptr, nullptr, nullptr, nullptr)
-            if (t->fmt == 2) { if (t->k == 4096u) W4_LAUNCH(32, 2); else if (t->k == 2048u) W4_LAUNCH(16, 2); else W4_LAUNCH(8, 2); }
-            else if (t->fmt) { if (t->k == 4096u) W4_LAUNCH(32, 1); else if (t->k == 2048u) W4_LAUNCH(16, 1); else W4_LAUNCH(8, 1); }
-            else { if (t->k == 4096u) W4_LAUNCH(32, 0); else if (t->k == 2048u) W4_LAUNCH(16, 0); else W4_LAUNCH(8, 0); }
+            if (t->fmt == 2) { if (t->k == 4096u) W4_LAUNCH(32, 2); else if (t->k == 2048u) W4_LAUNCH(16, 2); else if (t->k == 1024u) W4_LAUNCH(8, 2); else W4_LAUNCH(6, 2); }
+            else if (t->fmt) { if (t->k == 4096u) W4_LAUNCH(32, 1); else if (t->k == 2048u) W4_LAUNCH(16, 1); else if (t->k == 1024u) W4_LAUNCH(8, 1); else W4_LAUNCH(6, 1); }
+            else { if (t->k == 4096u) W4_LAUNCH(32, 0); else if (t->k == 2048u) W4_LAUNCH(16, 0); else if (t->k == 1024u) W4_LAUNCH(8, 0); else W4_LAUNCH(6, 0); }
 #undef W4_LAUNCH
         }
         return cudaGetLastError();
@@ -409,7 +416,7 @@ static cudaError_t w4_launch(const OmegaGpuW4Tensor *t, uint32_t m, const uint16
  * the rows to multiply come sorted by expert with a tile table of a routing plan made with tile_rows = 16 (omega_gpu_moe_plan_async: tiles {expert, first
  * row, rows}, header[2] = tiles). reserve allocates the per-tile scratch once (blocking); the async entry queues one launch and allocates nothing. */
 int omega_gpu_w4_reserve_grouped(OmegaGpuW4Tensor *t, uint32_t n_per_expert, uint32_t max_tiles) {
-    if (!t || !n_per_expert || !max_tiles || n_per_expert % 128u || t->n % n_per_expert || !(t->k == 1024u || t->k == 2048u || t->k == 4096u)) return OMEGA_GPU_FP8_BAD_ARGS;
+    if (!t || !n_per_expert || !max_tiles || n_per_expert % 128u || t->n % n_per_expert || !(t->k == 768u || t->k == 1024u || t->k == 2048u || t->k == 4096u)) return OMEGA_GPU_FP8_BAD_ARGS;
     Lock l;
     if (!dev_open()) return OMEGA_GPU_FP8_CHIP_FAIL;
     if (t->gpart) { cudaFree(t->gpart); t->gpart = nullptr; }
@@ -431,9 +438,9 @@ int omega_gpu_w4_gemm_grouped_async(const OmegaGpuW4Tensor *t, uint64_t tiles_va
     const uint16_t *dx = (const uint16_t *)(uintptr_t)x_bf16_va; uint16_t *d16 = (uint16_t *)(uintptr_t)y_bf16_va; float *d32 = (float *)(uintptr_t)y_f32_va;
 #define W4_GROUPED(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(0u, 0u, t->gn, t->k, t->w, t->s, dx, d16, d32, t->gpart, t->gcounters, \
         (const uint4 *)(uintptr_t)tiles_va, (const uint32_t *)(uintptr_t)header_va, (const uint32_t *)(uintptr_t)xmap_va, (const uint32_t *)(uintptr_t)ymap_va)
-    if (t->fmt == 2) { if (t->k == 4096u) W4_GROUPED(32, 2); else if (t->k == 2048u) W4_GROUPED(16, 2); else W4_GROUPED(8, 2); }
-    else if (t->fmt) { if (t->k == 4096u) W4_GROUPED(32, 1); else if (t->k == 2048u) W4_GROUPED(16, 1); else W4_GROUPED(8, 1); }
-    else { if (t->k == 4096u) W4_GROUPED(32, 0); else if (t->k == 2048u) W4_GROUPED(16, 0); else W4_GROUPED(8, 0); }
+    if (t->fmt == 2) { if (t->k == 4096u) W4_GROUPED(32, 2); else if (t->k == 2048u) W4_GROUPED(16, 2); else if (t->k == 1024u) W4_GROUPED(8, 2); else W4_GROUPED(6, 2); }
+    else if (t->fmt) { if (t->k == 4096u) W4_GROUPED(32, 1); else if (t->k == 2048u) W4_GROUPED(16, 1); else if (t->k == 1024u) W4_GROUPED(8, 1); else W4_GROUPED(6, 1); }
+    else { if (t->k == 4096u) W4_GROUPED(32, 0); else if (t->k == 2048u) W4_GROUPED(16, 0); else if (t->k == 1024u) W4_GROUPED(8, 0); else W4_GROUPED(6, 0); }
 #undef W4_GROUPED
     return cuda_ok(cudaGetLastError(), "w4 grouped launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }

@@ -69,13 +69,13 @@ void omega_gpu_w4_free(OmegaGpuW4Tensor *t);
 /* ---- MXFP4 weights: E2M1 nibbles (two per byte along K, low nibble = even column) with one E8M0 scale byte per 32 columns, the format of the
  * reference's docs/models/MXFP4.md; every element's value is what its scalar decoder native/models/mxfp4.om returns (checked against that unit's
  * own verification oracle). packed [n][k/2], scale_e8m0 [n][k/32]; scale 255 (a NaN block) is refused with NAN_WEIGHT. n a multiple of 128,
- * k 1024, 2048 or 4096. The tensor is used with omega_gpu_w4_gemm_bf16 / _async and freed with omega_gpu_w4_free. The product y = x W^T: per
+ * k 768, 1024, 2048 or 4096. The tensor is used with omega_gpu_w4_gemm_bf16 / _async and freed with omega_gpu_w4_free. The product y = x W^T: per
  * group the sum of x * element, times 2^(scale - 127), accumulated in f32; with activations that are themselves MXFP4 values (element x scale, exact in
  * bf16) this is the reference's block-scaled product (native/models/mxdot.om `mxmm`) up to the rounding of the f32 running sum. */
 int omega_gpu_mxfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_e8m0, OmegaGpuW4Tensor **out);
 /* NVFP4 weights: E2M1 nibbles [n][k/2] (low nibble = even column) and one unsigned E4M3 scale per 16 columns [n][k/16], the reference's
  * native/models/nvfp4.om (docs/models/MXFMT.md); an element's value is what its nvfp4bits returns; no second-level per-tensor scale, as there.
- * Scale 127 (NaN) -> NAN_WEIGHT, a scale with the sign bit set -> BAD_ARGS (that unit refuses both); n % 128 == 0, k 1024, 2048 or 4096.
+ * Scale 127 (NaN) -> NAN_WEIGHT, a scale with the sign bit set -> BAD_ARGS (that unit refuses both); n % 128 == 0, k 768, 1024, 2048 or 4096.
  * The tensor runs through omega_gpu_w4_gemm_bf16 / _async. */
 int omega_gpu_nvfp4_upload(uint32_t n, uint32_t k, const uint8_t *packed, const uint8_t *scale_ue4m3, OmegaGpuW4Tensor **out);
 /* bf16 rows [rows][k] (host, k % 16 == 0) -> NVFP4 codes and scales on the GPU, bit for bit what the reference's block encoder gives (native/models/nvfp4.om

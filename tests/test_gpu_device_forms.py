@@ -172,7 +172,7 @@ def test_w4_gemm_full_size():
     api.lib.omega_gpu_w4_free(t)
 
 
-@pytest.mark.parametrize("n,k,m", [(256, 1024, 16), (128, 2048, 21), (4096, 4096, 16)])
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 16), (128, 2048, 21), (4096, 4096, 16), (256, 768, 19)])
 def test_mxfp4_gemm(n, k, m):
     """MXFP4 weights (E2M1 + E8M0 per 32: docs/models/MXFP4.md of the reference) times bf16 activations against the double checker, whose element
     decoder equals the reference's own verification oracle record for record (tests/test_oracle_pin.py). Every nibble value and a wide range of
@@ -196,7 +196,7 @@ def test_mxfp4_gemm(n, k, m):
     api.lib.omega_gpu_w4_free(t)
 
 
-@pytest.mark.parametrize("n,k,m", [(256, 1024, 16), (128, 2048, 21), (4096, 4096, 16)])
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 16), (128, 2048, 21), (4096, 4096, 16), (256, 768, 19)])
 def test_nvfp4_gemm(n, k, m):
     """NVFP4 weights (E2M1 + one unsigned E4M3 scale per 16 columns: native/models/nvfp4.om of the reference) times bf16 activations against the
     double checker, whose element x scale decoder equals the reference's verification oracle for every pair (tests/test_oracle_pin.py). Every nibble

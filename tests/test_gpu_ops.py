@@ -196,7 +196,7 @@ def test_glue_ops():
     assert np.array_equal(api.act_quant_f32(x, 1)[1][:, 0], q1)
 
 
-@pytest.mark.parametrize("n,k,m", [(512, 1024, 16), (256, 2048, 40), (130, 1536, 16)])
+@pytest.mark.parametrize("n,k,m", [(512, 1024, 16), (256, 2048, 40), (130, 1536, 16), (256, 768, 24)])
 def test_w4_gemm(n, k, m):
     """W4 configuration (self-oracle: the reference has no integer-W4 arithmetic). The first two shapes take the tensor-core kernel (the second
     in three passes of 16 activation rows, the last one partly filled), the third the general CUDA-core kernel; same bars for both."""
