@@ -30,6 +30,14 @@ struct OmegaGpuFp8Tensor {
 struct Seg32 { uint64_t w_va, s_va; uint32_t row0, cnt; uint64_t pad; };
 static_assert(sizeof(Seg32) == OMEGA_GEMM_SEG_BYTES, "segment record layout");
 
+// 4-bit weight tensor (w4_gemm.cu): int4 + fp16 scales, MXFP4 or NVFP4; one matrix, or the matrices of several experts one after the other
+struct OmegaGpuW4Tensor {
+    uint32_t n, k; uint8_t *w; uint16_t *s;   // s: fp16 scales (int4 format) or, viewed as bytes, E8M0 scales (MXFP4 format)
+    uint32_t fmt;                              // 0: signed int4 + fp16 scale per 32; 1: MXFP4 = E2M1 + E8M0 scale per 32
+    float *part; uint32_t *counters;   // scratch of the tensor-core kernel: K-quarter partial sums [4][16][n] f32 and one arrival counter per 128 output rows
+    float *gpart; uint32_t *gcounters; uint32_t gtiles, gn;   // the same for the grouped form: per row tile [4][16][gn]; set by omega_gpu_w4_reserve_grouped
+};
+
 namespace b200 {
 
 #define POISON_F32 (-999.0f)
@@ -93,7 +101,7 @@ uint32_t plan_launch_count(uint32_t picks, uint32_t experts, const uint32_t *scr
 struct PlanBatch { uint32_t *counts, *starts, *xmap, *ymap, *pos, *header; uint4 *tiles; size_t map_stride, tile_stride; };
 cudaError_t launch_plan_batch(uint32_t layers, uint32_t tokens, uint32_t slots, uint32_t experts, uint32_t ystride, uint32_t tile_rows, const uint32_t *ids,
                               const PlanBatch &b, cudaStream_t s);
-cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s);
+cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s, uint16_t *act_bf16 = nullptr);   // act_bf16: the same values rounded to bf16 (either output may be null)
 cudaError_t launch_combine(uint32_t tokens, uint32_t slots, uint32_t hidden, const float *w, const float *d, float *out_f32, uint16_t *out_bf16, cudaStream_t s);
 // quantise rows of x (f32 or bf16; gathered through xmap when given) into e4m3 pieces: q [rows][pieces][k], s [rows][k/128]
 cudaError_t launch_act_quant(uint32_t rows, uint32_t k, uint32_t pieces, const void *x, int x_bf16, const uint32_t *xmap,
@@ -128,6 +136,9 @@ struct FfnLaunch {
     const unsigned long long *gate, *gate_base; const uint64_t *out_peers, *ret_counters; uint32_t rows_per_rank, ret_index;   // expert parallelism, as in MmaLaunch
     uint32_t wait_limit;
 };
+// grouped 4-bit GEMM over a plan's 16-row tiles (the tensor must have been given its per-tile scratch by omega_gpu_w4_reserve_grouped)
+cudaError_t launch_w4_grouped(const OmegaGpuW4Tensor *t, const void *tiles, const uint32_t *header, const uint32_t *xmap, const uint32_t *ymap,
+                              const uint16_t *x_bf16, uint16_t *y_bf16, float *y_f32, cudaStream_t s);
 bool ffn_shape_ok(uint32_t hidden, uint32_t inter);
 cudaError_t launch_ffn(const void *tm_gu, const void *tm_qx, const void *tm_dn, const void *tm_qa, uint32_t px, uint32_t pa, const FfnLaunch &m, cudaStream_t s, bool pdl);
 bool layer_forward(OmegaGpuMoeLayer *L, uint32_t tokens, const uint16_t *logits, const uint16_t *x, float *out32, uint16_t *out16, cudaStream_t s,

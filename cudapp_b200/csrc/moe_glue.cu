@@ -10,18 +10,20 @@ namespace b200 {
 // (src/omega_blackwell_codegen_dec.c:291-324).
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
 
-__global__ void __launch_bounds__(256) swiglu_kernel(uint32_t rows, uint32_t inter, const float *__restrict__ gu, float *__restrict__ act) {
+__global__ void __launch_bounds__(256) swiglu_kernel(uint32_t rows, uint32_t inter, const float *__restrict__ gu, float *__restrict__ act, uint16_t *__restrict__ act16) {
     const size_t total = (size_t)rows * inter;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / inter, c = i - r * inter;
-        act[i] = silu_mul(gu[r * 2 * inter + c], gu[r * 2 * inter + inter + c]);
+        const float v = silu_mul(gu[r * 2 * inter + c], gu[r * 2 * inter + inter + c]);
+        if (act) act[i] = v;
+        if (act16) act16[i] = (uint16_t)bf16_rne_bits(v);
     }
 }
-cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s) {
+cudaError_t launch_swiglu(uint32_t rows, uint32_t inter, const float *gu, float *act, cudaStream_t s, uint16_t *act_bf16) {
     const size_t total = (size_t)rows * inter;
     if (!total) return cudaSuccess;
     size_t blocks = (total + 255) / 256; if (blocks > 148 * 8) blocks = 148 * 8;
-    swiglu_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, inter, gu, act);
+    swiglu_kernel<<<(unsigned)blocks, 256, 0, s>>>(rows, inter, gu, act, act_bf16);
     return cudaGetLastError();
 }
 

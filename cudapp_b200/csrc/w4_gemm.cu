@@ -10,12 +10,6 @@
 #include <stdlib.h>
 #include "internal.h"
 
-struct OmegaGpuW4Tensor {
-    uint32_t n, k; uint8_t *w; uint16_t *s;   // s: fp16 scales (int4 format) or, viewed as bytes, E8M0 scales (MXFP4 format)
-    uint32_t fmt;                              // 0: signed int4 + fp16 scale per 32; 1: MXFP4 = E2M1 + E8M0 scale per 32
-    float *part; uint32_t *counters;   // scratch of the tensor-core kernel: K-quarter partial sums [4][16][n] f32 and one arrival counter per 128 output rows
-    float *gpart; uint32_t *gcounters; uint32_t gtiles, gn;   // the same for the grouped form: per row tile [4][16][gn]; set by omega_gpu_w4_reserve_grouped
-};
 
 namespace b200 {
 
@@ -287,6 +281,18 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_kernel(size_t blocks, cons
     scales[b] = (uint8_t)sc;
 }
 
+cudaError_t launch_w4_grouped(const OmegaGpuW4Tensor *t, const void *tiles, const uint32_t *header, const uint32_t *xmap, const uint32_t *ymap,
+                              const uint16_t *dx, uint16_t *d16, float *d32, cudaStream_t s) {
+    const dim3 grid(t->gn / 128u, 4, t->gtiles);
+#define W4_GROUPED(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(0u, 0u, t->gn, t->k, t->w, t->s, dx, d16, d32, t->gpart, t->gcounters, \
+        (const uint4 *)tiles, header, xmap, ymap)
+    if (t->fmt == 2) { if (t->k == 4096u) W4_GROUPED(32, 2); else if (t->k == 2048u) W4_GROUPED(16, 2); else if (t->k == 1024u) W4_GROUPED(8, 2); else W4_GROUPED(6, 2); }
+    else if (t->fmt) { if (t->k == 4096u) W4_GROUPED(32, 1); else if (t->k == 2048u) W4_GROUPED(16, 1); else if (t->k == 1024u) W4_GROUPED(8, 1); else W4_GROUPED(6, 1); }
+    else { if (t->k == 4096u) W4_GROUPED(32, 0); else if (t->k == 2048u) W4_GROUPED(16, 0); else if (t->k == 1024u) W4_GROUPED(8, 0); else W4_GROUPED(6, 0); }
+#undef W4_GROUPED
+    return cudaGetLastError();
+}
+
 }  // namespace b200
 using namespace b200;
 
@@ -433,16 +439,9 @@ int omega_gpu_w4_gemm_grouped_async(const OmegaGpuW4Tensor *t, uint64_t tiles_va
     if (!t || !tiles_va || !header_va || !x_bf16_va || (!y_bf16_va && !y_f32_va)) return OMEGA_GPU_FP8_BAD_ARGS;
     if (!t->gpart || !t->gtiles) { set_error("w4 grouped gemm: call omega_gpu_w4_reserve_grouped first"); return OMEGA_GPU_FP8_BAD_ARGS; }
     if (!st().opened || st().latched) return OMEGA_GPU_FP8_CHIP_FAIL;
-    const dim3 grid(t->gn / 128u, 4, t->gtiles);
-    cudaStream_t s = (cudaStream_t)stream;
-    const uint16_t *dx = (const uint16_t *)(uintptr_t)x_bf16_va; uint16_t *d16 = (uint16_t *)(uintptr_t)y_bf16_va; float *d32 = (float *)(uintptr_t)y_f32_va;
-#define W4_GROUPED(GQV, FMTV) w4_mma_kernel<GQV, FMTV><<<grid, 512, 16 * (GQV * 64 + 64), s>>>(0u, 0u, t->gn, t->k, t->w, t->s, dx, d16, d32, t->gpart, t->gcounters, \
-        (const uint4 *)(uintptr_t)tiles_va, (const uint32_t *)(uintptr_t)header_va, (const uint32_t *)(uintptr_t)xmap_va, (const uint32_t *)(uintptr_t)ymap_va)
-    if (t->fmt == 2) { if (t->k == 4096u) W4_GROUPED(32, 2); else if (t->k == 2048u) W4_GROUPED(16, 2); else if (t->k == 1024u) W4_GROUPED(8, 2); else W4_GROUPED(6, 2); }
-    else if (t->fmt) { if (t->k == 4096u) W4_GROUPED(32, 1); else if (t->k == 2048u) W4_GROUPED(16, 1); else if (t->k == 1024u) W4_GROUPED(8, 1); else W4_GROUPED(6, 1); }
-    else { if (t->k == 4096u) W4_GROUPED(32, 0); else if (t->k == 2048u) W4_GROUPED(16, 0); else if (t->k == 1024u) W4_GROUPED(8, 0); else W4_GROUPED(6, 0); }
-#undef W4_GROUPED
-    return cuda_ok(cudaGetLastError(), "w4 grouped launch") ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
+    return cuda_ok(launch_w4_grouped(t, (const void *)(uintptr_t)tiles_va, (const uint32_t *)(uintptr_t)header_va, (const uint32_t *)(uintptr_t)xmap_va, (const uint32_t *)(uintptr_t)ymap_va,
+                                     (const uint16_t *)(uintptr_t)x_bf16_va, (uint16_t *)(uintptr_t)y_bf16_va, (float *)(uintptr_t)y_f32_va, (cudaStream_t)stream), "w4 grouped launch")
+               ? OMEGA_GPU_FP8_OK : OMEGA_GPU_FP8_CHIP_FAIL;
 }
 int omega_gpu_w4_gemm_async(const OmegaGpuW4Tensor *t, uint32_t m, uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream) {
     if (!t || !m || !x_bf16_va || (!y_bf16_va && !y_f32_va)) return OMEGA_GPU_FP8_BAD_ARGS;

@@ -95,6 +95,20 @@ int omega_gpu_w4_reserve_grouped(OmegaGpuW4Tensor *t, uint32_t n_per_expert, uin
 int omega_gpu_w4_gemm_grouped_async(const OmegaGpuW4Tensor *t, uint64_t tiles_va, uint64_t header_va, uint64_t xmap_va, uint64_t ymap_va,
                                     uint64_t x_bf16_va, uint64_t y_bf16_va, uint64_t y_f32_va, void *stream);
 
+/* ---- one MoE layer with 4-bit expert weights (any of the three formats above; MXFP4 and NVFP4 are the reference's own 4-bit expert formats).
+ * gate_up: experts x 2I rows of k = hidden (gate rows first, then up rows, per expert); down: experts x hidden rows of k = I; both uploaded with the
+ * upload entry of their format, not owned by the layer and not usable by another layer at the same time (the layer reserves their grouped scratch).
+ * hidden and I in {768, 1024, 2048, 4096}. Steps: top-k of the bf16 logits (the reference's selection rule), routing plan, grouped gate|up, SiLU gate
+ * rounded to bf16, grouped down, slot-order combine; 6 launches. */
+typedef struct OmegaGpuMoeW4Layer OmegaGpuMoeW4Layer;
+int omega_gpu_moe_w4_layer_create(OmegaGpuW4Tensor *gate_up, OmegaGpuW4Tensor *down, uint32_t experts, uint32_t topk, uint32_t max_tokens, int norm_topk,
+                                  OmegaGpuMoeW4Layer **out);
+void omega_gpu_moe_w4_layer_free(OmegaGpuMoeW4Layer *l);
+int omega_gpu_moe_w4_layer_bf16(OmegaGpuMoeW4Layer *l, uint32_t tokens, const uint16_t *logits_bf16, const uint16_t *x_bf16, uint16_t *out_bf16, float *out_f32,
+                                uint32_t *ids, float *wts);
+int omega_gpu_moe_w4_layer_async(OmegaGpuMoeW4Layer *l, uint32_t tokens, uint64_t logits_va, uint64_t x_va, uint64_t out_f32_va, uint64_t out_bf16_va, void *stream);
+uint32_t omega_gpu_moe_w4_layer_launches(const OmegaGpuMoeW4Layer *l);
+
 /* ---- the MoE layer: top-k -> plan -> gate|up grouped GEMM + SiLU gate -> down grouped GEMM -> weighted combine
  * (the MoE part of src/omega_gpu_decode_graph.c:341-351 for decode, src/omega_gpu_q36_graph.c:1147 for prefill). */
 typedef struct OmegaGpuMoeLayer OmegaGpuMoeLayer;

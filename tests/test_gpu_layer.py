@@ -369,3 +369,51 @@ def test_layer_with_shared_expert(engine):
             api.lib.omega_gpu_moe_router_free(r)
         api.lib.omega_gpu_moe_layer_free(layer2)
     api.lib.omega_gpu_moe_layer_free(layer); api.fp8_tensor_free(tgu); api.fp8_tensor_free(tdn)
+
+
+@pytest.mark.parametrize("fmt", [0, 1, 2])
+def test_w4_layer(fmt):
+    """One MoE layer with 4-bit expert weights (int4 + fp16 scales, MXFP4, NVFP4) against the checker: the reference's top-k rule, per expert the double
+    GEMM over the decoded weights (the decoders are pinned to the reference's oracles), the SiLU gate rounded to bf16 as the layer rounds it, the
+    slot-order combine. hidden 1024, expert intermediate 768 (the six-group K quarter of the down projection), 8 experts, top-2, 40 tokens."""
+    rng = np.random.default_rng(300 + fmt)
+    E, H, I, K, T = 8, 1024, 768, 2, 40
+    pgu = rng.integers(0, 256, (E * 2 * I, H // 2)).astype(np.uint8); pdn = rng.integers(0, 256, (E * H, I // 2)).astype(np.uint8)
+    if fmt == 0:
+        sgu = rng.uniform(0.002, 0.006, (E * 2 * I, H // 32)).astype(np.float16).view(np.uint16); sdn = rng.uniform(0.002, 0.006, (E * H, I // 32)).astype(np.float16).view(np.uint16)
+        up, gemm = api.lib.omega_gpu_w4_upload, lambda p, sc, x: orc.w4_gemm(p, sc.view(np.float16), x)
+    elif fmt == 1:
+        sgu = rng.integers(117, 121, (E * 2 * I, H // 32)).astype(np.uint8); sdn = rng.integers(117, 121, (E * H, I // 32)).astype(np.uint8)
+        up, gemm = api.lib.omega_gpu_mxfp4_upload, orc.mxfp4_gemm
+    else:
+        sgu = rng.integers(24, 40, (E * 2 * I, H // 16)).astype(np.uint8); sdn = rng.integers(24, 40, (E * H, I // 16)).astype(np.uint8)
+        up, gemm = api.lib.omega_gpu_nvfp4_upload, orc.nvfp4_gemm
+    tg, td = C.c_void_p(), C.c_void_p()
+    assert up(C.c_uint32(E * 2 * I), C.c_uint32(H), pgu.ctypes.data_as(C.c_void_p), sgu.ctypes.data_as(C.c_void_p), C.byref(tg)) == 0, api.last_error()
+    assert up(C.c_uint32(E * H), C.c_uint32(I), pdn.ctypes.data_as(C.c_void_p), sdn.ctypes.data_as(C.c_void_p), C.byref(td)) == 0, api.last_error()
+    layer = C.c_void_p()
+    assert api.lib.omega_gpu_moe_w4_layer_create(tg, td, C.c_uint32(E + 1), C.c_uint32(K), C.c_uint32(64), C.c_int(1), C.byref(layer)) == api.BAD_ARGS
+    assert api.lib.omega_gpu_moe_w4_layer_create(tg, td, C.c_uint32(E), C.c_uint32(K), C.c_uint32(64), C.c_int(1), C.byref(layer)) == 0, api.last_error()
+    logits = orc.bf16_bits(rng.normal(0, 1, (T, E)).astype(np.float32)); xb = orc.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32))
+    o16 = np.zeros((T, H), np.uint16); o32 = np.zeros((T, H), np.float32); ids = np.zeros((T, K), np.uint32); wts = np.zeros((T, K), np.float32)
+    P = lambda a: a.ctypes.data_as(C.c_void_p)
+    assert api.lib.omega_gpu_moe_w4_layer_bf16(layer, C.c_uint32(T), P(logits), P(xb), P(o16), P(o32), P(ids), P(wts)) == 0, api.last_error()
+    rid, rw = orc.topk(orc.bf16_to_f32(logits), K, True)
+    assert np.array_equal(ids, rid) and np.max(np.abs(wts - rw)) <= 1e-5
+    x = orc.bf16_to_f32(xb)
+    dn = np.zeros((T, K, H), np.float32)
+    for e in range(E):
+        tk, sl = np.nonzero(ids == e)
+        if len(tk) == 0:
+            continue
+        gu = gemm(pgu[e * 2 * I:(e + 1) * 2 * I], np.ascontiguousarray(sgu[e * 2 * I:(e + 1) * 2 * I]), x[tk]).astype(np.float32)
+        act = orc.bf16_to_f32(orc.bf16_bits(orc.swiglu(gu)))
+        dn[tk, sl] = gemm(pdn[e * H:(e + 1) * H], np.ascontiguousarray(sdn[e * H:(e + 1) * H]), act).astype(np.float32)
+    ref = orc.combine(wts, dn)
+    err, rl2 = float(np.max(np.abs(o32 - ref))), rel_l2(o32, ref)
+    assert err <= 1e-2 * max(1.0, float(np.max(np.abs(ref)))) and rl2 <= 1e-3, (err, rl2, float(np.max(np.abs(ref))))
+    assert np.array_equal(o16, orc.bf16_bits(o32))
+    o32b = np.zeros_like(o32)
+    assert api.lib.omega_gpu_moe_w4_layer_bf16(layer, C.c_uint32(T), P(logits), P(xb), None, P(o32b), None, None) == 0 and np.array_equal(o32b.view(np.uint32), o32.view(np.uint32))
+    assert api.lib.omega_gpu_moe_w4_layer_launches(layer) == 6
+    api.lib.omega_gpu_moe_w4_layer_free(layer); api.lib.omega_gpu_w4_free(tg); api.lib.omega_gpu_w4_free(td)
