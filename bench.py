@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--engine", type=int, default=0, help="0 auto, 1 CUDA-core, 2 tensor-core")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8)
     ap.add_argument("--skip-cpu", action="store_true", help="leave the CPU baseline and the prefill-layer measurement out (profiling runs)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "w4", "mxfp4", "nvfp4", "decode_layer"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv", "w4", "mxfp4", "nvfp4", "decode_layer", "mxfp4_layer"],
                     help="decode: the 48-layer stack the metric is quoted on (default); prefill: one layer, 4096 tokens, skewed routing, plain FP8 activations; "
                          "gemv: the single FP8 projection [768, 2048] on cold weights; w4: the W4 GEMM 16 x 4096 x 4096 on cold weights; decode_layer: one layer, 64 tokens")
     ap.add_argument("--tile-rows", type=int, default=0, help="prefill: 0 = library's choice, 32 or 128 = force the row-tile size")
@@ -373,7 +373,7 @@ def run_ours(args, rank, world):
         except Exception as e:   # the headline line is printed whatever happens to the side measurement
             out["prefill"] = {"error": "%s: %s" % (type(e).__name__, e)}
         # the three smaller configurations of the benchmark definition, each on cold weights
-        for key, fn in (("gemv", run_gemv), ("w4", run_w4), ("mxfp4", run_mxfp4), ("nvfp4", run_nvfp4), ("decode_layer", run_decode_layer)):
+        for key, fn in (("gemv", run_gemv), ("w4", run_w4), ("mxfp4", run_mxfp4), ("nvfp4", run_nvfp4), ("decode_layer", run_decode_layer), ("mxfp4_layer", run_mxfp4_layer)):
             try:
                 r = fn(pa)
                 out[key] = {"workload": r["config"]["workload"], "value": r["value"], "unit": r["unit"], "us_per_call": r["ms_per_step"] * 1e3, "roofline": r["roofline"], "gpu_launches": r["gpu_launches"]}
@@ -655,14 +655,62 @@ def run_decode_layer(args):
                          "peak_kind": kind + " copy bandwidth", "algorithmic_bytes": alg, "kernel_ms": gemm_ms, "traffic": None}}
 
 
+def run_mxfp4_layer(args):
+    """One MoE layer of the benchmark's architecture (128 experts, top-8, hidden 2048, expert intermediate 768) with MXFP4 expert weights on 64 decode
+    tokens: 302 MB of weights + 19 MB of scales per call, more than L2. Stream-ordered entry, device-resident inputs, CUDA events."""
+    import torch
+    from cudapp_b200 import api
+    torch.cuda.set_device(0); dev = torch.device("cuda", 0)
+    T = 64
+    rng = np.random.default_rng(0)
+    pgu = rng.integers(0, 256, (E * 2 * I, H // 2)).astype(np.uint8); sgu = rng.integers(118, 124, (E * 2 * I, H // 32)).astype(np.uint8)
+    pdn = rng.integers(0, 256, (E * H, I // 2)).astype(np.uint8); sdn = rng.integers(118, 124, (E * H, I // 32)).astype(np.uint8)
+    tg, td, layer = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    P = lambda a: a.ctypes.data_as(C.c_void_p)
+    assert api.lib.omega_gpu_mxfp4_upload(C.c_uint32(E * 2 * I), C.c_uint32(H), P(pgu), P(sgu), C.byref(tg)) == 0, api.last_error()
+    assert api.lib.omega_gpu_mxfp4_upload(C.c_uint32(E * H), C.c_uint32(I), P(pdn), P(sdn), C.byref(td)) == 0, api.last_error()
+    assert api.lib.omega_gpu_moe_w4_layer_create(tg, td, C.c_uint32(E), C.c_uint32(TOPK), C.c_uint32(T), C.c_int(1), C.byref(layer)) == 0, api.last_error()
+    logits_d = torch.from_numpy(api.bf16_bits(rng.normal(0, 1, (T, E)).astype(np.float32)).view(np.int16)).to(dev)
+    x_d = torch.from_numpy(api.bf16_bits(rng.normal(0, 1, (T, H)).astype(np.float32)).view(np.int16)).to(dev)
+    out32 = torch.empty((T, H), dtype=torch.float32, device=dev)
+    stream = torch.cuda.Stream()
+
+    def step():
+        rc = api.lib.omega_gpu_moe_w4_layer_async(layer, C.c_uint32(T), C.c_uint64(logits_d.data_ptr()), C.c_uint64(x_d.data_ptr()), C.c_uint64(out32.data_ptr()), C.c_uint64(0), C.c_void_p(stream.cuda_stream))
+        assert rc == 0, api.last_error()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(20):
+            step()
+        e1.record(stream); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    assert bool(torch.isfinite(out32).all())
+    launches = int(api.lib.omega_gpu_moe_w4_layer_launches(layer))
+    api.lib.omega_gpu_moe_w4_layer_free(layer); api.lib.omega_gpu_w4_free(tg); api.lib.omega_gpu_w4_free(td)
+    alg = pgu.nbytes + sgu.nbytes + pdn.nbytes + sdn.nbytes + T * E * 2 + 2 * T * H * 2
+    peak, kind = measured_peak()
+    ach = alg / (ms * 1e-3) / 1e9
+    return {"metric": "moe_layer_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": 20, "warmup": 3, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "MXFP4 weights (E2M1 + E8M0 per 32), bf16 activations, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "one MoE decode layer with MXFP4 expert weights, 64 tokens, 128 experts top-8, hidden 2048, inter 768", "tokens_per_step": T,
+                       "l2": "0.32 GB of weights and scales per call: larger than L2"},
+            "gpu_launches": launches * 20,
+            "roofline": {"bound": "hbm", "kernel": "whole layer (grouped gate|up and down on mma.sync with in-register expansion, plus routing and glue)", "achieved": ach, "peak": peak, "unit": "GB/s",
+                         "frac": ach / peak, "peak_kind": kind + " copy bandwidth", "algorithmic_bytes": alg, "kernel_ms": ms, "traffic": None}}
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
-    elif args.workload in ("prefill", "gemv", "w4", "mxfp4", "nvfp4", "decode_layer"):
+    elif args.workload in ("prefill", "gemv", "w4", "mxfp4", "nvfp4", "decode_layer", "mxfp4_layer"):
         if rank == 0:
-            print(json.dumps({"prefill": run_prefill, "gemv": run_gemv, "w4": run_w4, "mxfp4": run_mxfp4, "nvfp4": run_nvfp4, "decode_layer": run_decode_layer}[args.workload](args)))
+            print(json.dumps({"prefill": run_prefill, "gemv": run_gemv, "w4": run_w4, "mxfp4": run_mxfp4, "nvfp4": run_nvfp4, "decode_layer": run_decode_layer, "mxfp4_layer": run_mxfp4_layer}[args.workload](args)))
     else:
         run_ours(args, rank, world)
 
