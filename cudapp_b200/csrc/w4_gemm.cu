@@ -129,7 +129,7 @@ __device__ __forceinline__ void e2m1x8_bf16(uint32_t v, uint32_t *b) {
 // 16..31. Thread t of a quad then feeds columns 4t .. 4t+3 to the first MMA and 16+4t .. 16+4t+3 to the second: the two 16-bit halves it needs sit in
 // the words of quad threads t/2 and 2 + t/2 (one shuffle each); each MMA goes into its own fresh accumulator and is scaled by its own scale.
 template <int GQ, int FMT>   // 32-column groups per K quarter: k = 128 * GQ; FMT 0: int4 + fp16 scales, 1: E2M1 + E8M0 scales (MXFP4), 2: E2M1 + UE4M3 per 16 (NVFP4)
-__global__ void __launch_bounds__(512, 1) w4_mma_kernel(uint32_t m0, uint32_t m, uint32_t n, uint32_t k, const uint8_t *__restrict__ w, const uint16_t *__restrict__ sc,
+__global__ void __launch_bounds__(512, GQ <= 16 ? 2 : 1) w4_mma_kernel(uint32_t m0, uint32_t m, uint32_t n, uint32_t k, const uint8_t *__restrict__ w, const uint16_t *__restrict__ sc,
                                                         const uint16_t *__restrict__ x, uint16_t *__restrict__ y16, float *__restrict__ y32, float *part, uint32_t *counters,
                                                         const uint4 *__restrict__ tiles, const uint32_t *__restrict__ header, const uint32_t *__restrict__ xmap, const uint32_t *__restrict__ ymap) {
     constexpr uint32_t KQ = GQ * 32u, XS = KQ * 2u + 64u;   // columns per quarter; bytes between panel rows (the 64 keep a quarter-warp's 16-byte reads on separate banks)
