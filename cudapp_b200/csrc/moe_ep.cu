@@ -335,6 +335,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     __shared__ double red[8];
     __shared__ float s_scale;
     __shared__ uint32_t s_d[32], s_row[32], s_fail;
+    __shared__ uint8_t *s_q[32]; __shared__ float *s_sx[32];   // per pick: the destination rank's piece and scale buffers of the next layer's parity
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, kb_total = hidden / 128u;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next gate|up GEMM may start fetching weights
@@ -372,6 +373,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         const size_t i = (size_t)t * topk + tid;        // ids_next / pos_next are already offset to this rank's first token
         const uint32_t d = ids_next[i] / experts_local;
         s_d[tid] = d; s_row[tid] = pos_next[i] - starts_next[d * experts_local];
+        s_q[tid] = reinterpret_cast<uint8_t *>(q_peers[d]) + q_off; s_sx[tid] = reinterpret_cast<float *>(sx_peers[d] + sx_off);
     }
     __syncthreads();
     if (q_peers && tid < topk && !s_fail) {
@@ -392,6 +394,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     __syncthreads();
     if (s_fail) return;
     double sq = 0.0;
+    float4 k0 = make_float4(0, 0, 0, 0), k1 = k0;   // this thread's columns of h (tid * 4 and 1024 + tid * 4): the quantiser below uses the same mapping
     for (uint32_t c = tid * 4; c < hidden; c += 1024) {
         const size_t i = (size_t)t * hidden + c;
         float4 v;
@@ -402,6 +405,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
             v = make_float4(__fadd_rn(v.x, m.x), __fadd_rn(v.y, m.y), __fadd_rn(v.z, m.z), __fadd_rn(v.w, m.w));
         }
         *reinterpret_cast<float4 *>(h + i) = v;
+        if (c < 1024u) k0 = v; else if (c < 2048u) k1 = v;
         if (h16) {
             auto rne = [](float f) -> uint32_t { const uint32_t b = __float_as_uint(f); return ((b & 0x7fffffffu) > 0x7f800000u) ? ((b >> 16) | 0x40u) : ((b + 0x7fffu + ((b >> 16) & 1u)) >> 16); };
             uint2 pk; pk.x = rne(v.x) | (rne(v.y) << 16); pk.y = rne(v.z) | (rne(v.w) << 16);
@@ -418,7 +422,7 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
     const float sc = s_scale;
     for (uint32_t kb = tid >> 5; kb < kb_total; kb += 8) {
         const uint32_t c = kb * 128u + lane * 4u;
-        const float4 hv = *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);
+        const float4 hv = c < 1024u ? k0 : c < 2048u ? k1 : *reinterpret_cast<const float4 *>(h + (size_t)t * hidden + c);   // c = tid * 4 + 1024 j: this thread's own columns
         const float4 wv = __ldg(reinterpret_cast<const float4 *>(nw + c));
         // the same arithmetic, value for value, as combine_norm_scatter_kernel of the single-GPU stack: xn = bf16(h * s * w), then the shared quantiser
         float v[4] = {__fmul_rn(__fmul_rn(hv.x, sc), wv.x), __fmul_rn(__fmul_rn(hv.y, sc), wv.y), __fmul_rn(__fmul_rn(hv.z, sc), wv.z), __fmul_rn(__fmul_rn(hv.w, sc), wv.w)};
@@ -427,9 +431,9 @@ __global__ void __launch_bounds__(256) ep_combine_norm_scatter_kernel(
         uint32_t codes[4];
         const float qs = quant_pieces_warp(v, pieces, codes);
         for (uint32_t s = 0; s < topk; s++) {
-            uint8_t *q = reinterpret_cast<uint8_t *>(q_peers[s_d[s]]) + q_off;
+            uint8_t *q = s_q[s];
             for (uint32_t p = 0; p < pieces; p++) *reinterpret_cast<uint32_t *>(q + (size_t)p * piece_stride + (size_t)s_row[s] * hidden + c) = codes[p];
-            if (lane == 0) reinterpret_cast<float *>(sx_peers[s_d[s]] + sx_off)[(size_t)s_row[s] * kb_total + kb] = qs;
+            if (lane == 0) s_sx[s][(size_t)s_row[s] * kb_total + kb] = qs;
         }
     }
     // publish: every thread's stores are ordered before the barrier; the few publishing threads then fence at system scope (a fence is
